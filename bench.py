@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark of the gated-GQA attention path.
+
+    python bench.py --gpus N --steps K --warmup W [--workload decode_b8|decode_b1|decode_b64|decode_int8_b8|pp512|chunked_b1]
+    python bench.py --impl reference ...      # the reference's scalar CPU math (oracle port) on the host cores
+
+Default workload (the one the headline metric is quoted on): decode at 32K context across all 16 attention layers, fp16
+KV cache, 8 independent sequences per GPU with context lengths uniform in [16K, 32K], one new token per step. A step is
+one pass of the hot path over the batch: per layer, append the token's K/V row (norm, RoPE, fp16 store) and attend over
+the whole cached context (split-KV decode with the merge and the output gate fused). With N GPUs each rank holds its own
+8 sequences (batch sharding, no data-path collective): weak scaling; N=8 is the 64-sequence configuration.
+
+Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, barrier and synchronize on both
+sides, max over ranks. The KV working set per step (GBs) is far larger than L2, so no explicit flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+N_LAYERS = 16
+WORKLOADS = {
+    # name: (kind, batch per GPU, kv mode, max length, min length)
+    "decode_b8": ("decode", 8, "fp16", 32768, 16384),
+    "decode_b1": ("decode", 1, "fp16", 32768, 32768),
+    "decode_b64": ("decode", 64, "fp16", 32768, 16384),
+    "decode_int8_b8": ("decode", 8, "int8", 32768, 16384),
+    "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
+    "pp512": ("prefill", 1, "fp16", 512, 512),
+    "chunked_b1": ("chunked", 1, "fp16", 7300, 7300),
+    "chunked_b16": ("chunked", 16, "fp16", 7300, 7300),
+}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------- the CUDA arm
+def run_decode(args, rank, world, kind_cfg):
+    import torch
+    import torch.distributed as dist
+    from kata_b200 import capi, synth
+
+    _, B, kv_mode, lmax, lmin = kind_cfg
+    dev = torch.device("cuda", torch.cuda.current_device())
+    steps_total = args.warmup + args.steps + 2
+    lens = synth.seq_lengths(1234 + rank, B, lmin, lmax).astype(np.int64)
+    lens = np.minimum(lens, lmax)
+    ctx = capi.AttnContext(N_LAYERS, [int(l) + 2 * steps_total + 8 for l in lens], kv_mode=kv_mode)
+    gen = torch.Generator(device=dev); gen.manual_seed(4321 + rank)
+    seqs = list(range(B))
+    qn = (1 + 0.05 * torch.randn(N_LAYERS, 256, generator=gen, device=dev)).contiguous()
+    kn = (1 + 0.05 * torch.randn(N_LAYERS, 256, generator=gen, device=dev)).contiguous()
+    # fill the caches through prep (K/V head slots only): contents are normed, rotated fp16 (or int8) rows, as in a real run
+    CH = 1024
+    for layer in range(N_LAYERS):
+        for sq in seqs:
+            for start in range(0, int(lens[sq]), CH):
+                m = min(CH, int(lens[sq]) - start)
+                kp = torch.randn(1, m, 1024, generator=gen, device=dev)
+                vp = torch.randn(1, m, 1024, generator=gen, device=dev)
+                ctx.prep(layer, [sq], [start], m, None, kp, vp, None, kn[layer], h0=24, nh=8)
+    ctx.check()
+    qfull = torch.randn(N_LAYERS, B, 1, 12288, generator=gen, device=dev)
+    kproj = torch.randn(N_LAYERS, B, 1, 1024, generator=gen, device=dev)
+    vproj = torch.randn(N_LAYERS, B, 1, 1024, generator=gen, device=dev)
+    q16 = torch.empty(N_LAYERS, B, 1, 6144, dtype=torch.float16, device=dev)
+    gate = torch.empty(N_LAYERS, B, 1, 6144, dtype=torch.float32, device=dev)
+    out = torch.empty(N_LAYERS, B, 1, 6144, dtype=torch.float32, device=dev)
+    pos = lens.copy()
+
+    def step(p):
+        for layer in range(N_LAYERS):
+            ctx.prep(layer, seqs, p, 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], q16=q16[layer], gate=gate[layer])
+            ctx.decode(layer, seqs, p, 1, q16[layer], gate[layer], out=out[layer])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(pos); pos = pos + 1
+    ctx.check()
+    sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
+    l0 = ctx.launches()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    pos_timed0 = pos.copy()
+    for _ in range(args.steps):
+        step(pos); pos = pos + 1
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = ctx.launches() - l0
+    clocks = sampler.stop()
+    ctx.check()
+    assert torch.isfinite(out).all()
+
+    # the dominant kernel alone: the decode launches of the same steps, timed on the same stream
+    for layer in range(N_LAYERS):
+        ctx.decode(layer, seqs, pos_timed0, 1, q16[layer], gate[layer], out=out[layer])
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    reps = max(2, args.steps)
+    for _ in range(reps):
+        for layer in range(N_LAYERS):
+            ctx.decode(layer, seqs, pos_timed0, 1, q16[layer], gate[layer], out=out[layer])
+    k1.record(); torch.cuda.synchronize()
+    kern_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
+
+    # end to end through the C ABI with HOST buffers: per layer H2D of the token's projections, append, attend, D2H of the output
+    hq = torch.randn(N_LAYERS, B, 1, 12288).pin_memory(); hk = torch.randn(N_LAYERS, B, 1, 1024).pin_memory(); hv = torch.randn(N_LAYERS, B, 1, 1024).pin_memory()
+    hout = torch.empty(N_LAYERS, B, 1, 6144).pin_memory()
+    dq, dk, dv = torch.empty_like(qfull), torch.empty_like(kproj), torch.empty_like(vproj)
+
+    def step_e2e(p):
+        for layer in range(N_LAYERS):
+            dq[layer].copy_(hq[layer], non_blocking=True); dk[layer].copy_(hk[layer], non_blocking=True); dv[layer].copy_(hv[layer], non_blocking=True)
+            ctx.prep(layer, seqs, p, 1, dq[layer], dk[layer], dv[layer], qn[layer], kn[layer], q16=q16[layer], gate=gate[layer])
+            ctx.decode(layer, seqs, p, 1, q16[layer], gate[layer], out=out[layer])
+            hout[layer].copy_(out[layer], non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller holds the step's result on the host before the next step
+
+    pos_e = pos_timed0.copy()
+    step_e2e(pos_e)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e(pos_e); pos_e = pos_e + 1
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    h2d = N_LAYERS * B * (12288 + 2048) * 4
+    d2h = N_LAYERS * B * 6144 * 4
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    row_bytes = 4096 if kv_mode == "fp16" else 2064           # K+V bytes per key per layer (int8: codes + both fp16 scales)
+    mean_len = float(np.mean([pos_timed0 + i + 1 for i in range(args.steps)]))   # keys attended per sequence per step (the new key included)
+    bytes_per_launch = float(np.sum(pos_timed0 + 1)) * row_bytes
+    pk = peaks()
+    ach = bytes_per_launch / (kern_ms * 1e-3) / 1e9
+    res = {
+        "metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * B * args.steps / (ms * 1e-3), "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16" if kv_mode == "fp16" else "int8", "data": "synthetic",
+        "config": {"workload": f"decode, {N_LAYERS} layers, {kv_mode} KV, ctx 32768, batch {B}/GPU (lengths uniform [{lmin},{lmax}]), 1 new token/step, append+attend per layer",
+                   "batch_per_gpu": B, "global_batch": world * B, "mean_context": mean_len, "parallelism": f"batch-sharded x{world}", "l2": "inputs larger than L2 (no flush needed)"},
+        "clocks": clocks, "gpu_launches": int(launches),
+        "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_src": pk["src"],
+                     "frac_of_nominal_8TBs": ach / 8000.0, "us_per_launch": kern_ms * 1e3, "algorithmic_bytes_per_launch": bytes_per_launch, "traffic": None},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        res["cpu_baseline"] = cpu_baseline_decode(ctx, lens, pos_timed0, B, kv_mode)
+    ctx.close()
+    return res
+
+
+def cpu_baseline_decode(ctx, lens, pos, B, kv_mode):
+    """The oracle's scalar decode (the reference's k_attn_decode math) on the host cores, on a bounded sample: layer 0 of
+    the same caches (copied back from the GPU), all sequences at full length; tok/s extrapolated to 16 layers."""
+    from oracle import kata_oracle as orc
+    if kv_mode != "fp16":
+        return {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": "not run for int8 (the scalar CPU decode reads an fp16 cache)"}
+    nb = min(B, 8)
+    ks = [ctx.plane_read(0, s, 0, 0, int(pos[s]) + 1).view(np.uint16) for s in range(nb)]
+    vs = [ctx.plane_read(0, s, 1, 0, int(pos[s]) + 1).view(np.uint16) for s in range(nb)]
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((nb, 6144)).astype(np.float32); g = rng.standard_normal((nb, 6144)).astype(np.float32)
+    cores = orc.hw_threads()
+    t0 = time.perf_counter()
+    orc.decode_batch(q, g, ks, vs, [int(p) for p in pos[:nb]], threads=cores)
+    dt = time.perf_counter() - t0
+    return {"value": nb / (dt * N_LAYERS), "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"1 of {N_LAYERS} layers, {nb} sequences at full length ({dt:.2f} s), tok/s extrapolated x{N_LAYERS} layers"}
+
+
+# ------------------------------------------------------------------------------------------------- the reference arm
+def run_reference(args, kind_cfg):
+    """The reference's own CPU implementation of the path: its scalar attention math (k_attn_decode restated in the
+    oracle; the reference's kernels are Metal and cannot run here) on all host threads. Each step is a bounded sample:
+    one of the 16 layers for the whole batch at full context; tok/s is extrapolated to 16 layers."""
+    from oracle import kata_oracle as orc
+    from kata_b200 import synth
+    _, B, kv_mode, lmax, lmin = kind_cfg
+    lens = synth.seq_lengths(1234, B, lmin, lmax)
+    rng = np.random.default_rng(99)
+    ks = [rng.standard_normal((int(l) + 1, 1024), dtype=np.float32).astype(np.float16).view(np.uint16) for l in lens]
+    vs = [rng.standard_normal((int(l) + 1, 1024), dtype=np.float32).astype(np.float16).view(np.uint16) for l in lens]
+    q = rng.standard_normal((B, 6144)).astype(np.float32); g = rng.standard_normal((B, 6144)).astype(np.float32)
+    cores = orc.hw_threads()
+    pos = [int(l) for l in lens]
+    for _ in range(min(args.warmup, 1)):
+        orc.decode_batch(q, g, ks, vs, pos, threads=cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.decode_batch(q, g, ks, vs, pos, threads=cores)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = B / (dt * N_LAYERS)
+    return {"impl": "reference", "metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * N_LAYERS * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": f"decode, {N_LAYERS} layers, fp16 KV, ctx 32768, batch {B} (lengths uniform [{lmin},{lmax}]), scalar CPU attention", "batch_per_gpu": B},
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": f"each step = 1 of {N_LAYERS} layers for the whole batch at full context; x{N_LAYERS} extrapolated"},
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="kata_b200", choices=["kata_b200", "reference"])
+    ap.add_argument("--workload", default="decode_b8", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "kata_b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args, cfg)), flush=True)
+        return
+
+    import torch
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback for the product path"
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if cfg[0] == "decode":
+        res = run_decode(args, rank, world, cfg)
+    else:
+        from kata_b200 import bench_prefill
+        res = bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,140 @@
+/* kata_attn.h - C ABI of the B200 gated-GQA attention path of the kata engine.
+ *
+ * The reference engine (wolfjpy/kata) has no plugin or FFI interface: its attention kernels are looked up by name in a
+ * Metal library and encoded inline by Engine (src/gpu.cpp:17-25). The boundary this library replaces is therefore the
+ * set of per-layer attention calls Engine makes and the raw KV-plane access the prefix cache uses. Each entry point
+ * below names the reference call site it stands in for (paths relative to the reference project root).
+ *
+ * Model geometry is fixed (config/kata_m6.h:16-32): 24 query heads, 4 KV heads (6 query heads per KV head), head_dim
+ * 256, rotary dims 64 (pairs (i, i+32)), theta 1e7, RMSNorm eps 1e-6, softmax scale 1/16.
+ *
+ * Conventions
+ *  - Every pointer named d_* is DEVICE memory owned by the caller; h_* is HOST memory. The context owns the KV cache,
+ *    the scale planes and all scratch; nothing is allocated after kata_attn_create returns, except where noted.
+ *  - Calls enqueue work on the caller's CUDA stream (a cudaStream_t passed as void*; NULL = the default stream) and
+ *    return without synchronising, except the plane read/write and kata_attn_check calls.
+ *  - Every function returns KATA_OK or an error code; nothing aborts the process (the reference prints and exit(1)s,
+ *    src/engine.cpp:195). kata_attn_last_error gives a message for the last failing call on that context.
+ *  - One context per GPU; a context is not re-entrant.
+ *  - Batches: the reference is single-sequence. Here a context holds n_seqs independent sequences; calls take a list
+ *    of sequence ids with one position each. Per-sequence semantics are exactly the batch-1 semantics.
+ */
+#ifndef KATA_ATTN_H
+#define KATA_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KATA_HEADS 24
+#define KATA_KV_HEADS 4
+#define KATA_HEAD_DIM 256
+#define KATA_Q_DIM 6144      /* 24 * 256: one token's query / gate / output row */
+#define KATA_KV_DIM 1024     /* 4 * 256: one token's K or V row */
+#define KATA_QFULL_DIM 12288 /* per head [query 256 | gate 256] */
+#define KATA_MAX_BATCH 64    /* sequences per call */
+#define KATA_MAX_CHUNK 1024  /* tokens per prefill call (Engine::kMaxChunk, src/engine.h:38) */
+#define KATA_MAX_VERIFY 8    /* tokens per scalar decode call (Engine::kMaxVerify, src/engine.h:97) */
+
+enum { KATA_OK = 0, KATA_ERR_ARG = 1, KATA_ERR_RANGE = 2, KATA_ERR_MODE = 3, KATA_ERR_CUDA = 4, KATA_ERR_DEVICE_WAIT = 5, KATA_ERR_NOMEM = 6 };
+enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1 };             /* KATA_KV=fp16|int8 (src/engine.cpp:54-58) */
+enum { KATA_ROUND_RINT = 0, KATA_ROUND_HALF_AWAY = 1 };  /* rint (ties to even) is what the reference kernel does (shaders/flash.metal:170) */
+enum { KATA_ACT_F32 = 0, KATA_ACT_BF16 = 1 };            /* dtype of qfull / kproj / vproj / out */
+
+typedef struct kata_attn_ctx kata_attn_ctx;
+
+typedef struct kata_attn_config {
+    int32_t device;         /* CUDA device ordinal */
+    int32_t n_layers;       /* attention layers sharing this context (16 for the trunk; the MTP head is a 1-layer context) */
+    int32_t n_seqs;         /* independent sequences held (reference: 1) */
+    const int32_t* max_ctx; /* [n_seqs] rows reserved per layer for each sequence (Engine::maxCtx) */
+    int32_t kv_mode;        /* KATA_KV_* ; fixed for the life of the context (docs/reports/M11-int8-kv.en.md:69-71) */
+    int32_t quant_round;    /* KATA_ROUND_* ; int8 mode only */
+    int32_t dec_chunk;      /* keys per decode split; 0 = sized from the SM count (reference: 128, KATA_DEC_CHUNK) */
+    int32_t reserved;
+} kata_attn_config;
+
+/* Engine::load, cache part (src/engine.cpp:54-60,79): allocates, zero-filled (src/gpu.cpp:26-30), per sequence
+ * K and V planes [n_layers][max_ctx][1024] (fp16, or int8 plus fp16 scale planes [n_layers][max_ctx][4]) and all scratch. */
+int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out);
+int kata_attn_destroy(kata_attn_ctx* ctx);
+
+/* Engine::resetState, cache part (src/engine.cpp:88-95): zero the caches and scale planes. */
+int kata_attn_reset(kata_attn_ctx* ctx, void* stream);
+
+/* Engine::numericsTag, KV part (src/engine.cpp:517-521): "fp16" or "fp16+kv8"; checkpoints of different tags never mix. */
+const char* kata_attn_numerics_tag(const kata_attn_ctx* ctx);
+const char* kata_attn_last_error(const kata_attn_ctx* ctx);
+
+/* Synchronises the stream and reports a device-side wait that ran out (KATA_ERR_DEVICE_WAIT) or a CUDA error.
+ * Device-side waits in this library are bounded; none can spin forever. */
+int kata_attn_check(kata_attn_ctx* ctx, void* stream);
+
+/* k_attn_prep / k_attn_prep_b (shaders/attn.metal:5-37, shaders/prefill.metal:179-206; encoded at src/engine.cpp:168,
+ * 274, 360, 404, 473, 608), with k_cvt_q_half (shaders/flash.metal:71) and, in int8 mode, k_kv_quant_sym
+ * (Engine::dKvQuant, src/engine.cpp:524-527) fused in.
+ * For sequence seq_ids[b] and token t < T at position pos0[b]+t, head slots [h0, h0+nh): slots 0..23 query heads
+ * (RMSNorm, partial RoPE, gate split), 24..27 key heads (RMSNorm, RoPE, append to the K plane), 28..31 value heads
+ * (append to the V plane). h0=24, nh=8 appends K/V only (src/engine.cpp:402-404).
+ *   d_qfull [n][T][12288], d_kproj, d_vproj [n][T][1024]: act_dtype; d_qnorm, d_knorm: fp32 [256].
+ *   d_q16   [n][T][6144] fp16, the query after norm and RoPE times 1/16 (what the matrix attention kernels read); may be NULL.
+ *   d_q32   [n][T][6144] fp32, unscaled (the reference's qout; read by kata_attn_decode_scalar); may be NULL.
+ *   d_gate  [n][T][6144] fp32 gate logits; may be NULL when nh covers no query head. */
+int kata_attn_prep(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos0, int32_t T,
+                   const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype,
+                   const float* d_qnorm, const float* d_knorm, void* d_q16, float* d_q32, float* d_gate,
+                   int32_t h0, int32_t nh, void* stream);
+
+/* Engine::dKvQuant + k_kv_quant_sym (src/engine.cpp:524-527, shaders/flash.metal:157-178) as a stand-alone call:
+ * quantise T fp16 rows d_ks, d_vs [T][1024] into rows pos0.. of one sequence's int8 planes. Bit-exact with the
+ * reference arithmetic: scale = fp16(amax/127) (1.0 for an all-zero row), code = clamp(round(v * (1/float(scale)))). */
+int kata_attn_kv_quant(kata_attn_ctx* ctx, int32_t layer, int32_t seq, const void* d_ks, const void* d_vs, int32_t T, int32_t pos0, void* stream);
+
+/* Engine::dDecAttn (src/engine.cpp:119-127): k_dec_q_pack + k_attn_dec_split[_q8] + k_attn_dec_combine
+ * (shaders/flash.metal:77-152). T in {1,2} query tokens per sequence at positions pos_base[b]+t; token t sees keys
+ * [first_pos, pos_base[b]+t]; first_pos is 0 for the trunk and 1 for the MTP-head cache (src/engine.cpp:362).
+ *   d_q16, d_gate as written by kata_attn_prep; d_out [n][T][6144] out_dtype = softmax(q k^T) v * sigmoid(gate). */
+int kata_attn_decode(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,
+                     const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+
+/* The scalar path: k_attn_split(_b) + k_attn_combine(_b) (shaders/attn.metal:66-117, shaders/prefill.metal:209-261;
+ * KATA_SCALAR_DEC, src/engine.cpp:169-175, 365, 478, 617). fp32 query, fp16 cache only, T <= KATA_MAX_VERIFY. */
+int kata_attn_decode_scalar(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,
+                            const float* d_q32, const float* d_gate, float* d_out, void* stream);
+
+/* k_flash_prefill / k_flash_prefill_q8 (shaders/flash.metal:10-68; encoded at src/engine.cpp:279, 614): causal flash
+ * attention of M <= KATA_MAX_CHUNK query rows per sequence at positions pos_base[b]+r over keys [0, pos_base[b]+r] of
+ * the cache (this chunk's rows must already have been appended by kata_attn_prep). d_q16, d_gate, d_out: [n][M][6144]. */
+int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t M,
+                      const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+
+/* Split-KV across GPUs (no reference counterpart: the reference is single-device). Each rank holds keys
+ * [key_lo, key_hi) of sequence seq in ITS context at rows [0, key_hi-key_lo) (row = key - key_lo) and computes, per
+ * (token, head), the unnormalised partial of k_attn_dec_split merged over its local splits:
+ *   d_part [T*24][258] fp32 = { O[256], m, l }. The ranks exchange parts (e.g. an NCCL all-gather) and each calls
+ * kata_attn_merge_parts, which applies k_attn_dec_combine's merge (shaders/flash.metal:147-151) over ranks and the gate. */
+int kata_attn_decode_partial(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
+                             const void* d_q16, float* d_part, void* stream);
+int kata_attn_merge_parts(kata_attn_ctx* ctx, const float* d_parts, int32_t n_parts, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+
+/* KV planes for the prefix cache: Engine::kvPlanes / kvPlaneRow / kvPlanePtr (src/engine.h:74-81), used by
+ * PrefixCache::restore and ::writeFile (src/ckpt.cpp:98, 134). Plane order and row sizes match the reference:
+ * fp16 -> {K, V} rows of 2048 B; int8 -> {K, V, K scales, V scales} rows of 1024, 1024, 8, 8 B.
+ * The reference reads and writes shared memory directly; here the copy is explicit and synchronous. */
+int32_t kata_attn_kv_planes(const kata_attn_ctx* ctx);
+size_t kata_attn_kv_plane_row_bytes(const kata_attn_ctx* ctx, int32_t plane);
+int kata_attn_kv_plane_read(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, void* h_dst);
+int kata_attn_kv_plane_write(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, const void* h_src);
+/* Device address of row 0 of a plane (kvPlanePtr). */
+void* kata_attn_kv_plane_ptr(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane);
+
+/* Number of kernels this library has launched on this context since creation (for accounting in benchmarks). */
+uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KATA_ATTN_H */

@@ -1,0 +1,195 @@
+"""ctypes binding of ``libkata_attn.so`` (the C ABI in ``include/kata_attn.h``) for the tests and the benchmark.
+
+torch is used only to own device memory and streams; every attention computation goes through the C ABI into the
+hand-written CUDA kernels. There is no CPU or PyTorch fallback: if the library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkata_attn.so")
+
+OK = 0
+KV_FP16, KV_INT8 = 0, 1
+ROUND_RINT, ROUND_HALF_AWAY = 0, 1
+ACT_F32, ACT_BF16 = 0, 1
+QD, KVD, QFULL, MAX_BATCH = 6144, 1024, 12288, 64
+
+EXPORTS = [
+    "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
+    "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
+    "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count",
+]
+
+
+class Config(C.Structure):
+    _fields_ = [("device", C.c_int32), ("n_layers", C.c_int32), ("n_seqs", C.c_int32), ("max_ctx", C.POINTER(C.c_int32)),
+                ("kv_mode", C.c_int32), ("quant_round", C.c_int32), ("dec_chunk", C.c_int32), ("reserved", C.c_int32)]
+
+
+class KataError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"kata_attn error {code}: {msg}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the library; raises if it has not been built (``python -m kata_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m kata_b200.build` (there is no fallback path)")
+        L = C.CDLL(LIB_PATH)
+        L.kata_attn_numerics_tag.restype = C.c_char_p
+        L.kata_attn_last_error.restype = C.c_char_p
+        L.kata_attn_kv_plane_row_bytes.restype = C.c_size_t
+        L.kata_attn_kv_plane_ptr.restype = C.c_void_p
+        L.kata_attn_launch_count.restype = C.c_uint64
+        for name in EXPORTS:
+            getattr(L, name)
+        _lib = L
+    return _lib
+
+
+def _i32(xs):
+    a = np.ascontiguousarray(np.asarray(xs, dtype=np.int32).reshape(-1))
+    return a, a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def _dp(t):
+    if t is None:
+        return C.c_void_p(0)
+    assert t.is_cuda and t.is_contiguous()
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class AttnContext:
+    """One context per GPU: the KV caches of ``len(max_ctx)`` sequences x ``n_layers`` layers plus all scratch."""
+
+    def __init__(self, n_layers: int, max_ctx, kv_mode: str = "fp16", quant_round: str = "rint", device: int | None = None, dec_chunk: int = 0):
+        self.L = lib()
+        self.device = torch.cuda.current_device() if device is None else device
+        self.max_ctx, mp = _i32(max_ctx)
+        self.n_layers, self.n_seqs = n_layers, len(self.max_ctx)
+        self.int8 = kv_mode == "int8"
+        cfg = Config(self.device, n_layers, self.n_seqs, mp, KV_INT8 if self.int8 else KV_FP16, ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, 0)
+        self.h = C.c_void_p()
+        rc = self.L.kata_attn_create(C.byref(cfg), C.byref(self.h))
+        if rc != OK:
+            raise KataError(rc, "kata_attn_create failed")
+
+    def close(self):
+        if self.h:
+            self.L.kata_attn_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, rc):
+        if rc != OK:
+            raise KataError(rc, self.L.kata_attn_last_error(self.h).decode())
+
+    def tag(self) -> str:
+        return self.L.kata_attn_numerics_tag(self.h).decode()
+
+    def reset(self):
+        self._ck(self.L.kata_attn_reset(self.h, _stream()))
+
+    def check(self):
+        self._ck(self.L.kata_attn_check(self.h, _stream()))
+
+    def launches(self) -> int:
+        return int(self.L.kata_attn_launch_count(self.h))
+
+    def prep(self, layer, seq_ids, pos0, T, qfull, kproj, vproj, qnorm, knorm, h0=0, nh=32, q16=None, q32=None, gate=None, want_q32=False):
+        """Returns (q16, q32 or None, gate). qfull [n][T][12288], kproj/vproj [n][T][1024] in fp32 or bf16."""
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos0)
+        n = len(sa)
+        ref = kproj if kproj is not None else qfull
+        act = ACT_BF16 if ref.dtype == torch.bfloat16 else ACT_F32
+        dev = ref.device
+        if h0 < 24:
+            q16 = torch.empty((n, T, QD), dtype=torch.float16, device=dev) if q16 is None else q16
+            gate = torch.empty((n, T, QD), dtype=torch.float32, device=dev) if gate is None else gate
+            if want_q32 and q32 is None:
+                q32 = torch.empty((n, T, QD), dtype=torch.float32, device=dev)
+        self._ck(self.L.kata_attn_prep(self.h, layer, n, sp, pp, T, _dp(qfull), _dp(kproj), _dp(vproj), act, _dp(qnorm), _dp(knorm),
+                                       _dp(q16), _dp(q32), _dp(gate), h0, nh, _stream()))
+        return q16, q32, gate
+
+    def kv_quant(self, layer, seq, ks, vs, pos0):
+        self._ck(self.L.kata_attn_kv_quant(self.h, layer, seq, _dp(ks), _dp(vs), ks.shape[0], pos0, _stream()))
+
+    def decode(self, layer, seq_ids, pos_base, T, q16, gate, first_pos=0, out=None, out_dtype=torch.float32):
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos_base)
+        n = len(sa)
+        out = torch.empty((n, T, QD), dtype=out_dtype, device=q16.device) if out is None else out
+        self._ck(self.L.kata_attn_decode(self.h, layer, n, sp, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        return out
+
+    def decode_scalar(self, layer, seq_ids, pos_base, T, q32, gate, first_pos=0, out=None):
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos_base)
+        n = len(sa)
+        out = torch.empty((n, T, QD), dtype=torch.float32, device=q32.device) if out is None else out
+        self._ck(self.L.kata_attn_decode_scalar(self.h, layer, n, sp, pp, T, first_pos, _dp(q32), _dp(gate), _dp(out), _stream()))
+        return out
+
+    def prefill(self, layer, seq_ids, pos_base, M, q16, gate, out=None, out_dtype=torch.float32):
+        sa, sp = _i32(seq_ids)
+        pa, pp = _i32(pos_base)
+        n = len(sa)
+        out = torch.empty((n, M, QD), dtype=out_dtype, device=q16.device) if out is None else out
+        self._ck(self.L.kata_attn_prefill(self.h, layer, n, sp, pp, M, _dp(q16), _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        return out
+
+    def decode_partial(self, layer, seq, pos_base, T, key_lo, key_hi, q16, part=None):
+        part = torch.empty((T * 24, 258), dtype=torch.float32, device=q16.device) if part is None else part
+        self._ck(self.L.kata_attn_decode_partial(self.h, layer, seq, pos_base, T, key_lo, key_hi, _dp(q16), _dp(part), _stream()))
+        return part
+
+    def merge_parts(self, parts, T, gate, out=None, out_dtype=torch.float32):
+        n_parts = parts.shape[0]
+        out = torch.empty((T, QD), dtype=out_dtype, device=parts.device) if out is None else out
+        self._ck(self.L.kata_attn_merge_parts(self.h, _dp(parts), n_parts, T, _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        return out
+
+    # ---- KV planes (prefix-cache contract) ----
+    def kv_planes(self) -> int:
+        return int(self.L.kata_attn_kv_planes(self.h))
+
+    def plane_row_bytes(self, plane: int) -> int:
+        return int(self.L.kata_attn_kv_plane_row_bytes(self.h, plane))
+
+    def plane_read(self, layer, seq, plane, row0, nrows) -> np.ndarray:
+        buf = np.empty(nrows * self.plane_row_bytes(plane), np.uint8)
+        self._ck(self.L.kata_attn_kv_plane_read(self.h, layer, seq, plane, row0, nrows, buf.ctypes.data_as(C.c_void_p)))
+        return buf
+
+    def plane_write(self, layer, seq, plane, row0, data: np.ndarray):
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        rb = self.plane_row_bytes(plane)
+        assert rb and data.size % rb == 0
+        self._ck(self.L.kata_attn_kv_plane_write(self.h, layer, seq, plane, row0, data.size // rb, data.ctypes.data_as(C.c_void_p)))
+
+    def plane_ptr(self, layer, seq, plane) -> int:
+        return int(self.L.kata_attn_kv_plane_ptr(self.h, layer, seq, plane) or 0)

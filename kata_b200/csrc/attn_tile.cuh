@@ -1,0 +1,147 @@
+// One warp, one 16-row query block, one 16-key tile: S = Q K^T, masked online softmax, O += P V.
+// Shared by the decode kernel (rows = 6 heads x T tokens of a KV head) and the mma.sync prefill kernel (rows = 16
+// consecutive query positions of one head). Tile order and rounding points follow the reference's matrix kernels
+// (shaders/flash.metal:39-60, 112-132): fp16 Q (prescaled by 1/16) x fp16 or int8 K with fp32 accumulation; int8
+// scores multiplied by the key's fp16 scale; P = exp(S - m) rounded to fp16 (after the V scale in int8 mode);
+// l accumulated from the unrounded p; fully masked rows keep m = -inf and contribute nothing.
+//
+// Fragment layouts (mma.sync.m16n8k16, g = lane/4, t4 = lane%4): accumulator element 0,1 = row g, columns 2*t4, 2*t4+1;
+// elements 2,3 = row g+8. K/V rows sit in shared memory with a 16-byte pad per row so the eight row addresses of an
+// ldmatrix fall in distinct banks. int8 rows are dequantised in registers: ldmatrix moves raw bytes (as b16 pairs),
+// a byte permute drops them onto the fp16 pattern 0x64xx (= 1024 + x), and one half2 subtract removes the bias.
+#pragma once
+#include "kata_internal.cuh"
+#include "ptx.cuh"
+
+namespace kata {
+
+template <bool I8> struct TileGeo {
+    static constexpr int kRowBytes = I8 ? 256 : 512;      // one head's K or V row in the cache
+    static constexpr int kRowStride = kRowBytes + 16;     // in shared memory
+};
+constexpr int kQStride = 528;                              // bytes per staged Q row (256 fp16 + 16 pad)
+
+// dimension held by O accumulator element (n-tile j, column c in {0,1}) of a thread with quad index t4
+template <bool I8> __device__ __forceinline__ int dim_of(int j, int c, int t4) {
+    if (!I8) return 8 * j + 2 * t4 + c;
+    return (j >> 1) * 16 + 4 * t4 + 2 * c + (j & 1);
+}
+
+// int8 mode wants the Q block's columns permuted inside each 16-dim block to the contraction order of the dequantised
+// K fragments: dim d = 4*tq + rem  ->  column (rem>>1)*8 + 2*tq + (rem&1).
+__device__ __forceinline__ int q8_col_of_dim(int d16) { const int tq = d16 >> 2, rem = d16 & 3; return (rem >> 1) * 8 + 2 * tq + (rem & 1); }
+
+__device__ __forceinline__ uint32_t deq2(uint32_t x, uint32_t sel) {   // two biased bytes of x -> half2 of the signed values
+    const uint32_t h = ptx::prmt(x, 0x64646464u, sel);
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __floats2half2_rn(1152.0f, 1152.0f));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+struct RowState {   // softmax state of rows g and g+8 (m in log2 units, l partial over this thread's columns) and the O block
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    float o[32][4];
+    __device__ __forceinline__ void clear() {
+        m0 = m1 = -INFINITY; l0 = l1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+    }
+    __device__ __forceinline__ void finish_l() {   // sum l over the quad that shares a row
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+};
+
+// q_sm: shared address of the warp's 16-row Q block (row stride kQStride). k_sm / v_sm: shared addresses of the tile's 16
+// K and V rows (row stride TileGeo::kRowStride). key0: index of the tile's first key; row g sees keys < lim0, row g+8
+// keys < lim1 (0 for a dead row). ks/vs: int8 mode, the fp16 scales of this thread's four score columns
+// (keys key0 + nt*8 + 2*t4 + e -> [nt][e]).
+template <bool I8>
+__device__ __forceinline__ void tile_qk_softmax_pv(const uint32_t q_sm, const uint32_t k_sm, const uint32_t v_sm, const int key0, const int lim0, const int lim1,
+                                                   const float (&ks)[2][2], const float (&vs)[2][2], RowState& st, const int lane) {
+    using G = TileGeo<I8>;
+    using namespace ptx;
+    const int t4 = lane & 3;
+    float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    const uint32_t qa = q_sm + (lane & 15) * kQStride + (lane >> 4) * 16;
+    const uint32_t ka = k_sm + ((lane & 7) + ((lane >> 4) << 3)) * G::kRowStride + ((lane >> 3) & 1) * 16;
+    if (!I8) {
+#pragma unroll
+        for (int kk = 0; kk < 16; kk++) {
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            ldsm_x4(qa + kk * 32, a0, a1, a2, a3); ldsm_x4(ka + kk * 32, b0, b1, b2, b3);
+            mma16816(s[0], a0, a1, a2, a3, b0, b1); mma16816(s[1], a0, a1, a2, a3, b2, b3);
+        }
+    } else {
+        // an 8x8 b16 matrix covers 8 keys x 16 int8 dims; a thread's register = dims 4*t4..4*t4+3 of key g
+#pragma unroll
+        for (int k2 = 0; k2 < 8; k2++) {
+            uint32_t r0, r1, r2, r3; ldsm_x4(ka + k2 * 32, r0, r1, r2, r3);   // r0: keys 0-7 block 2*k2, r1: keys 0-7 block 2*k2+1, r2, r3: keys 8-15
+            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(qa + (2 * k2) * 32, a0, a1, a2, a3);
+            mma16816(s[0], a0, a1, a2, a3, deq2(r0, 0x4140u), deq2(r0, 0x4342u)); mma16816(s[1], a0, a1, a2, a3, deq2(r2, 0x4140u), deq2(r2, 0x4342u));
+            ldsm_x4(qa + (2 * k2 + 1) * 32, a0, a1, a2, a3);
+            mma16816(s[0], a0, a1, a2, a3, deq2(r1, 0x4140u), deq2(r1, 0x4342u)); mma16816(s[1], a0, a1, a2, a3, deq2(r3, 0x4140u), deq2(r3, 0x4342u));
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) { s[nt][0] *= ks[nt][0]; s[nt][1] *= ks[nt][1]; s[nt][2] *= ks[nt][0]; s[nt][3] *= ks[nt][1]; }
+    }
+    // mask by select (never by arithmetic: rows past the valid range may hold anything)
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) { const int key = key0 + nt * 8 + 2 * t4 + e; if (key >= lim0) s[nt][e] = -INFINITY; if (key >= lim1) s[nt][2 + e] = -INFINITY; }
+    // online softmax in the log2 domain
+    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])) * kLog2e, mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3])) * kLog2e;
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+    const float al0 = (mn0 == -INFINITY) ? 1.0f : ex2(st.m0 - mn0), al1 = (mn1 == -INFINITY) ? 1.0f : ex2(st.m1 - mn1);
+    const float sub0 = (mn0 == -INFINITY) ? 0.0f : mn0, sub1 = (mn1 == -INFINITY) ? 0.0f : mn1;
+    st.m0 = mn0; st.m1 = mn1;
+    float pr[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) { pr[nt][0] = ex2(fmaf(s[nt][0], kLog2e, -sub0)); pr[nt][1] = ex2(fmaf(s[nt][1], kLog2e, -sub0)); pr[nt][2] = ex2(fmaf(s[nt][2], kLog2e, -sub1)); pr[nt][3] = ex2(fmaf(s[nt][3], kLog2e, -sub1)); }
+    st.l0 = st.l0 * al0 + ((pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
+    st.l1 = st.l1 * al1 + ((pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]));
+    if (__any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f)) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
+    }
+    if (I8) {
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) { pr[nt][0] *= vs[nt][0]; pr[nt][1] *= vs[nt][1]; pr[nt][2] *= vs[nt][0]; pr[nt][3] *= vs[nt][1]; }
+    }
+    const uint32_t pa0 = pack_h2(pr[0][0], pr[0][1]), pa1 = pack_h2(pr[0][2], pr[0][3]), pa2 = pack_h2(pr[1][0], pr[1][1]), pa3 = pack_h2(pr[1][2], pr[1][3]);
+    const uint32_t va = v_sm + ((lane & 7) + ((lane >> 3) & 1) * 8) * G::kRowStride + (lane >> 4) * 16;
+    if (!I8) {
+#pragma unroll
+        for (int j2 = 0; j2 < 16; j2++) {
+            uint32_t b0, b1, b2, b3; ldsm_x4_t(va + j2 * 32, b0, b1, b2, b3);
+            mma16816(st.o[2 * j2], pa0, pa1, pa2, pa3, b0, b1); mma16816(st.o[2 * j2 + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+    } else {
+        // transposed b16 load of int8 rows: register = { V[2*t4][2g], V[2*t4][2g+1], V[2*t4+1][2g], V[2*t4+1][2g+1] } within the matrix
+#pragma unroll
+        for (int j2 = 0; j2 < 8; j2++) {
+            uint32_t r0, r1, r2, r3; ldsm_x4_t(va + j2 * 32, r0, r1, r2, r3);   // r0: keys 0-7 block 2*j2, r1: keys 8-15 block 2*j2, r2, r3: block 2*j2+1
+            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+            mma16816(st.o[4 * j2 + 0], pa0, pa1, pa2, pa3, deq2(r0, 0x4240u), deq2(r1, 0x4240u));
+            mma16816(st.o[4 * j2 + 1], pa0, pa1, pa2, pa3, deq2(r0, 0x4341u), deq2(r1, 0x4341u));
+            mma16816(st.o[4 * j2 + 2], pa0, pa1, pa2, pa3, deq2(r2, 0x4240u), deq2(r3, 0x4240u));
+            mma16816(st.o[4 * j2 + 3], pa0, pa1, pa2, pa3, deq2(r2, 0x4341u), deq2(r3, 0x4341u));
+        }
+    }
+}
+
+// Stage one 16-byte chunk (8 fp16 values, dims c16*8..c16*8+7) of a Q row into shared memory, permuting for int8 mode.
+template <bool I8> __device__ __forceinline__ void stage_q_chunk(uint8_t* q_row_sm, int c16, uint4 v) {
+    if (!I8) { *reinterpret_cast<uint4*>(q_row_sm + c16 * 16) = v; return; }
+    const __half* hv = reinterpret_cast<const __half*>(&v); __half* dst = reinterpret_cast<__half*>(q_row_sm) + (c16 >> 1) * 16;
+#pragma unroll
+    for (int e = 0; e < 8; e++) dst[q8_col_of_dim((c16 & 1) * 8 + e)] = hv[e];
+}
+
+__device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+}  // namespace kata

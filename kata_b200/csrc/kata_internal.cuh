@@ -1,0 +1,62 @@
+// Internal declarations shared by the translation units of libkata_attn: the context object, the per-call batch
+// descriptor handed to kernels by value, and the launcher prototypes.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/kata_attn.h"
+
+namespace kata {
+
+constexpr int kH = KATA_HEADS, kKvh = KATA_KV_HEADS, kD = KATA_HEAD_DIM, kG = 6, kQD = KATA_Q_DIM, kKVD = KATA_KV_DIM, kQFull = KATA_QFULL_DIM;
+constexpr float kEps = 1e-6f;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kPartStride = 258;   // one (token, head) partial: O[256], m, l
+
+// What a kernel needs to find the cache rows of the sequences of one call. Passed by value (kernel parameter space),
+// so a call needs no host->device copy and no allocation. Row index of (sequence, layer, position) in the K/V arenas
+// is row_base[b] + position, with row_base already including the layer offset layer * max_ctx.
+struct Batch {
+    int32_t n;
+    int32_t pos[KATA_MAX_BATCH];        // pos0 / pos_base per sequence
+    int64_t row_base[KATA_MAX_BATCH];   // arena row of position 0 of (sequence, layer)
+    int32_t item_start[KATA_MAX_BATCH + 1];   // decode: first work item of sequence b (prefix sum of 4 * n_splits[b])
+    int32_t n_splits[KATA_MAX_BATCH];
+};
+
+struct Ctx {
+    kata_attn_config cfg{};
+    std::vector<int32_t> max_ctx;
+    std::vector<int64_t> seq_row0;     // arena row of (sequence, layer 0, position 0)
+    int64_t total_rows = 0;
+    int elt = 2;                        // bytes per cached K/V element
+    void* k_arena = nullptr; void* v_arena = nullptr;      // [total_rows][1024] fp16 or int8
+    __half* ksc = nullptr; __half* vsc = nullptr;          // [total_rows][4] fp16 (int8 mode)
+    // decode scratch: per work item (sequence, kv head, split) the unnormalised partial rows and their (m, l)
+    float* part_o = nullptr; float* part_ml = nullptr; int32_t* counters = nullptr; int32_t max_items = 0;
+    // scalar-path scratch (k_attn_split partials)
+    float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
+    int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
+    int sm_count = 148;
+    uint64_t launches = 0;
+    std::string err;
+    std::string tag;
+    int64_t row_of(int layer, int seq) const { return seq_row0[seq] + (int64_t)layer * max_ctx[seq]; }
+};
+
+// launchers (defined next to their kernels); each returns a cudaError_t from the launch
+cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const void* kproj, const void* vproj, int act_dtype,
+                        const float* qnorm, const float* knorm, __half* q16, float* q32, float* gate, int h0, int nh, cudaStream_t s);
+cudaError_t launch_kv_quant(Ctx& c, int64_t row0, const __half* ks, const __half* vs, int T, cudaStream_t s);
+cudaError_t launch_decode_mma(Ctx& c, const Batch& b, int T, int first_pos, int n_items, const __half* q16, const float* gate, void* out, int out_dtype,
+                              float* part_out /* non-null: write merged partials instead of the gated output */, cudaStream_t s);
+cudaError_t launch_merge_parts(Ctx& c, const float* parts, int n_parts, int T, const float* gate, void* out, int out_dtype, cudaStream_t s);
+cudaError_t launch_decode_scalar(Ctx& c, const Batch& b, int T, int first_pos, const float* q32, const float* gate, float* out, cudaStream_t s);
+cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
+void set_inv_freq(const float* host32);   // uploads the 32 inverse RoPE frequencies to constant memory of the current device
+
+}  // namespace kata

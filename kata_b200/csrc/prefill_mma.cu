@@ -1,0 +1,126 @@
+// Causal flash prefill on mma.sync tiles: the first, simple prefill path (64 query rows of one head per CTA, 32-key
+// K/V tiles double-buffered with cp.async, the per-warp 16x16 tile routine shared with the decode kernel).
+// Replaces k_flash_prefill / k_flash_prefill_q8 of the reference (shaders/flash.metal:10-68; encoded at
+// src/engine.cpp:279, 614): query row r of the chunk sits at position pos_base + r and attends keys [0, pos_base + r]
+// of the cache prefix; output = O / l * sigmoid(gate). Chunked prefill over a restored or earlier-computed prefix is
+// the same call with pos_base > 0.
+#include <algorithm>
+
+#include "attn_tile.cuh"
+
+namespace kata {
+namespace {
+
+using namespace ptx;
+
+constexpr int kPfWarps = 4, kPfThreads = kPfWarps * 32, kBM = 16 * kPfWarps, kBN = 32;
+
+template <bool I8> struct PfGeo {
+    static constexpr int kRowStride = TileGeo<I8>::kRowStride;
+    static constexpr int kChunks = TileGeo<I8>::kRowBytes / 16;          // 16-byte chunks per K or V row
+    static constexpr int kTileBytes = kBN * kRowStride;                   // K or V half of a stage
+    static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kOffStages = kBM * kQStride;
+    static constexpr int kSmem = kOffStages + 2 * kStageBytes;
+};
+
+template <bool I8>
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_mma_kernel(const Batch b, const int M, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
+                                                                    const uint8_t* __restrict__ k_arena, const uint8_t* __restrict__ v_arena, const __half* __restrict__ ksc, const __half* __restrict__ vsc) {
+    using G = PfGeo<I8>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, bi = blockIdx.z, kvh = h / kG;   // the longest (latest) query tiles start first
+    const int q0 = qt * kBM, rows_valid = min(kBM, M - q0), pos_base = b.pos[bi], kend = pos_base + q0 + rows_valid, n_tiles = (kend + kBN - 1) / kBN;
+    const uint32_t sm_base = smem_u32(smem);
+    constexpr int kElt = I8 ? 1 : 2;
+    const uint8_t* Kg = k_arena + (b.row_base[bi] * kKVD + kvh * kD) * kElt; const uint8_t* Vg = v_arena + (b.row_base[bi] * kKVD + kvh * kD) * kElt;
+
+    for (int ch = tid; ch < kBM * 32; ch += kPfThreads) {
+        const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(q16 + ((int64_t)bi * M + q0 + r) * kQD + h * kD + c16 * 8);
+        stage_q_chunk<I8>(smem + r * kQStride, c16, v);
+    }
+    auto load_tile = [&](int kt, int buf) {
+        const uint32_t dst0 = sm_base + G::kOffStages + buf * G::kStageBytes;
+        for (int idx = tid; idx < 2 * kBN * G::kChunks; idx += kPfThreads) {
+            const int which = idx / (kBN * G::kChunks), rem = idx - which * (kBN * G::kChunks), r = rem / G::kChunks, c = rem - r * G::kChunks;
+            const int key = kt * kBN + r; const bool ok = key < kend;
+            cp_async16(dst0 + which * G::kTileBytes + r * G::kRowStride + c * 16, (which ? Vg : Kg) + (int64_t)(ok ? key : 0) * (kKVD * kElt) + c * 16, ok ? 16u : 0u);   // rows past the range arrive as zeros
+        }
+    };
+    const int row0 = q0 + 16 * w + g, row1 = row0 + 8;
+    const int lim0 = row0 < M ? pos_base + row0 + 1 : 0, lim1 = row1 < M ? pos_base + row1 + 1 : 0;
+    const int warp_lim = pos_base + min(q0 + 16 * w + 16, M);   // no row of this warp sees keys >= warp_lim
+    RowState st; st.clear();
+    const uint32_t q_sm = sm_base + (16 * w) * kQStride;
+
+    load_tile(0, 0); cp_async_commit();
+    for (int kt = 0; kt < n_tiles; kt++) {
+        if (kt + 1 < n_tiles) load_tile(kt + 1, (kt + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t kbuf = sm_base + G::kOffStages + (kt & 1) * G::kStageBytes, vbuf = kbuf + G::kTileBytes;
+#pragma unroll 1
+        for (int sub = 0; sub < kBN / 16; sub++) {
+            const int key0 = kt * kBN + sub * 16;
+            if (key0 >= warp_lim) break;
+            float ks_[2][2] = {{1.f, 1.f}, {1.f, 1.f}}, vs_[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
+            if (I8) {
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) { const int key = min(key0 + nt * 8 + 2 * t4 + e, kend - 1); ks_[nt][e] = __half2float(ksc[(b.row_base[bi] + key) * 4 + kvh]); vs_[nt][e] = __half2float(vsc[(b.row_base[bi] + key) * 4 + kvh]); }
+            }
+            tile_qk_softmax_pv<I8>(q_sm, kbuf + sub * 16 * G::kRowStride, vbuf + sub * 16 * G::kRowStride, key0, lim0, lim1, ks_, vs_, st, lane);
+        }
+        __syncthreads();
+    }
+    st.finish_l();
+    const float inv0 = 1.0f / st.l0, inv1 = 1.0f / st.l1;
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int row = half ? row1 : row0; if (row >= M) continue;
+            const float inv = half ? inv1 : inv0; const int64_t base = ((int64_t)bi * M + row) * kQD + h * kD;
+            if (!I8) {
+                const int d = dim_of<false>(j, 0, t4); const float2 gt = *reinterpret_cast<const float2*>(gate + base + d);
+                const float y0 = st.o[j][2 * half] * inv * sigmoid_fast(gt.x), y1 = st.o[j][2 * half + 1] * inv * sigmoid_fast(gt.y);
+                if (out_bf16) *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(out) + base + d) = __floats2bfloat162_rn(y0, y1);
+                else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + base + d) = make_float2(y0, y1);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const int d = dim_of<true>(j, c, t4); const float y = st.o[j][2 * half + c] * inv * sigmoid_fast(gate[base + d]);
+                    if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[base + d] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[base + d] = y;
+                }
+            }
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
+    static bool attr_set[2] = {false, false};
+    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
+    if (!attr_set[i8]) {
+        cudaError_t e = i8 ? cudaFuncSetAttribute(prefill_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<true>::kSmem)
+                           : cudaFuncSetAttribute(prefill_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<false>::kSmem);
+        if (e != cudaSuccess) return e;
+        attr_set[i8] = true;
+    }
+    const dim3 grid((M + kBM - 1) / kBM, kH, b.n);
+    if (i8) prefill_mma_kernel<true><<<grid, kPfThreads, PfGeo<true>::kSmem, s>>>(b, M, q16, gate, out, out_dtype == KATA_ACT_BF16, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc);
+    else prefill_mma_kernel<false><<<grid, kPfThreads, PfGeo<false>::kSmem, s>>>(b, M, q16, gate, out, out_dtype == KATA_ACT_BF16, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc);
+    c.launches++;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
+    return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
+}
+
+}  // namespace kata

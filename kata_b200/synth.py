@@ -53,3 +53,12 @@ def to_bf16_bits(x: np.ndarray) -> np.ndarray:
 
 def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
     return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def token_rows_fast(seed: int, M: int, layer: int = 0, seq: int = 0):
+    """Same distributions as token_rows from ONE stream per tensor (fast for tens of thousands of rows; rows are not
+    position-independent, so use it only where a cache is filled in one go)."""
+    qf = _rng(seed, _T_QFULL, layer, seq).standard_normal((M, QFULL), dtype=np.float32)
+    kp = _rng(seed, _T_K, layer, seq).standard_normal((M, KVD), dtype=np.float32)
+    vp = _rng(seed, _T_V, layer, seq).standard_normal((M, KVD), dtype=np.float32)
+    return qf, kp, vp

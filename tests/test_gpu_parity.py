@@ -1,0 +1,364 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Bars: int8 codes and fp16 scales bit-exact; floating-point outputs within max-abs 2e-3 and mean-abs 2e-4 of the fp32
+evaluation of the same formula (the tolerance the benchmark statement gives). Shapes follow the reference's own check
+(tools/probe_flash.cpp: a prefix, a ragged tail tile, NaN beyond the valid keys) and its cross-path equalities.
+"""
+import numpy as np
+import pytest
+import torch
+
+from kata_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+TOL_MAX, TOL_MEAN = 2e-3, 2e-4
+NAN16 = 0x7E00
+
+
+def _close(got, ref, tmax=TOL_MAX, tmean=TOL_MEAN):
+    got = np.asarray(got, np.float32)
+    d = np.abs(got - ref)
+    assert np.isfinite(got).all(), "non-finite output"
+    assert d.max() < tmax and d.mean() < tmean, (float(d.max()), float(d.mean()))
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from kata_b200 import capi as m
+    assert torch.cuda.is_available()
+    m.lib()
+    return m
+
+
+def _dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def _upload_planes(ctx, planes, layer=0, seq=0, n=None):
+    n = planes.max_ctx if n is None else n
+    ctx.plane_write(layer, seq, 0, 0, planes.k[:n])
+    ctx.plane_write(layer, seq, 1, 0, planes.v[:n])
+    if planes.int8:
+        ctx.plane_write(layer, seq, 2, 0, planes.ksc[:n])
+        ctx.plane_write(layer, seq, 3, 0, planes.vsc[:n])
+
+
+def _oracle_fill(orc, seed, L, max_ctx, int8=False, poison=False, fast=False, layer=0, seq=0):
+    planes = orc.KvPlanes(max_ctx, int8=int8, poison=poison)
+    qn, kn = synth.norm_weights(seed, layer)
+    qf, kp, vp = (synth.token_rows_fast if fast else synth.token_rows)(seed, L, layer=layer, seq=seq)
+    q, gate = orc.prep(qf, kp, vp, qn, kn, planes, 0)
+    return planes, q, gate, (qf, kp, vp, qn, kn)
+
+
+# ------------------------------------------------------------------------------------------------ prep and quantiser
+def test_prep_fp16_matches_oracle(capi, orc):
+    L, pos0 = 70, 300
+    planes = orc.KvPlanes(512)
+    qn, kn = synth.norm_weights(21)
+    qf, kp, vp = synth.token_rows(21, L, start=pos0)
+    q_ref, gate_ref = orc.prep(qf, kp, vp, qn, kn, planes, pos0)
+    ctx = capi.AttnContext(2, [512])
+    q16, q32, gate = ctx.prep(1, [0], [pos0], L, _dev(qf[None]), _dev(kp[None]), _dev(vp[None]), _dev(qn), _dev(kn), want_q32=True)
+    ctx.check()
+    assert np.array_equal(gate.cpu().numpy()[0], gate_ref)
+    assert np.abs(q32.cpu().numpy()[0] - q_ref).max() < 2e-6
+    assert np.abs(q16.cpu().numpy()[0].astype(np.float32) * 16 - q_ref).max() < 6e-3
+    v = ctx.plane_read(1, 0, 1, 0, 512).view(np.uint16).reshape(512, 1024)
+    assert np.array_equal(v, planes.v)                                    # V is a pure fp16 rounding: bit-exact
+    k = ctx.plane_read(1, 0, 0, 0, 512).view(np.uint16).reshape(512, 1024)
+    assert (k[:pos0] == 0).all() and (k[pos0 + L:] == 0).all()            # zero-initialised, only rows pos0.. written
+    kd = np.abs(k.view(np.float16).astype(np.float32) - planes.k.view(np.float16).astype(np.float32))
+    assert kd.max() < 4e-3 and (k != planes.k).mean() < 0.02              # sin/cos differ from libm by an ulp at most
+    assert (ctx.plane_read(0, 0, 0, 0, 512) == 0).all()                   # the other layer is untouched
+
+
+def test_prep_kv_only_and_bf16(capi, orc):
+    L = 33
+    qn, kn = synth.norm_weights(22)
+    qf, kp, vp = synth.token_rows(22, L)
+    kb, vb = synth.to_bf16_bits(kp), synth.to_bf16_bits(vp)
+    planes = orc.KvPlanes(64)
+    orc.prep(None, synth.bf16_bits_to_f32(kb), synth.bf16_bits_to_f32(vb), qn, kn, planes, 5, h0=24, nh=8)
+    ctx = capi.AttnContext(1, [64])
+    ctx.prep(0, [0], [5], L, None, _dev(kb[None]).view(torch.bfloat16), _dev(vb[None]).view(torch.bfloat16), None, _dev(kn), h0=24, nh=8)
+    ctx.check()
+    v = ctx.plane_read(0, 0, 1, 0, 64).view(np.uint16).reshape(64, 1024)
+    k = ctx.plane_read(0, 0, 0, 0, 64).view(np.float16).reshape(64, 1024).astype(np.float32)
+    assert np.array_equal(v, planes.v)
+    assert np.abs(k - planes.k.view(np.float16).astype(np.float32)).max() < 4e-3
+
+
+@pytest.mark.parametrize("mode", ["rint", "half_away"])
+def test_kv_quant_bit_exact(capi, orc, mode):
+    rng = np.random.default_rng(31)
+    T = 40
+    rows = (rng.standard_normal((T, 1024)) * rng.uniform(0.01, 30, (T, 1))).astype(np.float16)
+    rows[1] = 0
+    rows[2, :8] = [127, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 3.5]
+    rows[2, 8:256] = 0
+    rows[3, :2] = [1001.0, -1001.0]
+    rows[3, 2:256] = 0
+    rows[4, :4] = [6e-6, -3e-6, 1e-6, 6e-8]
+    rows[4, 4:256] = 0
+    vrows = rows[::-1].copy()
+    ref = orc.KvPlanes(64, int8=True)
+    orc.kv_quant(rows.view(np.uint16), vrows.view(np.uint16), ref, 7, 1 if mode == "half_away" else 0)
+    ctx = capi.AttnContext(1, [64], kv_mode="int8", quant_round=mode)
+    ctx.kv_quant(0, 0, _dev(rows.view(np.uint16)).view(torch.float16), _dev(vrows.view(np.uint16)).view(torch.float16), 7)
+    ctx.check()
+    assert ctx.tag() == "fp16+kv8" and ctx.kv_planes() == 4 and [ctx.plane_row_bytes(p) for p in range(5)] == [1024, 1024, 8, 8, 0]
+    assert np.array_equal(ctx.plane_read(0, 0, 0, 0, 64).view(np.int8).reshape(64, 1024), ref.k)
+    assert np.array_equal(ctx.plane_read(0, 0, 1, 0, 64).view(np.int8).reshape(64, 1024), ref.v)
+    assert np.array_equal(ctx.plane_read(0, 0, 2, 0, 64).view(np.uint16).reshape(64, 4), ref.ksc)
+    assert np.array_equal(ctx.plane_read(0, 0, 3, 0, 64).view(np.uint16).reshape(64, 4), ref.vsc)
+    want = [127, 0, 2, 2, 0, -2, -2, 4] if mode == "rint" else [127, 1, 2, 3, -1, -2, -3, 4]
+    assert ref.k[9, :8].tolist() == want
+
+
+def test_prep_int8_quantise_on_append_bit_exact(capi, orc):
+    # the fused path must equal: fp16 rows as the fp16 path caches them -> the reference quantiser
+    L = 50
+    qn, kn = synth.norm_weights(23)
+    qf, kp, vp = synth.token_rows(23, L)
+    c16 = capi.AttnContext(1, [64])
+    c8 = capi.AttnContext(1, [64], kv_mode="int8")
+    args = (_dev(qf[None]), _dev(kp[None]), _dev(vp[None]), _dev(qn), _dev(kn))
+    c16.prep(0, [0], [3], L, *args)
+    c8.prep(0, [0], [3], L, *args)
+    c16.check(); c8.check()
+    k16 = c16.plane_read(0, 0, 0, 3, L).view(np.uint16).reshape(L, 1024)
+    v16 = c16.plane_read(0, 0, 1, 3, L).view(np.uint16).reshape(L, 1024)
+    ref = orc.KvPlanes(64, int8=True)
+    orc.kv_quant(k16, v16, ref, 3, 0)
+    assert np.array_equal(c8.plane_read(0, 0, 0, 0, 64).view(np.int8).reshape(64, 1024), ref.k)
+    assert np.array_equal(c8.plane_read(0, 0, 1, 0, 64).view(np.int8).reshape(64, 1024), ref.v)
+    assert np.array_equal(c8.plane_read(0, 0, 2, 0, 64).view(np.uint16).reshape(64, 4), ref.ksc)
+    assert np.array_equal(c8.plane_read(0, 0, 3, 0, 64).view(np.uint16).reshape(64, 4), ref.vsc)
+
+
+# ------------------------------------------------------------------------------------------------ decode
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("T", [1, 2])
+def test_decode_lengths(capi, orc, int8, T):
+    Lmax = 700
+    planes, q, gate, _ = _oracle_fill(orc, 41, Lmax, 1024, int8=int8, poison=not int8)
+    ctx = capi.AttnContext(1, [1024], kv_mode="int8" if int8 else "fp16")
+    for L in (T, 15, 16, 17, 63, 64, 65, 127, 128, 129, 300, 700):
+        if L < T:
+            continue
+        # the cache holds exactly L rows; everything beyond is NaN (fp16) or garbage codes with NaN scales (int8)
+        cut = orc.KvPlanes(1024, int8=int8, poison=True) if not int8 else orc.KvPlanes(1024, int8=True)
+        cut.k[:L], cut.v[:L] = planes.k[:L], planes.v[:L]
+        if int8:
+            cut.ksc[:L], cut.vsc[:L] = planes.ksc[:L], planes.vsc[:L]
+            cut.k[L:], cut.v[L:] = 77, -77
+            cut.ksc[L:], cut.vsc[L:] = NAN16, NAN16
+        _upload_planes(ctx, cut)
+        pb = L - T
+        out = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(q[pb:L])[None]).view(torch.float16), _dev(gate[pb:L][None]))
+        ctx.check()
+        got = out.cpu().numpy()[0]
+        _close(got, orc.formula_f32(q[pb:L], gate[pb:L], cut, pb))
+        assert np.abs(got - orc.dec_attn(q[pb:L], gate[pb:L], cut, pb, T=T)).max() < 3e-4   # same rounding points as the restated kernel
+
+
+def test_decode_first_pos_one(capi, orc):
+    planes, q, gate, _ = _oracle_fill(orc, 42, 90, 128)
+    planes.k[0] = NAN16
+    planes.v[0] = NAN16
+    ctx = capi.AttnContext(1, [128])
+    _upload_planes(ctx, planes)
+    out = ctx.decode(0, [0], [88], 2, _dev(orc.cvt_q_half(q[88:90])[None]).view(torch.float16), _dev(gate[88:90][None]), first_pos=1)
+    ctx.check()
+    _close(out.cpu().numpy()[0], orc.formula_f32(q[88:90], gate[88:90], planes, 88, first_pos=1))
+
+
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("dec_chunk", [0, 64, 1024])
+def test_decode_ragged_batch_and_split_merge(capi, orc, int8, dec_chunk):
+    lens = [1, 2000, 37, 513, 1200]
+    ctx = capi.AttnContext(3, [2048, 2048, 64, 1024, 2048], kv_mode="int8" if int8 else "fp16", dec_chunk=dec_chunk)
+    layer, T = 2, 1
+    refs, q16s, gates = [], [], []
+    for s, L in enumerate(lens):
+        planes, q, gate, _ = _oracle_fill(orc, 50 + s, L, int(ctx.max_ctx[s]), int8=int8, fast=True, seq=s)
+        _upload_planes(ctx, planes, layer=layer, seq=s)
+        refs.append(orc.formula_f32(q[L - 1:], gate[L - 1:], planes, L - 1)[0])
+        q16s.append(orc.cvt_q_half(q[L - 1:]))
+        gates.append(gate[L - 1:])
+    order = [4, 0, 3, 1, 2]                                    # the batch lists sequences in any order
+    out = ctx.decode(layer, order, [lens[s] - 1 for s in order], T, _dev(np.stack([q16s[s] for s in order])).view(torch.float16), _dev(np.stack([gates[s] for s in order])))
+    ctx.check()
+    got = out.cpu().numpy()
+    for i, s in enumerate(order):
+        _close(got[i, 0], refs[s])
+
+
+def test_decode_scalar_path_and_cross_path(capi, orc):
+    planes, q, gate, _ = _oracle_fill(orc, 43, 1500, 2048, fast=True)
+    ctx = capi.AttnContext(1, [2048])
+    _upload_planes(ctx, planes)
+    for T, pb in ((1, 1499), (2, 1498), (8, 100)):
+        qs, gs = q[pb:pb + T], gate[pb:pb + T]
+        out = ctx.decode_scalar(0, [0], [pb], T, _dev(qs[None]), _dev(gs[None]))
+        ctx.check()
+        ref = orc.attn_split_combine(qs, gs, planes, pb, T=T, S=min(32, max(1, (pb + T) // 64)))
+        assert np.abs(out.cpu().numpy()[0] - ref).max() < 2e-5
+        if T <= 2:   # the matrix path agrees with the scalar path on the same cache (the reference's KATA_SCALAR_DEC cross-check)
+            m = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(qs)[None]).view(torch.float16), _dev(gs[None]))
+            _close(m.cpu().numpy()[0], out.cpu().numpy()[0])
+
+
+def test_verify_t2_equals_two_decodes(capi, orc):
+    planes, q, gate, _ = _oracle_fill(orc, 44, 400, 512)
+    ctx = capi.AttnContext(1, [512])
+    _upload_planes(ctx, planes)
+    q16 = _dev(orc.cvt_q_half(q)).view(torch.float16)
+    g = _dev(gate)
+    v = ctx.decode(0, [0], [398], 2, q16[398:400][None].contiguous(), g[398:400][None].contiguous()).cpu().numpy()[0]
+    d0 = ctx.decode(0, [0], [398], 1, q16[398:399][None].contiguous(), g[398:399][None].contiguous()).cpu().numpy()[0, 0]
+    d1 = ctx.decode(0, [0], [399], 1, q16[399:400][None].contiguous(), g[399:400][None].contiguous()).cpu().numpy()[0, 0]
+    ctx.check()
+    assert np.abs(v[0] - d0).max() < 1e-5 and np.abs(v[1] - d1).max() < 1e-5
+
+
+def test_config1_golden_decode(capi, orc):
+    # benchmark config 1: one layer, 512 keys, one token; GPU prep builds the cache, then the committed golden output
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "attn_golden.npz"))
+    seed, L = 1001, 512
+    qn, kn = synth.norm_weights(seed)
+    qf, kp, vp = synth.token_rows(seed, L)
+    ctx = capi.AttnContext(1, [L])
+    q16, _, gate = ctx.prep(0, [0], [0], L, _dev(qf[None]), _dev(kp[None]), _dev(vp[None]), _dev(qn), _dev(kn))
+    out = ctx.decode(0, [0], [L - 1], 1, q16[:, L - 1:].contiguous(), gate[:, L - 1:].contiguous())
+    ver = ctx.decode(0, [0], [L - 2], 2, q16[:, L - 2:].contiguous(), gate[:, L - 2:].contiguous())
+    ctx.check()
+    _close(out.cpu().numpy()[0, 0], g["c1_decode_f32"])
+    assert np.abs(out.cpu().numpy()[0, 0] - g["c1_decode"]).max() < 3e-4
+    assert np.abs(ver.cpu().numpy()[0] - g["c1_verify_t2"]).max() < 3e-4
+    v = ctx.plane_read(0, 0, 1, 0, L).view(np.uint16).reshape(L, 1024)
+    assert np.array_equal(v[[0, 1, 255, 511]], g["c1_v_rows"])
+    c8 = capi.AttnContext(1, [L], kv_mode="int8")
+    q16b, _, gateb = c8.prep(0, [0], [0], L, _dev(qf[None]), _dev(kp[None]), _dev(vp[None]), _dev(qn), _dev(kn))
+    ver8 = c8.decode(0, [0], [L - 2], 2, q16b[:, L - 2:].contiguous(), gateb[:, L - 2:].contiguous())
+    c8.check()
+    assert np.array_equal(c8.plane_read(0, 0, 1, 0, L).view(np.int8).reshape(L, 1024)[[0, 1, 255, 511]], g["q8_v_codes"])
+    assert np.array_equal(c8.plane_read(0, 0, 3, 0, L).view(np.uint16).reshape(L, 4), g["q8_v_scales"])
+    assert (c8.plane_read(0, 0, 2, 0, L).view(np.uint16).reshape(L, 4) != g["q8_k_scales"]).mean() < 0.02
+    assert np.abs(ver8.cpu().numpy()[0] - g["q8_verify_t2"]).max() < 2e-3
+
+
+def test_split_kv_partials_merge(capi, orc):
+    # three "ranks" hold contiguous key slices (as three sequences of one context); merged partials == single-context decode
+    L, T = 1000, 2
+    planes, q, gate, _ = _oracle_fill(orc, 45, L, 1024, fast=True)
+    bounds = [(0, 400), (400, 401), (401, 1000), (1000, 1300)]   # the last rank holds no key yet
+    ctx = capi.AttnContext(1, [1024] * 4)
+    for s, (lo, hi) in enumerate(bounds):
+        n = max(0, min(hi, L) - lo)
+        if n:
+            ctx.plane_write(0, s, 0, 0, planes.k[lo:lo + n])
+            ctx.plane_write(0, s, 1, 0, planes.v[lo:lo + n])
+    pb = L - T
+    q16 = _dev(orc.cvt_q_half(q[pb:L])).view(torch.float16)
+    parts = torch.stack([ctx.decode_partial(0, s, pb, T, lo, hi, q16) for s, (lo, hi) in enumerate(bounds)])
+    out = ctx.merge_parts(parts, T, _dev(gate[pb:L]))
+    ctx.check()
+    assert parts[3, :, 257].abs().max().item() == 0 and torch.isinf(parts[3, :, 256]).all()
+    _close(out.cpu().numpy(), orc.formula_f32(q[pb:L], gate[pb:L], planes, pb))
+
+
+# ------------------------------------------------------------------------------------------------ prefill
+@pytest.mark.parametrize("int8", [False, True])
+def test_prefill_probe_shape(capi, orc, int8):
+    # the reference's probe: 70 rows (ragged tail) at position 300, NaN beyond the valid keys; plus M = 1, 15, 16, 17 and pos 0
+    planes, q, gate, _ = _oracle_fill(orc, 61, 370, 512, int8=int8, poison=not int8, fast=True)
+    if int8:
+        planes.ksc[370:], planes.vsc[370:] = NAN16, NAN16
+    ctx = capi.AttnContext(1, [512], kv_mode="int8" if int8 else "fp16")
+    _upload_planes(ctx, planes)
+    for pb, M in ((300, 70), (0, 1), (0, 15), (0, 16), (0, 17), (0, 70), (353, 17), (0, 370)):
+        sub = orc.KvPlanes(512, int8=int8, poison=not int8)
+        n = pb + M
+        sub.k[:n], sub.v[:n] = planes.k[:n], planes.v[:n]
+        if int8:
+            sub.ksc[:n], sub.vsc[:n] = planes.ksc[:n], planes.vsc[:n]
+        out = ctx.prefill(0, [0], [pb], M, _dev(orc.cvt_q_half(q[pb:n])[None]).view(torch.float16), _dev(gate[pb:n][None]))
+        ctx.check()
+        got = out.cpu().numpy()[0]
+        _close(got, orc.formula_f32(q[pb:n], gate[pb:n], sub, pb))
+        assert np.abs(got - orc.flash_prefill(orc.cvt_q_half(q[pb:n]), gate[pb:n], sub, pb)).max() < 3e-4
+
+
+def test_chunked_prefill_restore_equals_one_shot(capi, orc):
+    # prefill 0..150, export the planes, reset, import them (the prefix-cache restore), continue in chunks, compare with one shot
+    n, cut = 420, 150
+    qn, kn = synth.norm_weights(62)
+    qf, kp, vp = synth.token_rows_fast(62, n)
+    dq, dk, dv, dqn, dkn = _dev(qf), _dev(kp), _dev(vp), _dev(qn), _dev(kn)
+    one = capi.AttnContext(1, [512])
+    q16, _, g = one.prep(0, [0], [0], n, dq[None], dk[None], dv[None], dqn, dkn)
+    o1 = one.prefill(0, [0], [0], n, q16, g).cpu().numpy()[0]
+    ch = capi.AttnContext(1, [512])
+    q16a, _, ga = ch.prep(0, [0], [0], cut, dq[None, :cut].contiguous(), dk[None, :cut].contiguous(), dv[None, :cut].contiguous(), dqn, dkn)
+    oa = ch.prefill(0, [0], [0], cut, q16a, ga).cpu().numpy()[0]
+    saved = [ch.plane_read(0, 0, p, 0, cut) for p in range(ch.kv_planes())]
+    ch.reset()
+    assert (ch.plane_read(0, 0, 0, 0, 512) == 0).all()
+    for p, data in enumerate(saved):
+        ch.plane_write(0, 0, p, 0, data)
+    outs = [oa]
+    for start, m in ((150, 128), (278, 100), (378, 42)):
+        sl = slice(start, start + m)
+        q16c, _, gc = ch.prep(0, [0], [start], m, dq[None, sl].contiguous(), dk[None, sl].contiguous(), dv[None, sl].contiguous(), dqn, dkn)
+        outs.append(ch.prefill(0, [0], [start], m, q16c, gc).cpu().numpy()[0])
+    ch.check(); one.check()
+    for p in range(2):
+        assert np.array_equal(ch.plane_read(0, 0, p, 0, n), one.plane_read(0, 0, p, 0, n))
+    assert np.abs(np.concatenate(outs) - o1).max() < 2e-4
+    # and the T=2 verify that follows a chunked prefill
+    v = ch.decode(0, [0], [n - 2], 2, q16[:, n - 2:].contiguous(), g[:, n - 2:].contiguous()).cpu().numpy()[0]
+    assert np.abs(v - o1[n - 2:]).max() < 3e-4
+
+
+def test_prefill_batch_bf16_out(capi, orc):
+    M = 96
+    ctx = capi.AttnContext(2, [128, 256])
+    refs, q16s, gates = [], [], []
+    for s, pb in enumerate((0, 100)):
+        planes, q, gate, _ = _oracle_fill(orc, 63 + s, pb + M, int(ctx.max_ctx[s]), fast=True, seq=s)
+        _upload_planes(ctx, planes, layer=1, seq=s)
+        refs.append(orc.formula_f32(q[pb:], gate[pb:], planes, pb))
+        q16s.append(orc.cvt_q_half(q[pb:]))
+        gates.append(gate[pb:])
+    out = ctx.prefill(1, [0, 1], [0, 100], M, _dev(np.stack(q16s)).view(torch.float16), _dev(np.stack(gates)), out_dtype=torch.bfloat16)
+    ctx.check()
+    got = out.float().cpu().numpy()
+    for s in range(2):
+        d = np.abs(got[s] - refs[s])
+        assert (d <= TOL_MAX + np.abs(refs[s]) * 2.0 ** -8).all() and d.mean() < 2 * TOL_MEAN   # one bf16 rounding on top of the tolerance
+
+
+# ------------------------------------------------------------------------------------------------ errors
+def test_errors_are_codes_not_faults(capi):
+    ctx = capi.AttnContext(2, [64, 32])
+    z16 = torch.zeros((1, 1, 6144), dtype=torch.float16, device="cuda")
+    z32 = torch.zeros((1, 1, 6144), dtype=torch.float32, device="cuda")
+    for fn, code in (
+        (lambda: ctx.decode(2, [0], [0], 1, z16, z32), 2),          # layer out of range
+        (lambda: ctx.decode(0, [2], [0], 1, z16, z32), 2),          # sequence out of range
+        (lambda: ctx.decode(0, [1], [32], 1, z16, z32), 2),         # position beyond max_ctx
+        (lambda: ctx.decode(0, [0], [5], 3, z16, z32), 2),          # T > 2
+        (lambda: ctx.decode(0, [0], [5], 1, z16, z32, first_pos=6), 2),
+        (lambda: ctx.prefill(0, [0], [0], 2000, z16, z32), 2),      # chunk too long
+        (lambda: ctx.kv_quant(0, 0, z16, z16, 0), 3),               # fp16 context has no quantiser
+        (lambda: ctx.plane_read(0, 0, 2, 0, 1), 1),                 # no scale planes in fp16 mode
+    ):
+        with pytest.raises(capi.KataError) as e:
+            fn()
+        assert e.value.code == code
+    ctx.check()
+    assert ctx.tag() == "fp16" and ctx.kv_planes() == 2 and ctx.plane_row_bytes(0) == 2048
