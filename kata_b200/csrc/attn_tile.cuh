@@ -65,12 +65,19 @@ __device__ __forceinline__ void tile_qk_softmax_pv(const uint32_t q_sm, const ui
     const uint32_t qa = q_sm + (lane & 15) * kQStride + (lane >> 4) * 16;
     const uint32_t ka = k_sm + ((lane & 7) + ((lane >> 4) << 3)) * G::kRowStride + ((lane >> 3) & 1) * 16;
     if (!I8) {
+        float s2[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};   // second pair of accumulator chains: halves the dependent-MMA latency
 #pragma unroll
-        for (int kk = 0; kk < 16; kk++) {
-            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        for (int kk = 0; kk < 16; kk += 2) {
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
             ldsm_x4(qa + kk * 32, a0, a1, a2, a3); ldsm_x4(ka + kk * 32, b0, b1, b2, b3);
+            ldsm_x4(qa + kk * 32 + 32, c0, c1, c2, c3); ldsm_x4(ka + kk * 32 + 32, d0, d1, d2, d3);
             mma16816(s[0], a0, a1, a2, a3, b0, b1); mma16816(s[1], a0, a1, a2, a3, b2, b3);
+            mma16816(s2[0], c0, c1, c2, c3, d0, d1); mma16816(s2[1], c0, c1, c2, c3, d2, d3);
         }
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[nt][e] += s2[nt][e];
     } else {
         // an 8x8 b16 matrix covers 8 keys x 16 int8 dims; a thread's register = dims 4*t4..4*t4+3 of key g
 #pragma unroll
@@ -143,5 +150,123 @@ template <bool I8> __device__ __forceinline__ void stage_q_chunk(uint8_t* q_row_
 }
 
 __device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+}  // namespace kata
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Pair-split variant used by the decode kernel: two warps (h = 0, 1) share one 16-key tile. Each computes the scores of
+// its own 8 keys (no redundant Q.K^T), the pair exchanges row maxima and the fp16 P block through shared memory with two
+// 64-thread named barriers, and each accumulates its own 128-dim half of O over all 16 keys. Same arithmetic and rounding
+// points as tile_qk_softmax_pv; both warps see the same running maximum, and the row sums l of the two halves add up.
+namespace kata {
+
+constexpr int kPStride = 48;   // bytes per row of the exchanged 16x16 fp16 P block (32 + 16 pad: conflict-free ldmatrix)
+
+struct PairState {
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    float o[16][4];
+    __device__ __forceinline__ void clear() {
+        m0 = m1 = -INFINITY; l0 = l1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+    }
+    __device__ __forceinline__ void finish_l() {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+};
+
+// dimension of O element (n-tile j of 16, column c) held by warp half h
+template <bool I8> __device__ __forceinline__ int pair_dim_of(int h, int j, int c, int t4) { return h * 128 + dim_of<I8>(j, c, t4); }
+
+__device__ __forceinline__ void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+
+// k_sm / v_sm: shared addresses (1024-byte aligned) of the tile as TMA wrote it with the 128-byte swizzle: boxes of
+// [16 keys][128 bytes], box b holding bytes [128b, 128b+128) of every row, 16-byte chunk c of row r stored at chunk c ^ (r & 7).
+// maxbuf: float [2][16] in shared memory; p_sm: shared address of the [16][kPStride] P block; bar_id: named barrier of the pair.
+// ks/vs: int8 mode, scales of this thread's two score columns (keys key0 + 8h + 2*t4 + e). after_sync1 runs once between the
+// two barriers (the decode kernel refills the ring there: by then both warps have finished reading the previous tile).
+template <bool I8, class F>
+__device__ __forceinline__ void pair_tile(const uint32_t q_sm, const uint32_t k_sm, const uint32_t v_sm, float* maxbuf, const uint32_t p_sm, const int bar_id, const int h,
+                                          const int key0, const int lim0, const int lim1, const float (&ks)[2], const float (&vs)[2], PairState& st, const int lane, F&& after_sync1) {
+    using G = TileGeo<I8>;
+    using namespace ptx;
+    const int t4 = lane & 3, g = lane >> 2;
+    float s[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
+    const uint32_t qa = q_sm + (lane & 15) * kQStride + (lane >> 4) * 16;
+    constexpr uint32_t kBox = 16 * 128;
+    const uint32_t rx = lane & 7, qd = lane >> 3;
+    const uint32_t ka = k_sm + (8 * h + rx) * 128;                                   // my 8 key rows; lanes 8q..8q+7 fetch 16-byte chunk 4*k + q
+    const uint32_t ka_e = ka + ((qd ^ rx) << 4), ka_o = ka + (((4 + qd) ^ rx) << 4);   // even / odd groups of four chunks inside a 128-byte box
+    if (!I8) {
+#pragma unroll
+        for (int k2 = 0; k2 < 8; k2++) {   // chunks 0,1 = k-step 2*k2 (b0, b1); chunks 2,3 = k-step 2*k2+1
+            uint32_t b0, b1, b2, b3, a0, a1, a2, a3, c0, c1, c2, c3;
+            ldsm_x4(((k2 & 1) ? ka_o : ka_e) + (k2 >> 1) * kBox, b0, b1, b2, b3);
+            ldsm_x4(qa + (2 * k2) * 32, a0, a1, a2, a3); ldsm_x4(qa + (2 * k2 + 1) * 32, c0, c1, c2, c3);
+            mma16816(s, a0, a1, a2, a3, b0, b1); mma16816(s2, c0, c1, c2, c3, b2, b3);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) s[e] += s2[e];
+    } else {
+#pragma unroll
+        for (int k4 = 0; k4 < 4; k4++) {   // int8: each 16-byte chunk is a 16-dim block; register = dims 4*t4..4*t4+3 of key g
+            uint32_t r0, r1, r2, r3, a0, a1, a2, a3;
+            ldsm_x4(((k4 & 1) ? ka_o : ka_e) + (k4 >> 1) * kBox, r0, r1, r2, r3);
+            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+            ldsm_x4(qa + (4 * k4 + 0) * 32, a0, a1, a2, a3); mma16816(s, a0, a1, a2, a3, deq2(r0, 0x4140u), deq2(r0, 0x4342u));
+            ldsm_x4(qa + (4 * k4 + 1) * 32, a0, a1, a2, a3); mma16816(s2, a0, a1, a2, a3, deq2(r1, 0x4140u), deq2(r1, 0x4342u));
+            ldsm_x4(qa + (4 * k4 + 2) * 32, a0, a1, a2, a3); mma16816(s, a0, a1, a2, a3, deq2(r2, 0x4140u), deq2(r2, 0x4342u));
+            ldsm_x4(qa + (4 * k4 + 3) * 32, a0, a1, a2, a3); mma16816(s2, a0, a1, a2, a3, deq2(r3, 0x4140u), deq2(r3, 0x4342u));
+        }
+        s[0] = (s[0] + s2[0]) * ks[0]; s[1] = (s[1] + s2[1]) * ks[1]; s[2] = (s[2] + s2[2]) * ks[0]; s[3] = (s[3] + s2[3]) * ks[1];
+    }
+#pragma unroll
+    for (int e = 0; e < 2; e++) { const int key = key0 + 8 * h + 2 * t4 + e; if (key >= lim0) s[e] = -INFINITY; if (key >= lim1) s[2 + e] = -INFINITY; }
+    float mx0 = fmaxf(s[0], s[1]) * kLog2e, mx1 = fmaxf(s[2], s[3]) * kLog2e;
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if (t4 == 0) { maxbuf[h * 16 + g] = mx0; maxbuf[h * 16 + g + 8] = mx1; }
+    pair_barrier(bar_id);
+    after_sync1();
+    const float mn0 = fmaxf(st.m0, fmaxf(mx0, maxbuf[(h ^ 1) * 16 + g])), mn1 = fmaxf(st.m1, fmaxf(mx1, maxbuf[(h ^ 1) * 16 + g + 8]));
+    const float al0 = (mn0 == -INFINITY) ? 1.0f : ex2(st.m0 - mn0), al1 = (mn1 == -INFINITY) ? 1.0f : ex2(st.m1 - mn1);
+    const float sub0 = (mn0 == -INFINITY) ? 0.0f : mn0, sub1 = (mn1 == -INFINITY) ? 0.0f : mn1;
+    st.m0 = mn0; st.m1 = mn1;
+    float p0 = ex2(fmaf(s[0], kLog2e, -sub0)), p1 = ex2(fmaf(s[1], kLog2e, -sub0)), p2 = ex2(fmaf(s[2], kLog2e, -sub1)), p3 = ex2(fmaf(s[3], kLog2e, -sub1));
+    st.l0 = st.l0 * al0 + (p0 + p1); st.l1 = st.l1 * al1 + (p2 + p3);
+    if (__any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f)) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
+    }
+    if (I8) { p0 *= vs[0]; p1 *= vs[1]; p2 *= vs[0]; p3 *= vs[1]; }
+    {   // my 8 columns of the fp16 P block
+        const uint32_t off = (uint32_t)((8 * h + 2 * t4) * 2);
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + g * kPStride + off), "r"(pack_h2(p0, p1)) : "memory");
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + (g + 8) * kPStride + off), "r"(pack_h2(p2, p3)) : "memory");
+    }
+    pair_barrier(bar_id);
+    uint32_t pa0, pa1, pa2, pa3;
+    ldsm_x4(p_sm + (lane & 15) * kPStride + (lane >> 4) * 16, pa0, pa1, pa2, pa3);
+    const uint32_t va = v_sm + (rx + ((lane >> 3) & 1) * 8) * 128, ud = lane >> 4;   // key row of this lane; chunk 2*j + ud of my half
+    const uint32_t vo0 = ((0 + ud) ^ rx) << 4, vo1 = ((2 + ud) ^ rx) << 4, vo2 = ((4 + ud) ^ rx) << 4, vo3 = ((6 + ud) ^ rx) << 4;
+    if (!I8) {
+#pragma unroll
+        for (int j2 = 0; j2 < 8; j2++) {
+            uint32_t b0, b1, b2, b3; ldsm_x4_t(va + (2 * h + (j2 >> 2)) * kBox + ((j2 & 3) == 0 ? vo0 : (j2 & 3) == 1 ? vo1 : (j2 & 3) == 2 ? vo2 : vo3), b0, b1, b2, b3);
+            mma16816(st.o[2 * j2], pa0, pa1, pa2, pa3, b0, b1); mma16816(st.o[2 * j2 + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+    } else {
+#pragma unroll
+        for (int j2 = 0; j2 < 4; j2++) {
+            uint32_t r0, r1, r2, r3; ldsm_x4_t(va + h * kBox + (j2 == 0 ? vo0 : j2 == 1 ? vo1 : j2 == 2 ? vo2 : vo3), r0, r1, r2, r3);
+            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+            mma16816(st.o[4 * j2 + 0], pa0, pa1, pa2, pa3, deq2(r0, 0x4240u), deq2(r1, 0x4240u));
+            mma16816(st.o[4 * j2 + 1], pa0, pa1, pa2, pa3, deq2(r0, 0x4341u), deq2(r1, 0x4341u));
+            mma16816(st.o[4 * j2 + 2], pa0, pa1, pa2, pa3, deq2(r2, 0x4240u), deq2(r3, 0x4240u));
+            mma16816(st.o[4 * j2 + 3], pa0, pa1, pa2, pa3, deq2(r2, 0x4341u), deq2(r3, 0x4341u));
+        }
+    }
+}
 
 }  // namespace kata

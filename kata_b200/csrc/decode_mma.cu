@@ -8,16 +8,20 @@
 // Design (HBM-bound: 1 KiB of K+V per key and KV head at fp16, read exactly once):
 //  - The work is the list of 16-key tiles of every (sequence, KV head) segment. It is cut into one contiguous,
 //    equal-sized range per CTA (one CTA per SM), so ragged batches balance to within one tile and each key is read once.
-//  - Inside a CTA each of the 4 warps owns every 4th tile of the range and streams it through its own 3-stage shared
-//    memory ring: one 512-byte (fp16) or 256-byte (int8) bulk async copy per K or V row, issued one row per lane and
-//    tracked by an mbarrier per stage. Rows are padded by 16 bytes so ldmatrix reads are bank-conflict free.
-//  - Q.K^T and P.V run on mma.sync m16n8k16 (fp16 in, fp32 accumulate) straight from ldmatrix fragments; the softmax
-//    state lives in registers and uses quad shuffles only. int8 rows are dequantised in registers (byte permute onto
-//    the fp16 magic number 1024+x, then subtract), with the per-key scales applied to S and to P as the reference does.
+//  - Inside a CTA the tiles of the range go round-robin to 4 rings. A ring is a pair of warps on the same scheduler
+//    sharing a 3-stage shared-memory ring: one 512-byte (fp16) or 256-byte (int8) bulk async copy per K or V row, issued
+//    one row per lane and tracked by an mbarrier per stage. Rows are padded by 16 bytes so ldmatrix reads are bank-conflict
+//    free. Two warps per scheduler is what hides the fixed instruction latencies; shared memory bounds the ring count.
+//  - Q.K^T and P.V run on mma.sync m16n8k16 (fp16 in, fp32 accumulate) straight from ldmatrix fragments. The two warps
+//    of a ring split the tile: each scores its own 8 keys, they exchange row maxima and the fp16 P block through shared
+//    memory (two 64-thread named barriers), and each accumulates its own 128-dim half of O. The softmax state lives in
+//    registers and uses quad shuffles. int8 rows are dequantised in registers (byte permute onto the fp16 magic number
+//    1024+x, then subtract), with the per-key scales applied to S and to P as the reference does.
 //  - A CTA whose range ends inside a segment writes an unnormalised partial (O, m, l); the last CTA to finish a segment
 //    (atomic ticket) merges the partials, normalises, applies the gate and writes the output row. No second kernel.
 // Every mbarrier wait is bounded; on a timeout the kernel records an error word and skips the arithmetic.
 #include <algorithm>
+#include <cstdlib>
 
 #include "attn_tile.cuh"
 
@@ -26,19 +30,21 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kWarps = 4, kThreads = kWarps * 32, kStages = 3, kTile = 16;
-constexpr int kOffBars = 16 * kQStride;             // 8448
-constexpr int kOffMl = kOffBars + 128;              // per-warp (m, l) exchange: [4][16][2] floats = 512 B
-constexpr int kOffStages = kOffMl + 512;            // 9088, 16-byte aligned
-constexpr int kMergeStride = 264;                   // floats per row of the cross-warp merge buffer
+constexpr int kRings = 4, kWarps = 2 * kRings, kThreads = kWarps * 32, kStages = 3, kTile = 16;
+constexpr int kOffBars = 16 * kQStride;             // 8448: per ring and stage a 'full' and an 'empty' barrier, then the merge barrier
+constexpr int kOffMl = kOffBars + 256;              // per-ring (m, l0, l1) exchange: [4][16][3] floats = 768 B
+constexpr int kOffPair = kOffMl + 768;              // per-ring pair exchange: max [2][16] floats (128 B) + P block 16 x 48 B
+constexpr int kPairBytes = 128 + 16 * kPStride;     // 896
+constexpr int kOffStages = kOffPair + kRings * kPairBytes;   // the stage area itself starts at the next 1024-byte boundary of the shared window (found at run time)
+constexpr int kMergeStride = 264;                   // floats per row of the cross-ring merge buffer
 
 template <bool I8> struct Geo {
     static constexpr int kRowBytes = TileGeo<I8>::kRowBytes;
-    static constexpr int kRowStride = TileGeo<I8>::kRowStride;
-    static constexpr int kTileBytes = kTile * kRowStride;
+    static constexpr int kBoxes = kRowBytes / 128;               // 128-byte column boxes per K or V tile
+    static constexpr int kTileBytes = kTile * kRowBytes;          // boxes of [16 rows][128 bytes], 128-byte swizzle, no padding
     static constexpr int kStageBytes = 2 * kTileBytes;
-    static constexpr int kWarpBytes = (kStages * kStageBytes > 16 * kMergeStride * 4) ? kStages * kStageBytes : 16 * kMergeStride * 4;
-    static constexpr int kSmem = kOffStages + kWarps * kWarpBytes;
+    static constexpr int kRingBytes = (kStages * kStageBytes > 16 * kMergeStride * 4) ? kStages * kStageBytes : 16 * kMergeStride * 4;
+    static constexpr int kSmem = kOffStages + 1024 + kRings * kRingBytes;   // 1024 bytes of slack for the run-time alignment
 };
 
 struct DecPlan {
@@ -57,25 +63,30 @@ __device__ __forceinline__ int cta_of_tile(const DecPlan& p, int tile) {
 }
 
 template <bool I8>
-__global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
+__global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                                                                 const __grid_constant__ CUtensorMap pf_k, const __grid_constant__ CUtensorMap pf_v, const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
                                                                  float* __restrict__ part_out, const uint8_t* __restrict__ k_arena, const uint8_t* __restrict__ v_arena,
                                                                  const __half* __restrict__ ksc, const __half* __restrict__ vsc,
-                                                                 float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
+                                                                 float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err, const int dbg) {
     using G = Geo<I8>;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring and ring+4 sit on the same scheduler
     const uint32_t sm_base = smem_u32(smem);
-    const uint32_t q_base = sm_base, bars = sm_base + kOffBars + w * kStages * 8, my_stage0 = sm_base + kOffStages + w * G::kWarpBytes;
+    const uint32_t q_base = sm_base, bars = sm_base + kOffBars + ring * kStages * 8, ebars = sm_base + kOffBars + (kRings + ring) * kStages * 8, stage_off = ((sm_base + kOffStages + 1023u) & ~1023u) - sm_base, ring_stage0 = sm_base + stage_off + ring * G::kRingBytes;   // swizzled TMA boxes want 1024-byte alignment
     float* sm_ml = reinterpret_cast<float*>(smem + kOffMl);
-    __shared__ int s_flag;
+    float* maxbuf = reinterpret_cast<float*>(smem + kOffPair + ring * kPairBytes);
+    const uint32_t p_sm = sm_base + kOffPair + ring * kPairBytes + 128;
+    __shared__ int s_flag; __shared__ float s_ML[24];
+    const uint32_t merge_bar = sm_base + kOffBars + 2 * kRings * kStages * 8; uint32_t merge_phase = 0;
 
-    if (lane == 0) { for (int s = 0; s < kStages; s++) mbar_init(bars + s * 8, 1); }
+    if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 2); } }
+    if (tid == 0) mbar_init(merge_bar, 1);
     fence_mbar_init();
     __syncthreads();
 
     const int cta = blockIdx.x;
     int tile = cta_first_tile(p, cta); const int tile_end = cta_first_tile(p, cta + 1);
-    int b = 0; uint32_t it = 0; bool dead = false;   // it: tiles this warp has issued so far (ring position and phase)
+    int b = 0; uint32_t it = 0; bool dead = false;   // it: tiles this ring has consumed so far (ring position and phase)
 
     while (tile < tile_end) {
         while (p.tile_start[b + 1] <= tile) b++;
@@ -85,8 +96,34 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecPlan p
         const uint8_t* Kg = k_arena + (p.row_base[b] * kKVD + kvh * kD) * (I8 ? 1 : 2);
         const uint8_t* Vg = v_arena + (p.row_base[b] * kKVD + kvh * kD) * (I8 ? 1 : 2);
 
-        // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero). int8: columns permuted inside each 16-dim block to
-        // match the contraction order of the dequantised K fragments (logical c<8 -> dim 4*(c/2)+c%2, else 4*((c-8)/2)+2+c%2).
+        // ---- this ring's tiles of the segment: local tiles lt0 + ring, lt0 + ring + 4, ...
+        const int n_mine = n_here > ring ? (n_here - ring + kRings - 1) / kRings : 0;
+        PairState st; st.clear();
+        const int lim_row0 = (g < 6 * T) ? min(kend, pos_rel + (g >= 6 ? 1 : 0) + 1) : 0;          // rows g and g+8: exclusive local key limit
+        const int lim_row1 = (g + 8 < 6 * T) ? min(kend, pos_rel + 2) : 0;                          // rows 8..11 belong to token 1
+
+        const uint32_t it_seg = it;
+        const int pf = dbg >> 8;   // L2 prefetch distance in tiles beyond the shared-memory ring
+        const int row0 = (int)p.row_base[b];   // arena row of position 0 (row coordinates of the tensor maps are 32-bit)
+        auto prefetch = [&](int i) {   // the ring's i-th tile -> L2 only: one 16-row box of whole head rows for K and one for V
+            const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+            if (key0 < kend && lane < 2) tma_prefetch_3d(lane ? &pf_v : &pf_k, 0, kvh, row0 + key0);
+        };
+        auto issue = [&](int i) {   // warp h=0 of the ring brings in the ring's i-th tile: one TMA box per 128-byte column block of K and of V
+            const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+            const uint32_t sx = (it_seg + (uint32_t)i) % kStages, dst = ring_stage0 + sx * G::kStageBytes, bar = bars + sx * 8;
+            fence_proxy_async();
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)G::kStageBytes);   // TMA counts whole boxes, out-of-range rows included
+            __syncwarp();
+            if (lane < 2 * G::kBoxes) {
+                const int isv = lane >= G::kBoxes, bx = lane - isv * G::kBoxes;
+                tma_load_3d(dst + isv * G::kTileBytes + bx * (kTile * 128), isv ? &tm_v : &tm_k, bx * (128 / (I8 ? 1 : 2)), kvh, row0 + key0, bar);
+            }
+            if (pf > 0 && i + pf < n_mine) prefetch(i + pf);
+        };
+
+        if ((dbg & 255) != 2 && h == 0) { for (int i = 0; i < min(kStages, n_mine); i++) issue(i); for (int i = kStages; i < min(kStages + pf, n_mine); i++) prefetch(i); }   // every stage is free here; the first tiles fly while Q is staged
+        // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
             if (r < 6 * T) { const int t = r / 6, j = r - 6 * t; v = *reinterpret_cast<const uint4*>(q16 + ((int64_t)b * T + t) * kQD + (kvh * 6 + j) * kD + c16 * 8); }
@@ -94,89 +131,77 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecPlan p
         }
         __syncthreads();
 
-        // ---- this warp's tiles of the segment: local tiles lt0 + w, lt0 + w + 4, ...
-        const int n_mine = n_here > w ? (n_here - w + kWarps - 1) / kWarps : 0;
-        RowState st; st.clear();
-        const int lim_row0 = (g < 6 * T) ? min(kend, pos_rel + (g >= 6 ? 1 : 0) + 1) : 0;          // rows g and g+8: exclusive local key limit
-        const int lim_row1 = (g + 8 < 6 * T) ? min(kend, pos_rel + ((g + 8) >= 6 ? 1 : 0) + 1) : 0;
-
-        int n_issued = 0, n_waited = 0;
-        auto issue = [&](int i) {   // bring in this warp's i-th tile of the segment
-            if (dead) return;
-            n_issued = i + 1;
-            const int key0 = p.first_row + (lt0 + w + i * kWarps) * kTile, nk = max(0, min(kTile, kend - key0));
-            const uint32_t sx = (it + (uint32_t)i) % kStages, dst = my_stage0 + sx * G::kStageBytes, bar = bars + sx * 8;
-            fence_proxy_async();
-            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)(nk * 2 * G::kRowBytes));
-            __syncwarp();
-            const int r = lane & 15; const bool isv = lane >= 16;
-            if (r < nk) bulk_g2s(dst + (isv ? G::kTileBytes : 0) + r * G::kRowStride, (isv ? Vg : Kg) + (int64_t)(key0 + r) * (kKVD * (I8 ? 1 : 2)), G::kRowBytes, bar);
-            else if (isv) { uint4* z = reinterpret_cast<uint4*>(smem + (dst - sm_base) + G::kTileBytes + r * G::kRowStride); for (int c = 0; c < G::kRowBytes / 16; c++) z[c] = make_uint4(0, 0, 0, 0); }
-        };
-
-        const uint32_t it_seg = it;
-        for (int i = 0; i < min(kStages - 1, n_mine); i++) issue(i);
         for (int i = 0; i < n_mine; i++) {
-            __syncwarp();
-            if (i + kStages - 1 < n_mine) issue(i + kStages - 1);
             const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u;
-            const uint32_t kt = my_stage0 + stg * G::kStageBytes, vt = kt + G::kTileBytes;
-            const int key0 = p.first_row + (lt0 + w + i * kWarps) * kTile;
-            float ks_[2][2] = {{1.f, 1.f}, {1.f, 1.f}}, vs_[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
-            if (I8) {   // per-key scales of this thread's four score columns (keys key0 + nt*8 + 2*t4 + e)
+            const uint32_t kt = ring_stage0 + stg * G::kStageBytes, vt = kt + G::kTileBytes;
+            const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+            float ks_[2] = {1.f, 1.f}, vs_[2] = {1.f, 1.f};
+            if (I8) {   // per-key scales of this thread's two score columns (keys key0 + 8h + 2*t4 + e)
 #pragma unroll
-                for (int ntl = 0; ntl < 2; ntl++)
-#pragma unroll
-                    for (int e = 0; e < 2; e++) { const int key = min(key0 + ntl * 8 + 2 * t4 + e, max(kend - 1, 0)); ks_[ntl][e] = __half2float(ksc[(p.row_base[b] + key) * 4 + kvh]); vs_[ntl][e] = __half2float(vsc[(p.row_base[b] + key) * 4 + kvh]); }
+                for (int e = 0; e < 2; e++) { const int key = min(key0 + 8 * h + 2 * t4 + e, max(kend - 1, 0)); ks_[e] = __half2float(ksc[(p.row_base[b] + key) * 4 + kvh]); vs_[e] = __half2float(vsc[(p.row_base[b] + key) * 4 + kvh]); }
             }
-            if (dead) continue;
-            if (!mbar_wait_bounded(bars + stg * 8, par)) { dead = true; atomicExch(err, 1); continue; }
-            n_waited = i + 1;
-            tile_qk_softmax_pv<I8>(q_base, kt, vt, key0, lim_row0, lim_row1, ks_, vs_, st, lane);
-        }
-        if (dead) {   // give copies already in flight a bounded chance to land before this CTA's shared memory is reused or released
-            for (int x = n_waited + 1; x < n_issued; x++) { const uint32_t cur = it_seg + (uint32_t)x; mbar_wait_bounded(bars + (cur % kStages) * 8, (cur / kStages) & 1u, 1u << 16); }
+            // The stage of tile i-1 is free once both warps of the pair have read it: refill it with tile i+2 right away.
+            if (h == 0 && i >= 1 && i + kStages - 1 < n_mine && (dbg & 255) != 2) {
+                const uint32_t prev = cur - 1;
+                if (!dead && !mbar_wait_bounded(ebars + (prev % kStages) * 8, (prev / kStages) & 1u, err)) { dead = true; atomicExch(err, 3); }
+                issue(i + kStages - 1);
+            }
+            // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and the pair barriers) stay intact.
+            if ((dbg & 255) != 2 && !dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
+            if (key0 + kTile > kend && h == 0) {   // tail tile: rows past the range were loaded as they lie in memory; zero those V rows (0 x garbage must stay 0)
+                const int nk = max(0, kend - key0);
+                for (int idx = lane; idx < (kTile - nk) * G::kBoxes * 8; idx += 32) {
+                    const int r = nk + idx / (G::kBoxes * 8), rem = idx % (G::kBoxes * 8);
+                    *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (rem >> 3) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            if ((dbg & 255) != 1) pair_tile<I8>(q_base, kt, vt, maxbuf, p_sm, 1 + ring, h, key0, lim_row0, lim_row1, ks_, vs_, st, lane, [] {});
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ebars + stg * 8);
         }
         it = it_seg + (uint32_t)n_mine;
 
-        // ---- merge the 4 warps of the CTA (all copies of this segment have landed: every issued tile was waited for)
+        // ---- merge the 4 rings of the CTA (every issued tile was waited for, so no copy is in flight)
         st.finish_l();
-        __syncwarp();
-        float* mo = reinterpret_cast<float*>(smem + kOffStages + w * G::kWarpBytes);
+        __syncthreads();
+        float* mo = reinterpret_cast<float*>(smem + stage_off + ring * G::kRingBytes);
 #pragma unroll
-        for (int j = 0; j < 32; j++)
+        for (int j = 0; j < 16; j++)
 #pragma unroll
-            for (int c = 0; c < 2; c++) { const int d = dim_of<I8>(j, c, t4); mo[g * kMergeStride + d] = st.o[j][c]; mo[(g + 8) * kMergeStride + d] = st.o[j][2 + c]; }
-        if (t4 == 0) { sm_ml[(w * 16 + g) * 2] = st.m0; sm_ml[(w * 16 + g) * 2 + 1] = st.l0; sm_ml[(w * 16 + g + 8) * 2] = st.m1; sm_ml[(w * 16 + g + 8) * 2 + 1] = st.l1; }
+            for (int c = 0; c < 2; c++) { const int d = pair_dim_of<I8>(h, j, c, t4); mo[g * kMergeStride + d] = st.o[j][c]; mo[(g + 8) * kMergeStride + d] = st.o[j][2 + c]; }
+        if (t4 == 0) {
+            if (h == 0) { sm_ml[(ring * 16 + g) * 3] = st.m0; sm_ml[(ring * 16 + g + 8) * 3] = st.m1; }
+            sm_ml[(ring * 16 + g) * 3 + 1 + h] = st.l0; sm_ml[(ring * 16 + g + 8) * 3 + 1 + h] = st.l1;
+        }
         __syncthreads();
 
         const int seg = b * 4 + kvh, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_end - 1), n_contrib = c_last - c_first + 1;
-        const int d0 = 2 * tid;   // this thread merges dims d0, d0+1 of every live row
+        const int d0 = 2 * (tid & 127), rsel = tid >> 7;   // this thread merges dims d0, d0+1 of rows rsel, rsel+2, ...
         const bool whole = (n_contrib == 1);
+        const int rows = 6 * T;
         float* slot_o = scratch_o + (int64_t)(cta + seg) * (12 * kD); float* slot_ml = scratch_ml + (int64_t)(cta + seg) * 32;
-        for (int r = 0; r < 6 * T; r++) {
+        auto emit = [&](int r, float M, float L, float A0, float A1) {   // final value of row r, dims d0, d0+1
+            const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
+            if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[d0] = A0; po[d0 + 1] = A1; if ((tid & 127) == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
+            else {
+                const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + d0; const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
+                const float y0 = (A0 / L) * sigmoid_fast(gt.x), y1 = (A1 / L) * sigmoid_fast(gt.y);
+                if (out_bf16) reinterpret_cast<__nv_bfloat162*>(out)[oi >> 1] = __floats2bfloat162_rn(y0, y1); else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oi) = make_float2(y0, y1);
+            }
+        };
+        for (int r = rsel; r < rows; r += 2) {
             float M = -INFINITY;
 #pragma unroll
-            for (int ww = 0; ww < kWarps; ww++) M = fmaxf(M, sm_ml[(ww * 16 + r) * 2]);
+            for (int ww = 0; ww < kRings; ww++) M = fmaxf(M, sm_ml[(ww * 16 + r) * 3]);
             float L = 0.0f, A0 = 0.0f, A1 = 0.0f;
 #pragma unroll
-            for (int ww = 0; ww < kWarps; ww++) {
-                const float mm = sm_ml[(ww * 16 + r) * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
-                const float* src = reinterpret_cast<const float*>(smem + kOffStages + ww * G::kWarpBytes) + r * kMergeStride + d0;
-                L += sm_ml[(ww * 16 + r) * 2 + 1] * wt; A0 += src[0] * wt; A1 += src[1] * wt;
+            for (int ww = 0; ww < kRings; ww++) {
+                const float mm = sm_ml[(ww * 16 + r) * 3]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
+                const float* src = reinterpret_cast<const float*>(smem + stage_off + ww * G::kRingBytes) + r * kMergeStride + d0;
+                L += (sm_ml[(ww * 16 + r) * 3 + 1] + sm_ml[(ww * 16 + r) * 3 + 2]) * wt; A0 += src[0] * wt; A1 += src[1] * wt;
             }
-            if (whole) {
-                const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-                if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[d0] = A0; po[d0 + 1] = A1; if (tid == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
-                else {
-                    const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + d0; const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
-                    const float y0 = (A0 / L) * (1.0f / (1.0f + __expf(-gt.x))), y1 = (A1 / L) * (1.0f / (1.0f + __expf(-gt.y)));
-                    if (out_bf16) reinterpret_cast<__nv_bfloat162*>(out)[oi >> 1] = __floats2bfloat162_rn(y0, y1); else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oi) = make_float2(y0, y1);
-                }
-            } else {
-                *reinterpret_cast<float2*>(slot_o + r * kD + d0) = make_float2(A0, A1);
-                if (tid == 0) { slot_ml[r * 2] = M; slot_ml[r * 2 + 1] = L; }
-            }
+            if (whole) emit(r, M, L, A0, A1);
+            else { *reinterpret_cast<float2*>(slot_o + r * kD + d0) = make_float2(A0, A1); if ((tid & 127) == 0) { slot_ml[r * 2] = M; slot_ml[r * 2 + 1] = L; } }
         }
         if (!whole) {   // ticket: the last contributor of the segment merges everybody's partials
             __threadfence();
@@ -184,24 +209,42 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecPlan p
             if (tid == 0) { const int old = atomicAdd(&counters[seg], 1); s_flag = (old == n_contrib - 1); }
             __syncthreads();
             if (s_flag) {
+                // Every contributor's partial is visible (ticket + fences). Weights first (tiny), then the O rows are pulled
+                // into shared memory with bulk async copies (one per contributor) so the whole merge takes a few microseconds.
                 __threadfence();
-                for (int r = 0; r < 6 * T; r++) {
-                    float M = -INFINITY;
-                    for (int c = c_first; c <= c_last; c++) M = fmaxf(M, __ldcg(scratch_ml + (int64_t)(c + seg) * 32 + r * 2));
-                    float L = 0.0f, A0 = 0.0f, A1 = 0.0f;
-                    for (int c = c_first; c <= c_last; c++) {
-                        const float mm = __ldcg(scratch_ml + (int64_t)(c + seg) * 32 + r * 2); const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
-                        const float2 a = __ldcg(reinterpret_cast<const float2*>(scratch_o + (int64_t)(c + seg) * (12 * kD) + r * kD + d0));
-                        L += __ldcg(scratch_ml + (int64_t)(c + seg) * 32 + r * 2 + 1) * wt; A0 += a.x * wt; A1 += a.y * wt;
-                    }
-                    const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-                    if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[d0] = A0; po[d0 + 1] = A1; if (tid == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
-                    else {
-                        const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + d0; const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
-                        const float y0 = (A0 / L) * (1.0f / (1.0f + __expf(-gt.x))), y1 = (A1 / L) * (1.0f / (1.0f + __expf(-gt.y)));
-                        if (out_bf16) reinterpret_cast<__nv_bfloat162*>(out)[oi >> 1] = __floats2bfloat162_rn(y0, y1); else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oi) = make_float2(y0, y1);
-                    }
+                asm volatile("fence.proxy.async;" ::: "memory");
+                float* wl = reinterpret_cast<float*>(smem + stage_off);          // [n_contrib][rows][2]: m (then weight), l
+                const int wl_bytes = (n_contrib * rows * 8 + 127) & ~127;
+                for (int i = tid; i < n_contrib * rows * 2; i += kThreads) { const int c = i / (rows * 2), k = i - c * (rows * 2); wl[i] = __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + k); }
+                __syncthreads();
+                if (tid < rows) {
+                    float M = -INFINITY; for (int c = 0; c < n_contrib; c++) M = fmaxf(M, wl[(c * rows + tid) * 2]);
+                    float L = 0.0f;
+                    for (int c = 0; c < n_contrib; c++) { const float mm = wl[(c * rows + tid) * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M); L += wl[(c * rows + tid) * 2 + 1] * wt; wl[(c * rows + tid) * 2] = wt; }
+                    s_ML[tid * 2] = M; s_ML[tid * 2 + 1] = L;
                 }
+                __syncthreads();
+                const uint32_t obuf = sm_base + stage_off + wl_bytes; const int cap = (kRings * G::kRingBytes - wl_bytes) / (rows * 1024);
+                float A[6][2];
+#pragma unroll
+                for (int r = 0; r < 6; r++) { A[r][0] = 0.0f; A[r][1] = 0.0f; }
+                for (int base = 0; base < n_contrib; base += cap) {
+                    const int cnt = min(cap, n_contrib - base);
+                    if (tid == 0) mbar_arrive_expect_tx(merge_bar, (uint32_t)(cnt * rows * 1024));
+                    __syncthreads();
+                    if (tid < 32) for (int c = tid; c < cnt; c += 32) bulk_g2s(obuf + c * rows * 1024, scratch_o + (int64_t)(c_first + base + c + seg) * (12 * kD), (uint32_t)(rows * 1024), merge_bar);
+                    if (!mbar_wait_bounded(merge_bar, merge_phase, err)) { atomicExch(err, 2); }
+                    merge_phase ^= 1u;
+                    for (int c = 0; c < cnt; c++) {
+#pragma unroll
+                        for (int rr = 0; rr < 6; rr++) { const int r = 2 * rr + rsel; if (r < rows) {
+                            const float wt = wl[((base + c) * rows + r) * 2]; const float2 v = *reinterpret_cast<const float2*>(smem + stage_off + wl_bytes + (c * rows + r) * 1024 + d0 * 4);
+                            A[rr][0] += wt * v.x; A[rr][1] += wt * v.y; } }
+                    }
+                    __syncthreads();
+                }
+#pragma unroll
+                for (int rr = 0; rr < 6; rr++) { const int r = 2 * rr + rsel; if (r < rows) emit(r, s_ML[r * 2], s_ML[r * 2 + 1], A[rr][0], A[rr][1]); }
                 if (tid == 0) counters[seg] = 0;   // ready for the next call on this stream
             }
         }
@@ -242,14 +285,15 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
+    static const int dbg = (getenv("KATA_DEC_DEBUG") ? atoi(getenv("KATA_DEC_DEBUG")) : 0) | ((getenv("KATA_DEC_PF") ? atoi(getenv("KATA_DEC_PF")) : 4) << 8);
     if (!attr_set[i8]) {
         cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
                            : cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem);
         if (e != cudaSuccess) return e;
         attr_set[i8] = true;
     }
-    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
-    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(c.tm_k, c.tm_v, c.pf_k, c.pf_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, dbg);
+    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(c.tm_k, c.tm_v, c.pf_k, c.pf_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, dbg);
     c.launches++;
     return cudaGetLastError();
 }

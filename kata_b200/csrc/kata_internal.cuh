@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <string>
@@ -40,6 +41,9 @@ struct Ctx {
     float* part_o = nullptr; float* part_ml = nullptr; int32_t* counters = nullptr; int32_t max_items = 0;
     // scalar-path scratch (k_attn_split partials)
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
+    // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: tm_* load 16-row x 128-byte boxes with the
+    // 128-byte swizzle (decode ring); pf_* cover 16 rows x one whole head row and are used for L2 prefetch only.
+    CUtensorMap tm_k{}, tm_v{}, pf_k{}, pf_v{};
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
     int sm_count = 148;
     uint64_t launches = 0;
@@ -58,5 +62,7 @@ cudaError_t launch_merge_parts(Ctx& c, const float* parts, int n_parts, int T, c
 cudaError_t launch_decode_scalar(Ctx& c, const Batch& b, int T, int first_pos, const float* q32, const float* gate, float* out, cudaStream_t s);
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
 void set_inv_freq(const float* host32);   // uploads the 32 inverse RoPE frequencies to constant memory of the current device
+// rank-3 map over an arena [rows][4][256 elements of elt bytes]; box = {box_inner elements, 1, box_rows}; returns false on failure
+bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128);
 
 }  // namespace kata

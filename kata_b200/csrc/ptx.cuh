@@ -21,9 +21,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-// Bounded wait: true when the phase completed, false when the poll budget ran out (about a second of wall clock).
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t max_polls = (1u << 22)) {
-    for (uint32_t i = 0; i < max_polls; ++i) if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait: true when the phase completed, false when the poll budget ran out or another wait of this launch already
+// failed (abort_flag, a word in global memory that the failing waiter sets): one stuck barrier then ends the whole grid in
+// a fraction of a second instead of every waiter running out its own budget.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, const int32_t* abort_flag = nullptr, uint32_t max_polls = (1u << 20)) {
+    for (uint32_t i = 0; i < max_polls; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (abort_flag && (i & 255u) == 255u && *reinterpret_cast<const volatile int32_t*>(abort_flag) != 0) return false;
+    }
     return false;
 }
 
@@ -32,6 +37,23 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+
+// Prefetch of a contiguous global range into L2 only (no destination): the later copy into shared memory then hits L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// Tiled TMA load of one box of a rank-3 tensor map into shared memory (this CTA); completion counted in bytes on an mbarrier.
+// The innermost coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+// Tiled prefetch of one box into L2 only.
+__device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) { asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory"); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes /* 16, or 0 to zero-fill */) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");

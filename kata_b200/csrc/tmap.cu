@@ -1,0 +1,25 @@
+// Host-side construction of the TMA tensor maps over the KV arenas. The driver entry point is looked up at run time so
+// the library does not link against libcuda.
+#include <cudaTypedefs.h>
+
+#include "kata_internal.cuh"
+
+namespace kata {
+
+bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128) {
+    static PFN_cuTensorMapEncodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr; cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return false;
+        encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    const cuuint64_t gdim[3] = {(cuuint64_t)kD, (cuuint64_t)kKvh, (cuuint64_t)rows};
+    const cuuint64_t gstride[2] = {(cuuint64_t)kD * elt, (cuuint64_t)kKVD * elt};   // bytes between heads, between rows
+    const cuuint32_t box[3] = {(cuuint32_t)box_inner, 1u, (cuuint32_t)box_rows};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = encode(out, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace kata
