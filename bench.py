@@ -177,7 +177,7 @@ def run_decode(args, rank, world, kind_cfg):
     launches = ctx.launches() - l0
     clocks = sampler.stop(tw0, tw1)
     ctx.check()
-    assert os.environ.get("KATA_DEC_DEBUG") or torch.isfinite(out).all()
+    assert torch.isfinite(out).all()
 
     # the dominant kernel alone: the decode launches of the same steps, timed on the same stream
     for layer in range(N_LAYERS):

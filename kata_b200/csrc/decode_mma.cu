@@ -9,9 +9,11 @@
 //  - The work is the list of 16-key tiles of every (sequence, KV head) segment. It is cut into one contiguous,
 //    equal-sized range per CTA (one CTA per SM), so ragged batches balance to within one tile and each key is read once.
 //  - Inside a CTA the tiles of the range go round-robin to 4 rings. A ring is a pair of warps on the same scheduler
-//    sharing a 3-stage shared-memory ring: one 512-byte (fp16) or 256-byte (int8) bulk async copy per K or V row, issued
-//    one row per lane and tracked by an mbarrier per stage. Rows are padded by 16 bytes so ldmatrix reads are bank-conflict
-//    free. Two warps per scheduler is what hides the fixed instruction latencies; shared memory bounds the ring count.
+//    sharing a 3-stage shared-memory ring. A stage is filled by tiled TMA loads (16 rows x 128 bytes per box, 128-byte
+//    swizzle, so ldmatrix reads are bank-conflict free without padding), tracked by a 'full' mbarrier; an 'empty' mbarrier
+//    lets the issuing warp refill a stage the moment both warps have read it. Measured on B200: per-row bulk copies
+//    (one 512-byte copy per lane) capped the kernel near 4.9 TB/s because of the TMA unit's operation rate; boxes reach
+//    5.6 TB/s. Prefetching further ahead into L2 made it slower and is not used.
 //  - Q.K^T and P.V run on mma.sync m16n8k16 (fp16 in, fp32 accumulate) straight from ldmatrix fragments. The two warps
 //    of a ring split the tile: each scores its own 8 keys, they exchange row maxima and the fp16 P block through shared
 //    memory (two 64-thread named barriers), and each accumulates its own 128-dim half of O. The softmax state lives in
@@ -21,7 +23,6 @@
 //    (atomic ticket) merges the partials, normalises, applies the gate and writes the output row. No second kernel.
 // Every mbarrier wait is bounded; on a timeout the kernel records an error word and skips the arithmetic.
 #include <algorithm>
-#include <cstdlib>
 
 #include "attn_tile.cuh"
 
@@ -64,10 +65,9 @@ __device__ __forceinline__ int cta_of_tile(const DecPlan& p, int tile) {
 
 template <bool I8>
 __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                                                                 const __grid_constant__ CUtensorMap pf_k, const __grid_constant__ CUtensorMap pf_v, const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
-                                                                 float* __restrict__ part_out, const uint8_t* __restrict__ k_arena, const uint8_t* __restrict__ v_arena,
-                                                                 const __half* __restrict__ ksc, const __half* __restrict__ vsc,
-                                                                 float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err, const int dbg) {
+                                                                 const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
+                                                                 float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
+                                                                 float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<I8>;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring and ring+4 sit on the same scheduler
@@ -93,8 +93,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         const int nt = p.ntiles[b], kvh = (tile - p.tile_start[b]) / nt, lt0 = (tile - p.tile_start[b]) - kvh * nt;
         const int seg_first = p.tile_start[b] + kvh * nt, seg_end = seg_first + nt, my_end = min(tile_end, seg_end), n_here = my_end - tile;
         const int T = p.T, kend = p.kend[b], pos_rel = p.pos[b] - p.key_off;   // token t sees local rows < min(kend, pos_rel + t + 1)
-        const uint8_t* Kg = k_arena + (p.row_base[b] * kKVD + kvh * kD) * (I8 ? 1 : 2);
-        const uint8_t* Vg = v_arena + (p.row_base[b] * kKVD + kvh * kD) * (I8 ? 1 : 2);
 
         // ---- this ring's tiles of the segment: local tiles lt0 + ring, lt0 + ring + 4, ...
         const int n_mine = n_here > ring ? (n_here - ring + kRings - 1) / kRings : 0;
@@ -103,12 +101,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         const int lim_row1 = (g + 8 < 6 * T) ? min(kend, pos_rel + 2) : 0;                          // rows 8..11 belong to token 1
 
         const uint32_t it_seg = it;
-        const int pf = dbg >> 8;   // L2 prefetch distance in tiles beyond the shared-memory ring
         const int row0 = (int)p.row_base[b];   // arena row of position 0 (row coordinates of the tensor maps are 32-bit)
-        auto prefetch = [&](int i) {   // the ring's i-th tile -> L2 only: one 16-row box of whole head rows for K and one for V
-            const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-            if (key0 < kend && lane < 2) tma_prefetch_3d(lane ? &pf_v : &pf_k, 0, kvh, row0 + key0);
-        };
         auto issue = [&](int i) {   // warp h=0 of the ring brings in the ring's i-th tile: one TMA box per 128-byte column block of K and of V
             const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
             const uint32_t sx = (it_seg + (uint32_t)i) % kStages, dst = ring_stage0 + sx * G::kStageBytes, bar = bars + sx * 8;
@@ -119,10 +112,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 const int isv = lane >= G::kBoxes, bx = lane - isv * G::kBoxes;
                 tma_load_3d(dst + isv * G::kTileBytes + bx * (kTile * 128), isv ? &tm_v : &tm_k, bx * (128 / (I8 ? 1 : 2)), kvh, row0 + key0, bar);
             }
-            if (pf > 0 && i + pf < n_mine) prefetch(i + pf);
         };
 
-        if ((dbg & 255) != 2 && h == 0) { for (int i = 0; i < min(kStages, n_mine); i++) issue(i); for (int i = kStages; i < min(kStages + pf, n_mine); i++) prefetch(i); }   // every stage is free here; the first tiles fly while Q is staged
+        if (h == 0) for (int i = 0; i < min(kStages, n_mine); i++) issue(i);   // every stage is free here; the first tiles fly while Q is staged
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
@@ -141,13 +133,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 for (int e = 0; e < 2; e++) { const int key = min(key0 + 8 * h + 2 * t4 + e, max(kend - 1, 0)); ks_[e] = __half2float(ksc[(p.row_base[b] + key) * 4 + kvh]); vs_[e] = __half2float(vsc[(p.row_base[b] + key) * 4 + kvh]); }
             }
             // The stage of tile i-1 is free once both warps of the pair have read it: refill it with tile i+2 right away.
-            if (h == 0 && i >= 1 && i + kStages - 1 < n_mine && (dbg & 255) != 2) {
+            if (h == 0 && i >= 1 && i + kStages - 1 < n_mine) {
                 const uint32_t prev = cur - 1;
                 if (!dead && !mbar_wait_bounded(ebars + (prev % kStages) * 8, (prev / kStages) & 1u, err)) { dead = true; atomicExch(err, 3); }
                 issue(i + kStages - 1);
             }
             // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and the pair barriers) stay intact.
-            if ((dbg & 255) != 2 && !dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
+            if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
             if (key0 + kTile > kend && h == 0) {   // tail tile: rows past the range were loaded as they lie in memory; zero those V rows (0 x garbage must stay 0)
                 const int nk = max(0, kend - key0);
                 for (int idx = lane; idx < (kTile - nk) * G::kBoxes * 8; idx += 32) {
@@ -155,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                     *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (rem >> 3) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            if ((dbg & 255) != 1) pair_tile<I8>(q_base, kt, vt, maxbuf, p_sm, 1 + ring, h, key0, lim_row0, lim_row1, ks_, vs_, st, lane, [] {});
+            pair_tile<I8>(q_base, kt, vt, maxbuf, p_sm, 1 + ring, h, key0, lim_row0, lim_row1, ks_, vs_, st, lane, [] {});
             __syncwarp();
             if (lane == 0) mbar_arrive(ebars + stg * 8);
         }
@@ -285,15 +277,14 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
-    static const int dbg = (getenv("KATA_DEC_DEBUG") ? atoi(getenv("KATA_DEC_DEBUG")) : 0) | ((getenv("KATA_DEC_PF") ? atoi(getenv("KATA_DEC_PF")) : 4) << 8);
     if (!attr_set[i8]) {
         cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
                            : cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem);
         if (e != cudaSuccess) return e;
         attr_set[i8] = true;
     }
-    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(c.tm_k, c.tm_v, c.pf_k, c.pf_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, dbg);
-    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(c.tm_k, c.tm_v, c.pf_k, c.pf_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, dbg);
+    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(c.tm_k, c.tm_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(c.tm_k, c.tm_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     c.launches++;
     return cudaGetLastError();
 }

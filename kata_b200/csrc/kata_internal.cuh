@@ -41,9 +41,8 @@ struct Ctx {
     float* part_o = nullptr; float* part_ml = nullptr; int32_t* counters = nullptr; int32_t max_items = 0;
     // scalar-path scratch (k_attn_split partials)
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
-    // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: tm_* load 16-row x 128-byte boxes with the
-    // 128-byte swizzle (decode ring); pf_* cover 16 rows x one whole head row and are used for L2 prefetch only.
-    CUtensorMap tm_k{}, tm_v{}, pf_k{}, pf_v{};
+    // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
+    CUtensorMap tm_k{}, tm_v{};
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
     int sm_count = 148;
     uint64_t launches = 0;
