@@ -38,6 +38,7 @@ extern "C" {
 #define KATA_MAX_BATCH 64    /* sequences per call */
 #define KATA_MAX_CHUNK 1024  /* tokens per prefill call (Engine::kMaxChunk, src/engine.h:38) */
 #define KATA_MAX_VERIFY 8    /* tokens per scalar decode call (Engine::kMaxVerify, src/engine.h:97) */
+#define KATA_STATIC_MAX_BATCH 8 /* sequences per kata_attn_decode_static call */
 
 enum { KATA_OK = 0, KATA_ERR_ARG = 1, KATA_ERR_RANGE = 2, KATA_ERR_MODE = 3, KATA_ERR_CUDA = 4, KATA_ERR_DEVICE_WAIT = 5, KATA_ERR_NOMEM = 6 };
 enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1 };             /* KATA_KV=fp16|int8 (src/engine.cpp:54-58) */
@@ -130,6 +131,18 @@ int kata_attn_kv_plane_read(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int3
 int kata_attn_kv_plane_write(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, const void* h_src);
 /* Device address of row 0 of a plane (kvPlanePtr). */
 void* kata_attn_kv_plane_ptr(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane);
+
+/* No counterpart in the reference. kata_attn_decode for callers that cannot allocate device memory and therefore have no
+ * context: engines that give all device memory to their own pools at start-up (a library cudaMalloc then fails), and
+ * loops that forbid cudaMalloc/cudaFree because they synchronise the device. Allocates nothing: the caller owns the fp16
+ * K and V rows (d_k_rows, d_v_rows: [total_rows][1024], 16-byte aligned; sequence i's position p is row seq_row0[i] + p)
+ * and the split-KV scratch is a fixed array of about 2.2 MB inside the library image, held by every GPU that loads the
+ * library until the process exits. Same semantics and outputs as kata_attn_decode (fp16 cache). Limits: n <=
+ * KATA_STATIC_MAX_BATCH (more: KATA_ERR_RANGE), T in {1,2}, at most 148 CTAs. The first call on a device does that
+ * device's set-up and must be made outside stream capture. All calls on a device share the scratch: calls that overlap
+ * on the GPU race on it and must be serialised by the caller. A bounded device wait that runs out is not reported here. */
+int kata_attn_decode_static(const void* d_k_rows, const void* d_v_rows, int64_t total_rows, int32_t n, const int64_t* seq_row0, const int32_t* pos_base,
+                            int32_t T, int32_t first_pos, const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 
 /* Number of kernels this library has launched on this context since creation (for accounting in benchmarks). */
 uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);

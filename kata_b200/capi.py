@@ -24,7 +24,7 @@ EXPORTS = [
     "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
-    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static",
 ]
 
 
@@ -193,3 +193,16 @@ class AttnContext:
 
     def plane_ptr(self, layer, seq, plane) -> int:
         return int(self.L.kata_attn_kv_plane_ptr(self.h, layer, seq, plane) or 0)
+
+
+def decode_static(k_rows, v_rows, seq_row0, pos_base, T, q16, gate, first_pos=0, out=None, out_dtype=torch.float32):
+    """kata_attn_decode_static: decode over caller-owned fp16 K/V rows ([rows][1024] tensors) with no context and no
+    allocation inside the library. Returns (status code, out)."""
+    L = lib()
+    n = len(pos_base)
+    rows0 = (C.c_int64 * n)(*[int(x) for x in seq_row0])
+    pa, pp = _i32(pos_base)
+    out = torch.empty((n, T, QD), dtype=out_dtype, device=q16.device) if out is None else out
+    rc = L.kata_attn_decode_static(_dp(k_rows), _dp(v_rows), C.c_int64(k_rows.shape[0]), n, rows0, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out),
+                                   ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream())
+    return rc, out

@@ -300,3 +300,75 @@ cudaError_t launch_merge_parts(Ctx& c, const float* parts, int n_parts, int T, c
 }
 
 }  // namespace kata
+
+// =====================================================================================================================
+// kata_attn_decode_static: the decode/verify kernel above for callers that cannot allocate device memory.
+//
+// Who that is: a host engine that hands the whole GPU to its own memory pools at start-up (a later cudaMalloc from a
+// library simply fails there), and serving loops where cudaMalloc/cudaFree are banned because they synchronise the
+// device. Such a caller owns the K/V rows itself and has no kata_attn_ctx (creating one allocates the caches and scratch).
+//
+// The split-KV partials, their (m, l) pairs, the per-segment tickets and the error word live in the file-scope array
+// below instead of context memory. It has a fixed size (about 2.2 MB), is part of the library image, and every GPU that
+// loads the library keeps it until the process exits. Consequences the caller must know:
+//  - Limits: at most KATA_STATIC_MAX_BATCH sequences per call and at most 148 CTAs (more SMs are simply not used);
+//    a larger batch is rejected with KATA_ERR_RANGE. fp16 rows only.
+//  - The first call on a device performs the set-up for that device (symbol address lookup, shared-memory opt-in);
+//    make that first call outside any stream capture.
+//  - All calls on a device share the array and it keeps the previous call's contents. The ticket counters and the
+//    error word are cleared on the stream before every launch; partial slots are always written before they are read.
+//    Two calls that overlap on the GPU (different streams, or the same call issued from two threads) race on the array:
+//    serialise them.
+namespace kata {
+namespace {
+
+constexpr int kStaticMaxBatch = KATA_STATIC_MAX_BATCH, kStaticMaxCtas = 148, kStaticSlots = kStaticMaxCtas + 4 * kStaticMaxBatch;
+struct StaticScratch {
+    float part_o[kStaticSlots * 12 * kD];      // unnormalised partial O rows per (CTA, segment) slot
+    float part_ml[kStaticSlots * 32];          // their (m, l)
+    int32_t counters[4 * KATA_MAX_BATCH];      // segment tickets: must be zero at launch
+    int32_t err;                               // set when a bounded device wait runs out
+};
+static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
+
+struct StaticDev { bool ready = false; StaticScratch* scratch = nullptr; int sm_count = 0; };
+StaticDev g_static_dev[64];
+
+}  // namespace
+}  // namespace kata
+
+extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_rows, int64_t total_rows, int32_t n, const int64_t* seq_row0, const int32_t* pos_base,
+                                       int32_t T, int32_t first_pos, const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
+    using namespace kata;
+    if (!d_k_rows || !d_v_rows || !seq_row0 || !pos_base || !d_q16 || !d_gate || !d_out) return KATA_ERR_ARG;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16) return KATA_ERR_ARG;
+    if (n < 1 || n > kStaticMaxBatch || T < 1 || T > 2 || total_rows < 1 || total_rows > 0x7fffffffLL) return KATA_ERR_RANGE;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KATA_ERR_CUDA;
+    StaticDev& sd = g_static_dev[dev];
+    if (!sd.ready) {   // once per device, with that device current: the array's name is only a host-side handle, the kernel needs its device address
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return KATA_ERR_CUDA;
+        if (cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem) != cudaSuccess) return KATA_ERR_CUDA;
+        if (cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return KATA_ERR_CUDA;
+        sd.scratch = static_cast<StaticScratch*>(ptr); sd.ready = true;
+    }
+    DecPlan p{}; p.n = n; p.T = T; p.first_row = first_pos; p.key_off = 0;
+    int total = 0;
+    for (int i = 0; i < n; i++) {
+        if (pos_base[i] < 0 || first_pos < 0 || first_pos > pos_base[i] || seq_row0[i] < 0 || seq_row0[i] + pos_base[i] + T > total_rows) return KATA_ERR_RANGE;
+        p.pos[i] = pos_base[i]; p.row_base[i] = seq_row0[i]; p.kend[i] = pos_base[i] + T;
+        p.ntiles[i] = std::max(1, (p.kend[i] - first_pos + kTile - 1) / kTile);
+        p.tile_start[i] = total; total += 4 * p.ntiles[i];
+    }
+    for (int i = n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
+    const int n_ctas = std::max(1, std::min(std::min(sd.sm_count, kStaticMaxCtas), total));
+    p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
+    CUtensorMap tm_k, tm_v;   // encoded on the host; no device memory involved
+    if (!make_arena_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 64, 16, true) || !make_arena_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 64, 16, true)) return KATA_ERR_CUDA;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
+    decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,
+                                                                         sd.scratch->part_o, sd.scratch->part_ml, sd.scratch->counters, &sd.scratch->err);
+    return cudaGetLastError() == cudaSuccess ? KATA_OK : KATA_ERR_CUDA;
+}
