@@ -55,7 +55,7 @@ typedef struct kata_attn_config {
     int32_t kv_mode;        /* KATA_KV_* ; fixed for the life of the context (docs/reports/M11-int8-kv.en.md:69-71) */
     int32_t quant_round;    /* KATA_ROUND_* ; int8 mode only */
     int32_t dec_chunk;      /* keys per decode split; 0 = sized from the SM count (reference: 128, KATA_DEC_CHUNK) */
-    int32_t reserved;
+    int32_t flags;          /* bit 0: use the mma.sync prefill kernel for fp16 caches too (cross-check of the tcgen05 kernel) */
 } kata_attn_config;
 
 /* Engine::load, cache part (src/engine.cpp:54-60,79): allocates, zero-filled (src/gpu.cpp:26-30), per sequence

@@ -1,0 +1,141 @@
+"""Prefill workloads of bench.py: pp512 (benchmark config 2) and chunked prefill + T=2 verify (config 5).
+
+pp512: 512 prompt tokens, bf16 projections, all 16 layers; a step = per layer prep (norm, RoPE, append) + causal flash
+prefill. chunked: a 7,300-token prompt whose first 3,600 positions are restored through the KV-plane API, then prefilled
+in 512-token chunks (7 x 512 + 116) against the growing prefix, then one T=2 verify step; all 16 layers.
+The roofline object is the prefill kernel alone: useful FLOPs = sum over query rows of keys attended x 24 x 256 x 4.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+
+N_LAYERS = 16
+
+
+def _flops(pos0: int, m: int) -> float:
+    return float(sum(range(pos0 + 1, pos0 + m + 1))) * 24 * 256 * 4
+
+
+def run(args, rank, world, cfg, pk, ClockSampler):
+    import torch
+    import torch.distributed as dist
+    from kata_b200 import capi
+
+    kind, B, kv_mode, total, _ = cfg
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev); gen.manual_seed(99 + rank)
+    restore = 3600 if kind == "chunked" else 0
+    chunks, p = [], restore
+    while p < total:
+        m = min(512, total - p); chunks.append((p, m)); p += m
+    ctx = capi.AttnContext(N_LAYERS, [total + 8] * B, kv_mode=kv_mode)
+    seqs = list(range(B))
+    qn = (1 + 0.05 * torch.randn(N_LAYERS, 256, generator=gen, device=dev)).contiguous()
+    kn = (1 + 0.05 * torch.randn(N_LAYERS, 256, generator=gen, device=dev)).contiguous()
+    bf = torch.bfloat16
+    if restore:   # build the prefix once, export its planes, reset, import them: the prefix-cache restore
+        for layer in range(N_LAYERS):
+            for s in seqs:
+                for st in range(0, restore, 1024):
+                    m = min(1024, restore - st)
+                    ctx.prep(layer, [s], [st], m, None, torch.randn(1, m, 1024, generator=gen, device=dev).to(bf), torch.randn(1, m, 1024, generator=gen, device=dev).to(bf), None, kn[layer], h0=24, nh=8)
+        ctx.check()
+        saved = [[[ctx.plane_read(l, s, pl, 0, restore) for pl in range(ctx.kv_planes())] for s in seqs] for l in range(N_LAYERS)]
+        ctx.reset()
+        for l in range(N_LAYERS):
+            for s in seqs:
+                for pl in range(ctx.kv_planes()):
+                    ctx.plane_write(l, s, pl, 0, saved[l][s][pl])
+        del saved
+    mmax = max(m for _, m in chunks)
+    # one set of projections per chunk shape, reused across layers (values do not affect the timing)
+    qfull = torch.randn(B, mmax, 12288, generator=gen, device=dev).to(bf)
+    kproj = torch.randn(B, mmax, 1024, generator=gen, device=dev).to(bf)
+    vproj = torch.randn(B, mmax, 1024, generator=gen, device=dev).to(bf)
+    q16 = torch.empty(B, mmax, 6144, dtype=torch.float16, device=dev)
+    gate = torch.empty(B, mmax, 6144, dtype=torch.float32, device=dev)
+    out = torch.empty(B, mmax, 6144, dtype=torch.float32, device=dev)
+
+    def sl(t, m):
+        return t if m == mmax else t[:, :m].contiguous()
+
+    def step(with_prep=True, host=None):
+        for (p0, m) in chunks:
+            for layer in range(N_LAYERS):
+                if host is not None:
+                    qfull[:, :m].copy_(host[0][:, :m], non_blocking=True); kproj[:, :m].copy_(host[1][:, :m], non_blocking=True); vproj[:, :m].copy_(host[2][:, :m], non_blocking=True)
+                if m == mmax:
+                    if with_prep:
+                        ctx.prep(layer, seqs, [p0] * B, m, qfull, kproj, vproj, qn[layer], kn[layer], q16=q16, gate=gate)
+                    ctx.prefill(layer, seqs, [p0] * B, m, q16, gate, out=out)
+                else:
+                    q_, g_ = (ctx.prep(layer, seqs, [p0] * B, m, sl(qfull, m), sl(kproj, m), sl(vproj, m), qn[layer], kn[layer])[0::2] if with_prep else (sl(q16, m), sl(gate, m)))
+                    o_ = ctx.prefill(layer, seqs, [p0] * B, m, q_, g_)
+                    out[:, :m].copy_(o_)
+                if host is not None:
+                    host[3][:, :m].copy_(out[:, :m], non_blocking=True)
+        if kind == "chunked":   # the T=2 verify that follows (target token plus one draft)
+            for layer in range(N_LAYERS):
+                q2, _, g2 = ctx.prep(layer, seqs, [total] * B, 2, sl(qfull, 2), sl(kproj, 2), sl(vproj, 2), qn[layer], kn[layer])
+                ctx.decode(layer, seqs, [total] * B, 2, q2, g2)
+        if host is not None:
+            torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
+    for _ in range(args.warmup):
+        step()
+    ctx.check()
+    l0 = ctx.launches(); barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tw0 = time.perf_counter(); e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record(); barrier(); tw1 = time.perf_counter()
+    ms = e0.elapsed_time(e1); launches = ctx.launches() - l0
+    clocks = sampler.stop(tw0, tw1)
+    ctx.check()
+    assert torch.isfinite(out).all()
+    # the prefill kernel alone (q16/gate of the last prep are reused)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    full = [(p0, m) for (p0, m) in chunks if m == mmax]
+    for (p0, m) in full:
+        ctx.prefill(0, seqs, [p0] * B, m, q16, gate, out=out)
+    torch.cuda.synchronize(); k0.record()
+    reps = max(2, args.steps)
+    for _ in range(reps):
+        for (p0, m) in full:
+            for layer in range(N_LAYERS):
+                ctx.prefill(layer, seqs, [p0] * B, m, q16, gate, out=out)
+    k1.record(); torch.cuda.synchronize()
+    kern_ms = k0.elapsed_time(k1) / (reps * N_LAYERS * len(full))
+    flops_launch = B * float(np.mean([_flops(p0, m) for (p0, m) in full]))
+    # end to end with host buffers
+    host = [torch.randn(B, mmax, 12288).to(bf).pin_memory(), torch.randn(B, mmax, 1024).to(bf).pin_memory(), torch.randn(B, mmax, 1024).to(bf).pin_memory(), torch.empty(B, mmax, 6144).pin_memory()]
+    step(host=host); barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(host=host)
+    barrier(); e2e_ms = (time.perf_counter() - t0) * 1e3
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, e2e_ms = t.tolist()
+    toks = sum(m for _, m in chunks)
+    ach = flops_launch / (kern_ms * 1e-3) / 1e12
+    h2d = N_LAYERS * B * toks * (12288 + 2048) * 2; d2h = N_LAYERS * B * toks * 6144 * 4
+    name = "pp512" if kind == "prefill" else f"chunked prefill 3600->{total} in 512-token chunks after a plane restore at 3600, then a T=2 verify"
+    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * B * toks * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+           "config": {"workload": f"{name}; {N_LAYERS} layers, {kv_mode} KV, bf16 projections, batch {B}/GPU, prep+prefill per layer", "batch_per_gpu": B, "global_batch": world * B,
+                      "l2": "L2 flushed implicitly: each step streams the 16 layers' caches and activations (larger than L2 for the chunked workload); pp512 at batch 1 fits L2 and says so"},
+           "clocks": clocks, "gpu_launches": int(launches),
+           "e2e": {"value": world * B * toks * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+           "roofline": {"bound": "tensor", "kernel": "prefill kernel (see config.kernel)", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / pk["bf16_tflops"], "peak_src": pk["src"],
+                        "us_per_launch": kern_ms * 1e3, "algorithmic_flops_per_launch": flops_launch, "traffic": None}}
+    ctx.close()
+    return res

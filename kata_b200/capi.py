@@ -30,7 +30,7 @@ EXPORTS = [
 
 class Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("n_layers", C.c_int32), ("n_seqs", C.c_int32), ("max_ctx", C.POINTER(C.c_int32)),
-                ("kv_mode", C.c_int32), ("quant_round", C.c_int32), ("dec_chunk", C.c_int32), ("reserved", C.c_int32)]
+                ("kv_mode", C.c_int32), ("quant_round", C.c_int32), ("dec_chunk", C.c_int32), ("flags", C.c_int32)]
 
 
 class KataError(RuntimeError):
@@ -79,13 +79,13 @@ def _stream():
 class AttnContext:
     """One context per GPU: the KV caches of ``len(max_ctx)`` sequences x ``n_layers`` layers plus all scratch."""
 
-    def __init__(self, n_layers: int, max_ctx, kv_mode: str = "fp16", quant_round: str = "rint", device: int | None = None, dec_chunk: int = 0):
+    def __init__(self, n_layers: int, max_ctx, kv_mode: str = "fp16", quant_round: str = "rint", device: int | None = None, dec_chunk: int = 0, legacy_prefill: bool = False):
         self.L = lib()
         self.device = torch.cuda.current_device() if device is None else device
         self.max_ctx, mp = _i32(max_ctx)
         self.n_layers, self.n_seqs = n_layers, len(self.max_ctx)
         self.int8 = kv_mode == "int8"
-        cfg = Config(self.device, n_layers, self.n_seqs, mp, KV_INT8 if self.int8 else KV_FP16, ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, 0)
+        cfg = Config(self.device, n_layers, self.n_seqs, mp, KV_INT8 if self.int8 else KV_FP16, ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, 1 if legacy_prefill else 0)
         self.h = C.c_void_p()
         rc = self.L.kata_attn_create(C.byref(cfg), C.byref(self.h))
         if rc != OK:

@@ -97,7 +97,8 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     if (!ok) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_NOMEM; }
     {   // 128 bytes of a 16-row box line = 64 fp16 or 128 int8 elements
         const int inner = 128 / c.elt;
-        if (!kata::make_arena_tmap(&c.tm_k, c.k_arena, c.elt, rows, inner, 16, true) || !kata::make_arena_tmap(&c.tm_v, c.v_arena, c.elt, rows, inner, 16, true)) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
+        if (!kata::make_arena_tmap(&c.tm_k, c.k_arena, c.elt, rows, inner, 16, true) || !kata::make_arena_tmap(&c.tm_v, c.v_arena, c.elt, rows, inner, 16, true) ||
+            (c.elt == 2 && (!kata::make_arena_tmap(&c.tm_k128, c.k_arena, 2, rows, 64, 128, true) || !kata::make_arena_tmap(&c.tm_v128, c.v_arena, 2, rows, 64, 128, true)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);
     float invf[32]; for (int i = 0; i < 32; i++) invf[i] = powf(10000000.0f, -(float)i / 32.0f);   // shaders/attn.metal:26

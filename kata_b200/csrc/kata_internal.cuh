@@ -43,6 +43,7 @@ struct Ctx {
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
     // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
     CUtensorMap tm_k{}, tm_v{};
+    CUtensorMap tm_k128{}, tm_v128{};   // the same arenas with 128-row boxes (tcgen05 prefill tiles; fp16 mode)
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
     int sm_count = 148;
     uint64_t launches = 0;
@@ -62,6 +63,7 @@ cudaError_t launch_decode_scalar(Ctx& c, const Batch& b, int T, int first_pos, c
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
 void set_inv_freq(const float* host32);   // uploads the 32 inverse RoPE frequencies to constant memory of the current device
 // rank-3 map over an arena [rows][4][256 elements of elt bytes]; box = {box_inner elements, 1, box_rows}; returns false on failure
+bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows);
 bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128);
 
 }  // namespace kata

@@ -119,8 +119,4 @@ cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16,
     return cudaGetLastError();
 }
 
-cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
-    return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
-}
-
 }  // namespace kata

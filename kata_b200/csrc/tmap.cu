@@ -6,13 +6,27 @@
 
 namespace kata {
 
-bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128) {
+static PFN_cuTensorMapEncodeTiled get_encode() {
     static PFN_cuTensorMapEncodeTiled encode = nullptr;
     if (!encode) {
         void* fn = nullptr; cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return false;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return nullptr;
         encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
     }
+    return encode;
+}
+
+// rank-2 map over a row-major fp16 matrix [rows][cols]; box = {box_cols, box_rows}, 128-byte swizzle
+bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows) {
+    PFN_cuTensorMapEncodeTiled encode = get_encode(); if (!encode) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows}; const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows}; const cuuint32_t estr[2] = {1u, 1u};
+    return encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128) {
+    PFN_cuTensorMapEncodeTiled encode = get_encode(); if (!encode) return false;
     const cuuint64_t gdim[3] = {(cuuint64_t)kD, (cuuint64_t)kKvh, (cuuint64_t)rows};
     const cuuint64_t gstride[2] = {(cuuint64_t)kD * elt, (cuuint64_t)kKVD * elt};   // bytes between heads, between rows
     const cuuint32_t box[3] = {(cuuint32_t)box_inner, 1u, (cuuint32_t)box_rows};

@@ -272,13 +272,13 @@ def test_split_kv_partials_merge(capi, orc):
 
 
 # ------------------------------------------------------------------------------------------------ prefill
-@pytest.mark.parametrize("int8", [False, True])
-def test_prefill_probe_shape(capi, orc, int8):
+@pytest.mark.parametrize("int8,legacy", [(False, False), (False, True), (True, False)], ids=["fp16-tcgen05", "fp16-mma", "int8-mma"])
+def test_prefill_probe_shape(capi, orc, int8, legacy):
     # the reference's probe: 70 rows (ragged tail) at position 300, NaN beyond the valid keys; plus M = 1, 15, 16, 17 and pos 0
     planes, q, gate, _ = _oracle_fill(orc, 61, 370, 512, int8=int8, poison=not int8, fast=True)
     if int8:
         planes.ksc[370:], planes.vsc[370:] = NAN16, NAN16
-    ctx = capi.AttnContext(1, [512], kv_mode="int8" if int8 else "fp16")
+    ctx = capi.AttnContext(1, [512], kv_mode="int8" if int8 else "fp16", legacy_prefill=legacy)
     _upload_planes(ctx, planes)
     for pb, M in ((300, 70), (0, 1), (0, 15), (0, 16), (0, 17), (0, 70), (353, 17), (0, 370)):
         sub = orc.KvPlanes(512, int8=int8, poison=not int8)
@@ -291,6 +291,27 @@ def test_prefill_probe_shape(capi, orc, int8):
         got = out.cpu().numpy()[0]
         _close(got, orc.formula_f32(q[pb:n], gate[pb:n], sub, pb))
         assert np.abs(got - orc.flash_prefill(orc.cvt_q_half(q[pb:n]), gate[pb:n], sub, pb)).max() < 3e-4
+
+
+def test_prefill_long_tcgen05_vs_oracle_and_mma(capi, orc):
+    # several 128-row query tiles over many 128-key tiles (running-maximum rescales, diagonal and tail tiles), two sequences
+    pb, M = 700, 600
+    ctx = capi.AttnContext(1, [2048, 2048])
+    leg = capi.AttnContext(1, [2048, 2048], legacy_prefill=True)
+    q16s, gates, refs = [], [], []
+    for s, scale in enumerate((1.0, 3.0)):   # the second sequence has sharper scores: more maximum updates
+        planes, q, gate, _ = _oracle_fill(orc, 70 + s, pb + M, 2048, poison=True, fast=True, seq=s)
+        q = (q * scale).astype(np.float32)
+        _upload_planes(ctx, planes, seq=s); _upload_planes(leg, planes, seq=s)
+        q16s.append(orc.cvt_q_half(q[pb:])); gates.append(gate[pb:])
+        refs.append(orc.formula_f32(q[pb:], gate[pb:], planes, pb))
+    dq, dg = _dev(np.stack(q16s)).view(torch.float16), _dev(np.stack(gates))
+    out = ctx.prefill(0, [0, 1], [pb, pb], M, dq, dg)
+    ref2 = leg.prefill(0, [0, 1], [pb, pb], M, dq, dg)
+    ctx.check(); leg.check()
+    for s in range(2):
+        _close(out.cpu().numpy()[s], refs[s])
+        assert np.abs(out.cpu().numpy()[s] - ref2.cpu().numpy()[s]).max() < TOL_MAX   # the two kernels round P against different running maxima
 
 
 def test_chunked_prefill_restore_equals_one_shot(capi, orc):
