@@ -39,9 +39,12 @@ WORKLOADS = {
     "decode_b64": ("decode", 64, "fp16", 32768, 16384),
     "decode_int8_b8": ("decode", 8, "int8", 32768, 16384),
     "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
+    "splitkv_b1": ("splitkv", 1, "fp16", 32768, 32768),       # one 32K sequence, keys split across the ranks, NCCL merge per layer
     "pp512": ("prefill", 1, "fp16", 512, 512),
-    "chunked_b1": ("chunked", 1, "fp16", 7300, 7300),
-    "chunked_b16": ("chunked", 16, "fp16", 7300, 7300),
+    # chunked: (kind, batch, kv mode, prompt length, restored prefix)
+    "chunked_b1": ("chunked", 1, "fp16", 7300, 3600),
+    "chunked_b16": ("chunked", 16, "fp16", 7300, 3600),
+    "chunked_small": ("chunked", 4, "fp16", 3072, 1024),      # ~0.4 GB: the size used for ncu captures of the prefill kernel
 }
 
 
@@ -261,6 +264,92 @@ def cpu_baseline_decode(ctx, lens, pos, B, kv_mode):
             "sample": f"1 of {N_LAYERS} layers, {nb} sequences at full length ({dt:.2f} s), tok/s extrapolated x{N_LAYERS} layers"}
 
 
+def run_splitkv(args, rank, world, kind_cfg):
+    """Batch 1, context split by keys across the ranks: every rank holds keys [lo, hi) of all 16 layers, computes its
+    (O, m, l) part per layer, the parts are all-gathered over NCCL and merged on every rank. Strong scaling: total work fixed."""
+    import torch
+    import torch.distributed as dist
+    from kata_b200 import capi, multi
+
+    _, _, kv_mode, L, _ = kind_cfg
+    dev = torch.device("cuda", torch.cuda.current_device())
+    steps_total = args.warmup + args.steps + 2
+    lo, hi = multi.split_keys(L, world)[rank]
+    tail = rank == world - 1
+    ctx = capi.AttnContext(N_LAYERS, [max(hi - lo, 1) + steps_total + 8], kv_mode=kv_mode)
+    ctx.set_position_offset(0, lo)
+    gen = torch.Generator(device=dev); gen.manual_seed(777)   # same projections on every rank
+    qn = (1 + 0.05 * torch.randn(N_LAYERS, 256, generator=gen, device=dev)).contiguous()
+    kn = (1 + 0.05 * torch.randn(N_LAYERS, 256, generator=gen, device=dev)).contiguous()
+    qfull = torch.randn(N_LAYERS, 1, 1, 12288, generator=gen, device=dev)
+    kproj = torch.randn(N_LAYERS, 1, 1, 1024, generator=gen, device=dev)
+    vproj = torch.randn(N_LAYERS, 1, 1, 1024, generator=gen, device=dev)
+    g2 = torch.Generator(device=dev); g2.manual_seed(1000 + rank)
+    for layer in range(N_LAYERS):
+        for st in range(lo, hi, 1024):
+            m = min(1024, hi - st)
+            ctx.prep(layer, [0], [st], m, None, torch.randn(1, m, 1024, generator=g2, device=dev), torch.randn(1, m, 1024, generator=g2, device=dev), None, kn[layer], h0=24, nh=8)
+    ctx.check()
+    q16 = torch.empty(N_LAYERS, 1, 1, 6144, dtype=torch.float16, device=dev); gate = torch.empty(N_LAYERS, 1, 1, 6144, device=dev)
+    part = torch.empty(N_LAYERS, 24, 258, device=dev); parts = torch.empty(N_LAYERS, world, 24, 258, device=dev); out = torch.empty(N_LAYERS, 1, 6144, device=dev)
+    big = 1 << 30
+
+    def step(pos, batched):
+        for layer in range(N_LAYERS):
+            ctx.prep(layer, [0], [pos], 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], h0=0, nh=32 if tail else 24, q16=q16[layer], gate=gate[layer])
+            ctx.decode_partial(layer, 0, pos, 1, lo, big if tail else hi, q16[layer], part=part[layer])
+            if not batched:
+                if world > 1:
+                    dist.all_gather_into_tensor(parts[layer], part[layer])
+                else:
+                    parts[layer, 0].copy_(part[layer])
+                ctx.merge_parts(parts[layer], 1, gate[layer, 0], out=out[layer])
+        if batched:   # legal only because the 16 layers of this synthetic harness are independent
+            if world > 1:
+                gathered = torch.empty(world, N_LAYERS, 24, 258, device=dev); dist.all_gather_into_tensor(gathered, part)
+                parts.copy_(gathered.transpose(0, 1))
+            else:
+                parts[:, 0].copy_(part)
+            for layer in range(N_LAYERS):
+                ctx.merge_parts(parts[layer], 1, gate[layer, 0], out=out[layer])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(batched, pos):
+        for i in range(args.warmup):
+            step(pos, batched); pos += 1
+        ctx.check(); barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter(); e0.record()
+        for i in range(args.steps):
+            step(pos, batched); pos += 1
+        e1.record(); barrier(); t1 = time.perf_counter()
+        return e0.elapsed_time(e1), t0, t1
+
+    sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
+    l0 = ctx.launches()
+    ms, tw0, tw1 = timed(False, L)
+    launches = (ctx.launches() - l0) * args.steps // (args.steps + args.warmup)
+    clocks = sampler.stop(tw0, tw1)
+    ms_b, _, _ = timed(True, L)
+    ctx.check(); assert torch.isfinite(out).all()
+    if world > 1:
+        t = torch.tensor([ms, ms_b], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, ms_b = t.tolist()
+    pk = peaks(); bytes_step = N_LAYERS * (L + 1) * 4096.0
+    ach = bytes_step / (ms / args.steps * 1e-3) / 1e9
+    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+           "config": {"workload": f"decode, {N_LAYERS} layers, fp16 KV, ctx {L}, batch 1, keys split over {world} rank(s), NCCL all-gather of (O,m,l) + merge per layer", "global_batch": 1,
+                      "parallelism": f"split-KV x{world}", "tok_s_with_one_batched_all_gather_for_16_layers": args.steps / (ms_b * 1e-3), "l2": "inputs larger than L2"},
+           "clocks": clocks, "gpu_launches": int(launches), "e2e": {"value": None, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "not measured for this workload"},
+           "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": ach, "peak": pk["hbm_gbs"] * world, "unit": "GB/s", "frac": ach / (pk["hbm_gbs"] * world), "peak_src": pk["src"], "traffic": None}}
+    ctx.close()
+    return res
+
+
 # ------------------------------------------------------------------------------------------------- the reference arm
 def run_reference(args, kind_cfg):
     """The reference's own CPU implementation of the path: its scalar attention math (k_attn_decode restated in the
@@ -316,6 +405,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if cfg[0] == "decode":
         res = run_decode(args, rank, world, cfg)
+    elif cfg[0] == "splitkv":
+        res = run_splitkv(args, rank, world, cfg)
     else:
         from kata_b200 import bench_prefill
         res = bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler)

@@ -112,6 +112,11 @@ int kata_attn_decode_scalar(kata_attn_ctx* ctx, int32_t layer, int32_t n, const 
 int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t M,
                       const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 
+/* No reference counterpart. Declares that row 0 of sequence seq's planes holds absolute position first_position (default
+ * 0): afterwards every call takes absolute positions and the context maps position p to row p - first_position. Used
+ * when a long sequence is split by keys across GPUs and each rank stores only its slice. */
+int kata_attn_set_position_offset(kata_attn_ctx* ctx, int32_t seq, int32_t first_position);
+
 /* Split-KV across GPUs (no reference counterpart: the reference is single-device). Each rank holds keys
  * [key_lo, key_hi) of sequence seq in ITS context at rows [0, key_hi-key_lo) (row = key - key_lo) and computes, per
  * (token, head), the unnormalised partial of k_attn_dec_split merged over its local splits:

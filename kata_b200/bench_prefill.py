@@ -23,10 +23,10 @@ def run(args, rank, world, cfg, pk, ClockSampler):
     import torch.distributed as dist
     from kata_b200 import capi
 
-    kind, B, kv_mode, total, _ = cfg
+    kind, B, kv_mode, total, prefix = cfg
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev); gen.manual_seed(99 + rank)
-    restore = 3600 if kind == "chunked" else 0
+    restore = prefix if kind == "chunked" else 0
     chunks, p = [], restore
     while p < total:
         m = min(512, total - p); chunks.append((p, m)); p += m
@@ -128,7 +128,7 @@ def run(args, rank, world, cfg, pk, ClockSampler):
     toks = sum(m for _, m in chunks)
     ach = flops_launch / (kern_ms * 1e-3) / 1e12
     h2d = N_LAYERS * B * toks * (12288 + 2048) * 2; d2h = N_LAYERS * B * toks * 6144 * 4
-    name = "pp512" if kind == "prefill" else f"chunked prefill 3600->{total} in 512-token chunks after a plane restore at 3600, then a T=2 verify"
+    name = "pp512" if kind == "prefill" else f"chunked prefill {restore}->{total} in 512-token chunks after a plane restore at {restore}, then a T=2 verify"
     res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * B * toks * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
            "config": {"workload": f"{name}; {N_LAYERS} layers, {kv_mode} KV, bf16 projections, batch {B}/GPU, prep+prefill per layer", "batch_per_gpu": B, "global_batch": world * B,

@@ -24,7 +24,7 @@ EXPORTS = [
     "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
-    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset",
 ]
 
 
@@ -114,6 +114,9 @@ class AttnContext:
 
     def check(self):
         self._ck(self.L.kata_attn_check(self.h, _stream()))
+
+    def set_position_offset(self, seq: int, first_position: int):
+        self._ck(self.L.kata_attn_set_position_offset(self.h, seq, first_position))
 
     def launches(self) -> int:
         return int(self.L.kata_attn_launch_count(self.h))

@@ -38,15 +38,16 @@ struct DeviceGuard {
 };
 
 // validates (layer, sequence ids, positions) and fills the descriptor; rows [pos, pos+span) must exist for every sequence
-int make_batch(Ctx& c, int layer, int n, const int32_t* seq_ids, const int32_t* pos, int span, kata::Batch& b) {
+int make_batch(Ctx& c, int layer, int n, const int32_t* seq_ids, const int32_t* pos, int span, kata::Batch& b, bool touches_cache = true) {
     if (layer < 0 || layer >= c.cfg.n_layers) return fail(c, KATA_ERR_RANGE, "layer %d outside [0,%d)", layer, c.cfg.n_layers);
     if (n < 1 || n > KATA_MAX_BATCH || !seq_ids || !pos) return fail(c, KATA_ERR_ARG, "batch of %d sequences (1..%d) needs seq_ids and positions", n, KATA_MAX_BATCH);
     b.n = n;
     for (int i = 0; i < n; i++) {
         const int s = seq_ids[i];
         if (s < 0 || s >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "sequence id %d outside [0,%d)", s, c.cfg.n_seqs);
-        if (pos[i] < 0 || (int64_t)pos[i] + span > c.max_ctx[s]) return fail(c, KATA_ERR_RANGE, "positions [%d,%d) of sequence %d exceed max_ctx %d", pos[i], pos[i] + span, s, c.max_ctx[s]);
-        b.pos[i] = pos[i]; b.row_base[i] = c.row_of(layer, s);
+        const int64_t local = (int64_t)pos[i] - c.pos_off[s];
+        if (pos[i] < 0 || (touches_cache && (local < 0 || local + span > c.max_ctx[s]))) return fail(c, KATA_ERR_RANGE, "positions [%d,%d) of sequence %d fall outside its %d rows starting at position %d", pos[i], pos[i] + span, s, c.max_ctx[s], c.pos_off[s]);
+        b.pos[i] = pos[i]; b.row_base[i] = c.row_of(layer, s) - c.pos_off[s];
     }
     return KATA_OK;
 }
@@ -82,7 +83,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     int64_t rows = 0;
     for (int s = 0; s < cfg->n_seqs; s++) {
         if (cfg->max_ctx[s] < 1) { delete h; return KATA_ERR_ARG; }
-        c.max_ctx.push_back(cfg->max_ctx[s]); c.seq_row0.push_back(rows); rows += (int64_t)cfg->n_layers * cfg->max_ctx[s];
+        c.max_ctx.push_back(cfg->max_ctx[s]); c.pos_off.push_back(0); c.seq_row0.push_back(rows); rows += (int64_t)cfg->n_layers * cfg->max_ctx[s];
     }
     c.total_rows = rows;
     c.max_items = kata::decode_max_slots(c.sm_count * 8);
@@ -149,7 +150,7 @@ int kata_attn_prep(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* se
     if (act_dtype != KATA_ACT_F32 && act_dtype != KATA_ACT_BF16) return fail(c, KATA_ERR_ARG, "unknown activation dtype %d", act_dtype);
     const bool hasQ = h0 < 24, hasK = h0 < 28 && h0 + nh > 24, hasV = h0 + nh > 28;
     if ((hasQ && (!d_qfull || !d_qnorm)) || (hasK && (!d_kproj || !d_knorm)) || (hasV && !d_vproj)) return fail(c, KATA_ERR_ARG, "a projection or norm weight needed by head slots [%d,%d) is null", h0, h0 + nh);
-    kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos0, T, b)) return rc;
+    kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos0, T, b, /*touches_cache=*/h0 + nh > 24)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_prep(c, b, T, d_qfull, d_kproj, d_vproj, act_dtype, d_qnorm, d_knorm, (__half*)d_q16, d_q32, d_gate, h0, nh, (cudaStream_t)stream);
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "prep launch");
@@ -215,9 +216,9 @@ int kata_attn_decode_partial(kata_attn_ctx* h, int32_t layer, int32_t seq, int32
     if (!d_q16 || !d_part) return fail(c, KATA_ERR_ARG, "decode_partial needs q16 and part");
     if (key_lo < 0 || key_hi < key_lo || pos_base < 0) return fail(c, KATA_ERR_RANGE, "key range [%d,%d) / pos_base %d", key_lo, key_hi, pos_base);
     const int32_t local_rows = std::max(0, std::min(pos_base + T, key_hi) - key_lo);   // rows [0, local_rows) of this context hold keys key_lo..
-    const int32_t zero = 0;
-    kata::Batch b; if (int rc = make_batch(c, layer, 1, &seq, &zero, std::max(local_rows, 1), b)) return rc;
-    b.pos[0] = pos_base;
+    if (layer < 0 || layer >= c.cfg.n_layers || seq < 0 || seq >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "layer %d / sequence %d out of range", layer, seq);
+    if (local_rows > c.max_ctx[seq]) return fail(c, KATA_ERR_RANGE, "%d local rows exceed max_ctx %d", local_rows, c.max_ctx[seq]);
+    kata::Batch b; b.n = 1; b.pos[0] = pos_base; b.row_base[0] = c.row_of(layer, seq);
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_decode_mma_ex(c, b, T, 0, key_lo, &local_rows, (const __half*)d_q16, nullptr, nullptr, KATA_ACT_F32, d_part, (cudaStream_t)stream);
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "decode_partial launch");
@@ -230,6 +231,14 @@ int kata_attn_merge_parts(kata_attn_ctx* h, const float* d_parts, int32_t n_part
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_merge_parts(c, d_parts, n_parts, T, d_gate, d_out, out_dtype, (cudaStream_t)stream);
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "merge_parts launch");
+}
+
+int kata_attn_set_position_offset(kata_attn_ctx* h, int32_t seq, int32_t first_position) {
+    if (!h) return KATA_ERR_ARG;
+    Ctx& c = h->c;
+    if (seq < 0 || seq >= c.cfg.n_seqs || first_position < 0) return fail(c, KATA_ERR_RANGE, "sequence %d / first position %d", seq, first_position);
+    c.pos_off[seq] = first_position;
+    return KATA_OK;
 }
 
 int32_t kata_attn_kv_planes(const kata_attn_ctx* h) { return h ? (h->c.cfg.kv_mode == KATA_KV_INT8 ? 4 : 2) : 0; }

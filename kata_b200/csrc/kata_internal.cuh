@@ -32,6 +32,7 @@ struct Batch {
 struct Ctx {
     kata_attn_config cfg{};
     std::vector<int32_t> max_ctx;
+    std::vector<int32_t> pos_off;      // absolute position held by row 0 of each sequence (0 unless the sequence is a key slice)
     std::vector<int64_t> seq_row0;     // arena row of (sequence, layer 0, position 0)
     int64_t total_rows = 0;
     int elt = 2;                        // bytes per cached K/V element
