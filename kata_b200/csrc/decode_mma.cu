@@ -50,6 +50,7 @@ template <bool I8> struct Geo {
 
 struct DecPlan {
     int32_t n, T, first_row, key_off, n_ctas, q_tiles, r_tiles;   // CTA c owns tiles [c*q + min(c,r), (c+1)*q + min(c+1,r))
+    int32_t merge_in_kernel;             // 1: the last contributor of a segment merges its partials; 0: decode_combine_kernel does
     int32_t pos[KATA_MAX_BATCH];         // absolute position of token 0
     int32_t kend[KATA_MAX_BATCH];        // local rows [first_row, kend) hold this call's keys; absolute key = key_off + row
     int64_t row_base[KATA_MAX_BATCH];
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
     const uint32_t merge_bar = sm_base + kOffBars + 2 * kRings * kStages * 8; uint32_t merge_phase = 0;
 
     if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 2); } }
-    if (tid == 0) mbar_init(merge_bar, 1);
+    if (tid == 0) { mbar_init(merge_bar, 1); mbar_init(merge_bar + 8, 1); }
     fence_mbar_init();
     __syncthreads();
 
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             if (whole) emit(r, M, L, A0, A1);
             else { *reinterpret_cast<float2*>(slot_o + r * kD + d0) = make_float2(A0, A1); if ((tid & 127) == 0) { slot_ml[r * 2] = M; slot_ml[r * 2 + 1] = L; } }
         }
-        if (!whole) {   // ticket: the last contributor of the segment merges everybody's partials
+        if (!whole && p.merge_in_kernel) {   // ticket: the last contributor of the segment merges everybody's partials
             __threadfence();
             __syncthreads();
             if (tid == 0) { const int old = atomicAdd(&counters[seg], 1); s_flag = (old == n_contrib - 1); }
@@ -209,28 +210,45 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 const int wl_bytes = (n_contrib * rows * 8 + 127) & ~127;
                 for (int i = tid; i < n_contrib * rows * 2; i += kThreads) { const int c = i / (rows * 2), k = i - c * (rows * 2); wl[i] = __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + k); }
                 __syncthreads();
-                if (tid < rows) {
-                    float M = -INFINITY; for (int c = 0; c < n_contrib; c++) M = fmaxf(M, wl[(c * rows + tid) * 2]);
+                {   // per row: maximum, weights exp(m - M) and the merged l; 16 threads share a row
+                    const int r = tid >> 4, sub = tid & 15; const bool live = r < rows;
+                    float M = -INFINITY;
+                    if (live) for (int c = sub; c < n_contrib; c += 16) M = fmaxf(M, wl[(c * rows + r) * 2]);
+#pragma unroll
+                    for (int off = 8; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
                     float L = 0.0f;
-                    for (int c = 0; c < n_contrib; c++) { const float mm = wl[(c * rows + tid) * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M); L += wl[(c * rows + tid) * 2 + 1] * wt; wl[(c * rows + tid) * 2] = wt; }
-                    s_ML[tid * 2] = M; s_ML[tid * 2 + 1] = L;
+                    if (live) for (int c = sub; c < n_contrib; c += 16) { const float mm = wl[(c * rows + r) * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M); L += wl[(c * rows + r) * 2 + 1] * wt; wl[(c * rows + r) * 2] = wt; }
+#pragma unroll
+                    for (int off = 8; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+                    if (live && sub == 0) { s_ML[r * 2] = M; s_ML[r * 2 + 1] = L; }
                 }
                 __syncthreads();
-                const uint32_t obuf = sm_base + stage_off + wl_bytes; const int cap = (kRings * G::kRingBytes - wl_bytes) / (rows * 1024);
+                // O rows: two half-buffers, the copies of the next group of contributors fly while this group is accumulated
+                const int per = rows * 1024, cap = ((kRings * G::kRingBytes - wl_bytes) / 2) / per, n_groups = (n_contrib + cap - 1) / cap;
+                const uint32_t obuf = sm_base + stage_off + wl_bytes; const uint32_t half_bytes = (uint32_t)(cap * per);
+                auto issue_group = [&](int k) {
+                    const int base = k * cap, cnt = min(cap, n_contrib - base); const uint32_t mb = merge_bar + 8u * (uint32_t)(k & 1);
+                    if (tid < 32) {
+                        if (tid == 0) mbar_arrive_expect_tx(mb, (uint32_t)(cnt * per));
+                        __syncwarp();
+                        for (int c = tid; c < cnt; c += 32) bulk_g2s(obuf + (k & 1) * half_bytes + c * per, scratch_o + (int64_t)(c_first + base + c + seg) * (12 * kD), (uint32_t)per, mb);
+                    }
+                };
                 float A[6][2];
 #pragma unroll
                 for (int r = 0; r < 6; r++) { A[r][0] = 0.0f; A[r][1] = 0.0f; }
-                for (int base = 0; base < n_contrib; base += cap) {
-                    const int cnt = min(cap, n_contrib - base);
-                    if (tid == 0) mbar_arrive_expect_tx(merge_bar, (uint32_t)(cnt * rows * 1024));
-                    __syncthreads();
-                    if (tid < 32) for (int c = tid; c < cnt; c += 32) bulk_g2s(obuf + c * rows * 1024, scratch_o + (int64_t)(c_first + base + c + seg) * (12 * kD), (uint32_t)(rows * 1024), merge_bar);
-                    if (!mbar_wait_bounded(merge_bar, merge_phase, err)) { atomicExch(err, 2); }
-                    merge_phase ^= 1u;
+                issue_group(0);
+                for (int k = 0; k < n_groups; k++) {
+                    if (k + 1 < n_groups) issue_group(k + 1);
+                    if (!mbar_wait_bounded(merge_bar + 8u * (uint32_t)(k & 1), (merge_phase >> (k & 1)) & 1u, err)) { atomicExch(err, 2); }
+                    merge_phase ^= 1u << (k & 1);
+                    const int base = k * cap, cnt = min(cap, n_contrib - base);
+                    const uint8_t* ob = smem + stage_off + wl_bytes + (k & 1) * half_bytes + d0 * 4;
+#pragma unroll 4
                     for (int c = 0; c < cnt; c++) {
 #pragma unroll
                         for (int rr = 0; rr < 6; rr++) { const int r = 2 * rr + rsel; if (r < rows) {
-                            const float wt = wl[((base + c) * rows + r) * 2]; const float2 v = *reinterpret_cast<const float2*>(smem + stage_off + wl_bytes + (c * rows + r) * 1024 + d0 * 4);
+                            const float wt = wl[((base + c) * rows + r) * 2]; const float2 v = *reinterpret_cast<const float2*>(ob + (c * rows + r) * 1024);
                             A[rr][0] += wt * v.x; A[rr][1] += wt * v.y; } }
                     }
                     __syncthreads();
@@ -242,6 +260,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         }
         __syncthreads();   // merge buffers and the Q block are reused by the next segment
         tile = my_end;
+    }
+}
+
+// Merge of the per-CTA partials of every split segment, one CTA per (row, segment), thread = head dimension. Used instead of
+// the in-kernel ticket merge when a segment has many contributors (batch 1 at long context: ~37 per KV head): a single
+// last-arriver CTA then needs ~15 us to pull 220 KB of partials through one SM, while this grid does it in parallel.
+__global__ void __launch_bounds__(256) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, float* __restrict__ part_out,
+                                                             const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml) {
+    const int r = blockIdx.x, seg = blockIdx.y, b = seg >> 2, kvh = seg & 3, tid = threadIdx.x;
+    const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvh * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1);
+    if (c_last == c_first) return;   // a single contributor wrote the final row itself
+    float M = -INFINITY;
+    for (int c = c_first; c <= c_last; c++) M = fmaxf(M, scratch_ml[(int64_t)(c + seg) * 32 + r * 2]);
+    float L = 0.0f, A = 0.0f;
+#pragma unroll 4
+    for (int c = c_first; c <= c_last; c++) {
+        const float mm = scratch_ml[(int64_t)(c + seg) * 32 + r * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
+        L += scratch_ml[(int64_t)(c + seg) * 32 + r * 2 + 1] * wt; A += scratch_o[(int64_t)(c + seg) * (12 * kD) + r * kD + tid] * wt;
+    }
+    const int T = p.T, t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
+    if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[tid] = A; if (tid == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
+    else {
+        const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + tid; const float y = (A / L) * sigmoid_fast(gate[oi]);
+        if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
     }
 }
 
@@ -276,6 +318,12 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     n_ctas = std::max(1, std::min(std::min(n_ctas, total), c.sm_count * 8));
     if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
+    int max_contrib = 1;   // contributors of the most-split segment decide where the merge runs
+    {
+        auto cta_of = [&](int tile) { const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
+        for (int i = 0; i < b.n; i++) for (int kv = 0; kv < 4; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; max_contrib = std::max(max_contrib, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
+    }
+    p.merge_in_kernel = max_contrib <= 8;
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
     if (!attr_set[i8]) {
         cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
@@ -286,6 +334,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(c.tm_k, c.tm_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(c.tm_k, c.tm_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     c.launches++;
+    if (!p.merge_in_kernel) { decode_combine_kernel<<<dim3(6 * T, 4 * b.n), 256, 0, s>>>(p, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.part_o, c.part_ml); c.launches++; }
     return cudaGetLastError();
 }
 
@@ -363,7 +412,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     }
     for (int i = n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
     const int n_ctas = std::max(1, std::min(std::min(sd.sm_count, kStaticMaxCtas), total));
-    p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
+    p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas; p.merge_in_kernel = 1;
     CUtensorMap tm_k, tm_v;   // encoded on the host; no device memory involved
     if (!make_arena_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 64, 16, true) || !make_arena_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 64, 16, true)) return KATA_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
