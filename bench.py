@@ -169,12 +169,14 @@ def run_decode(args, rank, world, kind_cfg):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     tw0 = time.perf_counter()
+    torch.cuda.profiler.start()   # lets `ncu --profile-from-start off` capture exactly the timed steps; a no-op otherwise
     e0.record()
     pos_timed0 = pos.copy()
     for _ in range(args.steps):
         step(pos); pos = pos + 1
     e1.record()
     barrier()
+    torch.cuda.profiler.stop()
     tw1 = time.perf_counter()
     ms = e0.elapsed_time(e1)
     launches = ctx.launches() - l0
@@ -358,6 +360,7 @@ def run_reference(args, kind_cfg):
     from oracle import kata_oracle as orc
     from kata_b200 import synth
     _, B, kv_mode, lmax, lmin = kind_cfg
+    B = B * max(1, args.gpus)   # the same global batch as the CUDA arm at this GPU count (weak scaling)
     lens = synth.seq_lengths(1234, B, lmin, lmax)
     rng = np.random.default_rng(99)
     ks = [rng.standard_normal((int(l) + 1, 1024), dtype=np.float32).astype(np.float16).view(np.uint16) for l in lens]

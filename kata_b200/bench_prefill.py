@@ -94,10 +94,10 @@ def run(args, rank, world, cfg, pk, ClockSampler):
     ctx.check()
     l0 = ctx.launches(); barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    tw0 = time.perf_counter(); e0.record()
+    tw0 = time.perf_counter(); torch.cuda.profiler.start(); e0.record()
     for _ in range(args.steps):
         step()
-    e1.record(); barrier(); tw1 = time.perf_counter()
+    e1.record(); barrier(); torch.cuda.profiler.stop(); tw1 = time.perf_counter()
     ms = e0.elapsed_time(e1); launches = ctx.launches() - l0
     clocks = sampler.stop(tw0, tw1)
     ctx.check()
