@@ -383,3 +383,55 @@ def test_errors_are_codes_not_faults(capi):
         assert e.value.code == code
     ctx.check()
     assert ctx.tag() == "fp16" and ctx.kv_planes() == 2 and ctx.plane_row_bytes(0) == 2048
+
+
+# ------------------------------------------------------------------------------------------------ benchmark sizes
+def test_full_size_decode_32k_properties(capi, orc):
+    # one layer at the benchmark's context length: against the fp32 formula, and the size-independent properties the
+    # reference relies on (matrix path == scalar path, T=2 verify == two T=1 decodes, result independent of the split)
+    L = 32768
+    gen = torch.Generator(device="cuda"); gen.manual_seed(5)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    ctxs = [capi.AttnContext(1, [L + 8], dec_chunk=c) for c in (0, 2048)]
+    for st in range(0, L, 1024):
+        kp = torch.randn(1, 1024, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 1024, 1024, generator=gen, device="cuda")
+        for c in ctxs:
+            c.prep(0, [0], [st], 1024, None, kp, vp, None, kn, h0=24, nh=8)
+    qf = torch.randn(1, 2, 12288, generator=gen, device="cuda"); kp = torch.randn(1, 2, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 2, 1024, generator=gen, device="cuda")
+    outs = []
+    for c in ctxs:
+        q16, q32, g = c.prep(0, [0], [L - 2], 2, qf, kp, vp, qn, kn, want_q32=True)
+        outs.append(c.decode(0, [0], [L - 2], 2, q16, g))
+        c.check()
+    c = ctxs[0]
+    sc = c.decode_scalar(0, [0], [L - 2], 2, q32, g)
+    d0 = c.decode(0, [0], [L - 2], 1, q16[:, :1].contiguous(), g[:, :1].contiguous()); d1 = c.decode(0, [0], [L - 1], 1, q16[:, 1:].contiguous(), g[:, 1:].contiguous())
+    c.check()
+    a = outs[0].cpu().numpy()[0]
+    assert np.abs(a - outs[1].cpu().numpy()[0]).max() < 2e-5                       # split invariance
+    assert np.abs(a[0] - d0.cpu().numpy()[0, 0]).max() < 2e-5 and np.abs(a[1] - d1.cpu().numpy()[0, 0]).max() < 2e-5
+    _close(a, sc.cpu().numpy()[0])                                                  # matrix path vs scalar path
+    planes = orc.KvPlanes(L)
+    planes.k[:] = c.plane_read(0, 0, 0, 0, L).view(np.uint16).reshape(L, 1024); planes.v[:] = c.plane_read(0, 0, 1, 0, L).view(np.uint16).reshape(L, 1024)
+    _close(a, orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2))
+
+
+def test_full_size_prefill_chunk_over_7k_prefix(capi, orc):
+    # the last full chunk of the 7,300-token prompt: 512 rows at position 6,672, tcgen05 kernel vs the fp32 formula (sampled rows)
+    pb, M = 6672, 512
+    gen = torch.Generator(device="cuda"); gen.manual_seed(6)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    ctx = capi.AttnContext(1, [pb + M])
+    for st in range(0, pb, 1024):
+        m = min(1024, pb - st)
+        ctx.prep(0, [0], [st], m, None, torch.randn(1, m, 1024, generator=gen, device="cuda"), torch.randn(1, m, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    qf = torch.randn(1, M, 12288, generator=gen, device="cuda").to(torch.bfloat16); kp = torch.randn(1, M, 1024, generator=gen, device="cuda").to(torch.bfloat16); vp = torch.randn(1, M, 1024, generator=gen, device="cuda").to(torch.bfloat16)
+    q16, q32, g = ctx.prep(0, [0], [pb], M, qf, kp, vp, qn, kn, want_q32=True)
+    out = ctx.prefill(0, [0], [pb], M, q16, g).cpu().numpy()[0]
+    ctx.check()
+    planes = orc.KvPlanes(pb + M)
+    planes.k[:] = ctx.plane_read(0, 0, 0, 0, pb + M).view(np.uint16).reshape(-1, 1024); planes.v[:] = ctx.plane_read(0, 0, 1, 0, pb + M).view(np.uint16).reshape(-1, 1024)
+    rows = [0, 1, 127, 128, 300, 511]
+    for r in rows:
+        ref = orc.formula_f32(q32.cpu().numpy()[0, r:r + 1], g.cpu().numpy()[0, r:r + 1], planes, pb + r)
+        _close(out[r:r + 1], ref)
