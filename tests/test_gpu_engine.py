@@ -81,3 +81,37 @@ def test_split_kv_across_gpus_nccl(orc):
     assert all(p.exitcode == 0 for p in procs)
     d = np.abs(out - ref)
     assert d.max() < 2e-3 and d.mean() < 2e-4
+
+
+@pytest.mark.parametrize("mode", ["fp16", "int8"])
+def test_checkpoint_kv_segments_round_trip(tmp_path, mode):
+    # save the KV segments of a prefilled context, restore them into a fresh one: planes identical (the reference's
+    # test_cache.sh identity checks), another numerics mode refuses the file, a truncated file is refused and leaves zeros
+    from kata_b200 import capi
+    L = capi.lib()
+    n, n_attn = 333, 3
+    gen = torch.Generator(device="cuda"); gen.manual_seed(9)
+    kn = torch.ones(256, device="cuda")
+    a = capi.AttnContext(n_attn, [400], kv_mode=mode); m = capi.AttnContext(1, [400])
+    for layer in range(n_attn):
+        a.prep(layer, [0], [0], n, None, torch.randn(1, n, 1024, generator=gen, device="cuda"), torch.randn(1, n, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    m.prep(0, [0], [0], n, None, torch.randn(1, n, 1024, generator=gen, device="cuda"), torch.randn(1, n, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    a.check(); m.check()
+    toks = np.arange(1000, 1000 + n + 20, dtype=np.int32); tp = toks.ctypes.data_as(C.c_void_p)
+    path = str(tmp_path / "p.ckpt").encode()
+    args = (C.c_uint64(42), n_attn, C.c_uint64(4096), C.c_uint64(8192))
+    assert L.kata_ckpt_write_kv(a.h, m.h, 0, path, tp, n, *args, 5) == 0
+    b = capi.AttnContext(n_attn, [400], kv_mode=mode); mb = capi.AttnContext(1, [400]); got = C.c_uint32()
+    assert L.kata_ckpt_read_kv(b.h, mb.h, 0, path, tp, len(toks), *args, C.byref(got)) == 0 and got.value == n
+    for layer in range(n_attn):
+        for pl in range(a.kv_planes()):
+            assert np.array_equal(a.plane_read(layer, 0, pl, 0, 400), b.plane_read(layer, 0, pl, 0, 400))
+    for pl in range(2):
+        assert np.array_equal(m.plane_read(0, 0, pl, 0, 400), mb.plane_read(0, 0, pl, 0, 400))
+    other = capi.AttnContext(n_attn, [400], kv_mode="int8" if mode == "fp16" else "fp16")
+    assert L.kata_ckpt_read_kv(other.h, None, 0, path, tp, len(toks), *args, C.byref(got)) == 2
+    with open(path, "r+b") as f:
+        f.truncate(os.path.getsize(path) - 4096)
+    c = capi.AttnContext(n_attn, [400], kv_mode=mode)
+    assert L.kata_ckpt_read_kv(c.h, None, 0, path, tp, len(toks), *args, C.byref(got)) == 2
+    assert (c.plane_read(0, 0, 0, 0, 400) == 0).all()
