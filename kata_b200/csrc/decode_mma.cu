@@ -33,7 +33,8 @@ using namespace ptx;
 
 constexpr int kRings = 4, kWarps = 2 * kRings, kThreads = kWarps * 32, kStages = 3, kTile = 16;
 constexpr int kOffBars = 16 * kQStride;             // 8448: per ring and stage a 'full' and an 'empty' barrier, then the merge barrier
-constexpr int kOffMl = kOffBars + 256;              // per-ring (m, l0, l1) exchange: [4][16][3] floats = 768 B
+constexpr int kOffQsum = kOffBars + 256;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
+constexpr int kOffMl = kOffQsum + 64;               // per-ring (m, l0, l1) exchange: [4][16][3] floats = 768 B
 constexpr int kOffPair = kOffMl + 768;              // per-ring pair exchange: max [2][16] floats (128 B) + P block 16 x 48 B
 constexpr int kPairBytes = 128 + 16 * kPStride;     // 896
 constexpr int kOffStages = kOffPair + kRings * kPairBytes;   // the stage area itself starts at the next 1024-byte boundary of the shared window (found at run time)
@@ -123,6 +124,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             stage_q_chunk<I8>(smem + r * kQStride, c16, v);
         }
         __syncthreads();
+        if (I8) {   // row sums of the staged Q block (any column order): warp w sums rows 2w and 2w+1
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                const int r = 2 * w + rr; const uint4 v = *reinterpret_cast<const uint4*>(smem + r * kQStride + lane * 16); const __half2* hp = reinterpret_cast<const __half2*>(&v);
+                float a = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 4; e++) { const float2 f = __half22float2(hp[e]); a += f.x + f.y; }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+                if (lane == 0) reinterpret_cast<float*>(smem + kOffQsum)[r] = a;
+            }
+            __syncthreads();
+        }
+        const float qs_[2] = {I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g] : 0.0f, I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g + 8] : 0.0f};
 
         for (int i = 0; i < n_mine; i++) {
             const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u;
@@ -148,7 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                     *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (rem >> 3) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            pair_tile<I8>(q_base, kt, vt, maxbuf, p_sm, 1 + ring, h, key0, lim_row0, lim_row1, ks_, vs_, st, lane, [] {});
+            pair_tile<I8>(q_base, kt, vt, maxbuf, p_sm, 1 + ring, h, key0, lim_row0, lim_row1, ks_, vs_, qs_, st, lane, [] {});
             __syncwarp();
             if (lane == 0) mbar_arrive(ebars + stg * 8);
         }
@@ -156,6 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 
         // ---- merge the 4 rings of the CTA (every issued tile was waited for, so no copy is in flight)
         st.finish_l();
+        if (I8) st.finish_bias(kI8Bias);
         __syncthreads();
         float* mo = reinterpret_cast<float*>(smem + stage_off + ring * G::kRingBytes);
 #pragma unroll
