@@ -31,12 +31,13 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kRings = 4, kWarps = 2 * kRings, kThreads = kWarps * 32, kStages = 3, kTile = 16;
+constexpr int kRings = 4, kWarps = 2 * kRings, kThreads = kWarps * 32, kMaxStages = 8, kTile = 16;
 constexpr int kOffBars = 16 * kQStride;             // 8448: per ring and stage a 'full' and an 'empty' barrier, then the merge barrier
-constexpr int kOffQsum = kOffBars + 256;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
-constexpr int kOffMl = kOffQsum + 64;               // per-ring (m, l0, l1) exchange: [4][16][3] floats = 768 B
-constexpr int kOffPair = kOffMl + 768;              // per-ring pair exchange: max [2][16] floats (128 B) + P block 16 x 48 B
-constexpr int kPairBytes = 128 + 16 * kPStride;     // 896
+constexpr int kOffEBars = kRings * kMaxStages * 8, kOffMBar = 2 * kOffEBars, kOffPBars = kOffMBar + 16;                      // inside the barrier block: per ring two 'P full' and two 'P empty' barriers
+constexpr int kOffQsum = kOffBars + 704;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
+constexpr int kOffMl = kOffQsum + 64;               // per-ring (m, l) exchange: [4][16][2] floats = 512 B
+constexpr int kOffPair = kOffMl + 512;              // per-ring hand-over from the score warp to the value warp: two slots of (P block 16 x 48 B, 16 rescale factors)
+constexpr int kPairBytes = 2 * kPSlotBytes;         // 1664
 constexpr int kOffStages = kOffPair + kRings * kPairBytes;   // the stage area itself starts at the next 1024-byte boundary of the shared window (found at run time)
 constexpr int kMergeStride = 264;                   // floats per row of the cross-ring merge buffer
 
@@ -45,6 +46,7 @@ template <bool I8> struct Geo {
     static constexpr int kBoxes = kRowBytes / 128;               // 128-byte column boxes per K or V tile
     static constexpr int kTileBytes = kTile * kRowBytes;          // boxes of [16 rows][128 bytes], 128-byte swizzle, no padding
     static constexpr int kStageBytes = 2 * kTileBytes;
+    static constexpr int kStages = I8 ? 6 : 3;                    // tiles in flight per ring: 48 KB either way
     static constexpr int kRingBytes = (kStages * kStageBytes > 16 * kMergeStride * 4) ? kStages * kStageBytes : 16 * kMergeStride * 4;
     static constexpr int kSmem = kOffStages + 1024 + kRings * kRingBytes;   // 1024 bytes of slack for the run-time alignment
 };
@@ -70,18 +72,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
-    using G = Geo<I8>;
+    using G = Geo<I8>; constexpr int kStages = G::kStages;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring and ring+4 sit on the same scheduler
     const uint32_t sm_base = smem_u32(smem);
-    const uint32_t q_base = sm_base, bars = sm_base + kOffBars + ring * kStages * 8, ebars = sm_base + kOffBars + (kRings + ring) * kStages * 8, stage_off = ((sm_base + kOffStages + 1023u) & ~1023u) - sm_base, ring_stage0 = sm_base + stage_off + ring * G::kRingBytes;   // swizzled TMA boxes want 1024-byte alignment
+    const uint32_t q_base = sm_base, bars = sm_base + kOffBars + ring * kMaxStages * 8, ebars = sm_base + kOffBars + kOffEBars + ring * kMaxStages * 8, stage_off = ((sm_base + kOffStages + 1023u) & ~1023u) - sm_base, ring_stage0 = sm_base + stage_off + ring * G::kRingBytes;   // swizzled TMA boxes want 1024-byte alignment
     float* sm_ml = reinterpret_cast<float*>(smem + kOffMl);
-    float* maxbuf = reinterpret_cast<float*>(smem + kOffPair + ring * kPairBytes);
-    const uint32_t p_sm = sm_base + kOffPair + ring * kPairBytes + 128;
+    const uint32_t p_sm = sm_base + kOffPair + ring * kPairBytes;
+    const uint32_t pfull = sm_base + kOffBars + kOffPBars + ring * 16, pempty = pfull + kRings * 16;
     __shared__ int s_flag; __shared__ float s_ML[24];
-    const uint32_t merge_bar = sm_base + kOffBars + 2 * kRings * kStages * 8; uint32_t merge_phase = 0;
+    const uint32_t merge_bar = sm_base + kOffBars + kOffMBar; uint32_t merge_phase = 0;
 
-    if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 2); } }
+    if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 2); } for (int s = 0; s < 2; s++) { mbar_init(pfull + s * 8, 1); mbar_init(pempty + s * 8, 1); } }
     if (tid == 0) { mbar_init(merge_bar, 1); mbar_init(merge_bar + 8, 1); }
     fence_mbar_init();
     __syncthreads();
@@ -98,13 +100,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 
         // ---- this ring's tiles of the segment: local tiles lt0 + ring, lt0 + ring + 4, ...
         const int n_mine = n_here > ring ? (n_here - ring + kRings - 1) / kRings : 0;
-        PairState st; st.clear();
+        ScoreState ss;                 // softmax state, kept by the ring's score warp (h == 0)
+        ValueState vst; vst.clear();   // the 16 x 256 O block, kept by the ring's value warp (h == 1)
         const int lim_row0 = (g < 6 * T) ? min(kend, pos_rel + (g >= 6 ? 1 : 0) + 1) : 0;          // rows g and g+8: exclusive local key limit
         const int lim_row1 = (g + 8 < 6 * T) ? min(kend, pos_rel + 2) : 0;                          // rows 8..11 belong to token 1
 
         const uint32_t it_seg = it;
         const int row0 = (int)p.row_base[b];   // arena row of position 0 (row coordinates of the tensor maps are 32-bit)
-        auto issue = [&](int i) {   // warp h=0 of the ring brings in the ring's i-th tile: one TMA box per 128-byte column block of K and of V
+        auto issue = [&](int i) {   // the value warp of the ring brings in the ring's i-th tile: one TMA box per 128-byte column block of K and of V
             const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
             const uint32_t sx = (it_seg + (uint32_t)i) % kStages, dst = ring_stage0 + sx * G::kStageBytes, bar = bars + sx * 8;
             fence_proxy_async();
@@ -116,7 +119,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             }
         };
 
-        if (h == 0) for (int i = 0; i < min(kStages, n_mine); i++) issue(i);   // every stage is free here; the first tiles fly while Q is staged
+        if (h == 1) for (int i = 0; i < min(kStages, n_mine); i++) issue(i);   // every stage is free here; the first tiles fly while Q is staged
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
@@ -139,48 +142,84 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         }
         const float qs_[2] = {I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g] : 0.0f, I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g + 8] : 0.0f};
 
-        for (int i = 0; i < n_mine; i++) {
-            const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u;
-            const uint32_t kt = ring_stage0 + stg * G::kStageBytes, vt = kt + G::kTileBytes;
-            const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-            float ks_[2] = {1.f, 1.f}, vs_[2] = {1.f, 1.f};
-            if (I8) {   // per-key scales of this thread's two score columns (keys key0 + 8h + 2*t4 + e)
+        if (h == 0) {
+            // ---- score warp: S = Q K^T, online softmax, P and the rescale factors handed to the value warp; runs up to two tiles ahead
+            // int8: per-key scales of this thread's four score columns, fetched two tiles ahead and kept as raw fp16 bits so that
+            // nothing depends on the loads until the tile they belong to (a scale plane row is first touched here: DRAM latency)
+            unsigned short sA[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sB[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            auto load_scales = [&](int i, unsigned short (&dst)[8]) {
+                const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
 #pragma unroll
-                for (int e = 0; e < 2; e++) { const int key = min(key0 + 8 * h + 2 * t4 + e, max(kend - 1, 0)); ks_[e] = __half2float(ksc[(p.row_base[b] + key) * 4 + kvh]); vs_[e] = __half2float(vsc[(p.row_base[b] + key) * 4 + kvh]); }
+                for (int q = 0; q < 4; q++) {
+                    const int64_t idx = (p.row_base[b] + min(k0 + 8 * (q >> 1) + 2 * t4 + (q & 1), max(kend - 1, 0))) * 4 + kvh;
+                    dst[q] = __ldg(reinterpret_cast<const unsigned short*>(ksc) + idx); dst[4 + q] = __ldg(reinterpret_cast<const unsigned short*>(vsc) + idx);
+                }
+            };
+            if (I8 && n_mine > 0) load_scales(0, sA);
+            if (I8 && n_mine > 1) load_scales(1, sB);
+            for (int i = 0; i < n_mine; i++) {
+                const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
+                const uint32_t kt = ring_stage0 + stg * G::kStageBytes;
+                const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+                unsigned short sC[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) { sC[q] = sA[q]; sA[q] = sB[q]; }
+                if (I8 && i + 2 < n_mine) load_scales(i + 2, sB);
+                // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and every arrival) stays intact.
+                if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
+                float ks_[2][2] = {{1.f, 1.f}, {1.f, 1.f}}, vs_[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
+                if (I8) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) { ks_[q >> 1][q & 1] = __half2float(__ushort_as_half(sC[q])); vs_[q >> 1][q & 1] = __half2float(__ushort_as_half(sC[4 + q])); }
+                }
+                float pr[2][4], al0, al1;
+                score_tile<I8>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ebars + stg * 8);   // K of this stage is no longer needed
+                if (cur >= 2 && !dead && !mbar_wait_bounded(pempty + slot * 8, ((cur >> 1) - 1u) & 1u, err)) { dead = true; atomicExch(err, 4); }
+                score_publish(p_sm + slot * kPSlotBytes, reinterpret_cast<float*>(smem + kOffPair + ring * kPairBytes + slot * kPSlotBytes + 16 * kPStride), pr, al0, al1, lane);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pfull + slot * 8);
             }
-            // The stage of tile i-1 is free once both warps of the pair have read it: refill it with tile i+2 right away.
-            if (h == 0 && i >= 1 && i + kStages - 1 < n_mine) {
-                const uint32_t prev = cur - 1;
-                if (!dead && !mbar_wait_bounded(ebars + (prev % kStages) * 8, (prev / kStages) & 1u, err)) { dead = true; atomicExch(err, 3); }
-                issue(i + kStages - 1);
-            }
-            // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and the pair barriers) stay intact.
-            if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
-            if (key0 + kTile > kend && h == 0) {   // tail tile: rows past the range were loaded as they lie in memory; zero those V rows (0 x garbage must stay 0)
-                const int nk = max(0, kend - key0);
-                for (int idx = lane; idx < (kTile - nk) * G::kBoxes * 8; idx += 32) {
-                    const int r = nk + idx / (G::kBoxes * 8), rem = idx % (G::kBoxes * 8);
-                    *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (rem >> 3) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+            ss.l0 += __shfl_xor_sync(0xffffffffu, ss.l0, 1); ss.l0 += __shfl_xor_sync(0xffffffffu, ss.l0, 2);
+            ss.l1 += __shfl_xor_sync(0xffffffffu, ss.l1, 1); ss.l1 += __shfl_xor_sync(0xffffffffu, ss.l1, 2);
+            if (t4 == 0) { sm_ml[(ring * 16 + g) * 2] = ss.m0; sm_ml[(ring * 16 + g) * 2 + 1] = ss.l0; sm_ml[(ring * 16 + g + 8) * 2] = ss.m1; sm_ml[(ring * 16 + g + 8) * 2 + 1] = ss.l1; }
+        } else {
+            // ---- value warp: O = O * alpha + P V; releases the stage and refills it with the tile three ahead
+            for (int i = 0; i < n_mine; i++) {
+                const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
+                const uint32_t vt = ring_stage0 + stg * G::kStageBytes + G::kTileBytes;
+                const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+                if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
+                if (key0 + kTile > kend) {   // tail tile: rows past the range were loaded as they lie in memory; zero those V rows (0 x garbage must stay 0)
+                    const int nk = max(0, kend - key0);
+                    for (int idx = lane; idx < (kTile - nk) * G::kBoxes * 8; idx += 32) {
+                        const int r = nk + idx / (G::kBoxes * 8), rem = idx % (G::kBoxes * 8);
+                        *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (rem >> 3) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
+                if (!dead && !mbar_wait_bounded(pfull + slot * 8, (cur >> 1) & 1u, err)) { dead = true; atomicExch(err, 5); }
+                value_tile<I8>(vt, p_sm + slot * kPSlotBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * kPSlotBytes + 16 * kPStride), vst, lane);
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(pempty + slot * 8); mbar_arrive(ebars + stg * 8); }
+                if (i + kStages < n_mine) {   // the score warp released this stage before it published P: refill it right away
+                    if (!dead && !mbar_wait_bounded(ebars + stg * 8, par, err)) { dead = true; atomicExch(err, 3); }
+                    issue(i + kStages);
                 }
             }
-            pair_tile<I8>(q_base, kt, vt, maxbuf, p_sm, 1 + ring, h, key0, lim_row0, lim_row1, ks_, vs_, qs_, st, lane, [] {});
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ebars + stg * 8);
+            if (I8) vst.finish_bias(kI8Bias);
         }
         it = it_seg + (uint32_t)n_mine;
 
         // ---- merge the 4 rings of the CTA (every issued tile was waited for, so no copy is in flight)
-        st.finish_l();
-        if (I8) st.finish_bias(kI8Bias);
         __syncthreads();
         float* mo = reinterpret_cast<float*>(smem + stage_off + ring * G::kRingBytes);
+        if (h == 1) {
 #pragma unroll
-        for (int j = 0; j < 16; j++)
+            for (int j = 0; j < 32; j++)
 #pragma unroll
-            for (int c = 0; c < 2; c++) { const int d = pair_dim_of<I8>(h, j, c, t4); mo[g * kMergeStride + d] = st.o[j][c]; mo[(g + 8) * kMergeStride + d] = st.o[j][2 + c]; }
-        if (t4 == 0) {
-            if (h == 0) { sm_ml[(ring * 16 + g) * 3] = st.m0; sm_ml[(ring * 16 + g + 8) * 3] = st.m1; }
-            sm_ml[(ring * 16 + g) * 3 + 1 + h] = st.l0; sm_ml[(ring * 16 + g + 8) * 3 + 1 + h] = st.l1;
+                for (int c = 0; c < 2; c++) { const int d = dim_of<I8>(j, c, t4); mo[g * kMergeStride + d] = vst.o[j][c]; mo[(g + 8) * kMergeStride + d] = vst.o[j][2 + c]; }
         }
         __syncthreads();
 
@@ -201,13 +240,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         for (int r = rsel; r < rows; r += 2) {
             float M = -INFINITY;
 #pragma unroll
-            for (int ww = 0; ww < kRings; ww++) M = fmaxf(M, sm_ml[(ww * 16 + r) * 3]);
+            for (int ww = 0; ww < kRings; ww++) M = fmaxf(M, sm_ml[(ww * 16 + r) * 2]);
             float L = 0.0f, A0 = 0.0f, A1 = 0.0f;
 #pragma unroll
             for (int ww = 0; ww < kRings; ww++) {
-                const float mm = sm_ml[(ww * 16 + r) * 3]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
+                const float mm = sm_ml[(ww * 16 + r) * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
                 const float* src = reinterpret_cast<const float*>(smem + stage_off + ww * G::kRingBytes) + r * kMergeStride + d0;
-                L += (sm_ml[(ww * 16 + r) * 3 + 1] + sm_ml[(ww * 16 + r) * 3 + 2]) * wt; A0 += src[0] * wt; A1 += src[1] * wt;
+                L += sm_ml[(ww * 16 + r) * 2 + 1] * wt; A0 += src[0] * wt; A1 += src[1] * wt;
             }
             if (whole) emit(r, M, L, A0, A1);
             else { *reinterpret_cast<float2*>(slot_o + r * kD + d0) = make_float2(A0, A1); if ((tid & 127) == 0) { slot_ml[r * 2] = M; slot_ml[r * 2 + 1] = L; } }
