@@ -304,19 +304,19 @@ namespace kata {
 constexpr int kPSlotBytes = 16 * kPStride + 64;   // P block + 16 rescale factors
 
 struct ScoreState { float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f; };
-struct ValueState {
+template <int NJ> struct ValueStateT {   // NJ n-tiles of 8 dims: 32 = the whole head, 16 = one half of it
     float ps0 = 0.0f, ps1 = 0.0f;   // int8 mode: running sums of the fp16-rounded P (bias term of the biased V fragments)
-    float o[32][4];
+    float o[NJ][4];
     __device__ __forceinline__ void clear() {
         ps0 = ps1 = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 32; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+        for (int j = 0; j < NJ; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
     }
     __device__ __forceinline__ void finish_bias(float bias) {
         ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1); ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
         ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1); ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
 #pragma unroll
-        for (int j = 0; j < 32; j++) { o[j][0] -= bias * ps0; o[j][1] -= bias * ps0; o[j][2] -= bias * ps1; o[j][3] -= bias * ps1; }
+        for (int j = 0; j < NJ; j++) { o[j][0] -= bias * ps0; o[j][1] -= bias * ps0; o[j][2] -= bias * ps1; o[j][3] -= bias * ps1; }
     }
 };
 
@@ -395,9 +395,9 @@ __device__ __forceinline__ void score_publish(const uint32_t p_sm, float* alpha_
     if (t4 == 0) { alpha_gen[g] = al0; alpha_gen[g + 8] = al1; }
 }
 
-// Value warp, one tile: O = O * alpha + P V over the tile's 16 keys and all 256 dims.
-template <bool I8>
-__device__ __forceinline__ void value_tile(const uint32_t v_sm, const uint32_t p_sm, const float* alpha_gen, ValueState& st, const int lane) {
+// Value warp, one tile: O = O * alpha + P V over the tile's 16 keys and the dims [vh * 8 * NJ, (vh + 1) * 8 * NJ) of the head.
+template <bool I8, int NJ>
+__device__ __forceinline__ void value_tile(const uint32_t v_sm, const uint32_t p_sm, const float* alpha_gen, ValueStateT<NJ>& st, const int lane, const int vh) {
     using namespace ptx;
     constexpr uint32_t kBox = 16 * 128;
     const int g = lane >> 2;
@@ -406,7 +406,7 @@ __device__ __forceinline__ void value_tile(const uint32_t v_sm, const uint32_t p
     ldsm_x4(p_sm + (lane & 15) * kPStride + (lane >> 4) * 16, pa0, pa1, pa2, pa3);
     if (__any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f)) {
 #pragma unroll
-        for (int j = 0; j < 32; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
+        for (int j = 0; j < NJ; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
     }
     if (I8) {
         const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&pa0)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&pa1));
@@ -414,17 +414,18 @@ __device__ __forceinline__ void value_tile(const uint32_t v_sm, const uint32_t p
         st.ps0 = st.ps0 * al0 + ((f0.x + f0.y) + (f2.x + f2.y)); st.ps1 = st.ps1 * al1 + ((f1.x + f1.y) + (f3.x + f3.y));
     }
     const uint32_t rx = lane & 7, ud = lane >> 4;
-    const uint32_t va = v_sm + (rx + ((lane >> 3) & 1) * 8) * 128;
+    // fp16: 16-byte chunk 2*j + ud of the 512-byte row, j = vh * NJ/2 + j2; int8: chunk 2*j + ud of the 256-byte row, j = vh * NJ/4 + j2
+    const uint32_t va = v_sm + (rx + ((lane >> 3) & 1) * 8) * 128 + (uint32_t)vh * (NJ == 32 ? 0u : kBox * (I8 ? 1u : 2u));
     const uint32_t vo0 = ((0 + ud) ^ rx) << 4, vo1 = ((2 + ud) ^ rx) << 4, vo2 = ((4 + ud) ^ rx) << 4, vo3 = ((6 + ud) ^ rx) << 4;
     if (!I8) {
 #pragma unroll
-        for (int j2 = 0; j2 < 16; j2++) {
+        for (int j2 = 0; j2 < NJ / 2; j2++) {
             uint32_t b0, b1, b2, b3; ldsm_x4_t(va + (j2 >> 2) * kBox + ((j2 & 3) == 0 ? vo0 : (j2 & 3) == 1 ? vo1 : (j2 & 3) == 2 ? vo2 : vo3), b0, b1, b2, b3);
             mma16816(st.o[2 * j2], pa0, pa1, pa2, pa3, b0, b1); mma16816(st.o[2 * j2 + 1], pa0, pa1, pa2, pa3, b2, b3);
         }
     } else {
 #pragma unroll
-        for (int j2 = 0; j2 < 8; j2++) {   // r0: keys 0-7 block 2*j2, r1: keys 8-15 block 2*j2, r2, r3: block 2*j2+1
+        for (int j2 = 0; j2 < NJ / 4; j2++) {   // r0: keys 0-7 block 2*j, r1: keys 8-15 block 2*j, r2, r3: block 2*j+1
             uint32_t r0, r1, r2, r3; ldsm_x4_t(va + (j2 >> 2) * kBox + ((j2 & 3) == 0 ? vo0 : (j2 & 3) == 1 ? vo1 : (j2 & 3) == 2 ? vo2 : vo3), r0, r1, r2, r3);
             r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
             mma16816(st.o[4 * j2 + 0], pa0, pa1, pa2, pa3, deq2_biased(r0, 0x4240u), deq2_biased(r1, 0x4240u));

@@ -96,9 +96,9 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
         ok = cudaMalloc((void**)&c.sc_pm, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess && cudaMalloc((void**)&c.sc_pl, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess &&
              cudaMalloc((void**)&c.sc_pacc, kata::scalar_scratch_floats_acc() * 4) == cudaSuccess;
     if (!ok) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_NOMEM; }
-    {   // 128 bytes of a 16-row box line = 64 fp16 or 128 int8 elements
-        const int inner = 128 / c.elt;
-        if (!kata::make_arena_tmap(&c.tm_k, c.k_arena, c.elt, rows, inner, 16, true) || !kata::make_arena_tmap(&c.tm_v, c.v_arena, c.elt, rows, inner, 16, true) ||
+    {   // decode: rank-4 tile views (a 128-byte column block = 64 fp16 or 128 int8 elements); tcgen05 prefill (fp16): 128-row boxes of 64 columns
+        const int blocks = 256 * c.elt / 128;
+        if (!kata::make_tile_tmap(&c.tm_k_tile, c.k_arena, c.elt, rows, blocks) || !kata::make_tile_tmap(&c.tm_v_tile, c.v_arena, c.elt, rows, blocks) ||
             (c.elt == 2 && (!kata::make_arena_tmap(&c.tm_k128, c.k_arena, 2, rows, 64, 128, true) || !kata::make_arena_tmap(&c.tm_v128, c.v_arena, 2, rows, 64, 128, true)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);

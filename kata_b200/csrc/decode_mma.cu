@@ -31,7 +31,7 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kRings = 4, kWarps = 2 * kRings, kThreads = kWarps * 32, kMaxStages = 8, kTile = 16;
+constexpr int kRings = 4, kWarps = 3 * kRings + 1, kThreads = kWarps * 32, kMaxStages = 8, kTile = 16;
 constexpr int kOffBars = 16 * kQStride;             // 8448: per ring and stage a 'full' and an 'empty' barrier, then the merge barrier
 constexpr int kOffEBars = kRings * kMaxStages * 8, kOffMBar = 2 * kOffEBars, kOffPBars = kOffMBar + 16;                      // inside the barrier block: per ring two 'P full' and two 'P empty' barriers
 constexpr int kOffQsum = kOffBars + 704;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<I8>; constexpr int kStages = G::kStages;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring and ring+4 sit on the same scheduler
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps
     const uint32_t sm_base = smem_u32(smem);
     const uint32_t q_base = sm_base, bars = sm_base + kOffBars + ring * kMaxStages * 8, ebars = sm_base + kOffBars + kOffEBars + ring * kMaxStages * 8, stage_off = ((sm_base + kOffStages + 1023u) & ~1023u) - sm_base, ring_stage0 = sm_base + stage_off + ring * G::kRingBytes;   // swizzled TMA boxes want 1024-byte alignment
     float* sm_ml = reinterpret_cast<float*>(smem + kOffMl);
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
     __shared__ int s_flag; __shared__ float s_ML[24];
     const uint32_t merge_bar = sm_base + kOffBars + kOffMBar; uint32_t merge_phase = 0;
 
-    if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 2); } for (int s = 0; s < 2; s++) { mbar_init(pfull + s * 8, 1); mbar_init(pempty + s * 8, 1); } }
+    if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 3); } for (int s = 0; s < 2; s++) { mbar_init(pfull + s * 8, 1); mbar_init(pempty + s * 8, 2); } }
     if (tid == 0) { mbar_init(merge_bar, 1); mbar_init(merge_bar + 8, 1); }
     fence_mbar_init();
     __syncthreads();
@@ -101,25 +101,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         // ---- this ring's tiles of the segment: local tiles lt0 + ring, lt0 + ring + 4, ...
         const int n_mine = n_here > ring ? (n_here - ring + kRings - 1) / kRings : 0;
         ScoreState ss;                 // softmax state, kept by the ring's score warp (h == 0)
-        ValueState vst; vst.clear();   // the 16 x 256 O block, kept by the ring's value warp (h == 1)
+        ValueStateT<16> vst; vst.clear();   // 16 x 128 half of the O block, kept by the ring's value warps (h == 1: dims 0..127, h == 2: dims 128..255)
         const int lim_row0 = (g < 6 * T) ? min(kend, pos_rel + (g >= 6 ? 1 : 0) + 1) : 0;          // rows g and g+8: exclusive local key limit
         const int lim_row1 = (g + 8 < 6 * T) ? min(kend, pos_rel + 2) : 0;                          // rows 8..11 belong to token 1
 
         const uint32_t it_seg = it;
         const int row0 = (int)p.row_base[b];   // arena row of position 0 (row coordinates of the tensor maps are 32-bit)
-        auto issue = [&](int i) {   // the value warp of the ring brings in the ring's i-th tile: one TMA box per 128-byte column block of K and of V
-            const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-            const uint32_t sx = (it_seg + (uint32_t)i) % kStages, dst = ring_stage0 + sx * G::kStageBytes, bar = bars + sx * 8;
-            fence_proxy_async();
-            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)G::kStageBytes);   // TMA counts whole boxes, out-of-range rows included
-            __syncwarp();
-            if (lane < 2 * G::kBoxes) {
-                const int isv = lane >= G::kBoxes, bx = lane - isv * G::kBoxes;
-                tma_load_3d(dst + isv * G::kTileBytes + bx * (kTile * 128), isv ? &tm_v : &tm_k, bx * (128 / (I8 ? 1 : 2)), kvh, row0 + key0, bar);
+        // ---- producer warp (lane r serves ring r): brings in the ring's tiles of this segment, one TMA instruction for a K tile and one for a V
+        // tile, refilling a stage as soon as the ring's three warps have released it. The first kStages tiles per ring fly while Q is staged.
+        auto produce = [&](int i_from, int i_to) {
+            const int r = lane, nm = n_here > r ? (n_here - r + kRings - 1) / kRings : 0;
+            for (int i = i_from; i < min(i_to, nm); i++) {
+                const uint32_t cur = it + (uint32_t)i, sx = cur % kStages;
+                const uint32_t bar = sm_base + kOffBars + r * kMaxStages * 8 + sx * 8, ebar = bar + kOffEBars, dst = sm_base + stage_off + r * G::kRingBytes + sx * G::kStageBytes;
+                if (i >= kStages && !dead && !mbar_wait_bounded(ebar, ((cur / kStages) - 1u) & 1u, err)) { dead = true; atomicExch(err, 3); }
+                const int key0 = p.first_row + (lt0 + r + i * kRings) * kTile;
+                mbar_arrive_expect_tx(bar, (uint32_t)G::kStageBytes);   // TMA counts whole boxes, out-of-range rows included
+                tma_load_4d(dst, &tm_k, 0, row0 + key0, 0, kvh, bar); tma_load_4d(dst + G::kTileBytes, &tm_v, 0, row0 + key0, 0, kvh, bar);
             }
+            return nm;
         };
-
-        if (h == 1) for (int i = 0; i < min(kStages, n_mine); i++) issue(i);   // every stage is free here; the first tiles fly while Q is staged
+        if (h == 3 && lane < kRings) produce(0, kStages);   // every stage is free here
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         if (I8) {   // row sums of the staged Q block (any column order): warp w sums rows 2w and 2w+1
 #pragma unroll
             for (int rr = 0; rr < 2; rr++) {
-                const int r = 2 * w + rr; const uint4 v = *reinterpret_cast<const uint4*>(smem + r * kQStride + lane * 16); const __half2* hp = reinterpret_cast<const __half2*>(&v);
+                const int r = 2 * (w & 7) + rr; const uint4 v = *reinterpret_cast<const uint4*>(smem + r * kQStride + lane * 16); const __half2* hp = reinterpret_cast<const __half2*>(&v);
                 float a = 0.0f;
 #pragma unroll
                 for (int e = 0; e < 4; e++) { const float2 f = __half22float2(hp[e]); a += f.x + f.y; }
@@ -142,35 +144,36 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         }
         const float qs_[2] = {I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g] : 0.0f, I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g + 8] : 0.0f};
 
-        if (h == 0) {
+        if (h == 3) {
+            if (lane < kRings) it += (uint32_t)produce(kStages, 1 << 30);   // 'it' of producer lane r counts ring r's tiles
+            __syncwarp();
+        } else if (h == 0) {
             // ---- score warp: S = Q K^T, online softmax, P and the rescale factors handed to the value warp; runs up to two tiles ahead
-            // int8: per-key scales of this thread's four score columns, fetched two tiles ahead and kept as raw fp16 bits so that
-            // nothing depends on the loads until the tile they belong to (a scale plane row is first touched here: DRAM latency)
-            unsigned short sA[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sB[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            auto load_scales = [&](int i, unsigned short (&dst)[8]) {
+            // int8: the tile's 16 K scales (lanes 0-15) and 16 V scales (lanes 16-31), one load per lane, fetched three tiles ahead and kept
+            // as raw fp16 bits so that nothing depends on a load until its tile comes up (the scale planes are first touched here: DRAM latency)
+            const unsigned short* sc_plane = reinterpret_cast<const unsigned short*>(lane < 16 ? ksc : vsc);
+            auto load_scale = [&](int i) -> uint32_t {
                 const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int64_t idx = (p.row_base[b] + min(k0 + 8 * (q >> 1) + 2 * t4 + (q & 1), max(kend - 1, 0))) * 4 + kvh;
-                    dst[q] = __ldg(reinterpret_cast<const unsigned short*>(ksc) + idx); dst[4 + q] = __ldg(reinterpret_cast<const unsigned short*>(vsc) + idx);
-                }
+                return __ldg(sc_plane + (p.row_base[b] + min(k0 + (lane & 15), max(kend - 1, 0))) * 4 + kvh);
             };
-            if (I8 && n_mine > 0) load_scales(0, sA);
-            if (I8 && n_mine > 1) load_scales(1, sB);
+            uint32_t sA = 0, sB = 0, sC = 0;
+            if (I8) { if (n_mine > 0) sA = load_scale(0); if (n_mine > 1) sB = load_scale(1); if (n_mine > 2) sC = load_scale(2); }
             for (int i = 0; i < n_mine; i++) {
                 const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
                 const uint32_t kt = ring_stage0 + stg * G::kStageBytes;
                 const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-                unsigned short sC[8];
-#pragma unroll
-                for (int q = 0; q < 8; q++) { sC[q] = sA[q]; sA[q] = sB[q]; }
-                if (I8 && i + 2 < n_mine) load_scales(i + 2, sB);
+                const uint32_t s_cur = sA; sA = sB; sB = sC;
+                if (I8 && i + 3 < n_mine) sC = load_scale(i + 3);
                 // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and every arrival) stays intact.
                 if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
                 float ks_[2][2] = {{1.f, 1.f}, {1.f, 1.f}}, vs_[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
                 if (I8) {
 #pragma unroll
-                    for (int q = 0; q < 4; q++) { ks_[q >> 1][q & 1] = __half2float(__ushort_as_half(sC[q])); vs_[q >> 1][q & 1] = __half2float(__ushort_as_half(sC[4 + q])); }
+                    for (int q = 0; q < 4; q++) {
+                        const int src = 8 * (q >> 1) + 2 * t4 + (q & 1);
+                        ks_[q >> 1][q & 1] = __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, s_cur, src)));
+                        vs_[q >> 1][q & 1] = __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, s_cur, 16 + src)));
+                    }
                 }
                 float pr[2][4], al0, al1;
                 score_tile<I8>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
@@ -185,7 +188,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             ss.l1 += __shfl_xor_sync(0xffffffffu, ss.l1, 1); ss.l1 += __shfl_xor_sync(0xffffffffu, ss.l1, 2);
             if (t4 == 0) { sm_ml[(ring * 16 + g) * 2] = ss.m0; sm_ml[(ring * 16 + g) * 2 + 1] = ss.l0; sm_ml[(ring * 16 + g + 8) * 2] = ss.m1; sm_ml[(ring * 16 + g + 8) * 2 + 1] = ss.l1; }
         } else {
-            // ---- value warp: O = O * alpha + P V; releases the stage and refills it with the tile three ahead
+            // ---- value warps: O = O * alpha + P V on their half of the head dims
+            const int vh = h - 1;
             for (int i = 0; i < n_mine; i++) {
                 const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
                 const uint32_t vt = ring_stage0 + stg * G::kStageBytes + G::kTileBytes;
@@ -193,38 +197,36 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
                 if (key0 + kTile > kend) {   // tail tile: rows past the range were loaded as they lie in memory; zero those V rows (0 x garbage must stay 0)
                     const int nk = max(0, kend - key0);
-                    for (int idx = lane; idx < (kTile - nk) * G::kBoxes * 8; idx += 32) {
-                        const int r = nk + idx / (G::kBoxes * 8), rem = idx % (G::kBoxes * 8);
-                        *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (rem >> 3) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    constexpr int kHB = G::kBoxes / 2;   // boxes of this warp's half
+                    for (int idx = lane; idx < (kTile - nk) * kHB * 8; idx += 32) {
+                        const int r = nk + idx / (kHB * 8), rem = idx % (kHB * 8);
+                        *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (vh * kHB + (rem >> 3)) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
                     }
+                    fence_proxy_async();   // generic-proxy writes to a stage that a TMA write refills later
                     __syncwarp();
                 }
                 if (!dead && !mbar_wait_bounded(pfull + slot * 8, (cur >> 1) & 1u, err)) { dead = true; atomicExch(err, 5); }
-                value_tile<I8>(vt, p_sm + slot * kPSlotBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * kPSlotBytes + 16 * kPStride), vst, lane);
+                value_tile<I8, 16>(vt, p_sm + slot * kPSlotBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * kPSlotBytes + 16 * kPStride), vst, lane, vh);
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(pempty + slot * 8); mbar_arrive(ebars + stg * 8); }
-                if (i + kStages < n_mine) {   // the score warp released this stage before it published P: refill it right away
-                    if (!dead && !mbar_wait_bounded(ebars + stg * 8, par, err)) { dead = true; atomicExch(err, 3); }
-                    issue(i + kStages);
-                }
             }
             if (I8) vst.finish_bias(kI8Bias);
         }
-        it = it_seg + (uint32_t)n_mine;
+        if (h != 3) it = it_seg + (uint32_t)n_mine;
 
         // ---- merge the 4 rings of the CTA (every issued tile was waited for, so no copy is in flight)
         __syncthreads();
         float* mo = reinterpret_cast<float*>(smem + stage_off + ring * G::kRingBytes);
-        if (h == 1) {
+        if (h == 1 || h == 2) {
 #pragma unroll
-            for (int j = 0; j < 32; j++)
+            for (int j = 0; j < 16; j++)
 #pragma unroll
-                for (int c = 0; c < 2; c++) { const int d = dim_of<I8>(j, c, t4); mo[g * kMergeStride + d] = vst.o[j][c]; mo[(g + 8) * kMergeStride + d] = vst.o[j][2 + c]; }
+                for (int c = 0; c < 2; c++) { const int d = pair_dim_of<I8>(h - 1, j, c, t4); mo[g * kMergeStride + d] = vst.o[j][c]; mo[(g + 8) * kMergeStride + d] = vst.o[j][2 + c]; }
         }
         __syncthreads();
 
         const int seg = b * 4 + kvh, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_end - 1), n_contrib = c_last - c_first + 1;
-        const int d0 = 2 * (tid & 127), rsel = tid >> 7;   // this thread merges dims d0, d0+1 of rows rsel, rsel+2, ...
+        const int d0 = 2 * (tid & 127), rsel = tid >> 7; const bool merger = h < 3;   // a thread of the 12 ring warps merges dims d0, d0+1 of rows rsel, rsel+3, ...
         const bool whole = (n_contrib == 1);
         const int rows = 6 * T;
         float* slot_o = scratch_o + (int64_t)(cta + seg) * (12 * kD); float* slot_ml = scratch_ml + (int64_t)(cta + seg) * 32;
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 if (out_bf16) reinterpret_cast<__nv_bfloat162*>(out)[oi >> 1] = __floats2bfloat162_rn(y0, y1); else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oi) = make_float2(y0, y1);
             }
         };
-        for (int r = rsel; r < rows; r += 2) {
+        for (int r = merger ? rsel : rows; r < rows; r += kThreads / 128) {
             float M = -INFINITY;
 #pragma unroll
             for (int ww = 0; ww < kRings; ww++) M = fmaxf(M, sm_ml[(ww * 16 + r) * 2]);
@@ -289,9 +291,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                         for (int c = tid; c < cnt; c += 32) bulk_g2s(obuf + (k & 1) * half_bytes + c * per, scratch_o + (int64_t)(c_first + base + c + seg) * (12 * kD), (uint32_t)per, mb);
                     }
                 };
-                float A[6][2];
+                constexpr int kRS = kThreads / 128, kRR = 12 / kRS;   // row step and rows per thread of the merge
+                float A[kRR][2];
 #pragma unroll
-                for (int r = 0; r < 6; r++) { A[r][0] = 0.0f; A[r][1] = 0.0f; }
+                for (int r = 0; r < kRR; r++) { A[r][0] = 0.0f; A[r][1] = 0.0f; }
                 issue_group(0);
                 for (int k = 0; k < n_groups; k++) {
                     if (k + 1 < n_groups) issue_group(k + 1);
@@ -302,14 +305,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 #pragma unroll 4
                     for (int c = 0; c < cnt; c++) {
 #pragma unroll
-                        for (int rr = 0; rr < 6; rr++) { const int r = 2 * rr + rsel; if (r < rows) {
+                        for (int rr = 0; rr < kRR; rr++) { const int r = kRS * rr + rsel; if (merger && r < rows) {
                             const float wt = wl[((base + c) * rows + r) * 2]; const float2 v = *reinterpret_cast<const float2*>(ob + (c * rows + r) * 1024);
                             A[rr][0] += wt * v.x; A[rr][1] += wt * v.y; } }
                     }
                     __syncthreads();
                 }
 #pragma unroll
-                for (int rr = 0; rr < 6; rr++) { const int r = 2 * rr + rsel; if (r < rows) emit(r, s_ML[r * 2], s_ML[r * 2 + 1], A[rr][0], A[rr][1]); }
+                for (int rr = 0; rr < kRR; rr++) { const int r = kRS * rr + rsel; if (merger && r < rows) emit(r, s_ML[r * 2], s_ML[r * 2 + 1], A[rr][0], A[rr][1]); }
                 if (tid == 0) counters[seg] = 0;   // ready for the next call on this stream
             }
         }
@@ -379,6 +382,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
         for (int i = 0; i < b.n; i++) for (int kv = 0; kv < 4; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; max_contrib = std::max(max_contrib, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
     }
     p.merge_in_kernel = max_contrib <= 8;
+    const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
     if (!attr_set[i8]) {
         cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
@@ -386,8 +390,8 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
         if (e != cudaSuccess) return e;
         attr_set[i8] = true;
     }
-    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(c.tm_k, c.tm_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
-    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(c.tm_k, c.tm_v, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     c.launches++;
     if (!p.merge_in_kernel) { decode_combine_kernel<<<dim3(6 * T, 4 * b.n), 256, 0, s>>>(p, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.part_o, c.part_ml); c.launches++; }
     return cudaGetLastError();
@@ -469,7 +473,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     const int n_ctas = std::max(1, std::min(std::min(sd.sm_count, kStaticMaxCtas), total));
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas; p.merge_in_kernel = 1;
     CUtensorMap tm_k, tm_v;   // encoded on the host; no device memory involved
-    if (!make_arena_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 64, 16, true) || !make_arena_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 64, 16, true)) return KATA_ERR_CUDA;
+    if (!make_tile_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 4) || !make_tile_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 4)) return KATA_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
     if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
     decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,

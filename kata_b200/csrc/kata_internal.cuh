@@ -43,7 +43,7 @@ struct Ctx {
     // scalar-path scratch (k_attn_split partials)
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
     // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
-    CUtensorMap tm_k{}, tm_v{};
+    CUtensorMap tm_k_tile{}, tm_v_tile{};   // rank-4 views for decode: one TMA instruction per 16-key tile of one KV head
     CUtensorMap tm_k128{}, tm_v128{};   // the same arenas with 128-row boxes (tcgen05 prefill tiles; fp16 mode)
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
     int sm_count = 148;
@@ -66,5 +66,6 @@ void set_inv_freq(const float* host32);   // uploads the 32 inverse RoPE frequen
 // rank-3 map over an arena [rows][4][256 elements of elt bytes]; box = {box_inner elements, 1, box_rows}; returns false on failure
 bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows);
 bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128);
+bool make_tile_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_blocks);
 
 }  // namespace kata
