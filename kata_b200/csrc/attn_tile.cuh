@@ -154,157 +154,33 @@ __device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + _
 }  // namespace kata
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Pair-split variant used by the decode kernel: two warps (h = 0, 1) share one 16-key tile. Each computes the scores of
-// its own 8 keys (no redundant Q.K^T), the pair exchanges row maxima and the fp16 P block through shared memory with two
-// 64-thread named barriers, and each accumulates its own 128-dim half of O over all 16 keys. Same arithmetic and rounding
-// points as tile_qk_softmax_pv; both warps see the same running maximum, and the row sums l of the two halves add up.
+// Warp-specialised tile routines of the decode kernel. A ring of the kernel has one "score" warp and two "value" warps that
+// overlap across tiles: the score warp computes S = Q K^T for the tile's keys, the online-softmax state (m, l) and the fp16 P
+// block, and hands P plus the rescale factors of its two row groups to the value warps through a two-slot shared-memory
+// buffer; each value warp owns a 16 x 128 half of the O block, applies the rescale and accumulates O += P V. While the value
+// warps work on tile i the score warp is already on tile i+1. Arithmetic and rounding points are those of tile_qk_softmax_pv.
+//
+// A tile holds NK sub-blocks of 16 keys (NK = 1: fp16 cache, NK = 2: int8 cache, where the per-tile costs - barriers, shuffles,
+// the Q fragments - weigh more against half the bytes). K and V tiles are read as TMA wrote them: column blocks of
+// [16*NK keys][128 bytes], block b holding bytes [128b, 128b+128) of every row, 16-byte chunk c of row r stored at chunk c ^ (r & 7).
 namespace kata {
 
-constexpr int kPStride = 48;   // bytes per row of the exchanged 16x16 fp16 P block (32 + 16 pad: conflict-free ldmatrix)
-
-struct PairState {
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-    float ps0 = 0.0f, ps1 = 0.0f;   // int8 mode: running sums of the fp16-rounded P (the bias term of the biased V fragments)
-    float o[16][4];
-    __device__ __forceinline__ void clear() {
-        m0 = m1 = -INFINITY; l0 = l1 = 0.0f; ps0 = ps1 = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
-    }
-    __device__ __forceinline__ void finish_l() {
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    }
-    // int8 mode: O was accumulated against V codes biased by kI8Bias; take the bias term out (sum of P over the quad's 16 keys)
-    __device__ __forceinline__ void finish_bias(float bias) {
-        ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1); ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
-        ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1); ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
-#pragma unroll
-        for (int j = 0; j < 16; j++) { o[j][0] -= bias * ps0; o[j][1] -= bias * ps0; o[j][2] -= bias * ps1; o[j][3] -= bias * ps1; }
-    }
-};
-
-// In the pair-split int8 path the codes are not fully dequantised: the byte permute leaves code + 1152 in fp16 (exact:
+// In the int8 path the codes are not fully dequantised: the byte permute leaves code + 1152 in fp16 (exact:
 // 0x64xx = 1024 + (code ^ 0x80)), the MMAs run on these biased values, and the bias terms 1152 * sum_d q_d (scores) and
 // 1152 * sum_k P_k (output) are subtracted afterwards in fp32. This removes the half2 subtract per pair of codes.
 constexpr float kI8Bias = 1152.0f;
 __device__ __forceinline__ uint32_t deq2_biased(uint32_t x, uint32_t sel) { return ptx::prmt(x, 0x64646464u, sel); }
 
-// dimension of O element (n-tile j of 16, column c) held by warp half h
+// dimension of O element (n-tile j of 16, column c) held by the value warp of half h
 template <bool I8> __device__ __forceinline__ int pair_dim_of(int h, int j, int c, int t4) { return h * 128 + dim_of<I8>(j, c, t4); }
 
-__device__ __forceinline__ void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
-
-// k_sm / v_sm: shared addresses (1024-byte aligned) of the tile as TMA wrote it with the 128-byte swizzle: boxes of
-// [16 keys][128 bytes], box b holding bytes [128b, 128b+128) of every row, 16-byte chunk c of row r stored at chunk c ^ (r & 7).
-// maxbuf: float [2][16] in shared memory; p_sm: shared address of the [16][kPStride] P block; bar_id: named barrier of the pair.
-// ks/vs: int8 mode, scales of this thread's two score columns (keys key0 + 8h + 2*t4 + e); qs: int8 mode, sum over the 256
-// dims of Q rows g and g+8 (for the bias term). after_sync1 runs once between the
-// two barriers (the decode kernel refills the ring there: by then both warps have finished reading the previous tile).
-template <bool I8, class F>
-__device__ __forceinline__ void pair_tile(const uint32_t q_sm, const uint32_t k_sm, const uint32_t v_sm, float* maxbuf, const uint32_t p_sm, const int bar_id, const int h,
-                                          const int key0, const int lim0, const int lim1, const float (&ks)[2], const float (&vs)[2], const float (&qs)[2], PairState& st, const int lane, F&& after_sync1) {
-    using G = TileGeo<I8>;
-    using namespace ptx;
-    const int t4 = lane & 3, g = lane >> 2;
-    float s[4] = {0, 0, 0, 0}, s2[4] = {0, 0, 0, 0};
-    const uint32_t qa = q_sm + (lane & 15) * kQStride + (lane >> 4) * 16;
-    constexpr uint32_t kBox = 16 * 128;
-    const uint32_t rx = lane & 7, qd = lane >> 3;
-    const uint32_t ka = k_sm + (8 * h + rx) * 128;                                   // my 8 key rows; lanes 8q..8q+7 fetch 16-byte chunk 4*k + q
-    const uint32_t ka_e = ka + ((qd ^ rx) << 4), ka_o = ka + (((4 + qd) ^ rx) << 4);   // even / odd groups of four chunks inside a 128-byte box
-    if (!I8) {
-#pragma unroll
-        for (int k2 = 0; k2 < 8; k2++) {   // chunks 0,1 = k-step 2*k2 (b0, b1); chunks 2,3 = k-step 2*k2+1
-            uint32_t b0, b1, b2, b3, a0, a1, a2, a3, c0, c1, c2, c3;
-            ldsm_x4(((k2 & 1) ? ka_o : ka_e) + (k2 >> 1) * kBox, b0, b1, b2, b3);
-            ldsm_x4(qa + (2 * k2) * 32, a0, a1, a2, a3); ldsm_x4(qa + (2 * k2 + 1) * 32, c0, c1, c2, c3);
-            mma16816(s, a0, a1, a2, a3, b0, b1); mma16816(s2, c0, c1, c2, c3, b2, b3);
-        }
-#pragma unroll
-        for (int e = 0; e < 4; e++) s[e] += s2[e];
-    } else {
-#pragma unroll
-        for (int k4 = 0; k4 < 4; k4++) {   // int8: each 16-byte chunk is a 16-dim block; register = dims 4*t4..4*t4+3 of key g
-            uint32_t r0, r1, r2, r3, a0, a1, a2, a3;
-            ldsm_x4(((k4 & 1) ? ka_o : ka_e) + (k4 >> 1) * kBox, r0, r1, r2, r3);
-            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            ldsm_x4(qa + (4 * k4 + 0) * 32, a0, a1, a2, a3); mma16816(s, a0, a1, a2, a3, deq2_biased(r0, 0x4140u), deq2_biased(r0, 0x4342u));
-            ldsm_x4(qa + (4 * k4 + 1) * 32, a0, a1, a2, a3); mma16816(s2, a0, a1, a2, a3, deq2_biased(r1, 0x4140u), deq2_biased(r1, 0x4342u));
-            ldsm_x4(qa + (4 * k4 + 2) * 32, a0, a1, a2, a3); mma16816(s, a0, a1, a2, a3, deq2_biased(r2, 0x4140u), deq2_biased(r2, 0x4342u));
-            ldsm_x4(qa + (4 * k4 + 3) * 32, a0, a1, a2, a3); mma16816(s2, a0, a1, a2, a3, deq2_biased(r3, 0x4140u), deq2_biased(r3, 0x4342u));
-        }
-        const float b0 = kI8Bias * qs[0], b1 = kI8Bias * qs[1];   // the scores were formed against code + 1152
-        s[0] = (s[0] + s2[0] - b0) * ks[0]; s[1] = (s[1] + s2[1] - b0) * ks[1]; s[2] = (s[2] + s2[2] - b1) * ks[0]; s[3] = (s[3] + s2[3] - b1) * ks[1];
-    }
-#pragma unroll
-    for (int e = 0; e < 2; e++) { const int key = key0 + 8 * h + 2 * t4 + e; if (key >= lim0) s[e] = -INFINITY; if (key >= lim1) s[2 + e] = -INFINITY; }
-    float mx0 = fmaxf(s[0], s[1]) * kLog2e, mx1 = fmaxf(s[2], s[3]) * kLog2e;
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    if (t4 == 0) { maxbuf[h * 16 + g] = mx0; maxbuf[h * 16 + g + 8] = mx1; }
-    pair_barrier(bar_id);
-    after_sync1();
-    const float mn0 = fmaxf(st.m0, fmaxf(mx0, maxbuf[(h ^ 1) * 16 + g])), mn1 = fmaxf(st.m1, fmaxf(mx1, maxbuf[(h ^ 1) * 16 + g + 8]));
-    const float al0 = (mn0 == -INFINITY) ? 1.0f : ex2(st.m0 - mn0), al1 = (mn1 == -INFINITY) ? 1.0f : ex2(st.m1 - mn1);
-    const float sub0 = (mn0 == -INFINITY) ? 0.0f : mn0, sub1 = (mn1 == -INFINITY) ? 0.0f : mn1;
-    st.m0 = mn0; st.m1 = mn1;
-    float p0 = ex2(fmaf(s[0], kLog2e, -sub0)), p1 = ex2(fmaf(s[1], kLog2e, -sub0)), p2 = ex2(fmaf(s[2], kLog2e, -sub1)), p3 = ex2(fmaf(s[3], kLog2e, -sub1));
-    st.l0 = st.l0 * al0 + (p0 + p1); st.l1 = st.l1 * al1 + (p2 + p3);
-    if (__any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f)) {
-#pragma unroll
-        for (int j = 0; j < 16; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
-    }
-    if (I8) { p0 *= vs[0]; p1 *= vs[1]; p2 *= vs[0]; p3 *= vs[1]; }
-    {   // my 8 columns of the fp16 P block
-        const uint32_t off = (uint32_t)((8 * h + 2 * t4) * 2);
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + g * kPStride + off), "r"(pack_h2(p0, p1)) : "memory");
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + (g + 8) * kPStride + off), "r"(pack_h2(p2, p3)) : "memory");
-    }
-    pair_barrier(bar_id);
-    uint32_t pa0, pa1, pa2, pa3;
-    ldsm_x4(p_sm + (lane & 15) * kPStride + (lane >> 4) * 16, pa0, pa1, pa2, pa3);
-    if (I8) {   // bias term of the output: sum of the fp16-rounded P over this thread's four keys, rows g (pa0, pa2) and g+8 (pa1, pa3)
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&pa0)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&pa1));
-        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&pa2)), f3 = __half22float2(*reinterpret_cast<const __half2*>(&pa3));
-        st.ps0 = st.ps0 * al0 + ((f0.x + f0.y) + (f2.x + f2.y)); st.ps1 = st.ps1 * al1 + ((f1.x + f1.y) + (f3.x + f3.y));
-    }
-    const uint32_t va = v_sm + (rx + ((lane >> 3) & 1) * 8) * 128, ud = lane >> 4;   // key row of this lane; chunk 2*j + ud of my half
-    const uint32_t vo0 = ((0 + ud) ^ rx) << 4, vo1 = ((2 + ud) ^ rx) << 4, vo2 = ((4 + ud) ^ rx) << 4, vo3 = ((6 + ud) ^ rx) << 4;
-    if (!I8) {
-#pragma unroll
-        for (int j2 = 0; j2 < 8; j2++) {
-            uint32_t b0, b1, b2, b3; ldsm_x4_t(va + (2 * h + (j2 >> 2)) * kBox + ((j2 & 3) == 0 ? vo0 : (j2 & 3) == 1 ? vo1 : (j2 & 3) == 2 ? vo2 : vo3), b0, b1, b2, b3);
-            mma16816(st.o[2 * j2], pa0, pa1, pa2, pa3, b0, b1); mma16816(st.o[2 * j2 + 1], pa0, pa1, pa2, pa3, b2, b3);
-        }
-    } else {
-#pragma unroll
-        for (int j2 = 0; j2 < 4; j2++) {
-            uint32_t r0, r1, r2, r3; ldsm_x4_t(va + h * kBox + (j2 == 0 ? vo0 : j2 == 1 ? vo1 : j2 == 2 ? vo2 : vo3), r0, r1, r2, r3);
-            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            mma16816(st.o[4 * j2 + 0], pa0, pa1, pa2, pa3, deq2_biased(r0, 0x4240u), deq2_biased(r1, 0x4240u));
-            mma16816(st.o[4 * j2 + 1], pa0, pa1, pa2, pa3, deq2_biased(r0, 0x4341u), deq2_biased(r1, 0x4341u));
-            mma16816(st.o[4 * j2 + 2], pa0, pa1, pa2, pa3, deq2_biased(r2, 0x4240u), deq2_biased(r3, 0x4240u));
-            mma16816(st.o[4 * j2 + 3], pa0, pa1, pa2, pa3, deq2_biased(r2, 0x4341u), deq2_biased(r3, 0x4341u));
-        }
-    }
-}
-
-}  // namespace kata
-
-// ---------------------------------------------------------------------------------------------------------------------
-// Warp-specialised variant used by the decode kernel: the two warps of a ring run different halves of a tile and overlap
-// across tiles. The "score" warp computes S = Q K^T for the tile's 16 keys, the online-softmax state (m, l) and the fp16 P
-// block, and hands P plus the rescale factors of the two row groups to the "value" warp through a two-slot shared-memory
-// buffer; the value warp owns the whole 16 x 256 O block, applies the rescale and accumulates O += P V. While the value
-// warp works on tile i the score warp is already on tile i+1. Arithmetic and rounding points are those of
-// tile_qk_softmax_pv. K and V tiles are read as TMA wrote them (boxes of [16 keys][128 bytes], 128-byte swizzle).
-namespace kata {
-
-constexpr int kPSlotBytes = 16 * kPStride + 64;   // P block + 16 rescale factors
+template <int NK> struct PSlot {
+    static constexpr int kStride = 32 * NK + 16;          // bytes per row of the fp16 P block (16 pad: conflict-free ldmatrix)
+    static constexpr int kBytes = 16 * kStride + 64;      // P block + 16 rescale factors
+};
 
 struct ScoreState { float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f; };
-template <int NJ> struct ValueStateT {   // NJ n-tiles of 8 dims: 32 = the whole head, 16 = one half of it
+template <int NJ> struct ValueStateT {   // NJ n-tiles of 8 dims: 16 = one half of the head
     float ps0 = 0.0f, ps1 = 0.0f;   // int8 mode: running sums of the fp16-rounded P (bias term of the biased V fragments)
     float o[NJ][4];
     __device__ __forceinline__ void clear() {
@@ -320,119 +196,157 @@ template <int NJ> struct ValueStateT {   // NJ n-tiles of 8 dims: 32 = the whole
     }
 };
 
-// Score warp, one tile. Writes the fp16 P block (after the V scale in int8 mode) and the 16 rescale factors into the slot at
-// p_sm (shared address) / p_gen (generic pointer to the same slot). ks/vs: int8 scales of this thread's four score columns
-// (keys key0 + nt*8 + 2*t4 + e -> [nt][e]); qs: int8 mode, sums over the 256 dims of Q rows g and g+8.
-template <bool I8>
+// Score warp, one tile. Returns the unrounded-then-scaled P values pr[n-tile][4] (n-tile nt = 8 keys: keys key0 + 8*nt + 2*t4 + e are
+// elements e and 2 + e for rows g and g + 8) and the rescale factors of rows g and g + 8. ks/vs: int8 scales of this thread's score
+// columns ([nt][e]); qs: int8 mode, sums over the 256 dims of Q rows g and g+8.
+template <bool I8, int NK>
 __device__ __forceinline__ void score_tile(const uint32_t q_sm, const uint32_t k_sm, const int key0, const int lim0, const int lim1,
-                                           const float (&ks)[2][2], const float (&vs)[2][2], const float (&qs)[2], ScoreState& st, const int lane, float (&pr)[2][4], float& al0, float& al1) {
+                                           const float (&ks)[2 * NK][2], const float (&vs)[2 * NK][2], const float (&qs)[2], ScoreState& st, const int lane,
+                                           float (&pr)[2 * NK][4], float& al0, float& al1) {
     using namespace ptx;
-    constexpr uint32_t kBox = 16 * 128;
+    constexpr uint32_t kBlk = 16 * NK * 128;   // bytes of one 128-byte column block of the tile
+    constexpr int NT = 2 * NK;
     const int t4 = lane & 3;
     const uint32_t rx = lane & 7, q1 = (lane >> 3) & 1;
     const uint32_t qa = q_sm + (lane & 15) * kQStride + (lane >> 4) * 16;
-    const uint32_t ka = k_sm + (rx + ((lane >> 4) << 3)) * 128;   // lanes 0-15: keys 0-7, lanes 16-31: keys 8-15; two 16-byte chunks per step
-    const uint32_t ko0 = ((0 + q1) ^ rx) << 4, ko1 = ((2 + q1) ^ rx) << 4, ko2 = ((4 + q1) ^ rx) << 4, ko3 = ((6 + q1) ^ rx) << 4;
-    float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}}, s2[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    const uint32_t ka = k_sm + (rx + ((lane >> 4) << 3)) * 128;   // lanes 0-15: keys 0-7, lanes 16-31: keys 8-15 of a sub-block; two 16-byte chunks per step
+    const uint32_t ko[4] = {((0 + q1) ^ rx) << 4, ((2 + q1) ^ rx) << 4, ((4 + q1) ^ rx) << 4, ((6 + q1) ^ rx) << 4};
+    float s[NT][4], s2[NT][4];   // two accumulator chains per n-tile: halves the dependent-MMA latency
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) { s[nt][e] = 0.0f; s2[nt][e] = 0.0f; }
     if (!I8) {
 #pragma unroll
-        for (int kk = 0; kk < 16; kk += 2) {   // chunk 2*kk + q1 of the 512-byte row: box kk/4, chunk 2*(kk%4) + q1 inside it
-            uint32_t a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
-            ldsm_x4(qa + kk * 32, a0, a1, a2, a3); ldsm_x4(ka + (kk >> 2) * kBox + ((kk & 3) == 0 ? ko0 : ko2), b0, b1, b2, b3);
-            ldsm_x4(qa + kk * 32 + 32, c0, c1, c2, c3); ldsm_x4(ka + (kk >> 2) * kBox + ((kk & 3) == 0 ? ko1 : ko3), d0, d1, d2, d3);
-            mma16816(s[0], a0, a1, a2, a3, b0, b1); mma16816(s[1], a0, a1, a2, a3, b2, b3);
-            mma16816(s2[0], c0, c1, c2, c3, d0, d1); mma16816(s2[1], c0, c1, c2, c3, d2, d3);
+        for (int kk = 0; kk < 16; kk += 2) {   // chunk 2*kk + q1 of the 512-byte row: block kk/4, chunk 2*(kk%4) + q1 inside it
+            uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+            ldsm_x4(qa + kk * 32, a0, a1, a2, a3); ldsm_x4(qa + kk * 32 + 32, c0, c1, c2, c3);
+#pragma unroll
+            for (int sb = 0; sb < NK; sb++) {
+                uint32_t b0, b1, b2, b3, d0, d1, d2, d3;
+                ldsm_x4(ka + sb * 2048 + (kk >> 2) * kBlk + ko[kk & 3], b0, b1, b2, b3); ldsm_x4(ka + sb * 2048 + (kk >> 2) * kBlk + ko[(kk & 3) + 1], d0, d1, d2, d3);
+                mma16816(s[2 * sb], a0, a1, a2, a3, b0, b1); mma16816(s[2 * sb + 1], a0, a1, a2, a3, b2, b3);
+                mma16816(s2[2 * sb], c0, c1, c2, c3, d0, d1); mma16816(s2[2 * sb + 1], c0, c1, c2, c3, d2, d3);
+            }
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++)
+        for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) s[nt][e] += s2[nt][e];
     } else {
 #pragma unroll
         for (int k2 = 0; k2 < 8; k2++) {   // int8: 16-byte chunk = 16-dim block; r0: keys 0-7 block 2*k2, r1: keys 0-7 block 2*k2+1, r2, r3: keys 8-15
-            uint32_t r0, r1, r2, r3, a0, a1, a2, a3;
-            ldsm_x4(ka + (k2 >> 2) * kBox + ((k2 & 3) == 0 ? ko0 : (k2 & 3) == 1 ? ko1 : (k2 & 3) == 2 ? ko2 : ko3), r0, r1, r2, r3);
-            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            ldsm_x4(qa + (2 * k2) * 32, a0, a1, a2, a3);
-            mma16816(s[0], a0, a1, a2, a3, deq2_biased(r0, 0x4140u), deq2_biased(r0, 0x4342u)); mma16816(s[1], a0, a1, a2, a3, deq2_biased(r2, 0x4140u), deq2_biased(r2, 0x4342u));
-            ldsm_x4(qa + (2 * k2 + 1) * 32, a0, a1, a2, a3);
-            mma16816(s2[0], a0, a1, a2, a3, deq2_biased(r1, 0x4140u), deq2_biased(r1, 0x4342u)); mma16816(s2[1], a0, a1, a2, a3, deq2_biased(r3, 0x4140u), deq2_biased(r3, 0x4342u));
+            uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+            ldsm_x4(qa + (2 * k2) * 32, a0, a1, a2, a3); ldsm_x4(qa + (2 * k2 + 1) * 32, c0, c1, c2, c3);
+#pragma unroll
+            for (int sb = 0; sb < NK; sb++) {
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4(ka + sb * 2048 + (k2 >> 2) * kBlk + ko[k2 & 3], r0, r1, r2, r3);
+                r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+                mma16816(s[2 * sb], a0, a1, a2, a3, deq2_biased(r0, 0x4140u), deq2_biased(r0, 0x4342u)); mma16816(s[2 * sb + 1], a0, a1, a2, a3, deq2_biased(r2, 0x4140u), deq2_biased(r2, 0x4342u));
+                mma16816(s2[2 * sb], c0, c1, c2, c3, deq2_biased(r1, 0x4140u), deq2_biased(r1, 0x4342u)); mma16816(s2[2 * sb + 1], c0, c1, c2, c3, deq2_biased(r3, 0x4140u), deq2_biased(r3, 0x4342u));
+            }
         }
         const float b0 = kI8Bias * qs[0], b1 = kI8Bias * qs[1];   // the scores were formed against code + 1152
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) { s[nt][0] = (s[nt][0] + s2[nt][0] - b0) * ks[nt][0]; s[nt][1] = (s[nt][1] + s2[nt][1] - b0) * ks[nt][1]; s[nt][2] = (s[nt][2] + s2[nt][2] - b1) * ks[nt][0]; s[nt][3] = (s[nt][3] + s2[nt][3] - b1) * ks[nt][1]; }
+        for (int nt = 0; nt < NT; nt++) { s[nt][0] = (s[nt][0] + s2[nt][0] - b0) * ks[nt][0]; s[nt][1] = (s[nt][1] + s2[nt][1] - b0) * ks[nt][1]; s[nt][2] = (s[nt][2] + s2[nt][2] - b1) * ks[nt][0]; s[nt][3] = (s[nt][3] + s2[nt][3] - b1) * ks[nt][1]; }
     }
+    // mask by select (never by arithmetic: rows past the valid range may hold anything)
 #pragma unroll
-    for (int nt = 0; nt < 2; nt++)
+    for (int nt = 0; nt < NT; nt++)
 #pragma unroll
         for (int e = 0; e < 2; e++) { const int key = key0 + nt * 8 + 2 * t4 + e; if (key >= lim0) s[nt][e] = -INFINITY; if (key >= lim1) s[nt][2 + e] = -INFINITY; }
-    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])) * kLog2e, mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3])) * kLog2e;
+    // online softmax in the log2 domain
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) { mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1])); mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3])); }
+    mx0 *= kLog2e; mx1 *= kLog2e;
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
     al0 = (mn0 == -INFINITY) ? 1.0f : ex2(st.m0 - mn0); al1 = (mn1 == -INFINITY) ? 1.0f : ex2(st.m1 - mn1);
     const float sub0 = (mn0 == -INFINITY) ? 0.0f : mn0, sub1 = (mn1 == -INFINITY) ? 0.0f : mn1;
     st.m0 = mn0; st.m1 = mn1;
+    float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-    for (int nt = 0; nt < 2; nt++) { pr[nt][0] = ex2(fmaf(s[nt][0], kLog2e, -sub0)); pr[nt][1] = ex2(fmaf(s[nt][1], kLog2e, -sub0)); pr[nt][2] = ex2(fmaf(s[nt][2], kLog2e, -sub1)); pr[nt][3] = ex2(fmaf(s[nt][3], kLog2e, -sub1)); }
-    st.l0 = st.l0 * al0 + ((pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
-    st.l1 = st.l1 * al1 + ((pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]));
+    for (int nt = 0; nt < NT; nt += 2) {   // the row sum is formed per 16-key sub-block as (p0 + p1) + (p2 + p3), sub-blocks added in order
+        float q0 = 0.0f, q1s = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            pr[nt + u][0] = ex2(fmaf(s[nt + u][0], kLog2e, -sub0)); pr[nt + u][1] = ex2(fmaf(s[nt + u][1], kLog2e, -sub0));
+            pr[nt + u][2] = ex2(fmaf(s[nt + u][2], kLog2e, -sub1)); pr[nt + u][3] = ex2(fmaf(s[nt + u][3], kLog2e, -sub1));
+        }
+        q0 = (pr[nt][0] + pr[nt][1]) + (pr[nt + 1][0] + pr[nt + 1][1]); q1s = (pr[nt][2] + pr[nt][3]) + (pr[nt + 1][2] + pr[nt + 1][3]);
+        sum0 += q0; sum1 += q1s;
+    }
+    st.l0 = st.l0 * al0 + sum0; st.l1 = st.l1 * al1 + sum1;
     if (I8) {
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) { pr[nt][0] *= vs[nt][0]; pr[nt][1] *= vs[nt][1]; pr[nt][2] *= vs[nt][0]; pr[nt][3] *= vs[nt][1]; }
+        for (int nt = 0; nt < NT; nt++) { pr[nt][0] *= vs[nt][0]; pr[nt][1] *= vs[nt][1]; pr[nt][2] *= vs[nt][0]; pr[nt][3] *= vs[nt][1]; }
     }
 }
 
 // the score warp publishes P (fp16) and the two rescale factors of its rows into a slot
-__device__ __forceinline__ void score_publish(const uint32_t p_sm, float* alpha_gen, const float (&pr)[2][4], const float al0, const float al1, const int lane) {
+template <int NK>
+__device__ __forceinline__ void score_publish(const uint32_t p_sm, float* alpha_gen, const float (&pr)[2 * NK][4], const float al0, const float al1, const int lane) {
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
-    for (int nt = 0; nt < 2; nt++) {
+    for (int nt = 0; nt < 2 * NK; nt++) {
         const uint32_t off = (uint32_t)((8 * nt + 2 * t4) * 2);
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + g * kPStride + off), "r"(ptx::pack_h2(pr[nt][0], pr[nt][1])) : "memory");
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + (g + 8) * kPStride + off), "r"(ptx::pack_h2(pr[nt][2], pr[nt][3])) : "memory");
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + g * PSlot<NK>::kStride + off), "r"(ptx::pack_h2(pr[nt][0], pr[nt][1])) : "memory");
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(p_sm + (g + 8) * PSlot<NK>::kStride + off), "r"(ptx::pack_h2(pr[nt][2], pr[nt][3])) : "memory");
     }
     if (t4 == 0) { alpha_gen[g] = al0; alpha_gen[g + 8] = al1; }
 }
 
-// Value warp, one tile: O = O * alpha + P V over the tile's 16 keys and the dims [vh * 8 * NJ, (vh + 1) * 8 * NJ) of the head.
-template <bool I8, int NJ>
+// Value warp, one tile: O = O * alpha + P V over the tile's keys and the dims [vh * 8 * NJ, (vh + 1) * 8 * NJ) of the head.
+template <bool I8, int NJ, int NK>
 __device__ __forceinline__ void value_tile(const uint32_t v_sm, const uint32_t p_sm, const float* alpha_gen, ValueStateT<NJ>& st, const int lane, const int vh) {
     using namespace ptx;
-    constexpr uint32_t kBox = 16 * 128;
+    constexpr uint32_t kBlk = 16 * NK * 128;
     const int g = lane >> 2;
     const float al0 = alpha_gen[g], al1 = alpha_gen[g + 8];
-    uint32_t pa0, pa1, pa2, pa3;
-    ldsm_x4(p_sm + (lane & 15) * kPStride + (lane >> 4) * 16, pa0, pa1, pa2, pa3);
+    uint32_t pa[NK][4];
+#pragma unroll
+    for (int sb = 0; sb < NK; sb++) ldsm_x4(p_sm + (lane & 15) * PSlot<NK>::kStride + sb * 32 + (lane >> 4) * 16, pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3]);
     if (__any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f)) {
 #pragma unroll
         for (int j = 0; j < NJ; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
     }
     if (I8) {
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&pa0)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&pa1));
-        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&pa2)), f3 = __half22float2(*reinterpret_cast<const __half2*>(&pa3));
-        st.ps0 = st.ps0 * al0 + ((f0.x + f0.y) + (f2.x + f2.y)); st.ps1 = st.ps1 * al1 + ((f1.x + f1.y) + (f3.x + f3.y));
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (int sb = 0; sb < NK; sb++) {
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&pa[sb][0])), f1 = __half22float2(*reinterpret_cast<const __half2*>(&pa[sb][1]));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&pa[sb][2])), f3 = __half22float2(*reinterpret_cast<const __half2*>(&pa[sb][3]));
+            a0 += (f0.x + f0.y) + (f2.x + f2.y); a1 += (f1.x + f1.y) + (f3.x + f3.y);
+        }
+        st.ps0 = st.ps0 * al0 + a0; st.ps1 = st.ps1 * al1 + a1;
     }
     const uint32_t rx = lane & 7, ud = lane >> 4;
     // fp16: 16-byte chunk 2*j + ud of the 512-byte row, j = vh * NJ/2 + j2; int8: chunk 2*j + ud of the 256-byte row, j = vh * NJ/4 + j2
-    const uint32_t va = v_sm + (rx + ((lane >> 3) & 1) * 8) * 128 + (uint32_t)vh * (NJ == 32 ? 0u : kBox * (I8 ? 1u : 2u));
-    const uint32_t vo0 = ((0 + ud) ^ rx) << 4, vo1 = ((2 + ud) ^ rx) << 4, vo2 = ((4 + ud) ^ rx) << 4, vo3 = ((6 + ud) ^ rx) << 4;
+    const uint32_t va = v_sm + (rx + ((lane >> 3) & 1) * 8) * 128 + (uint32_t)vh * (NJ == 32 ? 0u : kBlk * (I8 ? 1u : 2u));
+    const uint32_t vo[4] = {((0 + ud) ^ rx) << 4, ((2 + ud) ^ rx) << 4, ((4 + ud) ^ rx) << 4, ((6 + ud) ^ rx) << 4};
     if (!I8) {
 #pragma unroll
-        for (int j2 = 0; j2 < NJ / 2; j2++) {
-            uint32_t b0, b1, b2, b3; ldsm_x4_t(va + (j2 >> 2) * kBox + ((j2 & 3) == 0 ? vo0 : (j2 & 3) == 1 ? vo1 : (j2 & 3) == 2 ? vo2 : vo3), b0, b1, b2, b3);
-            mma16816(st.o[2 * j2], pa0, pa1, pa2, pa3, b0, b1); mma16816(st.o[2 * j2 + 1], pa0, pa1, pa2, pa3, b2, b3);
-        }
+        for (int j2 = 0; j2 < NJ / 2; j2++)
+#pragma unroll
+            for (int sb = 0; sb < NK; sb++) {
+                uint32_t b0, b1, b2, b3; ldsm_x4_t(va + sb * 2048 + (j2 >> 2) * kBlk + vo[j2 & 3], b0, b1, b2, b3);
+                mma16816(st.o[2 * j2], pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3], b0, b1); mma16816(st.o[2 * j2 + 1], pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3], b2, b3);
+            }
     } else {
 #pragma unroll
-        for (int j2 = 0; j2 < NJ / 4; j2++) {   // r0: keys 0-7 block 2*j, r1: keys 8-15 block 2*j, r2, r3: block 2*j+1
-            uint32_t r0, r1, r2, r3; ldsm_x4_t(va + (j2 >> 2) * kBox + ((j2 & 3) == 0 ? vo0 : (j2 & 3) == 1 ? vo1 : (j2 & 3) == 2 ? vo2 : vo3), r0, r1, r2, r3);
-            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            mma16816(st.o[4 * j2 + 0], pa0, pa1, pa2, pa3, deq2_biased(r0, 0x4240u), deq2_biased(r1, 0x4240u));
-            mma16816(st.o[4 * j2 + 1], pa0, pa1, pa2, pa3, deq2_biased(r0, 0x4341u), deq2_biased(r1, 0x4341u));
-            mma16816(st.o[4 * j2 + 2], pa0, pa1, pa2, pa3, deq2_biased(r2, 0x4240u), deq2_biased(r3, 0x4240u));
-            mma16816(st.o[4 * j2 + 3], pa0, pa1, pa2, pa3, deq2_biased(r2, 0x4341u), deq2_biased(r3, 0x4341u));
-        }
+        for (int j2 = 0; j2 < NJ / 4; j2++)
+#pragma unroll
+            for (int sb = 0; sb < NK; sb++) {   // r0: keys 0-7 block 2*j, r1: keys 8-15 block 2*j, r2, r3: block 2*j+1
+                uint32_t r0, r1, r2, r3; ldsm_x4_t(va + sb * 2048 + (j2 >> 2) * kBlk + vo[j2 & 3], r0, r1, r2, r3);
+                r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+                mma16816(st.o[4 * j2 + 0], pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3], deq2_biased(r0, 0x4240u), deq2_biased(r1, 0x4240u));
+                mma16816(st.o[4 * j2 + 1], pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3], deq2_biased(r0, 0x4341u), deq2_biased(r1, 0x4341u));
+                mma16816(st.o[4 * j2 + 2], pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3], deq2_biased(r2, 0x4240u), deq2_biased(r3, 0x4240u));
+                mma16816(st.o[4 * j2 + 3], pa[sb][0], pa[sb][1], pa[sb][2], pa[sb][3], deq2_biased(r2, 0x4341u), deq2_biased(r3, 0x4341u));
+            }
     }
 }
 

@@ -31,22 +31,23 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kRings = 4, kWarps = 3 * kRings + 1, kThreads = kWarps * 32, kMaxStages = 8, kTile = 16;
+constexpr int kRings = 4, kWarps = 3 * kRings + 1, kThreads = kWarps * 32, kMaxStages = 8;
 constexpr int kOffBars = 16 * kQStride;             // 8448: per ring and stage a 'full' and an 'empty' barrier, then the merge barrier
 constexpr int kOffEBars = kRings * kMaxStages * 8, kOffMBar = 2 * kOffEBars, kOffPBars = kOffMBar + 16;                      // inside the barrier block: per ring two 'P full' and two 'P empty' barriers
 constexpr int kOffQsum = kOffBars + 704;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
 constexpr int kOffMl = kOffQsum + 64;               // per-ring (m, l) exchange: [4][16][2] floats = 512 B
 constexpr int kOffPair = kOffMl + 512;              // per-ring hand-over from the score warp to the value warp: two slots of (P block 16 x 48 B, 16 rescale factors)
-constexpr int kPairBytes = 2 * kPSlotBytes;         // 1664
+constexpr int kPairBytes = 2 * PSlot<2>::kBytes;    // 2688 (sized for the 32-key tiles of the int8 mode)
 constexpr int kOffStages = kOffPair + kRings * kPairBytes;   // the stage area itself starts at the next 1024-byte boundary of the shared window (found at run time)
 constexpr int kMergeStride = 264;                   // floats per row of the cross-ring merge buffer
 
 template <bool I8> struct Geo {
     static constexpr int kRowBytes = TileGeo<I8>::kRowBytes;
     static constexpr int kBoxes = kRowBytes / 128;               // 128-byte column boxes per K or V tile
-    static constexpr int kTileBytes = kTile * kRowBytes;          // boxes of [16 rows][128 bytes], 128-byte swizzle, no padding
+    static constexpr int kNK = I8 ? 2 : 1, kTile = 16 * kNK;      // keys per tile: 16 (fp16) or 32 (int8), 16 KiB of K+V either way
+    static constexpr int kTileBytes = kTile * kRowBytes;          // column blocks of [kTile rows][128 bytes], 128-byte swizzle, no padding
     static constexpr int kStageBytes = 2 * kTileBytes;
-    static constexpr int kStages = I8 ? 6 : 3;                    // tiles in flight per ring: 48 KB either way
+    static constexpr int kStages = 3;                             // tiles in flight per ring: 48 KB
     static constexpr int kRingBytes = (kStages * kStageBytes > 16 * kMergeStride * 4) ? kStages * kStageBytes : 16 * kMergeStride * 4;
     static constexpr int kSmem = kOffStages + 1024 + kRings * kRingBytes;   // 1024 bytes of slack for the run-time alignment
 };
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
-    using G = Geo<I8>; constexpr int kStages = G::kStages;
+    using G = Geo<I8>; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps
     const uint32_t sm_base = smem_u32(smem);
@@ -149,38 +150,39 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             __syncwarp();
         } else if (h == 0) {
             // ---- score warp: S = Q K^T, online softmax, P and the rescale factors handed to the value warp; runs up to two tiles ahead
-            // int8: the tile's 16 K scales (lanes 0-15) and 16 V scales (lanes 16-31), one load per lane, fetched three tiles ahead and kept
-            // as raw fp16 bits so that nothing depends on a load until its tile comes up (the scale planes are first touched here: DRAM latency)
-            const unsigned short* sc_plane = reinterpret_cast<const unsigned short*>(lane < 16 ? ksc : vsc);
-            auto load_scale = [&](int i) -> uint32_t {
+            // int8: lane j fetches the K and V scale of the tile's key j (mod the tile length), three tiles ahead; they are kept as raw fp16 bits so
+            // that nothing depends on a load until its tile comes up (the scale planes are first touched here: DRAM latency)
+            auto load_scale = [&](int i, const __half* plane) -> uint32_t {
                 const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-                return __ldg(sc_plane + (p.row_base[b] + min(k0 + (lane & 15), max(kend - 1, 0))) * 4 + kvh);
+                return __ldg(reinterpret_cast<const unsigned short*>(plane) + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 4 + kvh);
             };
-            uint32_t sA = 0, sB = 0, sC = 0;
-            if (I8) { if (n_mine > 0) sA = load_scale(0); if (n_mine > 1) sB = load_scale(1); if (n_mine > 2) sC = load_scale(2); }
+            uint32_t kA = 0, kB = 0, kC = 0, vA = 0, vB = 0, vC = 0;
+            if (I8) {
+                if (n_mine > 0) { kA = load_scale(0, ksc); vA = load_scale(0, vsc); }
+                if (n_mine > 1) { kB = load_scale(1, ksc); vB = load_scale(1, vsc); }
+                if (n_mine > 2) { kC = load_scale(2, ksc); vC = load_scale(2, vsc); }
+            }
             for (int i = 0; i < n_mine; i++) {
                 const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
                 const uint32_t kt = ring_stage0 + stg * G::kStageBytes;
                 const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-                const uint32_t s_cur = sA; sA = sB; sB = sC;
-                if (I8 && i + 3 < n_mine) sC = load_scale(i + 3);
+                const uint32_t k_cur = kA, v_cur = vA; kA = kB; kB = kC; vA = vB; vB = vC;
+                if (I8 && i + 3 < n_mine) { kC = load_scale(i + 3, ksc); vC = load_scale(i + 3, vsc); }
                 // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and every arrival) stays intact.
                 if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
-                float ks_[2][2] = {{1.f, 1.f}, {1.f, 1.f}}, vs_[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
-                if (I8) {
+                float ks_[2 * NK][2], vs_[2 * NK][2];
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const int src = 8 * (q >> 1) + 2 * t4 + (q & 1);
-                        ks_[q >> 1][q & 1] = __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, s_cur, src)));
-                        vs_[q >> 1][q & 1] = __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, s_cur, 16 + src)));
-                    }
+                for (int q = 0; q < 4 * NK; q++) {
+                    const int src = 8 * (q >> 1) + 2 * t4 + (q & 1);
+                    ks_[q >> 1][q & 1] = I8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, k_cur, src))) : 1.0f;
+                    vs_[q >> 1][q & 1] = I8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, v_cur, src))) : 1.0f;
                 }
-                float pr[2][4], al0, al1;
-                score_tile<I8>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
+                float pr[2 * NK][4], al0, al1;
+                score_tile<I8, NK>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(ebars + stg * 8);   // K of this stage is no longer needed
                 if (cur >= 2 && !dead && !mbar_wait_bounded(pempty + slot * 8, ((cur >> 1) - 1u) & 1u, err)) { dead = true; atomicExch(err, 4); }
-                score_publish(p_sm + slot * kPSlotBytes, reinterpret_cast<float*>(smem + kOffPair + ring * kPairBytes + slot * kPSlotBytes + 16 * kPStride), pr, al0, al1, lane);
+                score_publish<NK>(p_sm + slot * PS::kBytes, reinterpret_cast<float*>(smem + kOffPair + ring * kPairBytes + slot * PS::kBytes + 16 * PS::kStride), pr, al0, al1, lane);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pfull + slot * 8);
             }
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                     __syncwarp();
                 }
                 if (!dead && !mbar_wait_bounded(pfull + slot * 8, (cur >> 1) & 1u, err)) { dead = true; atomicExch(err, 5); }
-                value_tile<I8, 16>(vt, p_sm + slot * kPSlotBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * kPSlotBytes + 16 * kPStride), vst, lane, vh);
+                value_tile<I8, 16, NK>(vt, p_sm + slot * PS::kBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * PS::kBytes + 16 * PS::kStride), vst, lane, vh);
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(pempty + slot * 8); mbar_arrive(ebars + stg * 8); }
             }
@@ -363,6 +365,7 @@ int decode_max_slots(int sm_count) { return sm_count + 4 * KATA_MAX_BATCH; }
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s) {
     static bool attr_set[2] = {false, false};
+    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8; const int kTile = i8 ? Geo<true>::kTile : Geo<false>::kTile;
     DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off;
     int total = 0;
     for (int i = 0; i < b.n; i++) {
@@ -383,7 +386,6 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     }
     p.merge_in_kernel = max_contrib <= 8;
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
-    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
     if (!attr_set[i8]) {
         cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
                            : cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem);
@@ -466,14 +468,14 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     for (int i = 0; i < n; i++) {
         if (pos_base[i] < 0 || first_pos < 0 || first_pos > pos_base[i] || seq_row0[i] < 0 || seq_row0[i] + pos_base[i] + T > total_rows) return KATA_ERR_RANGE;
         p.pos[i] = pos_base[i]; p.row_base[i] = seq_row0[i]; p.kend[i] = pos_base[i] + T;
-        p.ntiles[i] = std::max(1, (p.kend[i] - first_pos + kTile - 1) / kTile);
+        p.ntiles[i] = std::max(1, (p.kend[i] - first_pos + Geo<false>::kTile - 1) / Geo<false>::kTile);
         p.tile_start[i] = total; total += 4 * p.ntiles[i];
     }
     for (int i = n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
     const int n_ctas = std::max(1, std::min(std::min(sd.sm_count, kStaticMaxCtas), total));
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas; p.merge_in_kernel = 1;
     CUtensorMap tm_k, tm_v;   // encoded on the host; no device memory involved
-    if (!make_tile_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 4) || !make_tile_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 4)) return KATA_ERR_CUDA;
+    if (!make_tile_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 16, 4) || !make_tile_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 16, 4)) return KATA_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
     if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
     decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,

@@ -66,6 +66,6 @@ void set_inv_freq(const float* host32);   // uploads the 32 inverse RoPE frequen
 // rank-3 map over an arena [rows][4][256 elements of elt bytes]; box = {box_inner elements, 1, box_rows}; returns false on failure
 bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows);
 bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128);
-bool make_tile_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_blocks);
+bool make_tile_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_rows, int box_blocks);
 
 }  // namespace kata
