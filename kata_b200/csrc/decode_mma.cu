@@ -74,6 +74,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<I8>; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent grid (the combine kernel) may be set up while this one runs; it waits for this grid's completion itself
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps
     const uint32_t sm_base = smem_u32(smem);
@@ -323,26 +324,46 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
     }
 }
 
-// Merge of the per-CTA partials of every split segment, one CTA per (row, segment), thread = head dimension. Used instead of
-// the in-kernel ticket merge when a segment has many contributors (batch 1 at long context: ~37 per KV head): a single
-// last-arriver CTA then needs ~15 us to pull 220 KB of partials through one SM, while this grid does it in parallel.
-__global__ void __launch_bounds__(256) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, float* __restrict__ part_out,
-                                                             const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml) {
-    const int r = blockIdx.x, seg = blockIdx.y, b = seg >> 2, kvh = seg & 3, tid = threadIdx.x;
-    const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvh * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1);
-    if (c_last == c_first) return;   // a single contributor wrote the final row itself
-    float M = -INFINITY;
-    for (int c = c_first; c <= c_last; c++) M = fmaxf(M, scratch_ml[(int64_t)(c + seg) * 32 + r * 2]);
-    float L = 0.0f, A = 0.0f;
-#pragma unroll 4
-    for (int c = c_first; c <= c_last; c++) {
-        const float mm = scratch_ml[(int64_t)(c + seg) * 32 + r * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
-        L += scratch_ml[(int64_t)(c + seg) * 32 + r * 2 + 1] * wt; A += scratch_o[(int64_t)(c + seg) * (12 * kD) + r * kD + tid] * wt;
+// Merge of the per-CTA partials of every split segment, one CTA per (row, segment). Used instead of the in-kernel ticket merge when a segment
+// has many contributors (batch 1 at long context: ~37 per KV head): a single last-arriver CTA then needs ~15 us to pull 220 KB of partials
+// through one SM, while this grid does it in parallel. Warp 0 forms the row maximum, the weights exp(m - M) and the merged l; then the
+// 1024 threads (4 groups of 256 head dims, group q taking contributors q, q+4, ...) accumulate the weighted O rows with independent loads.
+// Launched with programmatic stream serialisation: the grid is set up while the decode kernel drains and waits for it here.
+constexpr int kCombineThreads = 1024;
+__global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, float* __restrict__ part_out,
+                                                                         const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml) {
+    __shared__ float s_wt[160]; __shared__ float s_acc[3][256]; __shared__ float s_M, s_L;
+    const int r = blockIdx.x, seg = blockIdx.y, b = seg >> 2, kvh = seg & 3, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
+    const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvh * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the decode kernel's partials are complete and visible from here on
+    if (n_c == 1) return;   // a single contributor wrote the final row itself
+    if (tid < 32) {
+        float M = -INFINITY;
+        for (int c = tid; c < n_c; c += 32) M = fmaxf(M, __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        float L = 0.0f;
+        for (int c = tid; c < n_c; c += 32) {
+            const float mm = __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2); const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
+            L += __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2 + 1) * wt; s_wt[c] = wt;
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        if (tid == 0) { s_M = M; s_L = L; }
     }
+    __syncthreads();
+    float A = 0.0f;
+#pragma unroll 8
+    for (int c = q; c < n_c; c += 4) A += __ldcg(scratch_o + (int64_t)(c_first + c + seg) * (12 * kD) + r * kD + d) * s_wt[c];
+    if (q) s_acc[q - 1][d] = A;
+    __syncthreads();
+    if (q) return;
+    A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
+    const float M = s_M, L = s_L;
     const int T = p.T, t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-    if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[tid] = A; if (tid == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
+    if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[d] = A; if (d == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
     else {
-        const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + tid; const float y = (A / L) * sigmoid_fast(gate[oi]);
+        const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
         if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
     }
 }
@@ -395,7 +416,14 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     c.launches++;
-    if (!p.merge_in_kernel) { decode_combine_kernel<<<dim3(6 * T, 4 * b.n), 256, 0, s>>>(p, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.part_o, c.part_ml); c.launches++; }
+    if (!p.merge_in_kernel) {
+        cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(6 * T, 4 * b.n); cfg.blockDim = dim3(kCombineThreads); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+        cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, decode_combine_kernel, p, gate, out, (int)(out_dtype == KATA_ACT_BF16), part_out, (const float*)c.part_o, (const float*)c.part_ml);
+        if (e != cudaSuccess) return e;
+        c.launches++;
+    }
     return cudaGetLastError();
 }
 
