@@ -165,6 +165,7 @@ def run_decode(args, rank, world, kind_cfg):
     sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
     for _ in range(args.warmup):
         step(pos); pos = pos + 1
+        torch.cuda.current_stream().synchronize()   # as in serving, where every step ends with the host holding its result; also lets the decode range sizing settle
     ctx.check()
     l0 = ctx.launches()
     barrier()

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<I8>; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent grid (the combine kernel) may be set up while this one runs; it waits for this grid's completion itself
+    pdl_launch_dependents();   // the next kernel of the stream (the combine kernel, the next layer's prep) may be set up while this one runs; it waits for this grid's completion itself
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps
     const uint32_t sm_base = smem_u32(smem);
@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
     if (tid == 0) { mbar_init(merge_bar, 1); mbar_init(merge_bar + 8, 1); }
     fence_mbar_init();
     __syncthreads();
+    pdl_wait();   // launched with programmatic stream serialisation: everything above overlapped the previous kernel's tail; from here on its results (cache rows, Q, scratch) are read
 
     const int cta = blockIdx.x;
     int tile = cta_first_tile(p, cta); const int tile_end = cta_first_tile(p, cta + 1);
@@ -335,7 +336,8 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
     __shared__ float s_wt[160]; __shared__ float s_acc[3][256]; __shared__ float s_M, s_L;
     const int r = blockIdx.x, seg = blockIdx.y, b = seg >> 2, kvh = seg & 3, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
     const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvh * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
-    asm volatile("griddepcontrol.wait;" ::: "memory");   // the decode kernel's partials are complete and visible from here on
+    pdl_wait();              // the decode kernel's partials are complete and visible from here on
+    pdl_launch_dependents();
     if (n_c == 1) return;   // a single contributor wrote the final row itself
     if (tid < 32) {
         float M = -INFINITY;
@@ -402,7 +404,8 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
     int max_contrib = 1;   // contributors of the most-split segment decide where the merge runs
     {
-        auto cta_of = [&](int tile) { const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
+        auto cta_of = [&](int tile) {
+            const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
         for (int i = 0; i < b.n; i++) for (int kv = 0; kv < 4; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; max_contrib = std::max(max_contrib, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
     }
     p.merge_in_kernel = max_contrib <= 8;
@@ -413,14 +416,12 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
         if (e != cudaSuccess) return e;
         attr_set[i8] = true;
     }
-    if (i8) decode_mma_kernel<true><<<n_ctas, kThreads, Geo<true>::kSmem, s>>>(mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
-    else decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    const cudaError_t le = i8 ? launch_pdl(decode_mma_kernel<true>, dim3(n_ctas), dim3(kThreads), Geo<true>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
+                              : launch_pdl(decode_mma_kernel<false>, dim3(n_ctas), dim3(kThreads), Geo<false>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    if (le != cudaSuccess) return le;
     c.launches++;
     if (!p.merge_in_kernel) {
-        cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(6 * T, 4 * b.n); cfg.blockDim = dim3(kCombineThreads); cfg.dynamicSmemBytes = 0; cfg.stream = s;
-        cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, decode_combine_kernel, p, gate, out, (int)(out_dtype == KATA_ACT_BF16), part_out, (const float*)c.part_o, (const float*)c.part_ml);
+        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, 4 * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)(out_dtype == KATA_ACT_BF16), part_out, (const float*)c.part_o, (const float*)c.part_ml);
         if (e != cudaSuccess) return e;
         c.launches++;
     }

@@ -1,6 +1,7 @@
 // Internal declarations shared by the translation units of libkata_attn: the context object, the per-call batch
 // descriptor handed to kernels by value, and the launcher prototypes.
 #pragma once
+#include <utility>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <cuda.h>
@@ -64,6 +65,20 @@ cudaError_t launch_decode_scalar(Ctx& c, const Batch& b, int T, int first_pos, c
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
 void set_inv_freq(const float* host32);   // uploads the 32 inverse RoPE frequencies to constant memory of the current device
 // rank-3 map over an arena [rows][4][256 elements of elt bytes]; box = {box_inner elements, 1, box_rows}; returns false on failure
+// Launch with programmatic stream serialisation: the grid is set up (and its CTAs may start) while the previous kernel of the stream drains.
+// Such a kernel must execute griddepcontrol.wait (pdl_wait below) before it touches anything an earlier kernel wrote.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg{}; cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }                  // every earlier kernel of the stream is complete and visible
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }   // the next kernel may be set up from now on
+#endif
+
 bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows);
 bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128);
 bool make_tile_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_rows, int box_blocks);

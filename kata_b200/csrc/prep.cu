@@ -66,6 +66,7 @@ template <typename TIn, bool INT8>
 __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, const TIn* __restrict__ qfull, const TIn* __restrict__ kproj, const TIn* __restrict__ vproj,
                                                    const float* __restrict__ qnorm, const float* __restrict__ knorm, __half* __restrict__ q16, float* __restrict__ q32, float* __restrict__ gate,
                                                    void* k_arena, void* v_arena, __half* ksc, __half* vsc, const int h0, const int nh, const int round_mode) {
+    pdl_wait(); pdl_launch_dependents();   // launched with programmatic stream serialisation
     const int lane = threadIdx.x & 31, slot = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (slot >= nh) return;
     const int h = h0 + slot, t = blockIdx.y, bi = blockIdx.z;
@@ -142,10 +143,12 @@ cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const 
                         const float* qnorm, const float* knorm, __half* q16, float* q32, float* gate, int h0, int nh, cudaStream_t s) {
     const dim3 grid((nh + 7) / 8, T, b.n), block(256);
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
-#define KATA_PREP(TIN, I8) prep_kernel<TIN, I8><<<grid, block, 0, s>>>(b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, c.cfg.quant_round)
+    cudaError_t le = cudaSuccess;
+#define KATA_PREP(TIN, I8) le = launch_pdl(prep_kernel<TIN, I8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round)
     if (act_dtype == KATA_ACT_F32) { if (i8) KATA_PREP(float, true); else KATA_PREP(float, false); }
     else { if (i8) KATA_PREP(__nv_bfloat16, true); else KATA_PREP(__nv_bfloat16, false); }
 #undef KATA_PREP
+    if (le != cudaSuccess) return le;
     c.launches++;
     return cudaGetLastError();
 }
