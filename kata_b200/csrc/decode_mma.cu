@@ -32,8 +32,8 @@ namespace {
 using namespace ptx;
 
 constexpr int kRings = 4, kWarps = 3 * kRings + 1, kThreads = kWarps * 32, kMaxStages = 8;
-constexpr int kOffBars = 16 * kQStride;             // 8448: per ring and stage a 'full' and an 'empty' barrier, then the merge barrier
-constexpr int kOffEBars = kRings * kMaxStages * 8, kOffMBar = 2 * kOffEBars, kOffPBars = kOffMBar + 16;                      // inside the barrier block: per ring two 'P full' and two 'P empty' barriers
+constexpr int kOffBars = 16 * kQStride;             // 8448: the barrier block: per ring and stage a 'full' and an 'empty' barrier,
+constexpr int kOffEBars = kRings * kMaxStages * 8, kOffPBars = 2 * kOffEBars;   // inside the barrier block: then per ring two 'P full' and two 'P empty' barriers
 constexpr int kOffQsum = kOffBars + 704;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
 constexpr int kOffMl = kOffQsum + 64;               // per-ring (m, l) exchange: [4][16][2] floats = 512 B
 constexpr int kOffPair = kOffMl + 512;              // per-ring hand-over from the score warp to the value warp: two slots of (P block 16 x 48 B, 16 rescale factors)
@@ -82,11 +82,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
     float* sm_ml = reinterpret_cast<float*>(smem + kOffMl);
     const uint32_t p_sm = sm_base + kOffPair + ring * kPairBytes;
     const uint32_t pfull = sm_base + kOffBars + kOffPBars + ring * 16, pempty = pfull + kRings * 16;
-    __shared__ int s_flag; __shared__ float s_ML[24];
-    const uint32_t merge_bar = sm_base + kOffBars + kOffMBar; uint32_t merge_phase = 0;
+    __shared__ int s_flag;
 
     if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 3); } for (int s = 0; s < 2; s++) { mbar_init(pfull + s * 8, 1); mbar_init(pempty + s * 8, 2); } }
-    if (tid == 0) { mbar_init(merge_bar, 1); mbar_init(merge_bar + 8, 1); }
     fence_mbar_init();
     __syncthreads();
     pdl_wait();   // launched with programmatic stream serialisation: everything above overlapped the previous kernel's tail; from here on its results (cache rows, Q, scratch) are read
@@ -263,60 +261,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             if (tid == 0) { const int old = atomicAdd(&counters[seg], 1); s_flag = (old == n_contrib - 1); }
             __syncthreads();
             if (s_flag) {
-                // Every contributor's partial is visible (ticket + fences). Weights first (tiny), then the O rows are pulled
-                // into shared memory with bulk async copies (one per contributor) so the whole merge takes a few microseconds.
+                // Every contributor's partial is visible (ticket + fences). At most 8 contributors: every thread pulls its two dims of its rows straight
+                // from L2 (independent loads), forms the row maximum and the weights exp(m - M), and emits the final rows.
                 __threadfence();
-                asm volatile("fence.proxy.async;" ::: "memory");
-                float* wl = reinterpret_cast<float*>(smem + stage_off);          // [n_contrib][rows][2]: m (then weight), l
-                const int wl_bytes = (n_contrib * rows * 8 + 127) & ~127;
-                for (int i = tid; i < n_contrib * rows * 2; i += kThreads) { const int c = i / (rows * 2), k = i - c * (rows * 2); wl[i] = __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + k); }
-                __syncthreads();
-                {   // per row: maximum, weights exp(m - M) and the merged l; 16 threads share a row
-                    const int r = tid >> 4, sub = tid & 15; const bool live = r < rows;
+                for (int r = merger ? rsel : rows; r < rows; r += kThreads / 128) {
                     float M = -INFINITY;
-                    if (live) for (int c = sub; c < n_contrib; c += 16) M = fmaxf(M, wl[(c * rows + r) * 2]);
-#pragma unroll
-                    for (int off = 8; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-                    float L = 0.0f;
-                    if (live) for (int c = sub; c < n_contrib; c += 16) { const float mm = wl[(c * rows + r) * 2]; const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M); L += wl[(c * rows + r) * 2 + 1] * wt; wl[(c * rows + r) * 2] = wt; }
-#pragma unroll
-                    for (int off = 8; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
-                    if (live && sub == 0) { s_ML[r * 2] = M; s_ML[r * 2 + 1] = L; }
-                }
-                __syncthreads();
-                // O rows: two half-buffers, the copies of the next group of contributors fly while this group is accumulated
-                const int per = rows * 1024, cap = ((kRings * G::kRingBytes - wl_bytes) / 2) / per, n_groups = (n_contrib + cap - 1) / cap;
-                const uint32_t obuf = sm_base + stage_off + wl_bytes; const uint32_t half_bytes = (uint32_t)(cap * per);
-                auto issue_group = [&](int k) {
-                    const int base = k * cap, cnt = min(cap, n_contrib - base); const uint32_t mb = merge_bar + 8u * (uint32_t)(k & 1);
-                    if (tid < 32) {
-                        if (tid == 0) mbar_arrive_expect_tx(mb, (uint32_t)(cnt * per));
-                        __syncwarp();
-                        for (int c = tid; c < cnt; c += 32) bulk_g2s(obuf + (k & 1) * half_bytes + c * per, scratch_o + (int64_t)(c_first + base + c + seg) * (12 * kD), (uint32_t)per, mb);
-                    }
-                };
-                constexpr int kRS = kThreads / 128, kRR = 12 / kRS;   // row step and rows per thread of the merge
-                float A[kRR][2];
-#pragma unroll
-                for (int r = 0; r < kRR; r++) { A[r][0] = 0.0f; A[r][1] = 0.0f; }
-                issue_group(0);
-                for (int k = 0; k < n_groups; k++) {
-                    if (k + 1 < n_groups) issue_group(k + 1);
-                    if (!mbar_wait_bounded(merge_bar + 8u * (uint32_t)(k & 1), (merge_phase >> (k & 1)) & 1u, err)) { atomicExch(err, 2); }
-                    merge_phase ^= 1u << (k & 1);
-                    const int base = k * cap, cnt = min(cap, n_contrib - base);
-                    const uint8_t* ob = smem + stage_off + wl_bytes + (k & 1) * half_bytes + d0 * 4;
+                    for (int c = 0; c < n_contrib; c++) M = fmaxf(M, __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2));
+                    float L = 0.0f, A0 = 0.0f, A1 = 0.0f;
 #pragma unroll 4
-                    for (int c = 0; c < cnt; c++) {
-#pragma unroll
-                        for (int rr = 0; rr < kRR; rr++) { const int r = kRS * rr + rsel; if (merger && r < rows) {
-                            const float wt = wl[((base + c) * rows + r) * 2]; const float2 v = *reinterpret_cast<const float2*>(ob + (c * rows + r) * 1024);
-                            A[rr][0] += wt * v.x; A[rr][1] += wt * v.y; } }
+                    for (int c = 0; c < n_contrib; c++) {
+                        const int64_t sl = c_first + c + seg; const float mm = __ldcg(scratch_ml + sl * 32 + r * 2); const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
+                        const float2 oo = __ldcg(reinterpret_cast<const float2*>(scratch_o + sl * (12 * kD) + r * kD + d0));
+                        L += __ldcg(scratch_ml + sl * 32 + r * 2 + 1) * wt; A0 += oo.x * wt; A1 += oo.y * wt;
                     }
-                    __syncthreads();
+                    emit(r, M, L, A0, A1);
                 }
-#pragma unroll
-                for (int rr = 0; rr < kRR; rr++) { const int r = kRS * rr + rsel; if (merger && r < rows) emit(r, s_ML[r * 2], s_ML[r * 2 + 1], A[rr][0], A[rr][1]); }
                 if (tid == 0) counters[seg] = 0;   // ready for the next call on this stream
             }
         }
@@ -384,6 +343,13 @@ __global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restric
 
 int decode_max_slots(int sm_count) { return sm_count + 4 * KATA_MAX_BATCH; }
 
+static int max_contributors(const DecPlan& p) {
+    auto cta_of = [&](int tile) { const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
+    int m = 1;
+    for (int i = 0; i < p.n; i++) for (int kv = 0; kv < 4; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; m = std::max(m, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
+    return m;
+}
+
 // key_off / kend_override serve the split-KV-across-GPUs call: local row = absolute key - key_off, rows [first_row, kend).
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s) {
@@ -402,13 +368,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     n_ctas = std::max(1, std::min(std::min(n_ctas, total), c.sm_count * 8));
     if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
-    int max_contrib = 1;   // contributors of the most-split segment decide where the merge runs
-    {
-        auto cta_of = [&](int tile) {
-            const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
-        for (int i = 0; i < b.n; i++) for (int kv = 0; kv < 4; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; max_contrib = std::max(max_contrib, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
-    }
-    p.merge_in_kernel = max_contrib <= 8;
+    p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
     if (!attr_set[i8]) {
         cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
@@ -502,12 +462,13 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     }
     for (int i = n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
     const int n_ctas = std::max(1, std::min(std::min(sd.sm_count, kStaticMaxCtas), total));
-    p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas; p.merge_in_kernel = 1;
+    p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas; p.merge_in_kernel = max_contributors(p) <= 8;
     CUtensorMap tm_k, tm_v;   // encoded on the host; no device memory involved
     if (!make_tile_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 16, 4) || !make_tile_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 16, 4)) return KATA_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
     if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
     decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,
                                                                          sd.scratch->part_o, sd.scratch->part_ml, sd.scratch->counters, &sd.scratch->err);
+    if (!p.merge_in_kernel) decode_combine_kernel<<<dim3(6 * T, 4 * n), kCombineThreads, 0, s>>>(p, d_gate, d_out, (int)(out_dtype == KATA_ACT_BF16), nullptr, sd.scratch->part_o, sd.scratch->part_ml);
     return cudaGetLastError() == cudaSuccess ? KATA_OK : KATA_ERR_CUDA;
 }
