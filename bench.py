@@ -30,7 +30,7 @@ if ROOT not in sys.path:
 import numpy as np
 
 N_LAYERS = 16
-NCU_TRAFFIC_RATIO = 1.035   # (dram__bytes_read + dram__bytes_write) / algorithmic bytes of decode_mma_kernel, profiles/decode_mma_kernel__decode_small.md
+NCU_TRAFFIC_RATIO = 1.028   # (dram__bytes_read + dram__bytes_write) / algorithmic bytes of decode_mma_kernel, profiles/decode_mma_kernel__decode_small.md
 WORKLOADS = {
     # name: (kind, batch per GPU, kv mode, max length, min length)
     "decode_b8": ("decode", 8, "fp16", 32768, 16384),
@@ -242,7 +242,7 @@ def run_decode(args, rank, world, kind_cfg):
         "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_src": pk["src"],
                      "frac_of_nominal_8TBs": ach / 8000.0, "us_per_launch": kern_ms * 1e3, "algorithmic_bytes_per_launch": bytes_per_launch,
-                     "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO, "traffic_note": "dram read+write bytes per launch, scaled from the ncu capture of the decode_small workload (139.0 MB for 134.3 MB algorithmic)"},
+                     "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO, "traffic_note": "dram read+write bytes per launch, scaled from the ncu capture of the decode_small workload (138.1 MB for 134.3 MB algorithmic)"},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         res["cpu_baseline"] = cpu_baseline_decode(ctx, lens, pos_timed0, B, kv_mode)
