@@ -4,9 +4,11 @@
 // online softmax, P rounded to fp16 before P.V, l summed from the unrounded p, output O / l * sigmoid(gate).
 //
 // One CTA = 128 query rows of one head (row r of the chunk sits at position pos_base + r and sees keys [0, pos_base + r]).
-//   warps 0-3  softmax: thread t owns query row t = tensor-memory lane t
-//   warp 4     TMA producer for Q (once) and the K tiles;  warp 5  TMA producer for the V tiles
-//   warp 6     issues the MMAs (one elected thread)
+//   warps 0-7  softmax: two threads per query row (tensor-memory lane = row): warp w < 4 takes the first 64 keys of a tile, warp w + 4
+//              the last 64; the pair exchanges its row maxima through shared memory (64-thread named barrier) once per tile, each
+//              writes its half of P, keeps its own partial l, and owns 128 of the 256 O columns for rescales and the epilogue
+//   warp 8     TMA producer for Q (once) and the K tiles;  warp 9  TMA producer for the V tiles
+//   warp 10    issues the MMAs (one elected thread)
 // Shared memory: Q, one K tile and one V tile of 128 keys, each 4 column blocks of [128 rows][128 bytes] with the
 // 128-byte swizzle, exactly as TMA writes them and as the MMA descriptors read them (Q, K: K-major; V: MN-major, so the
 // [key][dim] rows of the cache are used as they lie). Tensor memory (512 columns): O 128x256 fp32 in columns [0,256),
@@ -28,7 +30,7 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kTcThreads = 224, kBMq = 128, kBNk = 128;
+constexpr int kTcThreads = 352, kBMq = 128, kBNk = 128;
 constexpr int kBlk = 128 * 128;                  // one column block: 128 rows x 128 bytes
 constexpr int kTileB = 4 * kBlk;                 // 64 KB: a 128 x 256 fp16 tile
 constexpr int kSmemTc = 3 * kTileB + 1024 + 256; // Q, K, V + alignment slack + barriers
@@ -52,11 +54,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
     const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + 2 * kTileB, bars = base + 3 * kTileB;
     uint8_t* v_gen = smem_raw + (v_sm - sm0);
-    __shared__ uint32_t s_tmem;
+    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128];   // [tile parity][key half][row]: row maxima (and at the end the partial l) exchanged by the two threads of a row
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     if (tid == 0) {
-        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1) ? 128u : 1u);
+        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1) ? 256u : 1u);
         fence_mbar_init();
     }
     if (w == 0) tc5::tmem_alloc(smem_u32(&s_tmem), 512);
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     tc5::fence_after_sync();
     const uint32_t tmem = s_tmem, t_o = tmem, t_s0 = tmem + 256;
 
-    if (w == 4) {
+    if (w == 8) {
         // ---- Q once, then K tiles: K(j) may overwrite the buffer when S(j-1) has completed
         if (lane == 0) {
             mbar_arrive_expect_tx(bar(B_QFULL), kTileB);
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 for (int kb = 0; kb < 4; kb++) tma_load_3d(k_sm + kb * kBlk, &tm_k, kb * 64, kvh, row0 + j * kBNk, bar(B_KFULL));
             }
         }
-    } else if (w == 5) {
+    } else if (w == 9) {
         if (lane == 0) {
             for (int j = 0; j < n_tiles; j++) {
                 if (j >= 1 && !mbar_wait_bounded(bar(B_VEMPTY), (uint32_t)(j - 1) & 1u, err)) { atomicExch(err, 12); break; }
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 for (int kb = 0; kb < 4; kb++) tma_load_3d(v_sm + kb * kBlk, &tm_v, kb * 64, kvh, row0 + j * kBNk, bar(B_VFULL));
             }
         }
-    } else if (w == 6) {
+    } else if (w == 10) {
         if (lane == 0) {
             auto issue_s = [&](int j) {   // S(j) = Q K(j)^T: 4 column blocks x 4 k-steps of 16 dims
                 const uint32_t d = t_s0 + (uint32_t)(j & 1) * 128u;
@@ -115,64 +117,70 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             }
         }
     } else {
-        // ---- softmax warps: thread = query row
-        const int r = tid, qpos = pos_base + q0 + r;               // this row sees keys <= qpos (and < kend)
+        // ---- softmax warps: two threads per query row, split by key half
+        const int g = w >> 2, r = tid & 127, qpos = pos_base + q0 + r;               // this row sees keys <= qpos (and < kend)
         const int lim = min(kend, qpos + 1);
-        const uint32_t lane_sel = (uint32_t)(w * 32) << 16;
+        const uint32_t lane_sel = (uint32_t)((w & 3) * 32) << 16;
+        const int pair_bar = 1 + (w & 3);   // named barrier of warps w and w + 4 (64 threads)
         float m = -INFINITY, l = 0.0f; bool alive = true;
-        for (int j = 0; j < n_tiles && alive; j++) {
+        // Every thread runs every iteration and meets its partner at the pair barrier whatever happens: a wait that ran out only switches the work off.
+        for (int j = 0; j < n_tiles; j++) {
             const uint32_t t_s = t_s0 + (uint32_t)(j & 1) * 128u + lane_sel;
-            if (!warp_wait(bar(B_SFULL0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; break; }
+            if (alive && !warp_wait(bar(B_SFULL0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
             tc5::fence_after_sync();
-            uint32_t v[4][32];
+            uint32_t v[2][32];
 #pragma unroll
-            for (int c = 0; c < 4; c++) tc5::ld32(t_s + c * 32, v[c]);
+            for (int c = 0; c < 2; c++) tc5::ld32(t_s + g * 64 + c * 32, v[c]);
             tc5::wait_ld();
-            const int key0 = j * kBNk;
-            if (key0 + kBNk > min(kend, pos_base + q0 + 1)) {   // the tile reaches past what the first row may see: mask by select
+            const int key0 = j * kBNk + g * 64;
+            if (j * kBNk + kBNk > min(kend, pos_base + q0 + 1)) {   // the tile reaches past what the first row may see: mask by select
 #pragma unroll
-                for (int c = 0; c < 4; c++)
+                for (int c = 0; c < 2; c++)
 #pragma unroll
                     for (int i = 0; i < 32; i++) if (key0 + c * 32 + i >= lim) v[c][i] = 0xff800000u;   // -inf
             }
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+            for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[c][i]));
-            const float mt = mx * kLog2e;
+            s_xmax[j & 1][g][r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // both halves of the row's scores are in registers and both maxima are visible
+            do {
+            if (!alive) break;
+            const float mt = fmaxf(mx, s_xmax[j & 1][g ^ 1][r]) * kLog2e;
             const bool need = (j == 0) ? false : (mt > m + 8.0f);
             if (j == 0) m = mt;
-            if (__any_sync(0xffffffffu, need)) {   // raise the reference maximum: rescale this warp's O rows after the previous P.V has landed
+            if (__any_sync(0xffffffffu, need)) {   // raise the reference maximum: rescale this thread's half of the O row after the previous P.V has landed
                 if (!warp_wait(bar(B_ODONE), (uint32_t)(j - 1) & 1u, err)) { atomicExch(err, 17); alive = false; break; }
                 tc5::fence_after_sync();
                 const float alpha = need ? ex2(m - mt) : 1.0f;
                 if (need) { m = mt; l *= alpha; }
 #pragma unroll 1
-                for (int c = 0; c < 8; c++) {
-                    uint32_t o[32]; tc5::ld32(t_o + lane_sel + c * 32, o); tc5::wait_ld();
+                for (int c = 0; c < 4; c++) {
+                    uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tc5::st32(t_o + lane_sel + c * 32, o);
+                    tc5::st32(t_o + lane_sel + g * 128 + c * 32, o);
                 }
                 tc5::wait_st();
             }
             const float msub = (m == -INFINITY) ? 0.0f : m;
-            float sum = 0.0f; uint32_t pk[2][32];
+            float sum = 0.0f; uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+            for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ex2(fmaf(__uint_as_float(v[c][i]), kLog2e, -msub)), p1 = ex2(fmaf(__uint_as_float(v[c][i + 1]), kLog2e, -msub));
-                    sum += p0 + p1; pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_h2(p0, p1);
+                    sum += p0 + p1; pk[c * 16 + (i >> 1)] = pack_h2(p0, p1);
                 }
             l += sum;
-            tc5::st32(t_s, pk[0]); tc5::st32(t_s + 32, pk[1]);
+            tc5::st32(t_s + g * 32, pk);   // P: keys 0-63 in columns [0,32), keys 64-127 in [32,64) of the S buffer (the partner's scores there are in its registers since the pair barrier)
             tc5::wait_st();
-            if (key0 + kBNk > kend) {   // tail tile: rows of V past the range were loaded as they lie in memory; zero them (0 x garbage must stay 0)
+            if (j * kBNk + kBNk > kend) {   // tail tile: rows of V past the range were loaded as they lie in memory; zero them (0 x garbage must stay 0)
                 // P(j-1).V(j-1) done first, so that the V barrier cannot still be in the phase of tile j-1 when its parity is tested
                 if ((j >= 1 && !warp_wait(bar(B_ODONE), (uint32_t)(j - 1) & 1u, err)) || !warp_wait(bar(B_VFULL), (uint32_t)j & 1u, err)) { atomicExch(err, 18); alive = false; break; }
-                if (key0 + r >= kend) {
+                if (g == 0 && j * kBNk + r >= kend) {
 #pragma unroll
                     for (int kb = 0; kb < 4; kb++)
 #pragma unroll
@@ -182,15 +190,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             }
             tc5::fence_before_sync();
             mbar_arrive(bar(B_PREADY0 + (j & 1)));
+            } while (0);
         }
-        // ---- epilogue: O / l * sigmoid(gate)
+        // ---- epilogue: O / l * sigmoid(gate); the two threads of a row add their partial l and write 128 columns each
+        s_xmax[n_tiles & 1][g][r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        l += s_xmax[n_tiles & 1][g ^ 1][r];
         if (alive && warp_wait(bar(B_ODONE), (uint32_t)(n_tiles - 1) & 1u, err)) {
             tc5::fence_after_sync();
             const float inv = 1.0f / l; const bool store = r < rows_valid;
-            const int64_t obase = ((int64_t)bi * M + q0 + r) * kQD + h * kD;
+            const int64_t obase = ((int64_t)bi * M + q0 + r) * kQD + h * kD + g * 128;
 #pragma unroll 1
-            for (int c = 0; c < 8; c++) {
-                uint32_t o[32]; tc5::ld32(t_o + lane_sel + c * 32, o); tc5::wait_ld();
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
                 if (store) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
