@@ -96,11 +96,11 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
         ok = cudaMalloc((void**)&c.sc_pm, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess && cudaMalloc((void**)&c.sc_pl, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess &&
              cudaMalloc((void**)&c.sc_pacc, kata::scalar_scratch_floats_acc() * 4) == cudaSuccess;
     if (!ok) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_NOMEM; }
-    {   // decode: rank-4 tile views (a 128-byte column block = 64 fp16 or 128 int8 elements); tcgen05 prefill (fp16): 128-row boxes of 64 columns
+    {   // decode: rank-4 tile views (a 128-byte column block = 64 fp16 or 128 int8 elements); tcgen05 prefill (fp16): the half tiles of a CTA pair
         const int blocks = 256 * c.elt / 128;
         const int tile_rows = c.elt == 1 ? 32 : 16;   // keys per decode tile
         if (!kata::make_tile_tmap(&c.tm_k_tile, c.k_arena, c.elt, rows, tile_rows, blocks) || !kata::make_tile_tmap(&c.tm_v_tile, c.v_arena, c.elt, rows, tile_rows, blocks) ||
-            (c.elt == 2 && (!kata::make_arena_tmap(&c.tm_k128, c.k_arena, 2, rows, 64, 128, true) || !kata::make_arena_tmap(&c.tm_v128, c.v_arena, 2, rows, 64, 128, true)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
+            (c.elt == 2 && (!kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);
     float invf[32]; for (int i = 0; i < 32; i++) invf[i] = powf(10000000.0f, -(float)i / 32.0f);   // shaders/attn.metal:26

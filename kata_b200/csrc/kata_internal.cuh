@@ -45,7 +45,7 @@ struct Ctx {
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
     // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
     CUtensorMap tm_k_tile{}, tm_v_tile{};   // rank-4 views for decode: one TMA instruction per 16-key tile of one KV head
-    CUtensorMap tm_k128{}, tm_v128{};   // the same arenas with 128-row boxes (tcgen05 prefill tiles; fp16 mode)
+    CUtensorMap tm_k64h{}, tm_v128h{};   // rank-4 views for the tcgen05 prefill (fp16 mode): 64 keys x 256 dims of K, 128 keys x 128 dims of V (the halves a CTA of a pair loads)
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
     int sm_count = 148;
     uint64_t launches = 0;

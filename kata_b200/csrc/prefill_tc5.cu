@@ -3,22 +3,27 @@
 // 614) with the same math: fp16 Q (prescaled by 1/16) x fp16 K -> fp32 scores, causal mask key > position -> -inf,
 // online softmax, P rounded to fp16 before P.V, l summed from the unrounded p, output O / l * sigmoid(gate).
 //
-// One CTA = 128 query rows of one head (row r of the chunk sits at position pos_base + r and sees keys [0, pos_base + r]).
+// Two CTAs (a cluster, cta_group::2) = 128 query rows of two heads of the same KV-head group (row r of the chunk sits at position
+// pos_base + r and sees keys [0, pos_base + r]). The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
+// accumulators and half of every K tile (64 of the 128 keys) and V tile (128 of the 256 dims); the tensor cores of the two SMs exchange
+// the halves, so each SM writes and reads half the K/V bytes through its shared memory, which is what bounds an M = 128 tile with
+// 256-wide heads (Q, K, V tiles plus their TMA writes ask for more than the 128 bytes per clock an SM's shared memory delivers).
 //   warps 0-7  softmax: two threads per query row (tensor-memory lane = row): warp w < 4 takes the first 64 keys of a tile, warp w + 4
 //              the last 64; the pair exchanges its row maxima through shared memory (64-thread named barrier) once per tile, each
 //              writes its half of P, keeps its own partial l, and owns 128 of the 256 O columns for rescales and the epilogue
-//   warp 8     TMA producer for Q (once) and the K tiles;  warp 9  TMA producer for the V tiles
-//   warp 10    issues the MMAs (one elected thread)
-// Shared memory: Q, one K tile and one V tile of 128 keys, each 4 column blocks of [128 rows][128 bytes] with the
-// 128-byte swizzle, exactly as TMA writes them and as the MMA descriptors read them (Q, K: K-major; V: MN-major, so the
-// [key][dim] rows of the cache are used as they lie). Tensor memory (512 columns): O 128x256 fp32 in columns [0,256),
-// two score buffers S0, S1 of 128x128 fp32 in [256,384) and [384,512); P (fp16, two per column) overwrites the first 64
-// columns of its S buffer and is the tensor-memory A operand of P.V.
+//   warp 8     TMA producer for Q (once) and the K half-tiles;  warp 9  TMA producer for the V half-tiles
+//   warp 10    (even CTA only) issues the MMAs and commits for both CTAs (one elected thread)
+// Shared memory per CTA: Q (4 column blocks of [128 rows][128 bytes]), two stages of a K half-tile (4 blocks of [64 keys][128 bytes]) and
+// two stages of a V half-tile (2 blocks of [128 keys][128 bytes]), all with the 128-byte swizzle, exactly as TMA writes them and as the MMA
+// descriptors read them (Q, K: K-major; V: MN-major, so the [key][dim] rows of the cache are used as they lie). TMA loads of both CTAs count
+// their bytes on the even CTA's 'full' barriers; 'empty', 'scores ready' and 'O done' are committed to both CTAs at once.
+// Tensor memory (512 columns per CTA): O 128x256 fp32 in columns [0,256), two score buffers S0, S1 of 128x128 fp32 in [256,384) and
+// [384,512); P (fp16, two per column) overwrites the first 64 columns of its S buffer and is the tensor-memory A operand of P.V.
 // Pipeline: the MMA thread issues S(j+1) = Q.K(j+1)^T before P(j).V(j), so the tensor pipe computes the next scores while
-// the softmax warps work on the current ones; K(j+1) is loaded as soon as S(j) has completed, V(j+1) as soon as P(j).V(j)
-// has. The running maximum is only raised when a row's new maximum exceeds it by more than 8 (in log2 units); then the
-// whole warp rescales its O rows in tensor memory after waiting for the previous P.V. P stays below 2^8, well inside fp16.
-// Every wait is bounded and shares the context's abort word; tensor memory is always released before the CTA exits.
+// the softmax warps work on the current ones; K and V tiles are loaded one tile ahead. The running maximum is only raised when a row's
+// new maximum exceeds it by more than 8 (in log2 units); then the warp rescales its O rows in tensor memory after waiting for the
+// previous P.V. P stays below 2^8, well inside fp16.
+// Every wait is bounded and shares the context's abort word; tensor memory is always released before the CTAs exit.
 #include <algorithm>
 
 #include "kata_internal.cuh"
@@ -31,13 +36,15 @@ namespace {
 using namespace ptx;
 
 constexpr int kTcThreads = 352, kBMq = 128, kBNk = 128;
-constexpr int kBlk = 128 * 128;                  // one column block: 128 rows x 128 bytes
-constexpr int kTileB = 4 * kBlk;                 // 64 KB: a 128 x 256 fp16 tile
-constexpr int kSmemTc = 3 * kTileB + 1024 + 256; // Q, K, V + alignment slack + barriers
-constexpr uint32_t kIdescS = tc5::idesc_f16(128, 128, false), kIdescPV = tc5::idesc_f16(128, 256, true);
+constexpr int kBlk = 128 * 128;                  // one column block of 128 rows x 128 bytes (Q, V)
+constexpr int kBlkKh = 64 * 128;                 // one column block of a K half-tile: 64 keys x 128 bytes
+constexpr int kTileB = 4 * kBlk;                 // 64 KB: the 128 x 256 fp16 Q block
+constexpr int kHalfB = 32 * 1024;                // a K or V half-tile
+constexpr int kSmemTc = kTileB + 4 * kHalfB + 1024 + 256; // Q, 2 x K half, 2 x V half + alignment slack + barriers
+constexpr uint32_t kIdescS = tc5::idesc_f16(256, 128, false), kIdescPV = tc5::idesc_f16(256, 256, true);
 
 // barrier slots (8 bytes each) after the tiles
-enum { B_QFULL = 0, B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY, B_SFULL0, B_SFULL1, B_PREADY0, B_PREADY1, B_ODONE, B_COUNT };
+enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_VLANDED, B_SFULL0, B_SFULL1, B_PREADY0, B_PREADY1, B_ODONE, B_COUNT };
 
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const int32_t* abort_flag) {   // same outcome for every lane of the warp
     const bool ok = mbar_wait_bounded(bar, parity, abort_flag);
@@ -48,72 +55,80 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                                                                    const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, bi = blockIdx.z, kvh = h / kG;   // longest query tiles first
+    const int qt = gridDim.y - 1 - blockIdx.y, h = blockIdx.x, bi = blockIdx.z, kvh = h / kG;   // longest query tiles first; heads 2i and 2i+1 form a pair (same KV head)
+    const uint32_t rank = tc5::cluster_rank();
     const int q0 = qt * kBMq, rows_valid = min(kBMq, M - q0), pos_base = b.pos[bi], kend = pos_base + q0 + rows_valid, n_tiles = (kend + kBNk - 1) / kBNk;
     const int row0 = (int)b.row_base[bi];
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
-    const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + 2 * kTileB, bars = base + 3 * kTileB;
-    uint8_t* v_gen = smem_raw + (v_sm - sm0);
+    const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + kTileB + 2 * kHalfB, bars = base + kTileB + 4 * kHalfB;   // K stage s at k_sm + s * kHalfB, V stage s at v_sm + s * kHalfB
     __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128];   // [tile parity][key half][row]: row maxima (and at the end the partial l) exchanged by the two threads of a row
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     if (tid == 0) {
-        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1) ? 256u : 1u);
+        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1) ? 16u : 1u);   // 'P ready': one arrival per softmax warp of both CTAs
         fence_mbar_init();
     }
-    if (w == 0) tc5::tmem_alloc(smem_u32(&s_tmem), 512);
+    __syncthreads();
+    tc5::cluster_sync_all();   // both CTAs' barriers exist before anything arrives on them from the other side
+    if (w == 0) tc5::tmem_alloc2(smem_u32(&s_tmem), 512);
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem = s_tmem, t_o = tmem, t_s0 = tmem + 256;
 
     if (w == 8) {
-        // ---- Q once, then K tiles: K(j) may overwrite the buffer when S(j-1) has completed
+        // ---- Q once, then this CTA's half (64 keys) of every K tile, one tile ahead: stage j & 1 is free when S(j-2) has completed
         if (lane == 0) {
-            mbar_arrive_expect_tx(bar(B_QFULL), kTileB);
-            for (int kb = 0; kb < 4; kb++) tma_load_2d(q_sm + kb * kBlk, &tm_q, h * kD + kb * 64, bi * M + q0, bar(B_QFULL));
+            if (rank == 0) mbar_arrive_expect_tx(bar(B_QFULL), 2 * kTileB);
+            for (int kb = 0; kb < 4; kb++) tc5::tma_load_2d_pair(q_sm + kb * kBlk, &tm_q, h * kD + kb * 64, bi * M + q0, bar(B_QFULL));
             for (int j = 0; j < n_tiles; j++) {
-                if (j >= 1 && !mbar_wait_bounded(bar(B_KEMPTY), (uint32_t)(j - 1) & 1u, err)) { atomicExch(err, 11); break; }
-                mbar_arrive_expect_tx(bar(B_KFULL), kTileB);
-                for (int kb = 0; kb < 4; kb++) tma_load_3d(k_sm + kb * kBlk, &tm_k, kb * 64, kvh, row0 + j * kBNk, bar(B_KFULL));
+                const int st = j & 1;
+                if (j >= 2 && !mbar_wait_bounded(bar(B_KEMPTY0 + st), (uint32_t)((j >> 1) - 1) & 1u, err)) { atomicExch(err, 11); break; }
+                if (rank == 0) mbar_arrive_expect_tx(bar(B_KFULL0 + st), 2 * kHalfB);
+                tc5::tma_load_4d_pair(k_sm + st * kHalfB, &tm_k, 0, row0 + j * kBNk + 64 * (int)rank, 0, kvh, bar(B_KFULL0 + st));
             }
         }
     } else if (w == 9) {
+        // ---- this CTA's half (128 dims) of every V tile
         if (lane == 0) {
             for (int j = 0; j < n_tiles; j++) {
-                if (j >= 1 && !mbar_wait_bounded(bar(B_VEMPTY), (uint32_t)(j - 1) & 1u, err)) { atomicExch(err, 12); break; }
-                mbar_arrive_expect_tx(bar(B_VFULL), kTileB);
-                for (int kb = 0; kb < 4; kb++) tma_load_3d(v_sm + kb * kBlk, &tm_v, kb * 64, kvh, row0 + j * kBNk, bar(B_VFULL));
+                const int st = j & 1;
+                if (j >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), (uint32_t)((j >> 1) - 1) & 1u, err)) { atomicExch(err, 12); break; }
+                if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
+                tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, row0 + j * kBNk, 2 * (int)rank, kvh, bar(B_VFULL0 + st));
             }
         }
     } else if (w == 10) {
-        if (lane == 0) {
-            auto issue_s = [&](int j) {   // S(j) = Q K(j)^T: 4 column blocks x 4 k-steps of 16 dims
-                const uint32_t d = t_s0 + (uint32_t)(j & 1) * 128u;
+        if (lane == 0 && rank == 0) {
+            auto issue_s = [&](int j) {   // S(j) = Q K(j)^T for both CTAs: 4 column blocks x 4 k-steps of 16 dims
+                const uint32_t d = t_s0 + (uint32_t)(j & 1) * 128u, kst = k_sm + (uint32_t)(j & 1) * kHalfB;
 #pragma unroll
                 for (int kb = 0; kb < 4; kb++)
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
-                        tc5::mma_ss(d, tc5::smem_desc_sw128(q_sm + kb * kBlk + ks * 32, 16, 1024), tc5::smem_desc_sw128(k_sm + kb * kBlk + ks * 32, 16, 1024), kIdescS, (kb | ks) != 0);
-                tc5::commit(bar(B_SFULL0 + (j & 1)));
-                tc5::commit(bar(B_KEMPTY));
+                        tc5::mma_ss2(d, tc5::smem_desc_sw128(q_sm + kb * kBlk + ks * 32, 16, 1024), tc5::smem_desc_sw128(kst + kb * kBlkKh + ks * 32, 16, 1024), kIdescS, (kb | ks) != 0);
+                tc5::commit2(bar(B_SFULL0 + (j & 1)));
+                tc5::commit2(bar(B_KEMPTY0 + (j & 1)));
             };
-            bool ok = mbar_wait_bounded(bar(B_QFULL), 0, err) && mbar_wait_bounded(bar(B_KFULL), 0, err);
+            bool ok = mbar_wait_bounded(bar(B_QFULL), 0, err) && mbar_wait_bounded(bar(B_KFULL0), 0, err);
             if (!ok) atomicExch(err, 13);
             if (ok) { tc5::fence_after_sync(); issue_s(0); }
             for (int j = 0; ok && j < n_tiles; j++) {
                 if (j + 1 < n_tiles) {
-                    if (!mbar_wait_bounded(bar(B_KFULL), (uint32_t)(j + 1) & 1u, err)) { atomicExch(err, 14); break; }
+                    if (!mbar_wait_bounded(bar(B_KFULL0 + ((j + 1) & 1)), (uint32_t)((j + 1) >> 1) & 1u, err)) { atomicExch(err, 14); break; }
                     tc5::fence_after_sync(); issue_s(j + 1);
                 }
-                if (!mbar_wait_bounded(bar(B_PREADY0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err) || !mbar_wait_bounded(bar(B_VFULL), (uint32_t)j & 1u, err)) { atomicExch(err, 15); break; }
+                // V(j) has landed in both CTAs: tell both (their softmax warps zero the rows past the range in the tail tile), then wait for P(j)
+                if (!mbar_wait_bounded(bar(B_VFULL0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 15); break; }
+                mbar_arrive(bar(B_VLANDED)); tc5::mbar_arrive_peer(bar(B_VLANDED));
+                if (!mbar_wait_bounded(bar(B_PREADY0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 15); break; }
                 tc5::fence_after_sync();
-                const uint32_t a = t_s0 + (uint32_t)(j & 1) * 128u;   // P(j): fp16 pairs in the first 64 columns of its S buffer
+                const uint32_t a = t_s0 + (uint32_t)(j & 1) * 128u, vst = v_sm + (uint32_t)(j & 1) * kHalfB;   // P(j): fp16 pairs in the first 64 columns of its S buffer
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++)   // 16 keys per step; V is MN-major: 64-dim blocks 16 KB apart, 8-key groups 1 KB apart
-                    tc5::mma_ts(t_o, a + ks * 8, tc5::smem_desc_sw128(v_sm + ks * 2048, kBlk, 1024), kIdescPV, (j | ks) != 0);
-                tc5::commit(bar(B_ODONE));
-                tc5::commit(bar(B_VEMPTY));
+                for (int ks = 0; ks < 8; ks++)   // 16 keys per step; V half is MN-major: 64-dim blocks 16 KB apart, 8-key groups 1 KB apart
+                    tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j | ks) != 0);
+                tc5::commit2(bar(B_ODONE));
+                tc5::commit2(bar(B_VEMPTY0 + (j & 1)));
             }
         }
     } else {
@@ -178,18 +193,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::st32(t_s + g * 32, pk);   // P: keys 0-63 in columns [0,32), keys 64-127 in [32,64) of the S buffer (the partner's scores there are in its registers since the pair barrier)
             tc5::wait_st();
             if (j * kBNk + kBNk > kend) {   // tail tile: rows of V past the range were loaded as they lie in memory; zero them (0 x garbage must stay 0)
-                // P(j-1).V(j-1) done first, so that the V barrier cannot still be in the phase of tile j-1 when its parity is tested
-                if ((j >= 1 && !warp_wait(bar(B_ODONE), (uint32_t)(j - 1) & 1u, err)) || !warp_wait(bar(B_VFULL), (uint32_t)j & 1u, err)) { atomicExch(err, 18); alive = false; break; }
+                // (the MMA thread announces every tile's V once it has landed in both CTAs)
+                if (!warp_wait(bar(B_VLANDED), (uint32_t)j & 1u, err)) { atomicExch(err, 18); alive = false; break; }
                 if (g == 0 && j * kBNk + r >= kend) {
+                    uint8_t* v_gen = smem_raw + (v_sm + (uint32_t)(j & 1) * kHalfB - sm0);
 #pragma unroll
-                    for (int kb = 0; kb < 4; kb++)
+                    for (int kb = 0; kb < 2; kb++)
 #pragma unroll
                         for (int c = 0; c < 8; c++) *reinterpret_cast<uint4*>(v_gen + kb * kBlk + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async();
             }
             tc5::fence_before_sync();
-            mbar_arrive(bar(B_PREADY0 + (j & 1)));
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive_leader(bar(B_PREADY0 + (j & 1)));
             } while (0);
         }
         // ---- epilogue: O / l * sigmoid(gate); the two threads of a row add their partial l and write 128 columns each
@@ -218,7 +235,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     }
     tc5::fence_before_sync();
     __syncthreads();
-    if (w == 0) tc5::tmem_dealloc(tmem, 512);
+    tc5::cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or arrive on its barriers
+    if (w == 0) tc5::tmem_dealloc2(tmem, 512);
 }
 
 }  // namespace
@@ -236,8 +254,11 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     }
     CUtensorMap tm_q;
     if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
-    const dim3 grid((M + kBMq - 1) / kBMq, kH, b.n);
-    prefill_tc5_kernel<<<grid, kTcThreads, kSmemTc, s>>>(tm_q, c.tm_k128, c.tm_v128, b, M, gate, out, out_dtype == KATA_ACT_BF16, c.d_err);
+    cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(kH, (M + kBMq - 1) / kBMq, b.n); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
+    cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // heads 2i, 2i+1 (a CTA pair is two neighbours along x)
+    cfg.attrs = at; cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, prefill_tc5_kernel, tm_q, c.tm_k64h, c.tm_v128h, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err);
+    if (le != cudaSuccess) return le;
     c.launches++;
     return cudaGetLastError();
 }
