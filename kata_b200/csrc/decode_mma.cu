@@ -6,21 +6,23 @@
 // P.V (after the V scale in int8 mode), l summed from the unrounded p, masked rows/keys at -inf, merge weights exp(m-M).
 //
 // Design (HBM-bound: 1 KiB of K+V per key and KV head at fp16, read exactly once):
-//  - The work is the list of 16-key tiles of every (sequence, KV head) segment. It is cut into one contiguous,
-//    equal-sized range per CTA (one CTA per SM), so ragged batches balance to within one tile and each key is read once.
-//  - Inside a CTA the tiles of the range go round-robin to 4 rings. A ring is a pair of warps on the same scheduler
-//    sharing a 3-stage shared-memory ring. A stage is filled by tiled TMA loads (16 rows x 128 bytes per box, 128-byte
-//    swizzle, so ldmatrix reads are bank-conflict free without padding), tracked by a 'full' mbarrier; an 'empty' mbarrier
-//    lets the issuing warp refill a stage the moment both warps have read it. Measured on B200: per-row bulk copies
-//    (one 512-byte copy per lane) capped the kernel near 4.9 TB/s because of the TMA unit's operation rate; boxes reach
-//    5.6 TB/s. Prefetching further ahead into L2 made it slower and is not used.
-//  - Q.K^T and P.V run on mma.sync m16n8k16 (fp16 in, fp32 accumulate) straight from ldmatrix fragments. The two warps
-//    of a ring split the tile: each scores its own 8 keys, they exchange row maxima and the fp16 P block through shared
-//    memory (two 64-thread named barriers), and each accumulates its own 128-dim half of O. The softmax state lives in
-//    registers and uses quad shuffles. int8 rows are dequantised in registers (byte permute onto the fp16 magic number
-//    1024+x, then subtract), with the per-key scales applied to S and to P as the reference does.
-//  - A CTA whose range ends inside a segment writes an unnormalised partial (O, m, l); the last CTA to finish a segment
-//    (atomic ticket) merges the partials, normalises, applies the gate and writes the output row. No second kernel.
+//  - The work is the list of tiles (16 keys at fp16, 32 at int8: 16 KiB of K+V) of every (sequence, KV head) segment. It is cut into
+//    one contiguous, equal-sized range per CTA (one CTA per SM), so ragged batches balance to within one tile and each key is read once.
+//  - Inside a CTA the tiles of the range go round-robin to 4 rings. A ring is a 3-stage shared-memory ring with three warps on one
+//    scheduler: a score warp (S = Q K^T, online softmax, P) and two value warps (O += P V on one half of the head dims each) that overlap
+//    across tiles through a two-slot P hand-over ('P full' / 'P empty' mbarriers). A 13th warp is the producer: its lane r refills ring
+//    r's stage as soon as the ring's three warps have released it ('full' / 'empty' mbarriers), with one TMA instruction per K tile and
+//    one per V tile (rank-4 tensor-map view of the arena, 128-byte swizzle, so ldmatrix reads are bank-conflict free without padding).
+//    Measured on B200: per-row bulk copies (one 512-byte copy per lane) capped the kernel near 4.9 TB/s because of the TMA unit's
+//    operation rate; 8 boxes per stage reached 5.8 TB/s but cost the issuing math warp ~600 clocks per tile; tile views issued by a
+//    warp of their own reach 6.1 TB/s at batch 8 and 6.8 TB/s at batch 64. Prefetching further ahead into L2 made it slower.
+//  - Q.K^T and P.V run on mma.sync m16n8k16 (fp16 in, fp32 accumulate) straight from ldmatrix fragments. The softmax state lives in
+//    registers and uses quad shuffles. int8 rows are dequantised in registers (byte permute onto the fp16 magic number 1024+x; the bias
+//    is taken out of the accumulators afterwards), with the per-key scales applied to S and to P as the reference does.
+//  - A CTA whose range ends inside a segment writes an unnormalised partial (O, m, l); with at most 8 contributors per segment the last
+//    CTA to finish it (atomic ticket) merges the partials straight from L2, normalises, applies the gate and writes the output row;
+//    segments split further (batch 1 at long context) are merged by decode_combine_kernel.
+//  - The kernels are launched with programmatic stream serialisation: barrier set-up overlaps the previous kernel's tail.
 // Every mbarrier wait is bounded; on a timeout the kernel records an error word and skips the arithmetic.
 #include <algorithm>
 
