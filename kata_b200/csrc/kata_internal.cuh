@@ -80,7 +80,6 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 #endif
 
 bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_cols, int box_rows);
-bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128);
 bool make_tile_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_rows, int box_blocks);
 
 }  // namespace kata

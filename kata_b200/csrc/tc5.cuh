@@ -94,10 +94,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar & kPeerBitMask) : "memory");
 }
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar & kPeerBitMask) : "memory");
-}
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void* tmap, int x, int y, int z, int w, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar & kPeerBitMask) : "memory");

@@ -25,18 +25,7 @@ bool make_matrix_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t 
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-bool make_arena_tmap(CUtensorMap* out, void* base, int elt, int64_t rows, int box_inner, int box_rows, bool swizzle128) {
-    PFN_cuTensorMapEncodeTiled encode = get_encode(); if (!encode) return false;
-    const cuuint64_t gdim[3] = {(cuuint64_t)kD, (cuuint64_t)kKvh, (cuuint64_t)rows};
-    const cuuint64_t gstride[2] = {(cuuint64_t)kD * elt, (cuuint64_t)kKVD * elt};   // bytes between heads, between rows
-    const cuuint32_t box[3] = {(cuuint32_t)box_inner, 1u, (cuuint32_t)box_rows};
-    const cuuint32_t estr[3] = {1u, 1u, 1u};
-    const CUresult r = encode(out, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
-// Rank-4 view of an arena for the decode kernel: a head row of 256 elements is cut into 128-byte column blocks and the block index is made
+// Rank-4 view of an arena for the decode and prefill kernels: a head row of 256 elements is cut into 128-byte column blocks and the block index is made
 // a dimension of its own, placed after the row dimension: {x: one 128-byte block, r: rows, c: blocks of the head row, h: KV heads}.
 // One box {block, box_rows rows, box_blocks blocks, 1 head} then brings a tile of box_rows keys of one head with a single TMA instruction
 // and lands in shared memory as [block][row][128 bytes], each block swizzled as a [rows][128-byte] box of a rank-3 map would be.
