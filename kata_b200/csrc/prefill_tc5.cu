@@ -3,8 +3,10 @@
 // 614) with the same math: fp16 Q (prescaled by 1/16) x fp16 K -> fp32 scores, causal mask key > position -> -inf,
 // online softmax, P rounded to fp16 before P.V, l summed from the unrounded p, output O / l * sigmoid(gate).
 //
-// Two CTAs (a cluster, cta_group::2) = 128 query rows of two heads of the same KV-head group (row r of the chunk sits at position
-// pos_base + r and sees keys [0, pos_base + r]). The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
+// A work item = 128 query rows of two heads of the same KV-head group (row r of the chunk sits at position pos_base + r and sees keys
+// [0, pos_base + r]), done by two CTAs (a cluster, cta_group::2). The kernel is persistent: one CTA pair per two SMs walks the items
+// (longest first, dealt round-robin) with its barriers, tensor memory and pipelines kept across items; the next item's Q, K and V loads and
+// first score MMAs run under the current item's epilogue. The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
 // accumulators and half of every K tile (64 of the 128 keys) and V tile (128 of the 256 dims); the tensor cores of the two SMs exchange
 // the halves, so each SM writes and reads half the K/V bytes through its shared memory, which is what bounds an M = 128 tile with
 // 256-wide heads (Q, K, V tiles plus their TMA writes ask for more than the 128 bytes per clock an SM's shared memory delivers).
@@ -44,28 +46,36 @@ constexpr int kSmemTc = kTileB + 4 * kHalfB + 1024 + 256; // Q, 2 x K half, 2 x 
 constexpr uint32_t kIdescS = tc5::idesc_f16(256, 128, false), kIdescPV = tc5::idesc_f16(256, 256, true);
 
 // barrier slots (8 bytes each) after the tiles
-enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_VLANDED, B_SFULL0, B_SFULL1, B_PREADY0, B_PREADY1, B_ODONE, B_COUNT };
+enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_VLANDED, B_SFULL0, B_SFULL1, B_PREADY0, B_PREADY1, B_ODONE, B_QEMPTY, B_OFREE, B_COUNT };
 
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const int32_t* abort_flag) {   // same outcome for every lane of the warp
     const bool ok = mbar_wait_bounded(bar, parity, abort_flag);
     return __all_sync(0xffffffffu, ok);
 }
 
+// One work item = (query tile, head pair, sequence); items are ordered longest first and dealt round-robin to the CTA pairs.
+struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, h, kvh, bi; };
+
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                                                                    const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-    const int qt = gridDim.y - 1 - blockIdx.y, h = blockIdx.x, bi = blockIdx.z, kvh = h / kG;   // longest query tiles first; heads 2i and 2i+1 form a pair (same KV head)
     const uint32_t rank = tc5::cluster_rank();
-    const int q0 = qt * kBMq, rows_valid = min(kBMq, M - q0), pos_base = b.pos[bi], kend = pos_base + q0 + rows_valid, n_tiles = (kend + kBNk - 1) / kBNk;
-    const int row0 = (int)b.row_base[bi];
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, n_items = n_q * per_q, n_pairs = gridDim.x / 2, pair = blockIdx.x / 2;
+    auto item_of = [&](int it) {   // it-th item of this CTA pair
+        const int idx = pair + it * n_pairs, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
+        PfItem t; t.bi = rem / (kH / 2); t.h = 2 * (rem % (kH / 2)) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
+        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = (int)b.row_base[t.bi];
+        return t;
+    };
+    const int my_items = pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
     const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + kTileB + 2 * kHalfB, bars = base + kTileB + 4 * kHalfB;   // K stage s at k_sm + s * kHalfB, V stage s at v_sm + s * kHalfB
-    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128];   // [tile parity][key half][row]: row maxima (and at the end the partial l) exchanged by the two threads of a row
+    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128], s_stage[8][32 * 17];   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     if (tid == 0) {
-        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1) ? 16u : 1u);   // 'P ready': one arrival per softmax warp of both CTAs
+        for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1 || i == B_OFREE) ? 16u : 1u);   // 'P ready', 'O free': one arrival per softmax warp of both CTAs
         fence_mbar_init();
     }
     __syncthreads();
@@ -75,73 +85,96 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem = s_tmem, t_o = tmem, t_s0 = tmem + 256;
+    // Running counters shared by construction: gt = key tiles so far over all items of this pair (stage, score buffer and phase of the
+    // per-tile barriers), it = items so far (phase of the per-item barriers).
 
     if (w == 8) {
-        // ---- Q once, then this CTA's half (64 keys) of every K tile, one tile ahead: stage j & 1 is free when S(j-2) has completed
+        // ---- per item Q (when the previous item's last S MMA has read the old one), then this CTA's half (64 keys) of every K tile, one tile
+        // ahead: stage gt & 1 is free when S(gt-2) has completed
         if (lane == 0) {
-            if (rank == 0) mbar_arrive_expect_tx(bar(B_QFULL), 2 * kTileB);
-            for (int kb = 0; kb < 4; kb++) tc5::tma_load_2d_pair(q_sm + kb * kBlk, &tm_q, h * kD + kb * 64, bi * M + q0, bar(B_QFULL));
-            for (int j = 0; j < n_tiles; j++) {
-                const int st = j & 1;
-                if (j >= 2 && !mbar_wait_bounded(bar(B_KEMPTY0 + st), (uint32_t)((j >> 1) - 1) & 1u, err)) { atomicExch(err, 11); break; }
-                if (rank == 0) mbar_arrive_expect_tx(bar(B_KFULL0 + st), 2 * kHalfB);
-                tc5::tma_load_4d_pair(k_sm + st * kHalfB, &tm_k, 0, row0 + j * kBNk + 64 * (int)rank, 0, kvh, bar(B_KFULL0 + st));
+            uint32_t gt = 0; bool ok = true;
+            for (int it = 0; ok && it < my_items; it++) {
+                const PfItem t = item_of(it);
+                if (it >= 1 && !mbar_wait_bounded(bar(B_QEMPTY), (uint32_t)(it - 1) & 1u, err)) { atomicExch(err, 10); break; }
+                if (rank == 0) mbar_arrive_expect_tx(bar(B_QFULL), 2 * kTileB);
+                for (int kb = 0; kb < 4; kb++) tc5::tma_load_2d_pair(q_sm + kb * kBlk, &tm_q, t.h * kD + kb * 64, t.bi * M + t.q0, bar(B_QFULL));
+                for (int j = 0; j < t.n_tiles; j++, gt++) {
+                    const uint32_t st = gt & 1u;
+                    if (gt >= 2 && !mbar_wait_bounded(bar(B_KEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 11); ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(bar(B_KFULL0 + st), 2 * kHalfB);
+                    tc5::tma_load_4d_pair(k_sm + st * kHalfB, &tm_k, 0, t.row0 + j * kBNk + 64 * (int)rank, 0, t.kvh, bar(B_KFULL0 + st));
+                }
             }
         }
     } else if (w == 9) {
         // ---- this CTA's half (128 dims) of every V tile
         if (lane == 0) {
-            for (int j = 0; j < n_tiles; j++) {
-                const int st = j & 1;
-                if (j >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), (uint32_t)((j >> 1) - 1) & 1u, err)) { atomicExch(err, 12); break; }
-                if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
-                tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, row0 + j * kBNk, 2 * (int)rank, kvh, bar(B_VFULL0 + st));
+            uint32_t gt = 0; bool ok = true;
+            for (int it = 0; ok && it < my_items; it++) {
+                const PfItem t = item_of(it);
+                for (int j = 0; j < t.n_tiles; j++, gt++) {
+                    const uint32_t st = gt & 1u;
+                    if (gt >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 12); ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
+                    tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, t.row0 + j * kBNk, 2 * (int)rank, t.kvh, bar(B_VFULL0 + st));
+                }
             }
         }
     } else if (w == 10) {
         if (lane == 0 && rank == 0) {
-            auto issue_s = [&](int j) {   // S(j) = Q K(j)^T for both CTAs: 4 column blocks x 4 k-steps of 16 dims
-                const uint32_t d = t_s0 + (uint32_t)(j & 1) * 128u, kst = k_sm + (uint32_t)(j & 1) * kHalfB;
+            uint32_t gt = 0; bool ok = true;
+            auto issue_s = [&](uint32_t g) {   // S of tile g = Q K^T for both CTAs: 4 column blocks x 4 k-steps of 16 dims
+                const uint32_t d = t_s0 + (g & 1u) * 128u, kst = k_sm + (g & 1u) * kHalfB;
 #pragma unroll
                 for (int kb = 0; kb < 4; kb++)
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
                         tc5::mma_ss2(d, tc5::smem_desc_sw128(q_sm + kb * kBlk + ks * 32, 16, 1024), tc5::smem_desc_sw128(kst + kb * kBlkKh + ks * 32, 16, 1024), kIdescS, (kb | ks) != 0);
-                tc5::commit2(bar(B_SFULL0 + (j & 1)));
-                tc5::commit2(bar(B_KEMPTY0 + (j & 1)));
+                tc5::commit2(bar(B_SFULL0 + (g & 1u)));
+                tc5::commit2(bar(B_KEMPTY0 + (g & 1u)));
             };
-            bool ok = mbar_wait_bounded(bar(B_QFULL), 0, err) && mbar_wait_bounded(bar(B_KFULL0), 0, err);
-            if (!ok) atomicExch(err, 13);
-            if (ok) { tc5::fence_after_sync(); issue_s(0); }
-            for (int j = 0; ok && j < n_tiles; j++) {
-                if (j + 1 < n_tiles) {
-                    if (!mbar_wait_bounded(bar(B_KFULL0 + ((j + 1) & 1)), (uint32_t)((j + 1) >> 1) & 1u, err)) { atomicExch(err, 14); break; }
-                    tc5::fence_after_sync(); issue_s(j + 1);
-                }
-                // V(j) has landed in both CTAs: tell both (their softmax warps zero the rows past the range in the tail tile), then wait for P(j)
-                if (!mbar_wait_bounded(bar(B_VFULL0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 15); break; }
-                mbar_arrive(bar(B_VLANDED)); tc5::mbar_arrive_peer(bar(B_VLANDED));
-                if (!mbar_wait_bounded(bar(B_PREADY0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 15); break; }
-                tc5::fence_after_sync();
-                const uint32_t a = t_s0 + (uint32_t)(j & 1) * 128u, vst = v_sm + (uint32_t)(j & 1) * kHalfB;   // P(j): fp16 pairs in the first 64 columns of its S buffer
+            for (int it = 0; ok && it < my_items; it++) {
+                const PfItem t = item_of(it);
+                ok = mbar_wait_bounded(bar(B_QFULL), (uint32_t)it & 1u, err) && mbar_wait_bounded(bar(B_KFULL0 + (gt & 1u)), (gt >> 1) & 1u, err);
+                if (!ok) { atomicExch(err, 13); break; }
+                tc5::fence_after_sync(); issue_s(gt);
+                if (t.n_tiles == 1) tc5::commit2(bar(B_QEMPTY));
+                for (int j = 0; j < t.n_tiles; j++, gt++) {
+                    if (j + 1 < t.n_tiles) {
+                        if (!mbar_wait_bounded(bar(B_KFULL0 + ((gt + 1) & 1u)), ((gt + 1) >> 1) & 1u, err)) { atomicExch(err, 14); ok = false; break; }
+                        tc5::fence_after_sync(); issue_s(gt + 1);
+                        if (j + 2 == t.n_tiles) tc5::commit2(bar(B_QEMPTY));   // the item's last S MMA: Q may be replaced
+                    }
+                    // V of the tile has landed in both CTAs: tell both (their softmax warps zero the rows past the range in the tail tile), then wait for P
+                    if (!mbar_wait_bounded(bar(B_VFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
+                    mbar_arrive(bar(B_VLANDED)); tc5::mbar_arrive_peer(bar(B_VLANDED));
+                    if (!mbar_wait_bounded(bar(B_PREADY0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
+                    if (j == 0 && it >= 1 && !mbar_wait_bounded(bar(B_OFREE), (uint32_t)(it - 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }   // the previous item's O has been read out
+                    tc5::fence_after_sync();
+                    const uint32_t a = t_s0 + (gt & 1u) * 128u, vst = v_sm + (gt & 1u) * kHalfB;   // P: fp16 pairs in the first 64 columns of its S buffer
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++)   // 16 keys per step; V half is MN-major: 64-dim blocks 16 KB apart, 8-key groups 1 KB apart
-                    tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j | ks) != 0);
-                tc5::commit2(bar(B_ODONE));
-                tc5::commit2(bar(B_VEMPTY0 + (j & 1)));
+                    for (int ks = 0; ks < 8; ks++)   // 16 keys per step; V half is MN-major: 64-dim blocks 16 KB apart, 8-key groups 1 KB apart
+                        tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j | ks) != 0);
+                    tc5::commit2(bar(B_ODONE));
+                    tc5::commit2(bar(B_VEMPTY0 + (gt & 1u)));
+                }
             }
         }
     } else {
         // ---- softmax warps: two threads per query row, split by key half
-        const int g = w >> 2, r = tid & 127, qpos = pos_base + q0 + r;               // this row sees keys <= qpos (and < kend)
-        const int lim = min(kend, qpos + 1);
+        const int g = w >> 2, r = tid & 127;
         const uint32_t lane_sel = (uint32_t)((w & 3) * 32) << 16;
         const int pair_bar = 1 + (w & 3);   // named barrier of warps w and w + 4 (64 threads)
-        float m = -INFINITY, l = 0.0f; bool alive = true;
+        uint32_t gt = 0; bool alive = true;
         // Every thread runs every iteration and meets its partner at the pair barrier whatever happens: a wait that ran out only switches the work off.
-        for (int j = 0; j < n_tiles; j++) {
-            const uint32_t t_s = t_s0 + (uint32_t)(j & 1) * 128u + lane_sel;
-            if (alive && !warp_wait(bar(B_SFULL0 + (j & 1)), (uint32_t)(j >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
+        for (int it = 0; it < my_items; it++) {
+        const PfItem t = item_of(it);
+        const int q0 = t.q0, rows_valid = t.rows_valid, pos_base = t.pos_base, kend = t.kend, n_tiles = t.n_tiles, h = t.h, bi = t.bi;
+        const int qpos = pos_base + q0 + r, lim = min(kend, qpos + 1);               // this row sees keys <= qpos (and < kend)
+        float m = -INFINITY, l = 0.0f;
+        for (int j = 0; j < n_tiles; j++, gt++) {
+            const uint32_t t_s = t_s0 + (gt & 1u) * 128u + lane_sel;
+            if (alive && !warp_wait(bar(B_SFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
             tc5::fence_after_sync();
             uint32_t v[2][32];
 #pragma unroll
@@ -159,15 +192,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[c][i]));
-            s_xmax[j & 1][g][r] = mx;
+            s_xmax[gt & 1u][g][r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");   // both halves of the row's scores are in registers and both maxima are visible
             do {
             if (!alive) break;
-            const float mt = fmaxf(mx, s_xmax[j & 1][g ^ 1][r]) * kLog2e;
+            const float mt = fmaxf(mx, s_xmax[gt & 1u][g ^ 1][r]) * kLog2e;
             const bool need = (j == 0) ? false : (mt > m + 8.0f);
             if (j == 0) m = mt;
             if (__any_sync(0xffffffffu, need)) {   // raise the reference maximum: rescale this thread's half of the O row after the previous P.V has landed
-                if (!warp_wait(bar(B_ODONE), (uint32_t)(j - 1) & 1u, err)) { atomicExch(err, 17); alive = false; break; }
+                if (!warp_wait(bar(B_ODONE), (gt - 1u) & 1u, err)) { atomicExch(err, 17); alive = false; break; }
                 tc5::fence_after_sync();
                 const float alpha = need ? ex2(m - mt) : 1.0f;
                 if (need) { m = mt; l *= alpha; }
@@ -194,9 +227,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::wait_st();
             if (j * kBNk + kBNk > kend) {   // tail tile: rows of V past the range were loaded as they lie in memory; zero them (0 x garbage must stay 0)
                 // (the MMA thread announces every tile's V once it has landed in both CTAs)
-                if (!warp_wait(bar(B_VLANDED), (uint32_t)j & 1u, err)) { atomicExch(err, 18); alive = false; break; }
+                if (!warp_wait(bar(B_VLANDED), gt & 1u, err)) { atomicExch(err, 18); alive = false; break; }
                 if (g == 0 && j * kBNk + r >= kend) {
-                    uint8_t* v_gen = smem_raw + (v_sm + (uint32_t)(j & 1) * kHalfB - sm0);
+                    uint8_t* v_gen = smem_raw + (v_sm + (gt & 1u) * kHalfB - sm0);
 #pragma unroll
                     for (int kb = 0; kb < 2; kb++)
 #pragma unroll
@@ -206,32 +239,59 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             }
             tc5::fence_before_sync();
             __syncwarp();
-            if (lane == 0) tc5::mbar_arrive_leader(bar(B_PREADY0 + (j & 1)));
+            if (lane == 0) tc5::mbar_arrive_leader(bar(B_PREADY0 + (gt & 1u)));
             } while (0);
         }
         // ---- epilogue: O / l * sigmoid(gate); the two threads of a row add their partial l and write 128 columns each
-        s_xmax[n_tiles & 1][g][r] = l;
+        s_lsum[g][r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-        l += s_xmax[n_tiles & 1][g ^ 1][r];
-        if (alive && warp_wait(bar(B_ODONE), (uint32_t)(n_tiles - 1) & 1u, err)) {
+        l += s_lsum[g ^ 1][r];
+        // Tensor memory hands a thread one row (32 columns at a time); global memory wants a warp on consecutive columns of one row (a thread per
+        // row would touch 32 sectors per instruction). Each warp therefore stages 32 rows x 16 columns in shared memory and writes them back
+        // row by row, half a warp per row: 64 contiguous bytes of gate in and of output out.
+        if (alive && warp_wait(bar(B_ODONE), (gt - 1u) & 1u, err)) {
             tc5::fence_after_sync();
-            const float inv = 1.0f / l; const bool store = r < rows_valid;
-            const int64_t obase = ((int64_t)bi * M + q0 + r) * kQD + h * kD + g * 128;
+            const float inv = 1.0f / l;
+            float* tile = s_stage[w];                     // [32 rows][17]
+            const int hw = lane >> 4, col = lane & 15, rbase = 32 * (w & 3);
+            const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + col;
+            float gv[16];   // gate logits of the round in flight, fetched one round (16 rows x 16 columns per half warp) ahead
+            auto load_gate = [&](int rd, float (&dst)[16]) {
+#pragma unroll
+                for (int rr = 0; rr < 16; rr++) { const int row = 2 * rr + hw; dst[rr] = (rbase + row < rows_valid) ? __ldg(gate + obase + (int64_t)row * kQD + rd * 16) : 0.0f; }
+            };
+            load_gate(0, gv);
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
                 uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
-                if (store) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float4 g4 = *reinterpret_cast<const float4*>(gate + obase + c * 32 + i);
-                        const float y0 = __uint_as_float(o[i]) * inv * (1.0f / (1.0f + __expf(-g4.x))), y1 = __uint_as_float(o[i + 1]) * inv * (1.0f / (1.0f + __expf(-g4.y)));
-                        const float y2 = __uint_as_float(o[i + 2]) * inv * (1.0f / (1.0f + __expf(-g4.z))), y3 = __uint_as_float(o[i + 3]) * inv * (1.0f / (1.0f + __expf(-g4.w)));
-                        if (out_bf16) { __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(out) + obase + c * 32 + i); d2[0] = __floats2bfloat162_rn(y0, y1); d2[1] = __floats2bfloat162_rn(y2, y3); }
-                        else *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + obase + c * 32 + i) = make_float4(y0, y1, y2, y3);
+                for (int half = 0; half < 2; half++) {
+                    const int rd = 2 * c + half;
+                    float gc[16];
+#pragma unroll
+                    for (int rr = 0; rr < 16; rr++) gc[rr] = gv[rr];
+                    if (rd + 1 < 8) load_gate(rd + 1, gv);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) tile[lane * 17 + i] = __uint_as_float(o[half * 16 + i]) * inv;
+                    __syncwarp();
+#pragma unroll
+                    for (int rr = 0; rr < 16; rr++) {
+                        const int row = 2 * rr + hw;
+                        if (rbase + row < rows_valid) {
+                            const int64_t oi = obase + (int64_t)row * kQD + rd * 16;
+                            const float y = tile[row * 17 + col] * (1.0f / (1.0f + __expf(-gc[rr])));
+                            if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
+                        }
                     }
+                    __syncwarp();
                 }
             }
-        } else if (alive) atomicExch(err, 19);
+            // this warp is done with the item's O: the first P.V of the next item may overwrite it
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive_leader(bar(B_OFREE));
+        } else if (alive) { atomicExch(err, 19); alive = false; }
+        }
     }
     tc5::fence_before_sync();
     __syncthreads();
@@ -254,8 +314,10 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     }
     CUtensorMap tm_q;
     if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
-    cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(kH, (M + kBMq - 1) / kBMq, b.n); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
-    cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // heads 2i, 2i+1 (a CTA pair is two neighbours along x)
+    // persistent CTA pairs: at most one pair per two SMs, items dealt round-robin (longest first)
+    const int n_items = ((M + kBMq - 1) / kBMq) * (kH / 2) * b.n, n_pairs = std::max(1, std::min(n_items, c.sm_count / 2));
+    cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(2 * n_pairs, 1, 1); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
+    cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
     cfg.attrs = at; cfg.numAttrs = 1;
     const cudaError_t le = cudaLaunchKernelEx(&cfg, prefill_tc5_kernel, tm_q, c.tm_k64h, c.tm_v128h, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err);
     if (le != cudaSuccess) return le;
