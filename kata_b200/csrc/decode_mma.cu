@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<I8>; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
+    if (threadIdx.x == 0) { prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); }
     pdl_launch_dependents();   // the next kernel of the stream (the combine kernel, the next layer's prep) may be set up while this one runs; it waits for this grid's completion itself
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps

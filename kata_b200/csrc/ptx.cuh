@@ -39,6 +39,8 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int 
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) { asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory"); }   // descriptor fetch off the first load's path
+
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes /* 16, or 0 to zero-fill */) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
