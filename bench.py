@@ -152,10 +152,16 @@ def run_decode(args, rank, world, kind_cfg):
     out = torch.empty(N_LAYERS, B, 1, 6144, dtype=torch.float32, device=dev)
     pos = lens.copy()
 
+    # per-layer views made once: slicing a tensor costs the host more than a microsecond, and at batch 1 a layer is 36 us of GPU time
+    L_ = range(N_LAYERS)
+    qfull_l, kproj_l, vproj_l, qn_l, kn_l = [qfull[l] for l in L_], [kproj[l] for l in L_], [vproj[l] for l in L_], [qn[l] for l in L_], [kn[l] for l in L_]
+    q16_l, gate_l, out_l = [q16[l] for l in L_], [gate[l] for l in L_], [out[l] for l in L_]
+
     def step(p):
-        for layer in range(N_LAYERS):
-            ctx.prep(layer, seqs, p, 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], q16=q16[layer], gate=gate[layer])
-            ctx.decode(layer, seqs, p, 1, q16[layer], gate[layer], out=out[layer])
+        p = p.tolist() if isinstance(p, np.ndarray) else p
+        for layer in L_:
+            ctx.prep(layer, seqs, p, 1, qfull_l[layer], kproj_l[layer], vproj_l[layer], qn_l[layer], kn_l[layer], q16=q16_l[layer], gate=gate_l[layer])
+            ctx.decode(layer, seqs, p, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
 
     def barrier():
         if world > 1:
@@ -187,15 +193,16 @@ def run_decode(args, rank, world, kind_cfg):
     assert torch.isfinite(out).all()
 
     # the dominant kernel alone: the decode launches of the same steps, timed on the same stream
-    for layer in range(N_LAYERS):
-        ctx.decode(layer, seqs, pos_timed0, 1, q16[layer], gate[layer], out=out[layer])
+    pos_k = pos_timed0.tolist()
+    for layer in L_:
+        ctx.decode(layer, seqs, pos_k, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
     reps = max(2, args.steps)
     for _ in range(reps):
-        for layer in range(N_LAYERS):
-            ctx.decode(layer, seqs, pos_timed0, 1, q16[layer], gate[layer], out=out[layer])
+        for layer in L_:
+            ctx.decode(layer, seqs, pos_k, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
     k1.record(); torch.cuda.synchronize()
     kern_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
 
@@ -203,12 +210,14 @@ def run_decode(args, rank, world, kind_cfg):
     hq = torch.randn(N_LAYERS, B, 1, 12288).pin_memory(); hk = torch.randn(N_LAYERS, B, 1, 1024).pin_memory(); hv = torch.randn(N_LAYERS, B, 1, 1024).pin_memory()
     hout = torch.empty(N_LAYERS, B, 1, 6144).pin_memory()
     dq, dk, dv = torch.empty_like(qfull), torch.empty_like(kproj), torch.empty_like(vproj)
+    dq_l, dk_l, dv_l = [dq[l] for l in L_], [dk[l] for l in L_], [dv[l] for l in L_]
 
     def step_e2e(p):   # one H2D of the step's projections (all layers), the step, one D2H of the step's outputs
         dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
-        for layer in range(N_LAYERS):
-            ctx.prep(layer, seqs, p, 1, dq[layer], dk[layer], dv[layer], qn[layer], kn[layer], q16=q16[layer], gate=gate[layer])
-            ctx.decode(layer, seqs, p, 1, q16[layer], gate[layer], out=out[layer])
+        p = p.tolist() if isinstance(p, np.ndarray) else p
+        for layer in L_:
+            ctx.prep(layer, seqs, p, 1, dq_l[layer], dk_l[layer], dv_l[layer], qn_l[layer], kn_l[layer], q16=q16_l[layer], gate=gate_l[layer])
+            ctx.decode(layer, seqs, p, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the caller holds the step's result on the host before the next step
 

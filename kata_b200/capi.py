@@ -61,8 +61,11 @@ def lib() -> C.CDLL:
 
 
 def _i32(xs):
-    a = np.ascontiguousarray(np.asarray(xs, dtype=np.int32).reshape(-1))
-    return a, a.ctypes.data_as(C.POINTER(C.c_int32))
+    """ctypes int32 array of a list / numpy vector of small integers (about 1 us; the numpy route costs three times that per call)."""
+    if isinstance(xs, np.ndarray):
+        xs = xs.reshape(-1).tolist()
+    a = (C.c_int32 * len(xs))(*[int(x) for x in xs])
+    return a, a
 
 
 def _dp(t):
