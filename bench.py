@@ -46,6 +46,7 @@ WORKLOADS = {
     "chunked_b1": ("chunked", 1, "fp16", 7300, 3600),
     "chunked_b16": ("chunked", 16, "fp16", 7300, 3600),
     "chunked_small": ("chunked", 4, "fp16", 3072, 1024),      # ~0.4 GB: the size used for ncu captures of the prefill kernel
+    "out_fwht": ("fwht", 32768, "fp32", 6144, 6144),          # the sign + Walsh-Hadamard transform that follows attention, on 32,768 output rows (805 MB in, 805 MB out)
 }
 
 
@@ -395,6 +396,45 @@ def run_reference(args, kind_cfg):
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
+def run_fwht(args, rank, world, cfg):
+    """The engine's attention output transform (k_rms_fwht mode 3) over cfg[1] rows of 6144 floats: one step = one pass, HBM-bound."""
+    import torch
+    import torch.distributed as dist
+    from kata_b200 import capi
+    rows, width = cfg[1], cfg[3]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev); gen.manual_seed(77 + rank)
+    x = torch.randn(rows, width, generator=gen, device=dev); y = torch.empty_like(x)
+    sign = torch.where(torch.rand(width, generator=gen, device=dev) < 0.5, -1.0, 1.0).to(torch.float32)
+    hx = torch.randn(rows, width).pin_memory(); hy = torch.empty(rows, width).pin_memory()
+    sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
+    for _ in range(args.warmup):
+        capi.out_fwht(x, sign, out=y)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tw0 = time.perf_counter(); e0.record()
+    for _ in range(args.steps):
+        capi.out_fwht(x, sign, out=y)
+    e1.record(); torch.cuda.synchronize(); tw1 = time.perf_counter()
+    ms = e0.elapsed_time(e1); clocks = sampler.stop(tw0, tw1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        x.copy_(hx, non_blocking=True); capi.out_fwht(x, sign, out=y); hy.copy_(y, non_blocking=True); torch.cuda.current_stream().synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, e2e_ms = t.tolist()
+    pk = peaks(); nbytes = rows * width * 8.0; ach = nbytes / (ms / args.steps * 1e-3) / 1e9
+    return {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * rows * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"attention output transform (sign, 1024-point Walsh-Hadamard per block, 1/32) over {rows} rows of {width} floats per GPU", "l2": "inputs larger than L2 (no flush needed)"},
+            "clocks": clocks, "gpu_launches": int(args.steps),
+            "e2e": {"value": world * rows * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": rows * width * 4, "d2h_bytes_per_step": rows * width * 4},
+            "roofline": {"bound": "hbm", "kernel": "out_fwht_kernel", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_src": pk["src"],
+                         "us_per_launch": ms / args.steps * 1e3, "algorithmic_bytes_per_launch": nbytes, "traffic": None}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -423,6 +463,8 @@ def main():
         res = run_decode(args, rank, world, cfg)
     elif cfg[0] == "splitkv":
         res = run_splitkv(args, rank, world, cfg)
+    elif cfg[0] == "fwht":
+        res = run_fwht(args, rank, world, cfg)
     else:
         from kata_b200 import bench_prefill
         res = bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler)

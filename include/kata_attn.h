@@ -126,6 +126,14 @@ int kata_attn_decode_partial(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int
                              const void* d_q16, float* d_part, void* stream);
 int kata_attn_merge_parts(kata_attn_ctx* ctx, const float* d_parts, int32_t n_parts, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 
+/* The transform the engine applies to the attention output before the output projection: per 1024-wide block of a row,
+ * y = (1/32) * H_1024 (sign (.) x), natural-order Walsh-Hadamard (k_rms_fwht mode 3 + fwht1024: shaders/ops.metal:23-50,
+ * shaders/common.h:22-42; Engine::dRmsFwht(..., 6144, 3) at src/engine.cpp:176 and the batched form at :287).
+ * d_x, d_out: [rows][width] fp32 (may alias), d_sign: [width] fp32 (+-1; the engine's sg6144), width a multiple of 1024.
+ * The butterflies run in the reference's order (bits 0-1, 2-6, 7-9, then the 1/32), so the result is bit-identical to an
+ * fp32 evaluation in that order. Needs no context. */
+int kata_attn_out_fwht(const float* d_x, const float* d_sign, float* d_out, int64_t rows, int32_t width, void* stream);
+
 /* KV planes for the prefix cache: Engine::kvPlanes / kvPlaneRow / kvPlanePtr (src/engine.h:74-81), used by
  * PrefixCache::restore and ::writeFile (src/ckpt.cpp:98, 134). Plane order and row sizes match the reference:
  * fp16 -> {K, V} rows of 2048 B; int8 -> {K, V, K scales, V scales} rows of 1024, 1024, 8, 8 B.

@@ -24,7 +24,7 @@ EXPORTS = [
     "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
-    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
 ]
 
 
@@ -77,6 +77,16 @@ def _dp(t):
 
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def out_fwht(x, sign, out=None):
+    """The engine's attention output transform (sign, 1024-point Walsh-Hadamard per block, 1/32): x [rows][width] fp32 on the GPU."""
+    out = torch.empty_like(x) if out is None else out
+    assert x.dtype == torch.float32 and sign.dtype == torch.float32 and x.dim() == 2
+    rc = lib().kata_attn_out_fwht(_dp(x), _dp(sign), _dp(out), C.c_int64(x.shape[0]), C.c_int32(x.shape[1]), _stream())
+    if rc != OK:
+        raise KataError(rc, "kata_attn_out_fwht")
+    return out
 
 
 class AttnContext:

@@ -15,6 +15,9 @@ namespace kata {
 size_t scalar_scratch_floats_pm();
 size_t scalar_scratch_floats_acc();
 int decode_max_slots(int sm_count);
+cudaError_t configure_decode(bool int8);
+cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s);
+cudaError_t configure_prefill(bool int8);
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s);
 }  // namespace kata
@@ -102,6 +105,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
         if (!kata::make_tile_tmap(&c.tm_k_tile, c.k_arena, c.elt, rows, tile_rows, blocks) || !kata::make_tile_tmap(&c.tm_v_tile, c.v_arena, c.elt, rows, tile_rows, blocks) ||
             (c.elt == 2 && (!kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
+    if (kata::configure_decode(cfg->kv_mode == KATA_KV_INT8) != cudaSuccess || kata::configure_prefill(cfg->kv_mode == KATA_KV_INT8) != cudaSuccess) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_CUDA; }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);
     float invf[32]; for (int i = 0; i < 32; i++) invf[i] = powf(10000000.0f, -(float)i / 32.0f);   // shaders/attn.metal:26
     kata::set_inv_freq(invf);
@@ -131,6 +135,13 @@ int kata_attn_reset(kata_attn_ctx* h, void* stream) {
 const char* kata_attn_numerics_tag(const kata_attn_ctx* h) { return h ? h->c.tag.c_str() : ""; }
 const char* kata_attn_last_error(const kata_attn_ctx* h) { return h ? h->c.err.c_str() : "null context"; }
 uint64_t kata_attn_launch_count(const kata_attn_ctx* h) { return h ? h->c.launches : 0; }
+
+int kata_attn_out_fwht(const float* d_x, const float* d_sign, float* d_out, int64_t rows, int32_t width, void* stream) {
+    if (!d_x || !d_sign || !d_out) return KATA_ERR_ARG;
+    if (rows < 0 || width < 1024 || width % 1024 != 0) return KATA_ERR_RANGE;
+    if (rows == 0) return KATA_OK;
+    return kata::launch_out_fwht(d_x, d_sign, d_out, rows, width, (cudaStream_t)stream) == cudaSuccess ? KATA_OK : KATA_ERR_CUDA;
+}
 
 int kata_attn_check(kata_attn_ctx* h, void* stream) {
     if (!h) return KATA_ERR_ARG;

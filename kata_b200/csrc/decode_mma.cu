@@ -346,6 +346,12 @@ __global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restric
 
 int decode_max_slots(int sm_count) { return sm_count + 4 * KATA_MAX_BATCH; }
 
+// Shared-memory opt-in of the decode kernel on the current device (function attributes are per device: done once per context).
+cudaError_t configure_decode(bool int8) {
+    return int8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
+                : cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem);
+}
+
 static int max_contributors(const DecPlan& p) {
     auto cta_of = [&](int tile) { const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
     int m = 1;
@@ -356,7 +362,6 @@ static int max_contributors(const DecPlan& p) {
 // key_off / kend_override serve the split-KV-across-GPUs call: local row = absolute key - key_off, rows [first_row, kend).
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s) {
-    static bool attr_set[2] = {false, false};
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8; const int kTile = i8 ? Geo<true>::kTile : Geo<false>::kTile;
     DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off;
     int total = 0;
@@ -373,12 +378,6 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
     p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
-    if (!attr_set[i8]) {
-        cudaError_t e = i8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
-                           : cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem);
-        if (e != cudaSuccess) return e;
-        attr_set[i8] = true;
-    }
     const cudaError_t le = i8 ? launch_pdl(decode_mma_kernel<true>, dim3(n_ctas), dim3(kThreads), Geo<true>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
                               : launch_pdl(decode_mma_kernel<false>, dim3(n_ctas), dim3(kThreads), Geo<false>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
     if (le != cudaSuccess) return le;

@@ -103,15 +103,13 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_mma_kernel(const Batch 
 
 }  // namespace
 
+cudaError_t configure_prefill_mma(bool int8) {   // per device, once per context
+    return int8 ? cudaFuncSetAttribute(prefill_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<true>::kSmem)
+                : cudaFuncSetAttribute(prefill_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<false>::kSmem);
+}
+
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
-    static bool attr_set[2] = {false, false};
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
-    if (!attr_set[i8]) {
-        cudaError_t e = i8 ? cudaFuncSetAttribute(prefill_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<true>::kSmem)
-                           : cudaFuncSetAttribute(prefill_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeo<false>::kSmem);
-        if (e != cudaSuccess) return e;
-        attr_set[i8] = true;
-    }
     const dim3 grid((M + kBM - 1) / kBM, kH, b.n);
     if (i8) prefill_mma_kernel<true><<<grid, kPfThreads, PfGeo<true>::kSmem, s>>>(b, M, q16, gate, out, out_dtype == KATA_ACT_BF16, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc);
     else prefill_mma_kernel<false><<<grid, kPfThreads, PfGeo<false>::kSmem, s>>>(b, M, q16, gate, out, out_dtype == KATA_ACT_BF16, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc);

@@ -302,16 +302,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
 }  // namespace
 
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
+cudaError_t configure_prefill_mma(bool int8);
+
+// Shared-memory opt-in of the prefill kernels on the current device (function attributes are per device: done once per context).
+cudaError_t configure_prefill(bool int8) {
+    cudaError_t e = configure_prefill_mma(int8);
+    if (e == cudaSuccess && !int8) e = cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+    return e;
+}
 
 // fp16 cache: tcgen05 kernel (unless the context was created with the legacy-path flag); int8 cache: mma.sync kernel.
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
     if (c.cfg.kv_mode == KATA_KV_INT8 || (c.cfg.flags & 1)) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
     CUtensorMap tm_q;
     if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
     // persistent CTA pairs: at most one pair per two SMs, items dealt round-robin (longest first)

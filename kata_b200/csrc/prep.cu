@@ -7,6 +7,8 @@
 // accesses, shuffles only (no shared memory, no block barrier). Arithmetic is written with explicit round-to-nearest intrinsics so that no
 // multiply-add is contracted: the sums, the normalisation and the quantiser then round exactly as the scalar
 // restatement does, and the int8 codes and scales are bit-exact.
+#include <algorithm>
+
 #include "kata_internal.cuh"
 
 namespace kata {
@@ -137,7 +139,54 @@ __global__ void __launch_bounds__(256) kv_quant_kernel(const __half* __restrict_
     quant_store_row(hv, (isV ? vq : kq) + row * kKVD + head * kD, (isV ? vsc : ksc) + row * 4 + head, lane, round_mode);
 }
 
+// grid (width / 1024, rows) x 256 threads: element i = tid*4 + r of the block; bits 0-1 of i live in the thread's float4, bits 2-6 in the lane,
+// bits 7-9 in the warp index, and the butterflies are taken in that order as fwht1024 does (shaders/common.h:22-42)
+__global__ void __launch_bounds__(256) out_fwht_kernel(const float* __restrict__ x, const float* __restrict__ sign, float* __restrict__ out, const int width, const int64_t rows) {
+    __shared__ float xs[1024];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const float4 sg = *reinterpret_cast<const float4*>(sign + blockIdx.x * 1024 + tid * 4);
+    for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {   // a CTA walks rows of its column block: fewer, longer-lived CTAs
+    const int64_t base = row * width + blockIdx.x * 1024 + tid * 4;
+    const float4 in = *reinterpret_cast<const float4*>(x + base);
+    float v0 = __fmul_rn(in.x, sg.x), v1 = __fmul_rn(in.y, sg.y), v2 = __fmul_rn(in.z, sg.z), v3 = __fmul_rn(in.w, sg.w);
+    { const float a = __fadd_rn(v0, v1), b = __fsub_rn(v0, v1), c = __fadd_rn(v2, v3), d = __fsub_rn(v2, v3); v0 = a; v1 = b; v2 = c; v3 = d; }
+    { const float a = __fadd_rn(v0, v2), b = __fadd_rn(v1, v3), c = __fsub_rn(v0, v2), d = __fsub_rn(v1, v3); v0 = a; v1 = b; v2 = c; v3 = d; }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+        const float p0 = __shfl_xor_sync(0xffffffffu, v0, m), p1 = __shfl_xor_sync(0xffffffffu, v1, m), p2 = __shfl_xor_sync(0xffffffffu, v2, m), p3 = __shfl_xor_sync(0xffffffffu, v3, m);
+        const bool up = lane & m;
+        v0 = up ? __fsub_rn(p0, v0) : __fadd_rn(v0, p0); v1 = up ? __fsub_rn(p1, v1) : __fadd_rn(v1, p1);
+        v2 = up ? __fsub_rn(p2, v2) : __fadd_rn(v2, p2); v3 = up ? __fsub_rn(p3, v3) : __fadd_rn(v3, p3);
+    }
+    *reinterpret_cast<float4*>(xs + tid * 4) = make_float4(v0, v1, v2, v3);
+    __syncthreads();
+    if (tid < 128) {
+        float e[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) e[j] = xs[tid + 128 * j];
+#pragma unroll
+        for (int s = 0; s < 3; s++) {
+            const int h = 1 << s;
+#pragma unroll
+            for (int j = 0; j < 8; j++) if (!(j & h)) { const float a = e[j], b = e[j | h]; e[j] = __fadd_rn(a, b); e[j | h] = __fsub_rn(a, b); }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) xs[tid + 128 * j] = e[j];
+    }
+    __syncthreads();
+    const float4 r = *reinterpret_cast<const float4*>(xs + tid * 4);
+    *reinterpret_cast<float4*>(out + base) = make_float4(r.x * 0.03125f, r.y * 0.03125f, r.z * 0.03125f, r.w * 0.03125f);
+    __syncthreads();   // xs is reused by the next row
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s) {
+    const int nb = width / 1024; const unsigned gy = (unsigned)std::min<int64_t>(rows, std::max(1, 148 * 8 / nb));
+    out_fwht_kernel<<<dim3(nb, gy), 256, 0, s>>>(x, sign, out, width, rows);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const void* kproj, const void* vproj, int act_dtype,
                         const float* qnorm, const float* knorm, __half* q16, float* q32, float* gate, int h0, int nh, cudaStream_t s) {

@@ -324,4 +324,22 @@ void kor_decode_batch(const float* q, const float* gate, const uint16_t* const* 
 
 uint32_t kor_hw_threads() { const uint32_t n = std::thread::hardware_concurrency(); return n ? n : 1; }
 
+// k_rms_fwht mode 3 + fwht1024 (shaders/ops.metal:23-50, shaders/common.h:22-42): per 1024-block y = H (sign (.) x) / 32 in natural order.
+// A butterfly stage gives the lower index a + b and the upper a - b whoever computes it, so taking the stages bit 0 .. bit 9 in order
+// reproduces the shader's fp32 result bit for bit (registers: bits 0-1, simd shuffles: 2-6, threadgroup transpose: 7-9).
+void kor_out_fwht(const float* x, const float* sign, float* out, uint32_t rows, uint32_t width) {
+    std::vector<float> v(1024);
+    for (uint32_t r = 0; r < rows; r++)
+        for (uint32_t blk = 0; blk < width / 1024; blk++) {
+            const float* src = x + (size_t)r * width + blk * 1024; const float* sg = sign + blk * 1024;
+            for (int i = 0; i < 1024; i++) v[i] = src[i] * sg[i];
+            for (int bit = 0; bit < 10; bit++) {
+                const int h = 1 << bit;
+                for (int i = 0; i < 1024; i++) if (!(i & h)) { const float a = v[i], b = v[i | h]; v[i] = a + b; v[i | h] = a - b; }
+            }
+            float* dst = out + (size_t)r * width + blk * 1024;
+            for (int i = 0; i < 1024; i++) dst[i] = v[i] * 0.03125f;
+        }
+}
+
 }  // extern "C"

@@ -177,6 +177,14 @@ def formula_f32(q, gate, planes: KvPlanes, pos_base: int, first_pos: int = 0, th
     return out
 
 
+def out_fwht(x, sign):
+    """sign (.) x through the normalised 1024-point Walsh-Hadamard transform per block (k_rms_fwht mode 3), fp32, the shader's stage order."""
+    x = np.ascontiguousarray(x, np.float32); sign = np.ascontiguousarray(sign, np.float32)
+    out = np.empty_like(x)
+    lib().kor_out_fwht(_p(x), _p(sign), _p(out), C.c_uint32(x.shape[0]), C.c_uint32(x.shape[1]))
+    return out
+
+
 def decode_batch(q, gate, k_planes, v_planes, pos, threads: int = 0):
     """CPU baseline: one layer's decode step for a batch (k_attn_decode per (sequence, head)) on `threads` host threads."""
     B = q.shape[0]

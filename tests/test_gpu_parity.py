@@ -435,3 +435,19 @@ def test_full_size_prefill_chunk_over_7k_prefix(capi, orc):
     for r in rows:
         ref = orc.formula_f32(q32.cpu().numpy()[0, r:r + 1], g.cpu().numpy()[0, r:r + 1], planes, pb + r)
         _close(out[r:r + 1], ref)
+
+
+@pytest.mark.gpu
+def test_out_fwht_bit_exact(capi, orc):
+    # the transform between attention and the output projection (k_rms_fwht mode 3): same butterflies in the same order -> same bits
+    rng = np.random.default_rng(11)
+    sign = np.where(rng.random(6144) < 0.5, -1.0, 1.0).astype(np.float32)
+    for rows, width in ((1, 6144), (7, 6144), (300, 6144), (5, 1024)):
+        x = (rng.standard_normal((rows, width)) * rng.choice([1e-3, 1.0, 50.0], size=(rows, 1))).astype(np.float32)
+        got = capi.out_fwht(_dev(x), _dev(sign[:width])).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), orc.out_fwht(x, sign[:width]).view(np.uint32))
+    d = _dev(x.copy())
+    capi.out_fwht(d, _dev(sign[:1024]), out=d)   # in place
+    assert np.array_equal(d.cpu().numpy().view(np.uint32), orc.out_fwht(x, sign[:1024]).view(np.uint32))
+    with pytest.raises(capi.KataError):
+        capi.out_fwht(torch.zeros(2, 1000, device="cuda"), _dev(sign[:1000]))

@@ -160,3 +160,18 @@ def test_golden_vectors(orc):
         else:
             # libm exp/sin/cos may differ in the last place between hosts; integer results above must not
             assert np.allclose(g[k], fresh[k], rtol=0, atol=2e-6), k
+
+
+def test_out_fwht_matches_a_dense_hadamard_and_is_an_involution(orc):
+    # k_rms_fwht mode 3: y = H_1024 (sign (.) x) / 32 per block; H / 32 is orthonormal and symmetric, so two applications with sign = 1 give x back
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((3, 2048)).astype(np.float32)
+    sign = np.where(rng.random(2048) < 0.5, -1.0, 1.0).astype(np.float32)
+    y = orc.out_fwht(x, sign)
+    H = np.array([[1.0]])
+    for _ in range(10):
+        H = np.block([[H, H], [H, -H]])   # natural (Sylvester) order
+    ref = np.concatenate([(x[:, b * 1024:(b + 1) * 1024].astype(np.float64) * sign[b * 1024:(b + 1) * 1024]) @ H.T / 32.0 for b in range(2)], axis=1)
+    assert np.abs(y - ref).max() < 2e-5
+    ones = np.ones(2048, np.float32)
+    assert np.abs(orc.out_fwht(orc.out_fwht(x, ones), ones) - x).max() < 2e-5
