@@ -95,7 +95,8 @@ int kata_attn_prep(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* 
 int kata_attn_kv_quant(kata_attn_ctx* ctx, int32_t layer, int32_t seq, const void* d_ks, const void* d_vs, int32_t T, int32_t pos0, void* stream);
 
 /* Engine::dDecAttn (src/engine.cpp:119-127): k_dec_q_pack + k_attn_dec_split[_q8] + k_attn_dec_combine
- * (shaders/flash.metal:77-152). T in {1,2} query tokens per sequence at positions pos_base[b]+t; token t sees keys
+ * (shaders/flash.metal:77-152). T in 1..KATA_MAX_VERIFY query tokens per sequence at positions pos_base[b]+t (1: step, 2: verify2,
+ * up to 8: Engine::verifyWide, src/engine.cpp:602-622, which the reference sends through its scalar kernels); token t sees keys
  * [first_pos, pos_base[b]+t]; first_pos is 0 for the trunk and 1 for the MTP-head cache (src/engine.cpp:362).
  *   d_q16, d_gate as written by kata_attn_prep; d_out [n][T][6144] out_dtype = softmax(q k^T) v * sigmoid(gate). */
 int kata_attn_decode(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,

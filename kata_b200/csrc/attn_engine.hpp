@@ -29,6 +29,11 @@ public:
     // Engine::verify2, attention branch (src/engine.cpp:469-483): k_attn_prep_b (32, 2) then dDecAttn(T=2).
     int verify2Attn(int ai, uint32_t pos, const float* pQfull, const float* pK, const float* pV, const float* qNorm, const float* kNorm,
                     void* q16, float* pGate, float* pAttnO, void* stream) { return decodeRows(attn_, ai, pos, 2, 0, pQfull, pK, pV, qNorm, kNorm, q16, pGate, pAttnO, stream); }
+    // Engine::verifyWide, attention branch (src/engine.cpp:602-622): k_attn_prep_b (32, T <= kMaxVerify = 8) then the decode of T tokens.
+    int verifyWideAttn(int ai, uint32_t T, uint32_t pos, const float* pQfull, const float* pK, const float* pV, const float* qNorm, const float* kNorm,
+                       void* q16, float* pGate, float* pAttnO, void* stream) { return decodeRows(attn_, ai, pos, (int)T, 0, pQfull, pK, pV, qNorm, kNorm, q16, pGate, pAttnO, stream); }
+    // Engine::dRmsFwht(e, bufAttnO, nullptr, sg6144, 0, bufXp, 6144, 3) (src/engine.cpp:176, 287): the transform between attention and the output projection
+    int attnOutFwht(const float* bufAttnO, const float* sg6144, float* bufXp, uint32_t rows, void* stream) { return kata_attn_out_fwht(bufAttnO, sg6144, bufXp, rows, KATA_Q_DIM, stream); }
     // Engine::mtpRows, attention part (src/engine.cpp:358-368): R <= 2 rows on the MTP head's cache, first valid key at position 1.
     int mtpRowsAttn(uint32_t R, uint32_t pos0, const float* mQfull, const float* mKp, const float* mVp, const float* qNorm, const float* kNorm,
                     void* q16, float* mGate, float* mAttnO, void* stream) { return decodeRows(mtp_, 0, pos0, (int)R, 1, mQfull, mKp, mVp, qNorm, kNorm, q16, mGate, mAttnO, stream); }

@@ -19,7 +19,7 @@ cudaError_t configure_decode(bool int8);
 cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s);
 cudaError_t configure_prefill(bool int8);
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
-                                 float* part_out, cudaStream_t s);
+                                 float* part_out, cudaStream_t s, int tok_stride = 0, int tok0 = 0);
 }  // namespace kata
 
 struct kata_attn_ctx { kata::Ctx c; };
@@ -183,14 +183,22 @@ int kata_attn_decode(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* 
                      const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c;
-    if (T < 1 || T > 2) return fail(c, KATA_ERR_RANGE, "decode takes 1 or 2 query tokens, not %d", T);
+    if (T < 1 || T > KATA_MAX_VERIFY) return fail(c, KATA_ERR_RANGE, "decode takes 1..%d query tokens, not %d", KATA_MAX_VERIFY, T);
     if (!d_q16 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "decode needs q16, gate and out");
     if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
     kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, T, b)) return rc;
     for (int i = 0; i < n; i++) if (first_pos < 0 || first_pos > pos_base[i]) return fail(c, KATA_ERR_RANGE, "first_pos %d outside [0, pos_base=%d]", first_pos, pos_base[i]);
     DeviceGuard guard(c.cfg.device);
-    cudaError_t e = kata::launch_decode_mma_ex(c, b, T, first_pos, 0, nullptr, (const __half*)d_q16, d_gate, d_out, out_dtype, nullptr, (cudaStream_t)stream);
-    return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "decode launch");
+    // The kernel takes the 6 heads of a KV head x 2 tokens as its 16-row block. A wide verify (T up to 8, Engine::verifyWide,
+    // src/engine.cpp:602-622) runs as launches of two tokens each: the rows of all T tokens are in the cache already and token t
+    // sees keys <= pos_base + t, so the passes are independent; the keys are read once per pass (wide verifies are short-context).
+    for (int t0 = 0; t0 < T; t0 += 2) {
+        kata::Batch bt = b;
+        for (int i = 0; i < n; i++) bt.pos[i] = b.pos[i] + t0;
+        cudaError_t e = kata::launch_decode_mma_ex(c, bt, std::min(2, T - t0), first_pos, 0, nullptr, (const __half*)d_q16, d_gate, d_out, out_dtype, nullptr, (cudaStream_t)stream, T, t0);
+        if (e != cudaSuccess) return cuda_fail(c, e, "decode launch");
+    }
+    return KATA_OK;
 }
 
 int kata_attn_decode_scalar(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,

@@ -56,6 +56,7 @@ template <bool I8> struct Geo {
 
 struct DecPlan {
     int32_t n, T, first_row, key_off, n_ctas, q_tiles, r_tiles;   // CTA c owns tiles [c*q + min(c,r), (c+1)*q + min(c+1,r))
+    int32_t tok_stride, tok0;            // rows of q16 / gate / out per sequence, and the row of this launch's token 0 (a wide verify runs as launches of 2 tokens)
     int32_t merge_in_kernel;             // 1: the last contributor of a segment merges its partials; 0: decode_combine_kernel does
     int32_t pos[KATA_MAX_BATCH];         // absolute position of token 0
     int32_t kend[KATA_MAX_BATCH];        // local rows [first_row, kend) hold this call's keys; absolute key = key_off + row
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < 6 * T) { const int t = r / 6, j = r - 6 * t; v = *reinterpret_cast<const uint4*>(q16 + ((int64_t)b * T + t) * kQD + (kvh * 6 + j) * kD + c16 * 8); }
+            if (r < 6 * T) { const int t = r / 6, j = r - 6 * t; v = *reinterpret_cast<const uint4*>(q16 + ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + (kvh * 6 + j) * kD + c16 * 8); }
             stage_q_chunk<I8>(smem + r * kQStride, c16, v);
         }
         __syncthreads();
@@ -237,9 +238,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         float* slot_o = scratch_o + (int64_t)(cta + seg) * (12 * kD); float* slot_ml = scratch_ml + (int64_t)(cta + seg) * 32;
         auto emit = [&](int r, float M, float L, float A0, float A1) {   // final value of row r, dims d0, d0+1
             const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-            if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[d0] = A0; po[d0 + 1] = A1; if ((tid & 127) == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
+            if (part_out) { float* po = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po[d0] = A0; po[d0 + 1] = A1; if ((tid & 127) == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
             else {
-                const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + d0; const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
+                const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d0; const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
                 const float y0 = (A0 / L) * sigmoid_fast(gt.x), y1 = (A1 / L) * sigmoid_fast(gt.y);
                 if (out_bf16) reinterpret_cast<__nv_bfloat162*>(out)[oi >> 1] = __floats2bfloat162_rn(y0, y1); else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oi) = make_float2(y0, y1);
             }
@@ -325,9 +326,9 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
     A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
     const float M = s_M, L = s_L;
     const int T = p.T, t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-    if (part_out) { float* po = part_out + ((int64_t)(b * T + t) * kH + head) * kPartStride; po[d] = A; if (d == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
+    if (part_out) { float* po = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po[d] = A; if (d == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
     else {
-        const int64_t oi = ((int64_t)b * T + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
+        const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
         if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
     }
 }
@@ -361,9 +362,9 @@ static int max_contributors(const DecPlan& p) {
 
 // key_off / kend_override serve the split-KV-across-GPUs call: local row = absolute key - key_off, rows [first_row, kend).
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
-                                 float* part_out, cudaStream_t s) {
+                                 float* part_out, cudaStream_t s, int tok_stride, int tok0) {
     const bool i8 = c.cfg.kv_mode == KATA_KV_INT8; const int kTile = i8 ? Geo<true>::kTile : Geo<false>::kTile;
-    DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off;
+    DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off; p.tok_stride = tok_stride > 0 ? tok_stride : T; p.tok0 = tok0;
     int total = 0;
     for (int i = 0; i < b.n; i++) {
         p.pos[i] = b.pos[i]; p.row_base[i] = b.row_base[i]; p.kend[i] = kend_override ? kend_override[i] : b.pos[i] + T;
@@ -391,7 +392,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
 }
 
 cudaError_t launch_decode_mma(Ctx& c, const Batch& b, int T, int first_pos, int, const __half* q16, const float* gate, void* out, int out_dtype, float* part_out, cudaStream_t s) {
-    return launch_decode_mma_ex(c, b, T, first_pos, 0, nullptr, q16, gate, out, out_dtype, part_out, s);
+    return launch_decode_mma_ex(c, b, T, first_pos, 0, nullptr, q16, gate, out, out_dtype, part_out, s, T, 0);
 }
 
 cudaError_t launch_merge_parts(Ctx& c, const float* parts, int n_parts, int T, const float* gate, void* out, int out_dtype, cudaStream_t s) {
@@ -454,7 +455,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
         if (cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return KATA_ERR_CUDA;
         sd.scratch = static_cast<StaticScratch*>(ptr); sd.ready = true;
     }
-    DecPlan p{}; p.n = n; p.T = T; p.first_row = first_pos; p.key_off = 0;
+    DecPlan p{}; p.n = n; p.T = T; p.first_row = first_pos; p.key_off = 0; p.tok_stride = T; p.tok0 = 0;
     int total = 0;
     for (int i = 0; i < n; i++) {
         if (pos_base[i] < 0 || first_pos < 0 || first_pos > pos_base[i] || seq_row0[i] < 0 || seq_row0[i] + pos_base[i] + T > total_rows) return KATA_ERR_RANGE;

@@ -145,9 +145,12 @@ __global__ void __launch_bounds__(256) out_fwht_kernel(const float* __restrict__
     __shared__ float xs[1024];
     const int tid = threadIdx.x, lane = tid & 31;
     const float4 sg = *reinterpret_cast<const float4*>(sign + blockIdx.x * 1024 + tid * 4);
-    for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {   // a CTA walks rows of its column block: fewer, longer-lived CTAs
-    const int64_t base = row * width + blockIdx.x * 1024 + tid * 4;
-    const float4 in = *reinterpret_cast<const float4*>(x + base);
+    const int64_t col = blockIdx.x * 1024 + tid * 4;
+    float4 nxt = blockIdx.y < rows ? *reinterpret_cast<const float4*>(x + (int64_t)blockIdx.y * width + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {   // a CTA walks rows of its column block (fewer, longer-lived CTAs), loading one row ahead
+    const int64_t base = row * width + col;
+    const float4 in = nxt;
+    if (row + gridDim.y < rows) nxt = *reinterpret_cast<const float4*>(x + (row + gridDim.y) * width + col);
     float v0 = __fmul_rn(in.x, sg.x), v1 = __fmul_rn(in.y, sg.y), v2 = __fmul_rn(in.z, sg.z), v3 = __fmul_rn(in.w, sg.w);
     { const float a = __fadd_rn(v0, v1), b = __fsub_rn(v0, v1), c = __fadd_rn(v2, v3), d = __fsub_rn(v2, v3); v0 = a; v1 = b; v2 = c; v3 = d; }
     { const float a = __fadd_rn(v0, v2), b = __fadd_rn(v1, v3), c = __fsub_rn(v0, v2), d = __fsub_rn(v1, v3); v0 = a; v1 = b; v2 = c; v3 = d; }

@@ -206,9 +206,30 @@ def test_decode_scalar_path_and_cross_path(capi, orc):
         ctx.check()
         ref = orc.attn_split_combine(qs, gs, planes, pb, T=T, S=min(32, max(1, (pb + T) // 64)))
         assert np.abs(out.cpu().numpy()[0] - ref).max() < 2e-5
-        if T <= 2:   # the matrix path agrees with the scalar path on the same cache (the reference's KATA_SCALAR_DEC cross-check)
-            m = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(qs)[None]).view(torch.float16), _dev(gs[None]))
-            _close(m.cpu().numpy()[0], out.cpu().numpy()[0])
+        # the matrix path agrees with the scalar path on the same cache (the reference's KATA_SCALAR_DEC cross-check); T = 8 is the wide verify
+        m = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(qs)[None]).view(torch.float16), _dev(gs[None]))
+        _close(m.cpu().numpy()[0], out.cpu().numpy()[0])
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_wide_verify_matches_single_token_decodes(capi, orc, int8):
+    # T = 5 and 8 query tokens per sequence (Engine::verifyWide) on the matrix path, two ragged sequences: every token must equal its own T = 1 decode
+    lens = (700, 333)
+    ctx = capi.AttnContext(1, [1024, 512], kv_mode="int8" if int8 else "fp16")
+    fills = []
+    for s, n in enumerate(lens):
+        planes, q, gate, _ = _oracle_fill(orc, 90 + s, n, int(ctx.max_ctx[s]), int8=int8, fast=True, seq=s)
+        _upload_planes(ctx, planes, seq=s); fills.append((planes, q, gate))
+    for T in (5, 8):
+        pbs = [n - T for n in lens]
+        q16 = np.stack([orc.cvt_q_half(fills[s][1][pbs[s]:pbs[s] + T]) for s in range(2)]); g = np.stack([fills[s][2][pbs[s]:pbs[s] + T] for s in range(2)])
+        wide = ctx.decode(0, [0, 1], pbs, T, _dev(q16).view(torch.float16), _dev(g)).cpu().numpy()
+        ctx.check()
+        for s in range(2):
+            _close(wide[s], orc.formula_f32(fills[s][1][pbs[s]:pbs[s] + T], fills[s][2][pbs[s]:pbs[s] + T], fills[s][0], pbs[s]))
+            for t in range(T):
+                one = ctx.decode(0, [s], [pbs[s] + t], 1, _dev(q16[s:s + 1, t:t + 1]).view(torch.float16), _dev(g[s:s + 1, t:t + 1])).cpu().numpy()[0, 0]
+                assert np.abs(one - wide[s, t]).max() < 1e-4
 
 
 def test_verify_t2_equals_two_decodes(capi, orc):
@@ -372,7 +393,7 @@ def test_errors_are_codes_not_faults(capi):
         (lambda: ctx.decode(2, [0], [0], 1, z16, z32), 2),          # layer out of range
         (lambda: ctx.decode(0, [2], [0], 1, z16, z32), 2),          # sequence out of range
         (lambda: ctx.decode(0, [1], [32], 1, z16, z32), 2),         # position beyond max_ctx
-        (lambda: ctx.decode(0, [0], [5], 3, z16, z32), 2),          # T > 2
+        (lambda: ctx.decode(0, [0], [5], 9, z16, z32), 2),          # T > 8
         (lambda: ctx.decode(0, [0], [5], 1, z16, z32, first_pos=6), 2),
         (lambda: ctx.prefill(0, [0], [0], 2000, z16, z32), 2),      # chunk too long
         (lambda: ctx.kv_quant(0, 0, z16, z16, 0), 3),               # fp16 context has no quantiser
