@@ -50,7 +50,7 @@ int make_batch(Ctx& c, int layer, int n, const int32_t* seq_ids, const int32_t* 
         if (s < 0 || s >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "sequence id %d outside [0,%d)", s, c.cfg.n_seqs);
         const int64_t local = (int64_t)pos[i] - c.pos_off[s];
         if (pos[i] < 0 || (touches_cache && (local < 0 || local + span > c.max_ctx[s]))) return fail(c, KATA_ERR_RANGE, "positions [%d,%d) of sequence %d fall outside its %d rows starting at position %d", pos[i], pos[i] + span, s, c.max_ctx[s], c.pos_off[s]);
-        b.pos[i] = pos[i]; b.row_base[i] = c.row_of(layer, s) - c.pos_off[s];
+        b.seq[i] = s; b.pos[i] = pos[i]; b.row_base[i] = c.row_of(layer, s) - c.pos_off[s];
     }
     return KATA_OK;
 }
@@ -86,7 +86,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     int64_t rows = 0;
     for (int s = 0; s < cfg->n_seqs; s++) {
         if (cfg->max_ctx[s] < 1) { delete h; return KATA_ERR_ARG; }
-        c.max_ctx.push_back(cfg->max_ctx[s]); c.pos_off.push_back(0); c.seq_row0.push_back(rows); rows += (int64_t)cfg->n_layers * cfg->max_ctx[s];
+        c.max_ctx.push_back(cfg->max_ctx[s]); c.pos_off.push_back(0); c.append_lo.push_back(INT32_MAX); c.seq_row0.push_back(rows); rows += (int64_t)cfg->n_layers * cfg->max_ctx[s];
     }
     c.total_rows = rows;
     c.max_items = kata::decode_max_slots(c.sm_count * 8);
@@ -165,6 +165,7 @@ int kata_attn_prep(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* se
     kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos0, T, b, /*touches_cache=*/h0 + nh > 24)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_prep(c, b, T, d_qfull, d_kproj, d_vproj, act_dtype, d_qnorm, d_knorm, (__half*)d_q16, d_q32, d_gate, h0, nh, (cudaStream_t)stream);
+    if (e == cudaSuccess) { std::fill(c.append_lo.begin(), c.append_lo.end(), INT32_MAX); for (int i = 0; i < n; i++) c.append_lo[b.seq[i]] = std::min(c.append_lo[b.seq[i]], b.pos[i]); c.prev_append = true; }
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "prep launch");
 }
 
@@ -176,6 +177,7 @@ int kata_attn_kv_quant(kata_attn_ctx* h, int32_t layer, int32_t seq, const void*
     kata::Batch b; if (int rc = make_batch(c, layer, 1, &seq, &pos0, T, b)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_kv_quant(c, b.row_base[0] + pos0, (const __half*)d_ks, (const __half*)d_vs, T, (cudaStream_t)stream);
+    if (e == cudaSuccess) { std::fill(c.append_lo.begin(), c.append_lo.end(), INT32_MAX); c.append_lo[seq] = pos0; c.prev_append = true; }
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "kv_quant launch");
 }
 
@@ -212,6 +214,7 @@ int kata_attn_decode_scalar(kata_attn_ctx* h, int32_t layer, int32_t n, const in
     for (int i = 0; i < n; i++) if (first_pos < 0 || first_pos > pos_base[i]) return fail(c, KATA_ERR_RANGE, "first_pos %d outside [0, pos_base=%d]", first_pos, pos_base[i]);
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_decode_scalar(c, b, T, first_pos, d_q32, d_gate, d_out, (cudaStream_t)stream);
+    c.prev_append = false;
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "scalar decode launch");
 }
 
@@ -225,6 +228,7 @@ int kata_attn_prefill(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t*
     kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, M, b)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_prefill(c, b, M, (const __half*)d_q16, d_gate, d_out, out_dtype, (cudaStream_t)stream);
+    c.prev_append = false;
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "prefill launch");
 }
 
@@ -250,6 +254,7 @@ int kata_attn_merge_parts(kata_attn_ctx* h, const float* d_parts, int32_t n_part
     if (!d_parts || !d_gate || !d_out || n_parts < 1 || T < 1 || T > 2) return fail(c, KATA_ERR_ARG, "merge_parts: %d parts, T=%d", n_parts, T);
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_merge_parts(c, d_parts, n_parts, T, d_gate, d_out, out_dtype, (cudaStream_t)stream);
+    c.prev_append = false;
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "merge_parts launch");
 }
 

@@ -60,6 +60,7 @@ struct DecPlan {
     int32_t merge_in_kernel;             // 1: the last contributor of a segment merges its partials; 0: decode_combine_kernel does
     int32_t pos[KATA_MAX_BATCH];         // absolute position of token 0
     int32_t kend[KATA_MAX_BATCH];        // local rows [first_row, kend) hold this call's keys; absolute key = key_off + row
+    int32_t safe_row[KATA_MAX_BATCH];    // local rows below this are not being written by the kernel launched just before: they may be loaded before the dependent-launch wait
     int64_t row_base[KATA_MAX_BATCH];
     int32_t tile_start[KATA_MAX_BATCH + 1];
     int32_t ntiles[KATA_MAX_BATCH];      // tiles per KV head of sequence b (>= 1)
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<I8>; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
     if (threadIdx.x == 0) { prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); }
-    pdl_launch_dependents();   // the next kernel of the stream (the combine kernel, the next layer's prep) may be set up while this one runs; it waits for this grid's completion itself
+    if (!p.merge_in_kernel) pdl_launch_dependents();   // the next kernel is the combine grid, which starts no loads of its own before it has waited for this one: it may be set up at once
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps
     const uint32_t sm_base = smem_u32(smem);
@@ -91,7 +92,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
     if (h == 0 && lane == 0) { for (int s = 0; s < kStages; s++) { mbar_init(bars + s * 8, 1); mbar_init(ebars + s * 8, 3); } for (int s = 0; s < 2; s++) { mbar_init(pfull + s * 8, 1); mbar_init(pempty + s * 8, 2); } }
     fence_mbar_init();
     __syncthreads();
-    pdl_wait();   // launched with programmatic stream serialisation: everything above overlapped the previous kernel's tail; from here on its results (cache rows, Q, scratch) are read
+    // Launched with programmatic stream serialisation: everything above overlapped the previous kernel's tail. Each warp waits for that kernel
+    // (griddepcontrol.wait) before it reads what it may have written (Q, gate, the newest cache rows, scratch); the producer warp first starts
+    // the loads of tiles that kernel cannot touch. Dependents are released only after the wait, so whatever ran before the previous kernel is complete.
+    bool waited = false;
 
     const int cta = blockIdx.x;
     int tile = cta_first_tile(p, cta); const int tile_end = cta_first_tile(p, cta + 1);
@@ -126,7 +130,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             }
             return nm;
         };
-        if (h == 3 && lane < kRings) produce(0, kStages);   // every stage is free here
+        if (h == 3) {   // every stage is free here
+            int n_early = 0;
+            if (!waited && lane < kRings) {   // leading tiles of this ring that lie wholly below the rows the previous kernel may be writing
+                while (n_early < kStages && p.first_row + (lt0 + lane + n_early * kRings + 1) * kTile <= p.safe_row[b]) n_early++;
+                produce(0, n_early);
+            }
+            if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
+            if (lane < kRings) produce(n_early, kStages);
+        } else if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
@@ -368,6 +380,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     int total = 0;
     for (int i = 0; i < b.n; i++) {
         p.pos[i] = b.pos[i]; p.row_base[i] = b.row_base[i]; p.kend[i] = kend_override ? kend_override[i] : b.pos[i] + T;
+        p.safe_row[i] = c.prev_append ? std::min<int64_t>(p.kend[i], (int64_t)c.append_lo[b.seq[i]] - key_off) : p.kend[i];
         const int nkeys = std::max(0, p.kend[i] - first_row); p.ntiles[i] = std::max(1, (nkeys + kTile - 1) / kTile);
         p.tile_start[i] = total; total += 4 * p.ntiles[i];
     }
@@ -377,10 +390,14 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     n_ctas = std::max(1, std::min(std::min(n_ctas, total), c.sm_count * 8));
     if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
+    // Early loads pay when a CTA streams for long (batch 8 at 16-32K: -2 us of 140); with short ranges (batch 1: 55 tiles per CTA) they take
+    // bandwidth from the previous kernel's last CTAs, which everybody then waits for (+2 us of 31): switched off there.
+    if (p.q_tiles < 128) for (int i = 0; i < b.n; i++) p.safe_row[i] = 0;
     p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
     const cudaError_t le = i8 ? launch_pdl(decode_mma_kernel<true>, dim3(n_ctas), dim3(kThreads), Geo<true>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
                               : launch_pdl(decode_mma_kernel<false>, dim3(n_ctas), dim3(kThreads), Geo<false>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+    c.prev_append = false;   // this kernel writes no cache rows
     if (le != cudaSuccess) return le;
     c.launches++;
     if (!p.merge_in_kernel) {

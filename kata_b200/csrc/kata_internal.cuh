@@ -24,6 +24,7 @@ constexpr int kPartStride = 258;   // one (token, head) partial: O[256], m, l
 // is row_base[b] + position, with row_base already including the layer offset layer * max_ctx.
 struct Batch {
     int32_t n;
+    int32_t seq[KATA_MAX_BATCH];        // sequence ids
     int32_t pos[KATA_MAX_BATCH];        // pos0 / pos_base per sequence
     int64_t row_base[KATA_MAX_BATCH];   // arena row of position 0 of (sequence, layer)
     int32_t item_start[KATA_MAX_BATCH + 1];   // decode: first work item of sequence b (prefix sum of 4 * n_splits[b])
@@ -41,6 +42,9 @@ struct Ctx {
     __half* ksc = nullptr; __half* vsc = nullptr;          // [total_rows][4] fp16 (int8 mode)
     // decode scratch: per work item (sequence, kv head, split) the unnormalised partial rows and their (m, l)
     float* part_o = nullptr; float* part_ml = nullptr; int32_t* counters = nullptr; int32_t max_items = 0;
+    // What the kernel launched last through this context wrote into the cache: nothing (prev_append false), or rows from position append_lo[s]
+    // on in sequence s. The decode kernel may load rows that kernel cannot be writing before it waits for it (dependent launch).
+    bool prev_append = false; std::vector<int32_t> append_lo;
     // scalar-path scratch (k_attn_split partials)
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
     // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
