@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem = s_tmem, t_o = tmem, t_s0 = tmem + 256;
+    pdl_wait(); pdl_launch_dependents();   // launched with programmatic stream serialisation: the set-up above overlapped the previous kernel (the chunk's prep); its rows and Q are read from here on
     // Running counters shared by construction: gt = key tiles so far over all items of this pair (stage, score buffer and phase of the
     // per-tile barriers), it = items so far (phase of the per-item barriers).
 
@@ -319,10 +320,12 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     // persistent CTA pairs: at most one pair per two SMs, items dealt round-robin (longest first)
     const int n_items = ((M + kBMq - 1) / kBMq) * (kH / 2) * b.n, n_pairs = std::max(1, std::min(n_items, c.sm_count / 2));
     cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(2 * n_pairs, 1, 1); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
-    cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
-    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaLaunchAttribute at[2]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 2;
     const cudaError_t le = cudaLaunchKernelEx(&cfg, prefill_tc5_kernel, tm_q, c.tm_k64h, c.tm_v128h, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err);
     if (le != cudaSuccess) return le;
+    c.prev_append = false;
     c.launches++;
     return cudaGetLastError();
 }
