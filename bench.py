@@ -45,6 +45,7 @@ WORKLOADS = {
     # chunked: (kind, batch, kv mode, prompt length, restored prefix)
     "chunked_b1": ("chunked", 1, "fp16", 7300, 3600),
     "chunked_b16": ("chunked", 16, "fp16", 7300, 3600),
+    "chunked_int8_b4": ("chunked", 4, "int8", 7300, 3600),    # the int8 cache goes through the mma.sync prefill kernel
     "chunked_small": ("chunked", 4, "fp16", 3072, 1024),      # ~0.4 GB: the size used for ncu captures of the prefill kernel
     "out_fwht": ("fwht", 32768, "fp32", 6144, 6144),          # the sign + Walsh-Hadamard transform that follows attention, on 32,768 output rows (805 MB in, 805 MB out)
 }

@@ -98,12 +98,19 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     if (ok && cfg->kv_mode == KATA_KV_FP16)
         ok = cudaMalloc((void**)&c.sc_pm, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess && cudaMalloc((void**)&c.sc_pl, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess &&
              cudaMalloc((void**)&c.sc_pacc, kata::scalar_scratch_floats_acc() * 4) == cudaSuccess;
+    int64_t stage_rows = 0;
+    if (ok && cfg->kv_mode == KATA_KV_INT8) {   // staging arena of the tcgen05 prefill: one layer of every sequence, codes expanded to fp16
+        for (int sq = 0; sq < cfg->n_seqs; sq++) { c.stage_row0.push_back(stage_rows); stage_rows += cfg->max_ctx[sq]; }
+        ok = cudaMalloc((void**)&c.k16_stage, (size_t)stage_rows * kata::kKVD * 2) == cudaSuccess && cudaMalloc((void**)&c.v16_stage, (size_t)stage_rows * kata::kKVD * 2) == cudaSuccess;
+        if (ok) { cudaMemset(c.k16_stage, 0, (size_t)stage_rows * kata::kKVD * 2); cudaMemset(c.v16_stage, 0, (size_t)stage_rows * kata::kKVD * 2); }
+    }
     if (!ok) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_NOMEM; }
     {   // decode: rank-4 tile views (a 128-byte column block = 64 fp16 or 128 int8 elements); tcgen05 prefill (fp16): the half tiles of a CTA pair
         const int blocks = 256 * c.elt / 128;
         const int tile_rows = c.elt == 1 ? 32 : 16;   // keys per decode tile
         if (!kata::make_tile_tmap(&c.tm_k_tile, c.k_arena, c.elt, rows, tile_rows, blocks) || !kata::make_tile_tmap(&c.tm_v_tile, c.v_arena, c.elt, rows, tile_rows, blocks) ||
-            (c.elt == 2 && (!kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
+            (c.elt == 2 && (!kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2))) ||
+            (c.elt == 1 && (!kata::make_tile_tmap(&c.tm_k64h_stage, c.k16_stage, 2, stage_rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h_stage, c.v16_stage, 2, stage_rows, 128, 2)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
     if (kata::configure_decode(cfg->kv_mode == KATA_KV_INT8) != cudaSuccess || kata::configure_prefill(cfg->kv_mode == KATA_KV_INT8) != cudaSuccess) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_CUDA; }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);
@@ -117,7 +124,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
 int kata_attn_destroy(kata_attn_ctx* h) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c; DeviceGuard guard(c.cfg.device);
-    void* ptrs[] = {c.k_arena, c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, c.sc_pm, c.sc_pl, c.sc_pacc};
+    void* ptrs[] = {c.k_arena, c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, c.sc_pm, c.sc_pl, c.sc_pacc, c.k16_stage, c.v16_stage};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete h;
     return KATA_OK;

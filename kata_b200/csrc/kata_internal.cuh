@@ -49,6 +49,8 @@ struct Ctx {
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
     // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
     CUtensorMap tm_k_tile{}, tm_v_tile{};   // rank-4 views for decode: one TMA instruction per 16-key tile of one KV head
+    __half* k16_stage = nullptr; __half* v16_stage = nullptr; std::vector<int64_t> stage_row0;   // int8 mode: one layer of fp16-expanded codes for the tcgen05 prefill, [sum of max_ctx][1024] each; first row per sequence
+    CUtensorMap tm_k64h_stage{}, tm_v128h_stage{};
     CUtensorMap tm_k64h{}, tm_v128h{};   // rank-4 views for the tcgen05 prefill (fp16 mode): 64 keys x 256 dims of K, 128 keys x 128 dims of V (the halves a CTA of a pair loads)
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
     int sm_count = 148;

@@ -54,10 +54,15 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const i
 }
 
 // One work item = (query tile, head pair, sequence); items are ordered longest first and dealt round-robin to the CTA pairs.
-struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, h, kvh, bi; };
+struct PfStage { int64_t kv_row0[KATA_MAX_BATCH]; };   // SCALED: first row of sequence b in the fp16 staging arena (position 0)
+struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, h, kvh, bi; int64_t sc_row0; };
 
+// SCALED: the K/V tiles are int8 codes expanded to fp16 (exact integers) in a staging arena whose rows are kv_row0[b] + position; the per-key
+// scales are applied as k_flash_prefill_q8 does (shaders/flash.metal:10-68 with Q8): S = (Q.Kq) * ksc[key], P~ = half(p * vsc[key]), l from p.
+template <bool SCALED>
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                                                                   const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err) {
+                                                                   const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err,
+                                                                   const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t rank = tc5::cluster_rank();
@@ -65,13 +70,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     auto item_of = [&](int it) {   // it-th item of this CTA pair
         const int idx = pair + it * n_pairs, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
         PfItem t; t.bi = rem / (kH / 2); t.h = 2 * (rem % (kH / 2)) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
-        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = (int)b.row_base[t.bi];
+        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
         return t;
     };
     const int my_items = pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
     const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + kTileB + 2 * kHalfB, bars = base + kTileB + 4 * kHalfB;   // K stage s at k_sm + s * kHalfB, V stage s at v_sm + s * kHalfB
-    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128], s_stage[8][32 * 17];   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
+    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128], s_stage[8][32 * 17]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     if (tid == 0) {
@@ -177,10 +182,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             const uint32_t t_s = t_s0 + (gt & 1u) * 128u + lane_sel;
             if (alive && !warp_wait(bar(B_SFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
             tc5::fence_after_sync();
+            if (SCALED) {   // the tile's 128 K scales and 128 V scales: one value per softmax thread into shared memory, then everybody reads its 64 + 64
+                const int key = min(j * kBNk + (tid & 127), max(kend - 1, 0));
+                s_sc[gt & 1u][tid >> 7][tid & 127] = (tid < 128 ? ksc : vsc)[(t.sc_row0 + key) * 4 + t.kvh];
+                asm volatile("bar.sync 9, 256;" ::: "memory");   // all eight softmax warps, every tile, whatever happened before
+            }
             uint32_t v[2][32];
 #pragma unroll
             for (int c = 0; c < 2; c++) tc5::ld32(t_s + g * 64 + c * 32, v[c]);
             tc5::wait_ld();
+            if (SCALED) {
+                const uint4* kq = reinterpret_cast<const uint4*>(&s_sc[gt & 1u][0][g * 64]);
+#pragma unroll
+                for (int q8 = 0; q8 < 8; q8++) {
+                    const uint4 u = kq[q8]; const __half2* hp = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __half22float2(hp[e]); const int i = q8 * 8 + 2 * e;
+                        v[i >> 5][i & 31] = __float_as_uint(__uint_as_float(v[i >> 5][i & 31]) * f.x); v[(i + 1) >> 5][(i + 1) & 31] = __float_as_uint(__uint_as_float(v[(i + 1) >> 5][(i + 1) & 31]) * f.y);
+                    }
+                }
+            }
             const int key0 = j * kBNk + g * 64;
             if (j * kBNk + kBNk > min(kend, pos_base + q0 + 1)) {   // the tile reaches past what the first row may see: mask by select
 #pragma unroll
@@ -221,7 +243,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ex2(fmaf(__uint_as_float(v[c][i]), kLog2e, -msub)), p1 = ex2(fmaf(__uint_as_float(v[c][i + 1]), kLog2e, -msub));
-                    sum += p0 + p1; pk[c * 16 + (i >> 1)] = pack_h2(p0, p1);
+                    sum += p0 + p1;
+                    if (SCALED) { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&s_sc[gt & 1u][1][g * 64 + c * 32 + i])); pk[c * 16 + (i >> 1)] = pack_h2(p0 * f.x, p1 * f.y); }
+                    else pk[c * 16 + (i >> 1)] = pack_h2(p0, p1);
                 }
             l += sum;
             tc5::st32(t_s + g * 32, pk);   // P: keys 0-63 in columns [0,32), keys 64-127 in [32,64) of the S buffer (the partner's scores there are in its registers since the pair barrier)
@@ -300,6 +324,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     if (w == 0) tc5::tmem_dealloc2(tmem, 512);
 }
 
+// int8 cache: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
+// the integers themselves (exact in fp16); the scales stay with the softmax. 64 threads per 1024-code row, 16 codes per thread.
+__global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const int M, const PfStage stg, const uint8_t* __restrict__ kq, const uint8_t* __restrict__ vq, __half* __restrict__ k16, __half* __restrict__ v16) {
+    const int bi = blockIdx.y, rows = b.pos[bi] + M;
+    const uint8_t* src = blockIdx.z ? vq : kq; __half* dst = blockIdx.z ? v16 : k16;
+    for (int r = blockIdx.x * 4 + (threadIdx.x >> 6); r < rows; r += gridDim.x * 4) {
+        const int c16 = threadIdx.x & 63;
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + (b.row_base[bi] + r) * kKVD) + c16);
+        const uint32_t wd[4] = {u.x ^ 0x80808080u, u.y ^ 0x80808080u, u.z ^ 0x80808080u, u.w ^ 0x80808080u};
+        uint32_t o[8];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {   // byte x -> fp16 0x64xx = 1024 + (code + 128); minus 1152 gives the code exactly
+            const uint32_t lo = prmt(wd[e], 0x64646464u, 0x4140u), hi = prmt(wd[e], 0x64646464u, 0x4342u);
+            const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+            const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias), c2 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+            o[2 * e] = *reinterpret_cast<const uint32_t*>(&a); o[2 * e + 1] = *reinterpret_cast<const uint32_t*>(&c2);
+        }
+        uint4* d4 = reinterpret_cast<uint4*>(dst + (stg.kv_row0[bi] + r) * kKVD) + 2 * c16;
+        d4[0] = make_uint4(o[0], o[1], o[2], o[3]); d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
@@ -308,22 +354,34 @@ cudaError_t configure_prefill_mma(bool int8);
 // Shared-memory opt-in of the prefill kernels on the current device (function attributes are per device: done once per context).
 cudaError_t configure_prefill(bool int8) {
     cudaError_t e = configure_prefill_mma(int8);
-    if (e == cudaSuccess && !int8) e = cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+    if (e == cudaSuccess) e = int8 ? cudaFuncSetAttribute(prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
+                                   : cudaFuncSetAttribute(prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
     return e;
 }
 
-// fp16 cache: tcgen05 kernel (unless the context was created with the legacy-path flag); int8 cache: mma.sync kernel.
+// tcgen05 kernel (unless the context was created with the legacy-path flag). An int8 cache goes through it as well: the layer's codes are first
+// expanded to fp16 in the context's staging arena (one pass over the prefix, a few per cent of the attention time), the scales are applied in
+// the softmax. The mma.sync kernel remains the cross-check and serves windowed caches (a position offset), which the staging arena does not cover.
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
-    if (c.cfg.kv_mode == KATA_KV_INT8 || (c.cfg.flags & 1)) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
+    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
+    bool windowed = false; for (int i = 0; i < b.n; i++) windowed |= c.pos_off[b.seq[i]] != 0;
+    if ((c.cfg.flags & 1) || (i8 && (!c.k16_stage || windowed))) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
     CUtensorMap tm_q;
     if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
+    PfStage stg{};
+    if (i8) {
+        int max_rows = 0; for (int i = 0; i < b.n; i++) { stg.kv_row0[i] = c.stage_row0[b.seq[i]]; max_rows = std::max(max_rows, b.pos[i] + M); }
+        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, 2), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage);
+        c.launches++;
+    }
     // persistent CTA pairs: at most one pair per two SMs, items dealt round-robin (longest first)
     const int n_items = ((M + kBMq - 1) / kBMq) * (kH / 2) * b.n, n_pairs = std::max(1, std::min(n_items, c.sm_count / 2));
     cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(2 * n_pairs, 1, 1); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
     cudaLaunchAttribute at[2]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, prefill_tc5_kernel, tm_q, c.tm_k64h, c.tm_v128h, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err);
+    const cudaError_t le = i8 ? cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<true>, tm_q, c.tm_k64h_stage, c.tm_v128h_stage, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc)
+                              : cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<false>, tm_q, c.tm_k64h, c.tm_v128h, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err, stg, (const __half*)nullptr, (const __half*)nullptr);
     if (le != cudaSuccess) return le;
     c.prev_append = false;
     c.launches++;
