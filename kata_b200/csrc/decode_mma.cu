@@ -139,6 +139,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
             if (lane < kRings) produce(n_early, kStages);
         } else if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
+        auto load_scale = [&](int i, const __half* plane) -> uint32_t {
+            const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+            return __ldg(reinterpret_cast<const unsigned short*>(plane) + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 4 + kvh);
+        };
+        uint32_t kA = 0, kB = 0, kC = 0, vA = 0, vB = 0, vC = 0;
+        if (I8 && h == 0) {   // score warp: the loads fly while the Q block is staged
+            if (n_mine > 0) { kA = load_scale(0, ksc); vA = load_scale(0, vsc); }
+            if (n_mine > 1) { kB = load_scale(1, ksc); vB = load_scale(1, vsc); }
+            if (n_mine > 2) { kC = load_scale(2, ksc); vC = load_scale(2, vsc); }
+        }
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
@@ -168,16 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             // ---- score warp: S = Q K^T, online softmax, P and the rescale factors handed to the value warp; runs up to two tiles ahead
             // int8: lane j fetches the K and V scale of the tile's key j (mod the tile length), three tiles ahead; they are kept as raw fp16 bits so
             // that nothing depends on a load until its tile comes up (the scale planes are first touched here: DRAM latency)
-            auto load_scale = [&](int i, const __half* plane) -> uint32_t {
-                const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-                return __ldg(reinterpret_cast<const unsigned short*>(plane) + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 4 + kvh);
-            };
-            uint32_t kA = 0, kB = 0, kC = 0, vA = 0, vB = 0, vC = 0;
-            if (I8) {
-                if (n_mine > 0) { kA = load_scale(0, ksc); vA = load_scale(0, vsc); }
-                if (n_mine > 1) { kB = load_scale(1, ksc); vB = load_scale(1, vsc); }
-                if (n_mine > 2) { kC = load_scale(2, ksc); vC = load_scale(2, vsc); }
-            }
+            // (the first three tiles' scales were requested before the Q block was staged)
             for (int i = 0; i < n_mine; i++) {
                 const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
                 const uint32_t kt = ring_stage0 + stg * G::kStageBytes;
