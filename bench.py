@@ -40,12 +40,14 @@ WORKLOADS = {
     "decode_b64": ("decode", 64, "fp16", 32768, 16384),
     "decode_int8_b8": ("decode", 8, "int8", 32768, 16384),
     "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
+    "decode_int8v_b8": ("decode", 8, "int8v", 32768, 16384),    # keys fp16, values int8 (the reference's KATA_KV=int8v)
     "splitkv_b1": ("splitkv", 1, "fp16", 32768, 32768),       # one 32K sequence, keys split across the ranks, NCCL merge per layer
     "pp512": ("prefill", 1, "fp16", 512, 512),
     # chunked: (kind, batch, kv mode, prompt length, restored prefix)
     "chunked_b1": ("chunked", 1, "fp16", 7300, 3600),
     "chunked_b16": ("chunked", 16, "fp16", 7300, 3600),
-    "chunked_int8_b4": ("chunked", 4, "int8", 7300, 3600),    # the int8 cache goes through the mma.sync prefill kernel
+    "chunked_int8_b4": ("chunked", 4, "int8", 7300, 3600),    # the codes are expanded to fp16 per layer for the tcgen05 kernel
+    "chunked_int8v_b4": ("chunked", 4, "int8v", 7300, 3600),
     "chunked_small": ("chunked", 4, "fp16", 3072, 1024),      # ~0.4 GB: the size used for ncu captures of the prefill kernel
     "out_fwht": ("fwht", 32768, "fp32", 6144, 6144),          # the sign + Walsh-Hadamard transform that follows attention, on 32,768 output rows (805 MB in, 805 MB out)
 }
@@ -238,7 +240,7 @@ def run_decode(args, rank, world, kind_cfg):
         t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
-    row_bytes = 4096 if kv_mode == "fp16" else 2064           # K+V bytes per key per layer (int8: codes + both fp16 scales)
+    row_bytes = {"fp16": 4096, "int8": 2064, "int8v": 3080}[kv_mode]   # K+V bytes per key per layer (int8: codes + both fp16 scales; int8v: fp16 keys, value codes + their scales)
     mean_len = float(np.mean([pos_timed0 + i + 1 for i in range(args.steps)]))   # keys attended per sequence per step (the new key included)
     bytes_per_launch = float(np.sum(pos_timed0 + 1)) * row_bytes
     pk = peaks()

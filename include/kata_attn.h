@@ -41,7 +41,7 @@ extern "C" {
 #define KATA_STATIC_MAX_BATCH 8 /* sequences per kata_attn_decode_static call */
 
 enum { KATA_OK = 0, KATA_ERR_ARG = 1, KATA_ERR_RANGE = 2, KATA_ERR_MODE = 3, KATA_ERR_CUDA = 4, KATA_ERR_DEVICE_WAIT = 5, KATA_ERR_NOMEM = 6 };
-enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1 };             /* KATA_KV=fp16|int8 (src/engine.cpp:54-58) */
+enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1, KATA_KV_INT8V = 2 };   /* KATA_KV=fp16|int8|int8v (src/engine.cpp:54-59); int8v: keys fp16, values int8 (src/engine.h:71-73) */
 enum { KATA_ROUND_RINT = 0, KATA_ROUND_HALF_AWAY = 1 };  /* rint (ties to even) is what the reference kernel does (shaders/flash.metal:170) */
 enum { KATA_ACT_F32 = 0, KATA_ACT_BF16 = 1 };            /* dtype of qfull / kproj / vproj / out */
 
@@ -59,7 +59,8 @@ typedef struct kata_attn_config {
 } kata_attn_config;
 
 /* Engine::load, cache part (src/engine.cpp:54-60,79): allocates, zero-filled (src/gpu.cpp:26-30), per sequence
- * K and V planes [n_layers][max_ctx][1024] (fp16, or int8 plus fp16 scale planes [n_layers][max_ctx][4]) and all scratch. */
+ * K and V planes [n_layers][max_ctx][1024] (fp16, or int8 plus fp16 scale planes [n_layers][max_ctx][4]; int8v: K fp16, V int8 plus
+ * its scale plane) and all scratch. */
 int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out);
 int kata_attn_destroy(kata_attn_ctx* ctx);
 
@@ -75,8 +76,8 @@ const char* kata_attn_last_error(const kata_attn_ctx* ctx);
 int kata_attn_check(kata_attn_ctx* ctx, void* stream);
 
 /* k_attn_prep / k_attn_prep_b (shaders/attn.metal:5-37, shaders/prefill.metal:179-206; encoded at src/engine.cpp:168,
- * 274, 360, 404, 473, 608), with k_cvt_q_half (shaders/flash.metal:71) and, in int8 mode, k_kv_quant_sym
- * (Engine::dKvQuant, src/engine.cpp:524-527) fused in.
+ * 274, 360, 404, 473, 608), with k_cvt_q_half (shaders/flash.metal:71) and, in the int8 modes, k_kv_quant_sym
+ * (Engine::dKvQuant, src/engine.cpp:524-527) fused in (int8v: for the value rows only; the key rows are stored as fp16).
  * For sequence seq_ids[b] and token t < T at position pos0[b]+t, head slots [h0, h0+nh): slots 0..23 query heads
  * (RMSNorm, partial RoPE, gate split), 24..27 key heads (RMSNorm, RoPE, append to the K plane), 28..31 value heads
  * (append to the V plane). h0=24, nh=8 appends K/V only (src/engine.cpp:402-404).
@@ -91,10 +92,11 @@ int kata_attn_prep(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* 
 
 /* Engine::dKvQuant + k_kv_quant_sym (src/engine.cpp:524-527, shaders/flash.metal:157-178) as a stand-alone call:
  * quantise T fp16 rows d_ks, d_vs [T][1024] into rows pos0.. of one sequence's int8 planes. Bit-exact with the
- * reference arithmetic: scale = fp16(amax/127) (1.0 for an all-zero row), code = clamp(round(v * (1/float(scale)))). */
+ * reference arithmetic: scale = fp16(amax/127) (1.0 for an all-zero row), code = clamp(round(v * (1/float(scale)))).
+ * int8v contexts quantise d_vs only (d_ks may be NULL and is ignored: the key plane holds fp16 rows). */
 int kata_attn_kv_quant(kata_attn_ctx* ctx, int32_t layer, int32_t seq, const void* d_ks, const void* d_vs, int32_t T, int32_t pos0, void* stream);
 
-/* Engine::dDecAttn (src/engine.cpp:119-127): k_dec_q_pack + k_attn_dec_split[_q8] + k_attn_dec_combine
+/* Engine::dDecAttn (src/engine.cpp:119-127): k_dec_q_pack + k_attn_dec_split[_q8|_k16v8] + k_attn_dec_combine
  * (shaders/flash.metal:77-152). T in 1..KATA_MAX_VERIFY query tokens per sequence at positions pos_base[b]+t (1: step, 2: verify2,
  * up to 8: Engine::verifyWide, src/engine.cpp:602-622, which the reference sends through its scalar kernels); token t sees keys
  * [first_pos, pos_base[b]+t]; first_pos is 0 for the trunk and 1 for the MTP-head cache (src/engine.cpp:362).
@@ -107,7 +109,7 @@ int kata_attn_decode(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t
 int kata_attn_decode_scalar(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,
                             const float* d_q32, const float* d_gate, float* d_out, void* stream);
 
-/* k_flash_prefill / k_flash_prefill_q8 (shaders/flash.metal:10-68; encoded at src/engine.cpp:279, 614): causal flash
+/* k_flash_prefill / k_flash_prefill_q8 / k_flash_prefill_k16v8 (shaders/flash.metal:10-68, 198-250; encoded at src/engine.cpp:279, 614): causal flash
  * attention of M <= KATA_MAX_CHUNK query rows per sequence at positions pos_base[b]+r over keys [0, pos_base[b]+r] of
  * the cache (this chunk's rows must already have been appended by kata_attn_prep). d_q16, d_gate, d_out: [n][M][6144]. */
 int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t M,
@@ -137,7 +139,8 @@ int kata_attn_out_fwht(const float* d_x, const float* d_sign, float* d_out, int6
 
 /* KV planes for the prefix cache: Engine::kvPlanes / kvPlaneRow / kvPlanePtr (src/engine.h:74-81), used by
  * PrefixCache::restore and ::writeFile (src/ckpt.cpp:98, 134). Plane order and row sizes match the reference:
- * fp16 -> {K, V} rows of 2048 B; int8 -> {K, V, K scales, V scales} rows of 1024, 1024, 8, 8 B.
+ * fp16 -> {K, V} rows of 2048 B; int8 -> {K, V, K scales, V scales} rows of 1024, 1024, 8, 8 B;
+ * int8v -> {K, V, V scales} rows of 2048, 1024, 8 B.
  * The reference reads and writes shared memory directly; here the copy is explicit and synchronous. */
 int32_t kata_attn_kv_planes(const kata_attn_ctx* ctx);
 size_t kata_attn_kv_plane_row_bytes(const kata_attn_ctx* ctx, int32_t plane);

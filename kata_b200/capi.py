@@ -15,7 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libkata_attn.so")
 
 OK = 0
-KV_FP16, KV_INT8 = 0, 1
+KV_FP16, KV_INT8, KV_INT8V = 0, 1, 2
+_KV_MODES = {"fp16": KV_FP16, "int8": KV_INT8, "int8v": KV_INT8V}   # the reference's KATA_KV values (src/engine.cpp:54)
 ROUND_RINT, ROUND_HALF_AWAY = 0, 1
 ACT_F32, ACT_BF16 = 0, 1
 QD, KVD, QFULL, MAX_BATCH = 6144, 1024, 12288, 64
@@ -97,8 +98,10 @@ class AttnContext:
         self.device = torch.cuda.current_device() if device is None else device
         self.max_ctx, mp = _i32(max_ctx)
         self.n_layers, self.n_seqs = n_layers, len(self.max_ctx)
-        self.int8 = kv_mode == "int8"
-        cfg = Config(self.device, n_layers, self.n_seqs, mp, KV_INT8 if self.int8 else KV_FP16, ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, 1 if legacy_prefill else 0)
+        if kv_mode not in _KV_MODES:
+            raise ValueError(f"kv_mode {kv_mode!r}: one of {sorted(_KV_MODES)}")
+        self.int8, self.kv_mode = kv_mode == "int8", kv_mode
+        cfg = Config(self.device, n_layers, self.n_seqs, mp, _KV_MODES[kv_mode], ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, 1 if legacy_prefill else 0)
         self.h = C.c_void_p()
         rc = self.L.kata_attn_create(C.byref(cfg), C.byref(self.h))
         if rc != OK:
@@ -152,7 +155,7 @@ class AttnContext:
         return q16, q32, gate
 
     def kv_quant(self, layer, seq, ks, vs, pos0):
-        self._ck(self.L.kata_attn_kv_quant(self.h, layer, seq, _dp(ks), _dp(vs), ks.shape[0], pos0, _stream()))
+        self._ck(self.L.kata_attn_kv_quant(self.h, layer, seq, _dp(ks), _dp(vs), vs.shape[0], pos0, _stream()))   # ks may be None on an int8v context
 
     def decode(self, layer, seq_ids, pos_base, T, q16, gate, first_pos=0, out=None, out_dtype=torch.float32):
         sa, sp = _i32(seq_ids)

@@ -3,7 +3,8 @@
 #include "attn_engine.hpp"
 
 extern "C" {
-void* kata_engine_create(int device, int nAttn, int maxCtx, int kvInt8) { try { return new kata::AttnEngine(device, nAttn, maxCtx, kvInt8 != 0); } catch (...) { return nullptr; } }
+// kvInt8: 0 fp16, 1 int8, 2 int8v
+void* kata_engine_create(int device, int nAttn, int maxCtx, int kvInt8) { try { return new kata::AttnEngine(device, nAttn, maxCtx, kvInt8 == 1, true, kvInt8 == 2); } catch (...) { return nullptr; } }
 void kata_engine_destroy(void* e) { delete static_cast<kata::AttnEngine*>(e); }
 int kata_engine_step_attn(void* e, int ai, uint32_t pos, const float* qfull, const float* k, const float* v, const float* qn, const float* kn, void* q16, float* gate, float* out, void* stream) {
     return static_cast<kata::AttnEngine*>(e)->stepAttn(ai, pos, qfull, k, v, qn, kn, q16, gate, out, stream); }

@@ -14,9 +14,10 @@ namespace kata {
 class AttnEngine {
 public:
     // Engine::load, cache part (src/engine.cpp:54-60,79): trunk caches for nAttn layers plus the MTP head's 1-layer fp16 cache.
-    AttnEngine(int device, int nAttn, int maxCtx, bool kvInt8, bool hasMtp = true) : maxCtx_(maxCtx), kvInt8_(kvInt8) {
+    // kvInt8K / kvInt8V as the reference derives them from KATA_KV = fp16 | int8 | int8v (src/engine.cpp:54): int8v keeps the keys in fp16.
+    AttnEngine(int device, int nAttn, int maxCtx, bool kvInt8K, bool hasMtp = true, bool kvInt8V = false) : maxCtx_(maxCtx), kvInt8_(kvInt8K || kvInt8V) {
         int32_t rows = maxCtx;
-        kata_attn_config cfg{device, nAttn, 1, &rows, kvInt8 ? KATA_KV_INT8 : KATA_KV_FP16, KATA_ROUND_RINT, 0, 0};
+        kata_attn_config cfg{device, nAttn, 1, &rows, kvInt8K ? KATA_KV_INT8 : kvInt8V ? KATA_KV_INT8V : KATA_KV_FP16, KATA_ROUND_RINT, 0, 0};
         if (kata_attn_create(&cfg, &attn_) != KATA_OK) throw std::runtime_error("kata_attn_create failed");
         if (hasMtp) { kata_attn_config m = cfg; m.n_layers = 1; m.kv_mode = KATA_KV_FP16; if (kata_attn_create(&m, &mtp_) != KATA_OK) { kata_attn_destroy(attn_); throw std::runtime_error("kata_attn_create (mtp) failed"); } }
     }

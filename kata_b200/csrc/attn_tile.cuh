@@ -55,10 +55,10 @@ struct RowState {   // softmax state of rows g and g+8 (m in log2 units, l parti
 // K and V rows (row stride TileGeo::kRowStride). key0: index of the tile's first key; row g sees keys < lim0, row g+8
 // keys < lim1 (0 for a dead row). ks/vs: int8 mode, the fp16 scales of this thread's four score columns
 // (keys key0 + nt*8 + 2*t4 + e -> [nt][e]).
-template <bool I8>
+template <bool I8, bool V8 = I8>   // I8: int8 keys, V8: int8 values
 __device__ __forceinline__ void tile_qk_softmax_pv(const uint32_t q_sm, const uint32_t k_sm, const uint32_t v_sm, const int key0, const int lim0, const int lim1,
                                                    const float (&ks)[2][2], const float (&vs)[2][2], RowState& st, const int lane) {
-    using G = TileGeo<I8>;
+    using G = TileGeo<I8>; using GV = TileGeo<V8>;
     using namespace ptx;
     const int t4 = lane & 3;
     float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
@@ -115,13 +115,13 @@ __device__ __forceinline__ void tile_qk_softmax_pv(const uint32_t q_sm, const ui
 #pragma unroll
         for (int j = 0; j < 32; j++) { st.o[j][0] *= al0; st.o[j][1] *= al0; st.o[j][2] *= al1; st.o[j][3] *= al1; }
     }
-    if (I8) {
+    if (V8) {
 #pragma unroll
         for (int nt = 0; nt < 2; nt++) { pr[nt][0] *= vs[nt][0]; pr[nt][1] *= vs[nt][1]; pr[nt][2] *= vs[nt][0]; pr[nt][3] *= vs[nt][1]; }
     }
     const uint32_t pa0 = pack_h2(pr[0][0], pr[0][1]), pa1 = pack_h2(pr[0][2], pr[0][3]), pa2 = pack_h2(pr[1][0], pr[1][1]), pa3 = pack_h2(pr[1][2], pr[1][3]);
-    const uint32_t va = v_sm + ((lane & 7) + ((lane >> 3) & 1) * 8) * G::kRowStride + (lane >> 4) * 16;
-    if (!I8) {
+    const uint32_t va = v_sm + ((lane & 7) + ((lane >> 3) & 1) * 8) * GV::kRowStride + (lane >> 4) * 16;
+    if (!V8) {
 #pragma unroll
         for (int j2 = 0; j2 < 16; j2++) {
             uint32_t b0, b1, b2, b3; ldsm_x4_t(va + j2 * 32, b0, b1, b2, b3);
@@ -199,7 +199,7 @@ template <int NJ> struct ValueStateT {   // NJ n-tiles of 8 dims: 16 = one half 
 // Score warp, one tile. Returns the unrounded-then-scaled P values pr[n-tile][4] (n-tile nt = 8 keys: keys key0 + 8*nt + 2*t4 + e are
 // elements e and 2 + e for rows g and g + 8) and the rescale factors of rows g and g + 8. ks/vs: int8 scales of this thread's score
 // columns ([nt][e]); qs: int8 mode, sums over the 256 dims of Q rows g and g+8.
-template <bool I8, int NK>
+template <bool I8, bool V8, int NK>   // I8: int8 keys; V8: int8 values (P takes the value scale before it is rounded to fp16)
 __device__ __forceinline__ void score_tile(const uint32_t q_sm, const uint32_t k_sm, const int key0, const int lim0, const int lim1,
                                            const float (&ks)[2 * NK][2], const float (&vs)[2 * NK][2], const float (&qs)[2], ScoreState& st, const int lane,
                                            float (&pr)[2 * NK][4], float& al0, float& al1) {
@@ -280,7 +280,7 @@ __device__ __forceinline__ void score_tile(const uint32_t q_sm, const uint32_t k
         sum0 += q0; sum1 += q1s;
     }
     st.l0 = st.l0 * al0 + sum0; st.l1 = st.l1 * al1 + sum1;
-    if (I8) {
+    if (V8) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) { pr[nt][0] *= vs[nt][0]; pr[nt][1] *= vs[nt][1]; pr[nt][2] *= vs[nt][0]; pr[nt][3] *= vs[nt][1]; }
     }

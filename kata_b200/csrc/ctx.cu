@@ -15,9 +15,9 @@ namespace kata {
 size_t scalar_scratch_floats_pm();
 size_t scalar_scratch_floats_acc();
 int decode_max_slots(int sm_count);
-cudaError_t configure_decode(bool int8);
+cudaError_t configure_decode(int kv_mode);
 cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s);
-cudaError_t configure_prefill(bool int8);
+cudaError_t configure_prefill(int kv_mode);
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s, int tok_stride = 0, int tok0 = 0);
 }  // namespace kata
@@ -57,11 +57,11 @@ int make_batch(Ctx& c, int layer, int n, const int32_t* seq_ids, const int32_t* 
 
 struct PlaneRef { uint8_t* base; size_t row_bytes; };
 bool plane_ref(Ctx& c, int plane, PlaneRef& r) {
-    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
-    if (plane == 0) { r = {(uint8_t*)c.k_arena, (size_t)kata::kKVD * c.elt}; return true; }
-    if (plane == 1) { r = {(uint8_t*)c.v_arena, (size_t)kata::kKVD * c.elt}; return true; }
-    if (i8 && plane == 2) { r = {(uint8_t*)c.ksc, 8}; return true; }
-    if (i8 && plane == 3) { r = {(uint8_t*)c.vsc, 8}; return true; }
+    // kvPlanePtr (src/engine.h:79-81): plane 2 is the K scales when the keys are int8, else the V scales
+    if (plane == 0) { r = {(uint8_t*)c.k_arena, (size_t)kata::kKVD * c.elt_k}; return true; }
+    if (plane == 1) { r = {(uint8_t*)c.v_arena, (size_t)kata::kKVD * c.elt_v}; return true; }
+    if (c.k8() && plane == 2) { r = {(uint8_t*)c.ksc, 8}; return true; }
+    if (c.v8() && plane == (c.k8() ? 3 : 2)) { r = {(uint8_t*)c.vsc, 8}; return true; }
     return false;
 }
 
@@ -72,7 +72,7 @@ extern "C" {
 int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     if (!cfg || !out) return KATA_ERR_ARG;
     *out = nullptr;
-    if (cfg->n_layers < 1 || cfg->n_seqs < 1 || !cfg->max_ctx || (cfg->kv_mode != KATA_KV_FP16 && cfg->kv_mode != KATA_KV_INT8) ||
+    if (cfg->n_layers < 1 || cfg->n_seqs < 1 || !cfg->max_ctx || (cfg->kv_mode != KATA_KV_FP16 && cfg->kv_mode != KATA_KV_INT8 && cfg->kv_mode != KATA_KV_INT8V) ||
         (cfg->quant_round != KATA_ROUND_RINT && cfg->quant_round != KATA_ROUND_HALF_AWAY) || cfg->dec_chunk < 0) return KATA_ERR_ARG;
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || cfg->device < 0 || cfg->device >= ndev) return KATA_ERR_CUDA;
@@ -81,8 +81,8 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     Ctx& c = h->c; c.cfg = *cfg; c.cfg.max_ctx = nullptr;
     DeviceGuard guard(cfg->device);
     cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, cfg->device);
-    c.elt = cfg->kv_mode == KATA_KV_INT8 ? 1 : 2;
-    c.tag = cfg->kv_mode == KATA_KV_INT8 ? "fp16+kv8" : "fp16";
+    c.elt_k = cfg->kv_mode == KATA_KV_INT8 ? 1 : 2; c.elt_v = cfg->kv_mode == KATA_KV_FP16 ? 2 : 1;
+    c.tag = cfg->kv_mode == KATA_KV_INT8 ? "fp16+kv8" : cfg->kv_mode == KATA_KV_INT8V ? "fp16+kv8v" : "fp16";   // Engine::numericsTag, src/engine.cpp:517-521
     int64_t rows = 0;
     for (int s = 0; s < cfg->n_seqs; s++) {
         if (cfg->max_ctx[s] < 1) { delete h; return KATA_ERR_ARG; }
@@ -90,29 +90,29 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     }
     c.total_rows = rows;
     c.max_items = kata::decode_max_slots(c.sm_count * 8);
-    const size_t arena = (size_t)rows * kata::kKVD * c.elt;
-    bool ok = cudaMalloc(&c.k_arena, arena) == cudaSuccess && cudaMalloc(&c.v_arena, arena) == cudaSuccess;
-    if (ok && cfg->kv_mode == KATA_KV_INT8) ok = cudaMalloc((void**)&c.ksc, (size_t)rows * 8) == cudaSuccess && cudaMalloc((void**)&c.vsc, (size_t)rows * 8) == cudaSuccess;
+    bool ok = cudaMalloc(&c.k_arena, (size_t)rows * kata::kKVD * c.elt_k) == cudaSuccess && cudaMalloc(&c.v_arena, (size_t)rows * kata::kKVD * c.elt_v) == cudaSuccess;
+    if (ok && c.k8()) ok = cudaMalloc((void**)&c.ksc, (size_t)rows * 8) == cudaSuccess;
+    if (ok && c.v8()) ok = cudaMalloc((void**)&c.vsc, (size_t)rows * 8) == cudaSuccess;
     ok = ok && cudaMalloc((void**)&c.part_o, (size_t)c.max_items * 12 * kata::kD * 4) == cudaSuccess && cudaMalloc((void**)&c.part_ml, (size_t)c.max_items * 32 * 4) == cudaSuccess &&
          cudaMalloc((void**)&c.counters, 4 * KATA_MAX_BATCH * 4) == cudaSuccess && cudaMalloc((void**)&c.d_err, 4) == cudaSuccess;
     if (ok && cfg->kv_mode == KATA_KV_FP16)
         ok = cudaMalloc((void**)&c.sc_pm, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess && cudaMalloc((void**)&c.sc_pl, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess &&
              cudaMalloc((void**)&c.sc_pacc, kata::scalar_scratch_floats_acc() * 4) == cudaSuccess;
     int64_t stage_rows = 0;
-    if (ok && cfg->kv_mode == KATA_KV_INT8) {   // staging arena of the tcgen05 prefill: one layer of every sequence, codes expanded to fp16
+    if (ok && c.v8()) {   // staging arena of the tcgen05 prefill: one layer of every sequence, the int8 planes' codes expanded to fp16
         for (int sq = 0; sq < cfg->n_seqs; sq++) { c.stage_row0.push_back(stage_rows); stage_rows += cfg->max_ctx[sq]; }
-        ok = cudaMalloc((void**)&c.k16_stage, (size_t)stage_rows * kata::kKVD * 2) == cudaSuccess && cudaMalloc((void**)&c.v16_stage, (size_t)stage_rows * kata::kKVD * 2) == cudaSuccess;
-        if (ok) { cudaMemset(c.k16_stage, 0, (size_t)stage_rows * kata::kKVD * 2); cudaMemset(c.v16_stage, 0, (size_t)stage_rows * kata::kKVD * 2); }
+        const size_t sb = (size_t)stage_rows * kata::kKVD * 2;
+        ok = cudaMalloc((void**)&c.v16_stage, sb) == cudaSuccess && cudaMemset(c.v16_stage, 0, sb) == cudaSuccess;
+        if (ok && c.k8()) ok = cudaMalloc((void**)&c.k16_stage, sb) == cudaSuccess && cudaMemset(c.k16_stage, 0, sb) == cudaSuccess;
     }
     if (!ok) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_NOMEM; }
     {   // decode: rank-4 tile views (a 128-byte column block = 64 fp16 or 128 int8 elements); tcgen05 prefill (fp16): the half tiles of a CTA pair
-        const int blocks = 256 * c.elt / 128;
-        const int tile_rows = c.elt == 1 ? 32 : 16;   // keys per decode tile
-        if (!kata::make_tile_tmap(&c.tm_k_tile, c.k_arena, c.elt, rows, tile_rows, blocks) || !kata::make_tile_tmap(&c.tm_v_tile, c.v_arena, c.elt, rows, tile_rows, blocks) ||
-            (c.elt == 2 && (!kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2))) ||
-            (c.elt == 1 && (!kata::make_tile_tmap(&c.tm_k64h_stage, c.k16_stage, 2, stage_rows, 64, 4) || !kata::make_tile_tmap(&c.tm_v128h_stage, c.v16_stage, 2, stage_rows, 128, 2)))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
+        const int tile_rows = c.k8() ? 32 : 16;   // keys per decode tile: 32 when both planes are int8
+        if (!kata::make_tile_tmap(&c.tm_k_tile, c.k_arena, c.elt_k, rows, tile_rows, 256 * c.elt_k / 128) || !kata::make_tile_tmap(&c.tm_v_tile, c.v_arena, c.elt_v, rows, tile_rows, 256 * c.elt_v / 128) ||
+            (!c.k8() && !kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4)) || (!c.v8() && !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2)) ||
+            (c.k8() && !kata::make_tile_tmap(&c.tm_k64h_stage, c.k16_stage, 2, stage_rows, 64, 4)) || (c.v8() && !kata::make_tile_tmap(&c.tm_v128h_stage, c.v16_stage, 2, stage_rows, 128, 2))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
-    if (kata::configure_decode(cfg->kv_mode == KATA_KV_INT8) != cudaSuccess || kata::configure_prefill(cfg->kv_mode == KATA_KV_INT8) != cudaSuccess) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_CUDA; }
+    if (kata::configure_decode(cfg->kv_mode) != cudaSuccess || kata::configure_prefill(cfg->kv_mode) != cudaSuccess) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_CUDA; }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);
     float invf[32]; for (int i = 0; i < 32; i++) invf[i] = powf(10000000.0f, -(float)i / 32.0f);   // shaders/attn.metal:26
     kata::set_inv_freq(invf);
@@ -133,9 +133,9 @@ int kata_attn_destroy(kata_attn_ctx* h) {
 int kata_attn_reset(kata_attn_ctx* h, void* stream) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c; DeviceGuard guard(c.cfg.device); cudaStream_t s = (cudaStream_t)stream;
-    const size_t arena = (size_t)c.total_rows * kata::kKVD * c.elt;
-    cudaError_t e = cudaMemsetAsync(c.k_arena, 0, arena, s); if (e == cudaSuccess) e = cudaMemsetAsync(c.v_arena, 0, arena, s);
-    if (e == cudaSuccess && c.ksc) { e = cudaMemsetAsync(c.ksc, 0, (size_t)c.total_rows * 8, s); if (e == cudaSuccess) e = cudaMemsetAsync(c.vsc, 0, (size_t)c.total_rows * 8, s); }
+    cudaError_t e = cudaMemsetAsync(c.k_arena, 0, (size_t)c.total_rows * kata::kKVD * c.elt_k, s); if (e == cudaSuccess) e = cudaMemsetAsync(c.v_arena, 0, (size_t)c.total_rows * kata::kKVD * c.elt_v, s);
+    if (e == cudaSuccess && c.ksc) e = cudaMemsetAsync(c.ksc, 0, (size_t)c.total_rows * 8, s);
+    if (e == cudaSuccess && c.vsc) e = cudaMemsetAsync(c.vsc, 0, (size_t)c.total_rows * 8, s);
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "reset");
 }
 
@@ -179,8 +179,8 @@ int kata_attn_prep(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* se
 int kata_attn_kv_quant(kata_attn_ctx* h, int32_t layer, int32_t seq, const void* d_ks, const void* d_vs, int32_t T, int32_t pos0, void* stream) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c;
-    if (c.cfg.kv_mode != KATA_KV_INT8) return fail(c, KATA_ERR_MODE, "kv_quant needs an int8 context (this one is %s)", c.tag.c_str());
-    if (!d_ks || !d_vs || T < 1 || T > KATA_MAX_CHUNK) return fail(c, KATA_ERR_ARG, "kv_quant of %d rows (1..%d) needs both scratch pointers", T, KATA_MAX_CHUNK);
+    if (!c.v8()) return fail(c, KATA_ERR_MODE, "kv_quant needs an int8 or int8v context (this one is %s)", c.tag.c_str());
+    if ((c.k8() && !d_ks) || !d_vs || T < 1 || T > KATA_MAX_CHUNK) return fail(c, KATA_ERR_ARG, "kv_quant of %d rows (1..%d) needs the scratch rows of every int8 plane", T, KATA_MAX_CHUNK);
     kata::Batch b; if (int rc = make_batch(c, layer, 1, &seq, &pos0, T, b)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_kv_quant(c, b.row_base[0] + pos0, (const __half*)d_ks, (const __half*)d_vs, T, (cudaStream_t)stream);
@@ -273,7 +273,7 @@ int kata_attn_set_position_offset(kata_attn_ctx* h, int32_t seq, int32_t first_p
     return KATA_OK;
 }
 
-int32_t kata_attn_kv_planes(const kata_attn_ctx* h) { return h ? (h->c.cfg.kv_mode == KATA_KV_INT8 ? 4 : 2) : 0; }
+int32_t kata_attn_kv_planes(const kata_attn_ctx* h) { return h ? 2 + (h->c.k8() ? 1 : 0) + (h->c.v8() ? 1 : 0) : 0; }   // Engine::kvPlanes, src/engine.h:74
 size_t kata_attn_kv_plane_row_bytes(const kata_attn_ctx* h, int32_t plane) {
     if (!h) return 0;
     PlaneRef r; return plane_ref(const_cast<Ctx&>(h->c), plane, r) ? r.row_bytes : 0;

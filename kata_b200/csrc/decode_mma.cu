@@ -1,12 +1,12 @@
 // Split-KV decode / T<=2 speculative-verify attention over the fp16 or int8 KV cache, with the merge of the splits and
 // the sigmoid output gate fused into the same kernel.
-// Replaces k_dec_q_pack + k_attn_dec_split[_q8] + k_attn_dec_combine of the reference (shaders/flash.metal:77-152,
-// host side Engine::dDecAttn, src/engine.cpp:119-127). Same math and rounding points: fp16 query prescaled by 1/16,
+// Replaces k_dec_q_pack + k_attn_dec_split[_q8 | _k16v8] + k_attn_dec_combine of the reference (shaders/flash.metal:77-152,
+// 252-306; host side Engine::dDecAttn, src/engine.cpp:119-127). Same math and rounding points: fp16 query prescaled by 1/16,
 // rows of the 16-row block = 6 heads of one KV head x T tokens (row = t*6 + j), fp32 scores, P rounded to fp16 before
-// P.V (after the V scale in int8 mode), l summed from the unrounded p, masked rows/keys at -inf, merge weights exp(m-M).
+// P.V (after the V scale where the values are int8), l summed from the unrounded p, masked rows/keys at -inf, merge weights exp(m-M).
 //
 // Design (HBM-bound: 1 KiB of K+V per key and KV head at fp16, read exactly once):
-//  - The work is the list of tiles (16 keys at fp16, 32 at int8: 16 KiB of K+V) of every (sequence, KV head) segment. It is cut into
+//  - The work is the list of tiles (16 keys at fp16, 32 at int8: 16 KiB of K+V; 16 keys = 12 KiB with fp16 keys and int8 values) of every (sequence, KV head) segment. It is cut into
 //    one contiguous, equal-sized range per CTA (one CTA per SM), so ragged batches balance to within one tile and each key is read once.
 //  - Inside a CTA the tiles of the range go round-robin to 4 rings. A ring is a 3-stage shared-memory ring with three warps on one
 //    scheduler: a score warp (S = Q K^T, online softmax, P) and two value warps (O += P V on one half of the head dims each) that overlap
@@ -43,13 +43,15 @@ constexpr int kPairBytes = 2 * PSlot<2>::kBytes;    // 2688 (sized for the 32-ke
 constexpr int kOffStages = kOffPair + kRings * kPairBytes;   // the stage area itself starts at the next 1024-byte boundary of the shared window (found at run time)
 constexpr int kMergeStride = 264;                   // floats per row of the cross-ring merge buffer
 
-template <bool I8> struct Geo {
-    static constexpr int kRowBytes = TileGeo<I8>::kRowBytes;
-    static constexpr int kBoxes = kRowBytes / 128;               // 128-byte column boxes per K or V tile
-    static constexpr int kNK = I8 ? 2 : 1, kTile = 16 * kNK;      // keys per tile: 16 (fp16) or 32 (int8), 16 KiB of K+V either way
-    static constexpr int kTileBytes = kTile * kRowBytes;          // column blocks of [kTile rows][128 bytes], 128-byte swizzle, no padding
-    static constexpr int kStageBytes = 2 * kTileBytes;
-    static constexpr int kStages = 3;                             // tiles in flight per ring: 48 KB
+// MODE = the context's cache mode: 0 fp16, 1 int8 (K and V), 2 int8v (K fp16, V int8: k_attn_dec_split_k16v8, shaders/flash.metal:252-306)
+template <int MODE> struct Geo {
+    static constexpr bool K8 = MODE == KATA_KV_INT8, V8 = MODE != KATA_KV_FP16;
+    static constexpr int kKRowBytes = TileGeo<K8>::kRowBytes, kVRowBytes = TileGeo<V8>::kRowBytes;
+    static constexpr int kVBoxes = kVRowBytes / 128;              // 128-byte column boxes per V tile
+    static constexpr int kNK = K8 ? 2 : 1, kTile = 16 * kNK;      // keys per tile: 16 (fp16 keys) or 32 (int8 keys): 16 KiB of K+V (12 KiB in int8v mode)
+    static constexpr int kKTileBytes = kTile * kKRowBytes, kVTileBytes = kTile * kVRowBytes;   // column blocks of [kTile rows][128 bytes], 128-byte swizzle, no padding
+    static constexpr int kStageBytes = kKTileBytes + kVTileBytes;
+    static constexpr int kStages = MODE == KATA_KV_INT8V ? 4 : 3;   // tiles in flight per ring: 48 KB
     static constexpr int kRingBytes = (kStages * kStageBytes > 16 * kMergeStride * 4) ? kStages * kStageBytes : 16 * kMergeStride * 4;
     static constexpr int kSmem = kOffStages + 1024 + kRings * kRingBytes;   // 1024 bytes of slack for the run-time alignment
 };
@@ -72,12 +74,12 @@ __device__ __forceinline__ int cta_of_tile(const DecPlan& p, int tile) {
     return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles;
 }
 
-template <bool I8>
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                                                                  const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
-    using G = Geo<I8>; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
+    using G = Geo<MODE>; constexpr bool K8 = G::K8, V8 = G::V8; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
     if (threadIdx.x == 0) { prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); }
     if (!p.merge_in_kernel) pdl_launch_dependents();   // the next kernel is the combine grid, which starts no loads of its own before it has waited for this one: it may be set up at once
     extern __shared__ __align__(128) uint8_t smem[];
@@ -126,7 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 if (i >= kStages && !dead && !mbar_wait_bounded(ebar, ((cur / kStages) - 1u) & 1u, err)) { dead = true; atomicExch(err, 3); }
                 const int key0 = p.first_row + (lt0 + r + i * kRings) * kTile;
                 mbar_arrive_expect_tx(bar, (uint32_t)G::kStageBytes);   // TMA counts whole boxes, out-of-range rows included
-                tma_load_4d(dst, &tm_k, 0, row0 + key0, 0, kvh, bar); tma_load_4d(dst + G::kTileBytes, &tm_v, 0, row0 + key0, 0, kvh, bar);
+                tma_load_4d(dst, &tm_k, 0, row0 + key0, 0, kvh, bar); tma_load_4d(dst + G::kKTileBytes, &tm_v, 0, row0 + key0, 0, kvh, bar);
             }
             return nm;
         };
@@ -144,19 +146,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             return __ldg(reinterpret_cast<const unsigned short*>(plane) + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 4 + kvh);
         };
         uint32_t kA = 0, kB = 0, kC = 0, vA = 0, vB = 0, vC = 0;
-        if (I8 && h == 0) {   // score warp: the loads fly while the Q block is staged
-            if (n_mine > 0) { kA = load_scale(0, ksc); vA = load_scale(0, vsc); }
-            if (n_mine > 1) { kB = load_scale(1, ksc); vB = load_scale(1, vsc); }
-            if (n_mine > 2) { kC = load_scale(2, ksc); vC = load_scale(2, vsc); }
+        if (V8 && h == 0) {   // score warp: the loads fly while the Q block is staged
+            if (n_mine > 0) { if (K8) kA = load_scale(0, ksc); vA = load_scale(0, vsc); }
+            if (n_mine > 1) { if (K8) kB = load_scale(1, ksc); vB = load_scale(1, vsc); }
+            if (n_mine > 2) { if (K8) kC = load_scale(2, ksc); vC = load_scale(2, vsc); }
         }
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
             const int r = ch >> 5, c16 = ch & 31; uint4 v = make_uint4(0, 0, 0, 0);
             if (r < 6 * T) { const int t = r / 6, j = r - 6 * t; v = *reinterpret_cast<const uint4*>(q16 + ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + (kvh * 6 + j) * kD + c16 * 8); }
-            stage_q_chunk<I8>(smem + r * kQStride, c16, v);
+            stage_q_chunk<K8>(smem + r * kQStride, c16, v);
         }
         __syncthreads();
-        if (I8) {   // row sums of the staged Q block (any column order): warp w sums rows 2w and 2w+1
+        if (K8) {   // row sums of the staged Q block (any column order): warp w sums rows 2w and 2w+1
 #pragma unroll
             for (int rr = 0; rr < 2; rr++) {
                 const int r = 2 * (w & 7) + rr; const uint4 v = *reinterpret_cast<const uint4*>(smem + r * kQStride + lane * 16); const __half2* hp = reinterpret_cast<const __half2*>(&v);
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             }
             __syncthreads();
         }
-        const float qs_[2] = {I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g] : 0.0f, I8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g + 8] : 0.0f};
+        const float qs_[2] = {K8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g] : 0.0f, K8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g + 8] : 0.0f};
 
         if (h == 3) {
             if (lane < kRings) it += (uint32_t)produce(kStages, 1 << 30);   // 'it' of producer lane r counts ring r's tiles
@@ -184,18 +186,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 const uint32_t kt = ring_stage0 + stg * G::kStageBytes;
                 const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
                 const uint32_t k_cur = kA, v_cur = vA; kA = kB; kB = kC; vA = vB; vB = vC;
-                if (I8 && i + 3 < n_mine) { kC = load_scale(i + 3, ksc); vC = load_scale(i + 3, vsc); }
+                if (V8 && i + 3 < n_mine) { if (K8) kC = load_scale(i + 3, ksc); vC = load_scale(i + 3, vsc); }
                 // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and every arrival) stays intact.
                 if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
                 float ks_[2 * NK][2], vs_[2 * NK][2];
 #pragma unroll
                 for (int q = 0; q < 4 * NK; q++) {
                     const int src = 8 * (q >> 1) + 2 * t4 + (q & 1);
-                    ks_[q >> 1][q & 1] = I8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, k_cur, src))) : 1.0f;
-                    vs_[q >> 1][q & 1] = I8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, v_cur, src))) : 1.0f;
+                    ks_[q >> 1][q & 1] = K8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, k_cur, src))) : 1.0f;
+                    vs_[q >> 1][q & 1] = V8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, v_cur, src))) : 1.0f;
                 }
                 float pr[2 * NK][4], al0, al1;
-                score_tile<I8, NK>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
+                score_tile<K8, V8, NK>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(ebars + stg * 8);   // K of this stage is no longer needed
                 if (cur >= 2 && !dead && !mbar_wait_bounded(pempty + slot * 8, ((cur >> 1) - 1u) & 1u, err)) { dead = true; atomicExch(err, 4); }
@@ -211,12 +213,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             const int vh = h - 1;
             for (int i = 0; i < n_mine; i++) {
                 const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
-                const uint32_t vt = ring_stage0 + stg * G::kStageBytes + G::kTileBytes;
+                const uint32_t vt = ring_stage0 + stg * G::kStageBytes + G::kKTileBytes;
                 const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
                 if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
                 if (key0 + kTile > kend) {   // tail tile: rows past the range were loaded as they lie in memory; zero those V rows (0 x garbage must stay 0)
                     const int nk = max(0, kend - key0);
-                    constexpr int kHB = G::kBoxes / 2;   // boxes of this warp's half
+                    constexpr int kHB = G::kVBoxes / 2;   // boxes of this warp's half
                     for (int idx = lane; idx < (kTile - nk) * kHB * 8; idx += 32) {
                         const int r = nk + idx / (kHB * 8), rem = idx % (kHB * 8);
                         *reinterpret_cast<uint4*>(smem + (vt - sm_base) + (vh * kHB + (rem >> 3)) * (kTile * 128) + r * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
@@ -225,11 +227,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                     __syncwarp();
                 }
                 if (!dead && !mbar_wait_bounded(pfull + slot * 8, (cur >> 1) & 1u, err)) { dead = true; atomicExch(err, 5); }
-                value_tile<I8, 16, NK>(vt, p_sm + slot * PS::kBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * PS::kBytes + 16 * PS::kStride), vst, lane, vh);
+                value_tile<V8, 16, NK>(vt, p_sm + slot * PS::kBytes, reinterpret_cast<const float*>(smem + kOffPair + ring * kPairBytes + slot * PS::kBytes + 16 * PS::kStride), vst, lane, vh);
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(pempty + slot * 8); mbar_arrive(ebars + stg * 8); }
             }
-            if (I8) vst.finish_bias(kI8Bias);
+            if (V8) vst.finish_bias(kI8Bias);
         }
         if (h != 3) it = it_seg + (uint32_t)n_mine;
 
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 #pragma unroll
             for (int j = 0; j < 16; j++)
 #pragma unroll
-                for (int c = 0; c < 2; c++) { const int d = pair_dim_of<I8>(h - 1, j, c, t4); mo[g * kMergeStride + d] = vst.o[j][c]; mo[(g + 8) * kMergeStride + d] = vst.o[j][2 + c]; }
+                for (int c = 0; c < 2; c++) { const int d = pair_dim_of<V8>(h - 1, j, c, t4); mo[g * kMergeStride + d] = vst.o[j][c]; mo[(g + 8) * kMergeStride + d] = vst.o[j][2 + c]; }
         }
         __syncthreads();
 
@@ -361,9 +363,10 @@ __global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restric
 int decode_max_slots(int sm_count) { return sm_count + 4 * KATA_MAX_BATCH; }
 
 // Shared-memory opt-in of the decode kernel on the current device (function attributes are per device: done once per context).
-cudaError_t configure_decode(bool int8) {
-    return int8 ? cudaFuncSetAttribute(decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<true>::kSmem)
-                : cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem);
+cudaError_t configure_decode(int kv_mode) {
+    return kv_mode == KATA_KV_INT8  ? cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_INT8>::kSmem)
+         : kv_mode == KATA_KV_INT8V ? cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_INT8V>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_INT8V>::kSmem)
+                                    : cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_FP16>::kSmem);
 }
 
 static int max_contributors(const DecPlan& p) {
@@ -376,7 +379,7 @@ static int max_contributors(const DecPlan& p) {
 // key_off / kend_override serve the split-KV-across-GPUs call: local row = absolute key - key_off, rows [first_row, kend).
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s, int tok_stride, int tok0) {
-    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8; const int kTile = i8 ? Geo<true>::kTile : Geo<false>::kTile;
+    const int mode = c.cfg.kv_mode, kTile = c.k8() ? 32 : 16;
     DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off; p.tok_stride = tok_stride > 0 ? tok_stride : T; p.tok0 = tok0;
     int total = 0;
     for (int i = 0; i < b.n; i++) {
@@ -396,8 +399,10 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (p.q_tiles < 128) for (int i = 0; i < b.n; i++) p.safe_row[i] = 0;
     p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
-    const cudaError_t le = i8 ? launch_pdl(decode_mma_kernel<true>, dim3(n_ctas), dim3(kThreads), Geo<true>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
-                              : launch_pdl(decode_mma_kernel<false>, dim3(n_ctas), dim3(kThreads), Geo<false>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err);
+#define KATA_DEC(M) launch_pdl(decode_mma_kernel<M>, dim3(n_ctas), dim3(kThreads), Geo<M>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
+    static_assert(Geo<KATA_KV_INT8>::kTile == 32 && Geo<KATA_KV_INT8V>::kTile == 16 && Geo<KATA_KV_FP16>::kTile == 16, "the tile views of the context are built for these tile heights");
+    const cudaError_t le = mode == KATA_KV_INT8 ? KATA_DEC(KATA_KV_INT8) : mode == KATA_KV_INT8V ? KATA_DEC(KATA_KV_INT8V) : KATA_DEC(KATA_KV_FP16);
+#undef KATA_DEC
     c.prev_append = false;   // this kernel writes no cache rows
     if (le != cudaSuccess) return le;
     c.launches++;
@@ -469,7 +474,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     if (!sd.ready) {   // once per device, with that device current: the array's name is only a host-side handle, the kernel needs its device address
         void* ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return KATA_ERR_CUDA;
-        if (cudaFuncSetAttribute(decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<false>::kSmem) != cudaSuccess) return KATA_ERR_CUDA;
+        if (cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_FP16>::kSmem) != cudaSuccess) return KATA_ERR_CUDA;
         if (cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return KATA_ERR_CUDA;
         sd.scratch = static_cast<StaticScratch*>(ptr); sd.ready = true;
     }
@@ -478,7 +483,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     for (int i = 0; i < n; i++) {
         if (pos_base[i] < 0 || first_pos < 0 || first_pos > pos_base[i] || seq_row0[i] < 0 || seq_row0[i] + pos_base[i] + T > total_rows) return KATA_ERR_RANGE;
         p.pos[i] = pos_base[i]; p.row_base[i] = seq_row0[i]; p.kend[i] = pos_base[i] + T;
-        p.ntiles[i] = std::max(1, (p.kend[i] - first_pos + Geo<false>::kTile - 1) / Geo<false>::kTile);
+        p.ntiles[i] = std::max(1, (p.kend[i] - first_pos + Geo<KATA_KV_FP16>::kTile - 1) / Geo<KATA_KV_FP16>::kTile);
         p.tile_start[i] = total; total += 4 * p.ntiles[i];
     }
     for (int i = n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
@@ -488,7 +493,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     if (!make_tile_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 16, 4) || !make_tile_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 16, 4)) return KATA_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
     if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
-    decode_mma_kernel<false><<<n_ctas, kThreads, Geo<false>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,
+    decode_mma_kernel<KATA_KV_FP16><<<n_ctas, kThreads, Geo<KATA_KV_FP16>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,
                                                                          sd.scratch->part_o, sd.scratch->part_ml, sd.scratch->counters, &sd.scratch->err);
     if (!p.merge_in_kernel) decode_combine_kernel<<<dim3(6 * T, 4 * n), kCombineThreads, 0, s>>>(p, d_gate, d_out, (int)(out_dtype == KATA_ACT_BF16), nullptr, sd.scratch->part_o, sd.scratch->part_ml);
     return cudaGetLastError() == cudaSuccess ? KATA_OK : KATA_ERR_CUDA;

@@ -37,9 +37,10 @@ struct Ctx {
     std::vector<int32_t> pos_off;      // absolute position held by row 0 of each sequence (0 unless the sequence is a key slice)
     std::vector<int64_t> seq_row0;     // arena row of (sequence, layer 0, position 0)
     int64_t total_rows = 0;
-    int elt = 2;                        // bytes per cached K/V element
+    int elt_k = 2, elt_v = 2;           // bytes per cached K / V element (int8: 1, 1; int8v: 2, 1)
+    bool k8() const { return elt_k == 1; } bool v8() const { return elt_v == 1; }
     void* k_arena = nullptr; void* v_arena = nullptr;      // [total_rows][1024] fp16 or int8
-    __half* ksc = nullptr; __half* vsc = nullptr;          // [total_rows][4] fp16 (int8 mode)
+    __half* ksc = nullptr; __half* vsc = nullptr;          // [total_rows][4] fp16 scales of the int8 planes
     // decode scratch: per work item (sequence, kv head, split) the unnormalised partial rows and their (m, l)
     float* part_o = nullptr; float* part_ml = nullptr; int32_t* counters = nullptr; int32_t max_items = 0;
     // What the kernel launched last through this context wrote into the cache: nothing (prev_append false), or rows from position append_lo[s]

@@ -1,5 +1,5 @@
-// Causal flash prefill on the 5th-generation tensor cores (tcgen05) for the fp16 KV cache.
-// Replaces k_cvt_q_half + k_flash_prefill of the reference (shaders/flash.metal:10-71; encoded at src/engine.cpp:279,
+// Causal flash prefill on the 5th-generation tensor cores (tcgen05) for the fp16 KV cache (int8 planes go through an fp16 staging arena).
+// Replaces k_cvt_q_half + k_flash_prefill[_q8 | _k16v8] of the reference (shaders/flash.metal:10-71, 198-250; encoded at src/engine.cpp:279,
 // 614) with the same math: fp16 Q (prescaled by 1/16) x fp16 K -> fp32 scores, causal mask key > position -> -inf,
 // online softmax, P rounded to fp16 before P.V, l summed from the unrounded p, output O / l * sigmoid(gate).
 //
@@ -55,14 +55,16 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const i
 
 // One work item = (query tile, head pair, sequence); items are ordered longest first and dealt round-robin to the CTA pairs.
 struct PfStage { int64_t kv_row0[KATA_MAX_BATCH]; };   // SCALED: first row of sequence b in the fp16 staging arena (position 0)
-struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, h, kvh, bi; int64_t sc_row0; };
+struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh, bi; int64_t sc_row0; };   // row0 / row0v: row of position 0 in the arena the K / V tiles come from
 
-// SCALED: the K/V tiles are int8 codes expanded to fp16 (exact integers) in a staging arena whose rows are kv_row0[b] + position; the per-key
-// scales are applied as k_flash_prefill_q8 does (shaders/flash.metal:10-68 with Q8): S = (Q.Kq) * ksc[key], P~ = half(p * vsc[key]), l from p.
-template <bool SCALED>
+// MODE = the context's cache mode. An int8 plane's tiles are its codes expanded to fp16 (exact integers) in a staging arena whose rows are
+// kv_row0[b] + position; the per-key scales are applied as k_flash_prefill_q8 does (shaders/flash.metal:10-68 with Q8): S = (Q.Kq) * ksc[key],
+// P~ = half(p * vsc[key]), l from p. int8v (k_flash_prefill_k16v8, shaders/flash.metal:198-250): K tiles straight from the fp16 plane, V staged and scaled.
+template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                                                                    const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err,
                                                                    const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc) {
+    constexpr bool KS = MODE == KATA_KV_INT8, SCALED = MODE != KATA_KV_FP16;   // KS: scores take the key scale; SCALED: P takes the value scale
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t rank = tc5::cluster_rank();
@@ -70,7 +72,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     auto item_of = [&](int it) {   // it-th item of this CTA pair
         const int idx = pair + it * n_pairs, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
         PfItem t; t.bi = rem / (kH / 2); t.h = 2 * (rem % (kH / 2)) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
-        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
+        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = KS ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.row0v = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
         return t;
     };
     const int my_items = pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                     const uint32_t st = gt & 1u;
                     if (gt >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 12); ok = false; break; }
                     if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
-                    tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, t.row0 + j * kBNk, 2 * (int)rank, t.kvh, bar(B_VFULL0 + st));
+                    tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, t.row0v + j * kBNk, 2 * (int)rank, t.kvh, bar(B_VFULL0 + st));
                 }
             }
         }
@@ -184,14 +186,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::fence_after_sync();
             if (SCALED) {   // the tile's 128 K scales and 128 V scales: one value per softmax thread into shared memory, then everybody reads its 64 + 64
                 const int key = min(j * kBNk + (tid & 127), max(kend - 1, 0));
-                s_sc[gt & 1u][tid >> 7][tid & 127] = (tid < 128 ? ksc : vsc)[(t.sc_row0 + key) * 4 + t.kvh];
+                if (KS || tid >= 128) s_sc[gt & 1u][tid >> 7][tid & 127] = (tid < 128 ? ksc : vsc)[(t.sc_row0 + key) * 4 + t.kvh];
                 asm volatile("bar.sync 9, 256;" ::: "memory");   // all eight softmax warps, every tile, whatever happened before
             }
             uint32_t v[2][32];
 #pragma unroll
             for (int c = 0; c < 2; c++) tc5::ld32(t_s + g * 64 + c * 32, v[c]);
             tc5::wait_ld();
-            if (SCALED) {
+            if (KS) {
                 const uint4* kq = reinterpret_cast<const uint4*>(&s_sc[gt & 1u][0][g * 64]);
 #pragma unroll
                 for (int q8 = 0; q8 < 8; q8++) {
@@ -324,11 +326,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     if (w == 0) tc5::tmem_dealloc2(tmem, 512);
 }
 
-// int8 cache: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
+// int8 planes: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
 // the integers themselves (exact in fp16); the scales stay with the softmax. 64 threads per 1024-code row, 16 codes per thread.
-__global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const int M, const PfStage stg, const uint8_t* __restrict__ kq, const uint8_t* __restrict__ vq, __half* __restrict__ k16, __half* __restrict__ v16) {
-    const int bi = blockIdx.y, rows = b.pos[bi] + M;
-    const uint8_t* src = blockIdx.z ? vq : kq; __half* dst = blockIdx.z ? v16 : k16;
+// grid.z = planes to expand: 2 (K then V), or 1 with first_plane = 1 (V only: the keys are fp16 already).
+__global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const int M, const PfStage stg, const uint8_t* __restrict__ kq, const uint8_t* __restrict__ vq, __half* __restrict__ k16, __half* __restrict__ v16, const int first_plane) {
+    const int bi = blockIdx.y, rows = b.pos[bi] + M; const bool isV = (blockIdx.z + first_plane) != 0;
+    const uint8_t* src = isV ? vq : kq; __half* dst = isV ? v16 : k16;
     for (int r = blockIdx.x * 4 + (threadIdx.x >> 6); r < rows; r += gridDim.x * 4) {
         const int c16 = threadIdx.x & 63;
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(src + (b.row_base[bi] + r) * kKVD) + c16);
@@ -349,13 +352,14 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const 
 }  // namespace
 
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
-cudaError_t configure_prefill_mma(bool int8);
+cudaError_t configure_prefill_mma(int kv_mode);
 
 // Shared-memory opt-in of the prefill kernels on the current device (function attributes are per device: done once per context).
-cudaError_t configure_prefill(bool int8) {
-    cudaError_t e = configure_prefill_mma(int8);
-    if (e == cudaSuccess) e = int8 ? cudaFuncSetAttribute(prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
-                                   : cudaFuncSetAttribute(prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+cudaError_t configure_prefill(int kv_mode) {
+    cudaError_t e = configure_prefill_mma(kv_mode);
+    if (e == cudaSuccess) e = kv_mode == KATA_KV_INT8  ? cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
+                            : kv_mode == KATA_KV_INT8V ? cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_INT8V>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
+                                                       : cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
     return e;
 }
 
@@ -363,15 +367,15 @@ cudaError_t configure_prefill(bool int8) {
 // expanded to fp16 in the context's staging arena (one pass over the prefix, a few per cent of the attention time), the scales are applied in
 // the softmax. The mma.sync kernel remains the cross-check and serves windowed caches (a position offset), which the staging arena does not cover.
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
-    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
+    const int mode = c.cfg.kv_mode; const bool i8 = c.v8();
     bool windowed = false; for (int i = 0; i < b.n; i++) windowed |= c.pos_off[b.seq[i]] != 0;
-    if ((c.cfg.flags & 1) || (i8 && (!c.k16_stage || windowed))) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
+    if ((c.cfg.flags & 1) || (i8 && (!c.v16_stage || windowed))) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
     CUtensorMap tm_q;
     if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
     PfStage stg{};
     if (i8) {
         int max_rows = 0; for (int i = 0; i < b.n; i++) { stg.kv_row0[i] = c.stage_row0[b.seq[i]]; max_rows = std::max(max_rows, b.pos[i] + M); }
-        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, 2), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage);
+        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1);
         c.launches++;
     }
     // persistent CTA pairs: at most one pair per two SMs, items dealt round-robin (longest first)
@@ -380,8 +384,9 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     cudaLaunchAttribute at[2]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
-    const cudaError_t le = i8 ? cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<true>, tm_q, c.tm_k64h_stage, c.tm_v128h_stage, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc)
-                              : cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<false>, tm_q, c.tm_k64h, c.tm_v128h, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err, stg, (const __half*)nullptr, (const __half*)nullptr);
+#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc)
+    const cudaError_t le = mode == KATA_KV_INT8 ? KATA_PF(KATA_KV_INT8, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8V ? KATA_PF(KATA_KV_INT8V, c.tm_k64h, c.tm_v128h_stage) : KATA_PF(KATA_KV_FP16, c.tm_k64h, c.tm_v128h);
+#undef KATA_PF
     if (le != cudaSuccess) return le;
     c.prev_append = false;
     c.launches++;

@@ -1,5 +1,5 @@
 // Attention prep for the gated-GQA layers: per-head Q/K RMSNorm, partial RoPE on dims 0..63, gate split, append of the
-// K and V rows to the cache, with the fp16 prescaled query and (int8 mode) quantise-on-append fused in.
+// K and V rows to the cache, with the fp16 prescaled query and quantise-on-append (int8 planes: both in int8 mode, V only in int8v mode) fused in.
 // Follows k_attn_prep / k_attn_prep_b (shaders/attn.metal:5-37, shaders/prefill.metal:179-206), k_cvt_q_half
 // (shaders/flash.metal:71) and k_kv_quant_sym (shaders/flash.metal:157-178) of the reference.
 //
@@ -64,7 +64,7 @@ __device__ __forceinline__ void quant_store_row(const __half (&hv)[8], int8_t* d
 }
 
 // grid (ceil(nh / 8), T, n) x 256 threads: warp w of a CTA handles head slot h0 + 8*blockIdx.x + w of one token
-template <typename TIn, bool INT8>
+template <typename TIn, bool K8, bool V8>
 __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, const TIn* __restrict__ qfull, const TIn* __restrict__ kproj, const TIn* __restrict__ vproj,
                                                    const float* __restrict__ qnorm, const float* __restrict__ knorm, __half* __restrict__ q16, float* __restrict__ q32, float* __restrict__ gate,
                                                    void* k_arena, void* v_arena, __half* ksc, __half* vsc, const int h0, const int nh, const int round_mode) {
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, c
         const int vh = h - 28; __half hv[8];
 #pragma unroll
         for (int s = 0; s < 8; s++) hv[s] = __float2half_rn(ldf(vproj + tok * kKVD + vh * kD + 32 * s + lane));
-        if (!INT8) {
+        if (!V8) {
 #pragma unroll
             for (int s = 0; s < 8; s++) reinterpret_cast<__half*>(v_arena)[row * kKVD + vh * kD + 32 * s + lane] = hv[s];
         } else quant_store_row(hv, reinterpret_cast<int8_t*>(v_arena) + row * kKVD + vh * kD, vsc + row * 4 + vh, lane, round_mode);
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, c
         const int kh = h - 24; __half hv[8];
 #pragma unroll
         for (int s = 0; s < 8; s++) hv[s] = __float2half_rn(x[s]);
-        if (!INT8) {
+        if (!K8) {
 #pragma unroll
             for (int s = 0; s < 8; s++) reinterpret_cast<__half*>(k_arena)[row * kKVD + kh * kD + 32 * s + lane] = hv[s];
         } else quant_store_row(hv, reinterpret_cast<int8_t*>(k_arena) + row * kKVD + kh * kD, ksc + row * 4 + kh, lane, round_mode);
@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, c
 // grid (T) x 256 threads: warp w < 4 key head w, else value head w-4 (the reference's k_kv_quant_sym covers the same 8 rows per token)
 __global__ void __launch_bounds__(256) kv_quant_kernel(const __half* __restrict__ ks, const __half* __restrict__ vs, int8_t* kq, int8_t* vq, __half* ksc, __half* vsc, const int64_t row0, const int round_mode) {
     const int lane = threadIdx.x & 31, wq = threadIdx.x >> 5, t = blockIdx.x; const bool isV = wq >= 4; const int head = wq & 3; const int64_t row = row0 + t;
+    if (!isV && !kq) return;   // int8v: the key plane holds fp16 rows
     __half hv[8];
 #pragma unroll
     for (int s = 0; s < 8; s++) hv[s] = (isV ? vs : ks)[(int64_t)t * kKVD + head * kD + 32 * s + lane];
@@ -194,11 +195,11 @@ cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64
 cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const void* kproj, const void* vproj, int act_dtype,
                         const float* qnorm, const float* knorm, __half* q16, float* q32, float* gate, int h0, int nh, cudaStream_t s) {
     const dim3 grid((nh + 7) / 8, T, b.n), block(256);
-    const bool i8 = c.cfg.kv_mode == KATA_KV_INT8;
+    const int mode = c.cfg.kv_mode;
     cudaError_t le = cudaSuccess;
-#define KATA_PREP(TIN, I8) le = launch_pdl(prep_kernel<TIN, I8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round)
-    if (act_dtype == KATA_ACT_F32) { if (i8) KATA_PREP(float, true); else KATA_PREP(float, false); }
-    else { if (i8) KATA_PREP(__nv_bfloat16, true); else KATA_PREP(__nv_bfloat16, false); }
+#define KATA_PREP(TIN, K8, V8) le = launch_pdl(prep_kernel<TIN, K8, V8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round)
+    if (act_dtype == KATA_ACT_F32) { if (mode == KATA_KV_INT8) KATA_PREP(float, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(float, false, true); else KATA_PREP(float, false, false); }
+    else { if (mode == KATA_KV_INT8) KATA_PREP(__nv_bfloat16, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__nv_bfloat16, false, true); else KATA_PREP(__nv_bfloat16, false, false); }
 #undef KATA_PREP
     if (le != cudaSuccess) return le;
     c.launches++;
@@ -206,7 +207,7 @@ cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const 
 }
 
 cudaError_t launch_kv_quant(Ctx& c, int64_t row0, const __half* ks, const __half* vs, int T, cudaStream_t s) {
-    kv_quant_kernel<<<dim3(T), 256, 0, s>>>(ks, vs, (int8_t*)c.k_arena, (int8_t*)c.v_arena, c.ksc, c.vsc, row0, c.cfg.quant_round);
+    kv_quant_kernel<<<dim3(T), 256, 0, s>>>(ks, vs, c.k8() ? (int8_t*)c.k_arena : nullptr, (int8_t*)c.v_arena, c.ksc, c.vsc, row0, c.cfg.quant_round);
     c.launches++;
     return cudaGetLastError();
 }

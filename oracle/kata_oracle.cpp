@@ -67,12 +67,16 @@ inline float simd_sum32(const float* v) {
 // (shaders/attn.metal:18-21, :50-54).
 inline float tg_sum256(const float* v) { float tot = 0.0f; for (int s = 0; s < 8; s++) tot += simd_sum32(v + 32 * s); return tot; }
 
-struct KvView {   // one layer's cache planes, fp16 or int8 + per-(position, head) fp16 scales
-    const void* k; const void* v; const uint16_t* ksc; const uint16_t* vsc; const uint16_t* kmn; bool q8;
+// One layer's cache planes. mode 0: K and V fp16; mode 1: both int8 with per-(position, head) fp16 scales (k_flash_prefill_q8 /
+// k_attn_dec_split_q8); mode 2: K fp16, V int8 with its scales (k_flash_prefill_k16v8 / k_attn_dec_split_k16v8, shaders/flash.metal:194-306:
+// the same tile body with the key scale and mean stripped out).
+struct KvView {
+    const void* k; const void* v; const uint16_t* ksc; const uint16_t* vsc; const uint16_t* kmn; bool q8, v8;
+    KvView(const void* k_, const void* v_, const uint16_t* ksc_, const uint16_t* vsc_, const uint16_t* kmn_, int mode) : k(k_), v(v_), ksc(ksc_), vsc(vsc_), kmn(kmn_), q8(mode == 1), v8(mode == 1 || mode == 2) {}
     float kraw(uint64_t pos, uint32_t kvh, uint32_t d) const { const uint64_t i = pos * kKVD + kvh * kD + d; return q8 ? (float)((const int8_t*)k)[i] : h2f(((const uint16_t*)k)[i]); }
-    float vraw(uint64_t pos, uint32_t kvh, uint32_t d) const { const uint64_t i = pos * kKVD + kvh * kD + d; return q8 ? (float)((const int8_t*)v)[i] : h2f(((const uint16_t*)v)[i]); }
+    float vraw(uint64_t pos, uint32_t kvh, uint32_t d) const { const uint64_t i = pos * kKVD + kvh * kD + d; return v8 ? (float)((const int8_t*)v)[i] : h2f(((const uint16_t*)v)[i]); }
     float kS(uint64_t pos, uint32_t kvh) const { return q8 ? h2f(ksc[pos * 4 + kvh]) : 1.0f; }
-    float vS(uint64_t pos, uint32_t kvh) const { return q8 ? h2f(vsc[pos * 4 + kvh]) : 1.0f; }
+    float vS(uint64_t pos, uint32_t kvh) const { return v8 ? h2f(vsc[pos * 4 + kvh]) : 1.0f; }
     float kM(uint64_t pos, uint32_t kvh) const { return (q8 && kmn) ? h2f(kmn[pos * 4 + kvh]) : 0.0f; }
 };
 
@@ -104,7 +108,7 @@ void tile_step(const uint16_t* q16 /*[16][stride]*/, size_t qStride, const float
         const float alpha = (mn == kNegInf) ? 1.0f : std::exp(mo - mn); st.m[r] = mn;
         const float sub = (mn == kNegInf) ? 0.0f : mn;
         float sum = 0.0f;
-        for (int c = 0; c < 64; c++) { const float p = std::exp(S[r][c] - sub); sum += p; const float pv = (kv.q8 && c < nk) ? p * kv.vS(k0 + c, kvh) : p; P[r][c] = h2f(f2h(pv)); }
+        for (int c = 0; c < 64; c++) { const float p = std::exp(S[r][c] - sub); sum += p; const float pv = (kv.v8 && c < nk) ? p * kv.vS(k0 + c, kvh) : p; P[r][c] = h2f(f2h(pv)); }
         st.l[r] = st.l[r] * alpha + sum;
         for (uint32_t d = 0; d < kD; d++) st.o[r][d] *= alpha;
         for (int c = 0; c < nk; c++) { const float p = P[r][c]; if (p == 0.0f) continue; for (uint32_t d = 0; d < kD; d++) st.o[r][d] += p * kv.vraw(k0 + c, kvh, d); }
@@ -156,7 +160,7 @@ void kor_prep(const float* qfull, const float* kproj, const float* vproj, const 
 // names it); mode 2: the reference's asymmetric-K variant (values stay symmetric), rint.
 void kor_kv_quant(const uint16_t* ks, const uint16_t* vs, int8_t* kq, int8_t* vq, uint16_t* ksc, uint16_t* vsc, uint16_t* kmn, uint32_t pos0, uint32_t T, int mode) {
     auto rnd = [&](float x) { return mode == 1 ? std::round(x) : std::rint(x); };
-    for (uint32_t t = 0; t < T; t++) for (uint32_t g = 0; g < 8; g++) {
+    for (uint32_t t = 0; t < T; t++) for (uint32_t g = kq ? 0 : 4; g < 8; g++) {   // kq == nullptr: values only (keys stay fp16)
         const bool isV = g >= 4; const uint32_t head = g & 3; const uint16_t* src = (isV ? vs : ks) + (uint64_t)t * kKVD + head * kD; const uint64_t pos = (uint64_t)pos0 + t;
         int8_t* dst = (isV ? vq : kq) + pos * kKVD + head * kD;
         if (isV || mode != 2) {
@@ -239,7 +243,7 @@ void kor_dec_q_pack(const float* q, uint16_t* qp, uint32_t T) {
 // posBase+r against keys [0, posBase+r], 16-row blocks, 64-key tiles, gated output. q16 is fp16 [M][6144] prescaled.
 void kor_flash_prefill(const uint16_t* q16, const void* kc, const void* vc, const float* gate, float* out, uint32_t posBase, uint32_t M,
                        const uint16_t* ksc, const uint16_t* vsc, const uint16_t* kmn, int q8, uint32_t threads) {
-    const KvView kv{kc, vc, ksc, vsc, kmn, q8 != 0}; const uint32_t nQt = (M + 15) / 16;
+    const KvView kv(kc, vc, ksc, vsc, kmn, q8); const uint32_t nQt = (M + 15) / 16;
     parallel_for(nQt * kH, threads, [&](uint32_t item) {
         const uint32_t qt = item / kH, h = item % kH, kvh = h / kG, q0 = qt * 16, rowsValid = std::min(16u, M - q0), posEnd = posBase + q0 + rowsValid, nTiles = (posEnd + 63) / 64;
         std::vector<uint16_t> qblk(16 * kD, 0); float qSum[16] = {};
@@ -255,7 +259,7 @@ void kor_flash_prefill(const uint16_t* q16, const void* kc, const void* vc, cons
 // covers keys [firstPos + split*chunk, min(+chunk, posBase+T)) in 64-key tiles; writes unnormalised O and (m, l).
 void kor_attn_dec_split(const uint16_t* qp, const void* kc, const void* vc, float* pacc, float* pm, float* pl, uint32_t posBase, uint32_t T, uint32_t firstPos, uint32_t chunk,
                         const uint16_t* ksc, const uint16_t* vsc, const uint16_t* kmn, int q8, uint32_t threads) {
-    const KvView kv{kc, vc, ksc, vsc, kmn, q8 != 0}; const uint32_t posEnd = posBase + T, nSplits = (posEnd - firstPos + chunk - 1) / chunk;
+    const KvView kv(kc, vc, ksc, vsc, kmn, q8); const uint32_t posEnd = posBase + T, nSplits = (posEnd - firstPos + chunk - 1) / chunk;
     parallel_for(nSplits * kKvh, threads, [&](uint32_t item) {
         const uint32_t split = item / kKvh, kvh = item % kKvh, lo = firstPos + split * chunk, hi = std::min(lo + chunk, posEnd);
         const uint16_t* qb = qp + (uint64_t)kvh * 16 * kD; float qSum[16] = {};
@@ -283,7 +287,7 @@ void kor_attn_dec_combine(const float* pacc, const float* pm, const float* pl, c
 // Works on fp16 or int8 (dequantised codes*scale + mean) caches. out is double [M][6144]; untouched entries stay as given.
 void kor_formula_f64(const uint16_t* q16, const void* kc, const void* vc, const float* gate, double* out, uint32_t posBase, uint32_t M, uint32_t firstPos, uint32_t tStep, uint32_t hStep,
                      const uint16_t* ksc, const uint16_t* vsc, const uint16_t* kmn, int q8, uint32_t threads) {
-    const KvView kv{kc, vc, ksc, vsc, kmn, q8 != 0}; const uint32_t nT = (M + tStep - 1) / tStep, nHh = (kH + hStep - 1) / hStep;
+    const KvView kv(kc, vc, ksc, vsc, kmn, q8); const uint32_t nT = (M + tStep - 1) / tStep, nHh = (kH + hStep - 1) / hStep;
     parallel_for(nT * nHh, threads, [&](uint32_t item) {
         const uint32_t t = (item / nHh) * tStep, h = (item % nHh) * hStep, kvh = h / 6, pos = posBase + t; std::vector<double> s(pos + 1 - firstPos); double m = -1e30;
         for (uint32_t j = firstPos; j <= pos; j++) { double a = 0; const double ks = kv.kS(j, kvh), km = kv.kM(j, kvh); for (uint32_t d = 0; d < kD; d++) a += (double)h2f(q16[(uint64_t)t * kQD + h * kD + d]) * ((double)kv.kraw(j, kvh, d) * ks + km); s[j - firstPos] = a; m = std::max(m, a); }
@@ -296,7 +300,7 @@ void kor_formula_f64(const uint16_t* q16, const void* kc, const void* vc, const 
 // to fp16), scale 1/16, softmax and the V sum in fp32, all rows and heads.
 void kor_formula_f32(const float* q, const void* kc, const void* vc, const float* gate, float* out, uint32_t posBase, uint32_t M, uint32_t firstPos,
                      const uint16_t* ksc, const uint16_t* vsc, const uint16_t* kmn, int q8, uint32_t threads) {
-    const KvView kv{kc, vc, ksc, vsc, kmn, q8 != 0};
+    const KvView kv(kc, vc, ksc, vsc, kmn, q8);
     parallel_for(M * kH, threads, [&](uint32_t item) {
         const uint32_t t = item / kH, h = item % kH, kvh = h / 6, pos = posBase + t; std::vector<float> s(pos + 1 - firstPos); float m = kNegInf;
         for (uint32_t j = firstPos; j <= pos; j++) { float a = 0; const float ks = kv.kS(j, kvh), km = kv.kM(j, kvh); for (uint32_t d = 0; d < kD; d++) a += (q[(uint64_t)t * kQD + h * kD + d] * 0.0625f) * (kv.kraw(j, kvh, d) * ks + km); s[j - firstPos] = a; m = std::max(m, a); }

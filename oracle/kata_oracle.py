@@ -58,27 +58,31 @@ def inv_freq() -> np.ndarray:
 
 class KvPlanes:
     """One attention layer's cache planes on the host, in the reference layout (src/engine.h:73-83):
-    K, V: [max_ctx][1024] fp16 (stored as uint16 bit patterns) or int8; scales/mean: [max_ctx][4] fp16."""
+    K, V: [max_ctx][1024] fp16 (stored as uint16 bit patterns) or int8; scales/mean: [max_ctx][4] fp16.
+    ``mode`` 0: fp16; 1 (``int8=True``): K and V int8; 2 (``int8v=True``): K fp16, V int8 (KATA_KV=int8v, src/engine.cpp:54-59)."""
 
-    def __init__(self, max_ctx: int, int8: bool = False, poison: bool = False):
+    def __init__(self, max_ctx: int, int8: bool = False, poison: bool = False, int8v: bool = False):
         self.max_ctx, self.int8 = max_ctx, int8
-        if int8:
+        self.mode = 1 if int8 else 2 if int8v else 0
+        fill = 0x7E00 if poison else 0  # fp16 quiet NaN
+        self.ksc = self.vsc = self.kmn = None
+        if self.mode == 1:
             self.k = np.zeros((max_ctx, KVD), np.int8)
-            self.v = np.zeros((max_ctx, KVD), np.int8)
             self.ksc = np.zeros((max_ctx, 4), np.uint16)
-            self.vsc = np.zeros((max_ctx, 4), np.uint16)
             self.kmn = np.zeros((max_ctx, 4), np.uint16)
         else:
-            fill = 0x7E00 if poison else 0  # fp16 quiet NaN
             self.k = np.full((max_ctx, KVD), fill, np.uint16)
+        if self.mode:
+            self.v = np.zeros((max_ctx, KVD), np.int8)
+            self.vsc = np.zeros((max_ctx, 4), np.uint16)
+        else:
             self.v = np.full((max_ctx, KVD), fill, np.uint16)
-            self.ksc = self.vsc = self.kmn = None
 
     def k_f32(self):
-        return self.k.astype(np.float32) if self.int8 else self.k.view(np.float16).astype(np.float32)
+        return self.k.astype(np.float32) if self.mode == 1 else self.k.view(np.float16).astype(np.float32)
 
     def v_f32(self):
-        return self.v.astype(np.float32) if self.int8 else self.v.view(np.float16).astype(np.float32)
+        return self.v.astype(np.float32) if self.mode else self.v.view(np.float16).astype(np.float32)
 
 
 def prep(qfull, kproj, vproj, qnorm, knorm, planes: KvPlanes, pos0: int, h0: int = 0, nh: int = 32, quant_mode: int = 0):
@@ -88,7 +92,13 @@ def prep(qfull, kproj, vproj, qnorm, knorm, planes: KvPlanes, pos0: int, h0: int
     gate = np.zeros((M, QD), np.float32)
     invf = inv_freq()
     qf = qfull if qfull is not None else np.zeros((M, QFULL), np.float32)
-    if planes.int8:
+    if planes.mode == 2:   # keys straight into the fp16 plane, values through the scratch rows and the quantiser
+        vs = np.zeros((M, KVD), np.uint16)
+        lib().kor_prep(_p(qf), _p(kproj), _p(vproj), _p(qnorm), _p(knorm), _p(invf), _p(q), _p(gate), _p(planes.k), _p(vs),
+                       C.c_uint32(pos0), C.c_uint32(M), C.c_uint32(h0), C.c_uint32(nh), C.c_uint32(0), C.c_uint32(pos0))
+        if h0 + nh > 28:
+            kv_quant(None, vs, planes, pos0, quant_mode)
+    elif planes.int8:
         ks = np.zeros((M, KVD), np.uint16)
         vs = np.zeros((M, KVD), np.uint16)
         lib().kor_prep(_p(qf), _p(kproj), _p(vproj), _p(qnorm), _p(knorm), _p(invf), _p(q), _p(gate), _p(ks), _p(vs),
@@ -102,14 +112,14 @@ def prep(qfull, kproj, vproj, qnorm, knorm, planes: KvPlanes, pos0: int, h0: int
 
 def kv_quant(ks, vs, planes: KvPlanes, pos0: int, mode: int = 0):
     """k_kv_quant_sym (mode 0, rint), half-away variant (mode 1), reference asymmetric-K (mode 2)."""
-    assert planes.int8 and ks.dtype == np.uint16 and vs.dtype == np.uint16
-    T = ks.shape[0]
-    lib().kor_kv_quant(_p(ks), _p(vs), _p(planes.k), _p(planes.v), _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_uint32(pos0), C.c_uint32(T), C.c_int(mode))
+    assert planes.mode and vs.dtype == np.uint16 and (ks is None) == (planes.mode == 2)
+    T = vs.shape[0]
+    lib().kor_kv_quant(_p(ks), _p(vs), _p(planes.k) if planes.mode == 1 else None, _p(planes.v), _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_uint32(pos0), C.c_uint32(T), C.c_int(mode))
 
 
 def attn_decode(q, gate, planes: KvPlanes, pos: int, threads: int = 1):
     """k_attn_decode: q, gate fp32 [6144] -> out fp32 [6144]."""
-    assert not planes.int8
+    assert planes.mode == 0
     out = np.zeros(QD, np.float32)
     lib().kor_attn_decode(_p(q), _p(gate), _p(planes.k), _p(planes.v), _p(out), C.c_uint32(pos), C.c_uint32(threads))
     return out
@@ -117,7 +127,7 @@ def attn_decode(q, gate, planes: KvPlanes, pos: int, threads: int = 1):
 
 def attn_split_combine(q, gate, planes: KvPlanes, pos_base: int, T: int = 1, first_pos: int = 0, S: int | None = None):
     """k_attn_split(_b) + k_attn_combine(_b); S defaults to the engine's choice (src/engine.cpp:171)."""
-    assert not planes.int8
+    assert planes.mode == 0
     if S is None:
         S = min(32, max(1, (pos_base + 1) // 64))
     pm = np.zeros((T * 24, S), np.float32)
@@ -140,7 +150,7 @@ def flash_prefill(q16, gate, planes: KvPlanes, pos_base: int, threads: int = 0):
     M = q16.shape[0]
     out = np.zeros((M, QD), np.float32)
     lib().kor_flash_prefill(_p(q16), _p(planes.k), _p(planes.v), _p(gate), _p(out), C.c_uint32(pos_base), C.c_uint32(M),
-                            _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(int(planes.int8)), C.c_uint32(threads or hw_threads()))
+                            _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(planes.mode), C.c_uint32(threads or hw_threads()))
     return out
 
 
@@ -153,7 +163,7 @@ def dec_attn(q, gate, planes: KvPlanes, pos_base: int, T: int = 1, first_pos: in
     pm = np.zeros(4 * ns * 16, np.float32)
     pl = np.zeros(4 * ns * 16, np.float32)
     lib().kor_attn_dec_split(_p(qp), _p(planes.k), _p(planes.v), _p(pacc), _p(pm), _p(pl), C.c_uint32(pos_base), C.c_uint32(T), C.c_uint32(first_pos), C.c_uint32(chunk),
-                             _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(int(planes.int8)), C.c_uint32(threads or hw_threads()))
+                             _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(planes.mode), C.c_uint32(threads or hw_threads()))
     out = np.zeros((T, QD), np.float32)
     lib().kor_attn_dec_combine(_p(pacc), _p(pm), _p(pl), _p(gate), _p(out), C.c_uint32(pos_base), C.c_uint32(T), C.c_uint32(first_pos), C.c_uint32(chunk))
     return out
@@ -164,7 +174,7 @@ def formula_f64(q16, gate, planes: KvPlanes, pos_base: int, first_pos: int = 0, 
     M = q16.shape[0]
     out = np.full((M, QD), np.nan, np.float64)
     lib().kor_formula_f64(_p(q16), _p(planes.k), _p(planes.v), _p(gate), _p(out), C.c_uint32(pos_base), C.c_uint32(M), C.c_uint32(first_pos), C.c_uint32(t_step), C.c_uint32(h_step),
-                          _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(int(planes.int8)), C.c_uint32(threads or hw_threads()))
+                          _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(planes.mode), C.c_uint32(threads or hw_threads()))
     return out
 
 
@@ -173,7 +183,7 @@ def formula_f32(q, gate, planes: KvPlanes, pos_base: int, first_pos: int = 0, th
     M = q.shape[0]
     out = np.zeros((M, QD), np.float32)
     lib().kor_formula_f32(_p(q), _p(planes.k), _p(planes.v), _p(gate), _p(out), C.c_uint32(pos_base), C.c_uint32(M), C.c_uint32(first_pos),
-                          _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(int(planes.int8)), C.c_uint32(threads or hw_threads()))
+                          _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_int(planes.mode), C.c_uint32(threads or hw_threads()))
     return out
 
 

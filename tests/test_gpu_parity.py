@@ -42,10 +42,12 @@ def _upload_planes(ctx, planes, layer=0, seq=0, n=None):
     if planes.int8:
         ctx.plane_write(layer, seq, 2, 0, planes.ksc[:n])
         ctx.plane_write(layer, seq, 3, 0, planes.vsc[:n])
+    elif planes.mode == 2:   # int8v: {K fp16, V int8, V scales}
+        ctx.plane_write(layer, seq, 2, 0, planes.vsc[:n])
 
 
-def _oracle_fill(orc, seed, L, max_ctx, int8=False, poison=False, fast=False, layer=0, seq=0):
-    planes = orc.KvPlanes(max_ctx, int8=int8, poison=poison)
+def _oracle_fill(orc, seed, L, max_ctx, int8=False, poison=False, fast=False, layer=0, seq=0, int8v=False):
+    planes = orc.KvPlanes(max_ctx, int8=int8, poison=poison, int8v=int8v)
     qn, kn = synth.norm_weights(seed, layer)
     qf, kp, vp = (synth.token_rows_fast if fast else synth.token_rows)(seed, L, layer=layer, seq=seq)
     q, gate = orc.prep(qf, kp, vp, qn, kn, planes, 0)
@@ -292,6 +294,93 @@ def test_split_kv_partials_merge(capi, orc):
     _close(out.cpu().numpy(), orc.formula_f32(q[pb:L], gate[pb:L], planes, pb))
 
 
+# ------------------------------------------------------------------------------------------------ int8v: keys fp16, values int8
+def _cut_v8(orc, planes, n, max_ctx):
+    """The first n rows of an int8v cache; beyond them NaN keys, garbage value codes and NaN value scales."""
+    cut = orc.KvPlanes(max_ctx, int8v=True, poison=True)
+    cut.k[:n], cut.v[:n], cut.vsc[:n] = planes.k[:n], planes.v[:n], planes.vsc[:n]
+    cut.v[n:], cut.vsc[n:] = -77, NAN16
+    return cut
+
+
+def test_int8v_planes_tag_and_append(capi, orc):
+    # KATA_KV=int8v (src/engine.cpp:54-59, src/engine.h:71-81): planes {K fp16, V int8, V scales}, tag suffix "+kv8v"
+    L, pos0 = 50, 3
+    qn, kn = synth.norm_weights(24)
+    qf, kp, vp = synth.token_rows(24, L)
+    c16, cv = capi.AttnContext(1, [64]), capi.AttnContext(1, [64], kv_mode="int8v")
+    assert cv.kv_planes() == 3 and [cv.plane_row_bytes(i) for i in range(4)] == [2048, 1024, 8, 0] and cv.tag() == "fp16+kv8v"
+    args = (_dev(qf[None]), _dev(kp[None]), _dev(vp[None]), _dev(qn), _dev(kn))
+    q16a, _, ga = c16.prep(0, [0], [pos0], L, *args)
+    q16b, _, gb = cv.prep(0, [0], [pos0], L, *args)
+    c16.check(); cv.check()
+    assert torch.equal(q16a, q16b) and torch.equal(ga, gb)
+    assert np.array_equal(cv.plane_read(0, 0, 0, 0, 64), c16.plane_read(0, 0, 0, 0, 64))          # keys: the fp16 path's rows, bit for bit
+    ref = orc.KvPlanes(64, int8v=True)
+    orc.prep(qf, kp, vp, qn, kn, ref, pos0)
+    assert np.array_equal(cv.plane_read(0, 0, 1, 0, 64).view(np.int8).reshape(64, 1024), ref.v)   # values: the reference quantiser, bit for bit
+    assert np.array_equal(cv.plane_read(0, 0, 2, 0, 64).view(np.uint16).reshape(64, 4), ref.vsc)
+    # stand-alone quantise call: value rows only
+    v16 = c16.plane_read(0, 0, 1, pos0, L).view(np.float16).reshape(L, 1024)
+    cv.reset()
+    cv.kv_quant(0, 0, None, _dev(v16), pos0)
+    cv.check()
+    assert np.array_equal(cv.plane_read(0, 0, 1, 0, 64).view(np.int8).reshape(64, 1024), ref.v)
+    assert np.array_equal(cv.plane_read(0, 0, 2, 0, 64).view(np.uint16).reshape(64, 4), ref.vsc)
+    assert (cv.plane_read(0, 0, 0, 0, 64) == 0).all()
+
+
+@pytest.mark.parametrize("T", [1, 2])
+def test_int8v_decode_lengths(capi, orc, T):
+    planes, q, gate, _ = _oracle_fill(orc, 45, 700, 1024, int8v=True, fast=True)
+    ctx = capi.AttnContext(1, [1024], kv_mode="int8v")
+    for L in (T, 15, 16, 17, 31, 33, 64, 65, 129, 300, 700):
+        if L < T:
+            continue
+        cut = _cut_v8(orc, planes, L, 1024)
+        _upload_planes(ctx, cut)
+        pb = L - T
+        out = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(q[pb:L])[None]).view(torch.float16), _dev(gate[pb:L][None]))
+        ctx.check()
+        got = out.cpu().numpy()[0]
+        _close(got, orc.formula_f32(q[pb:L], gate[pb:L], cut, pb))
+        assert np.abs(got - orc.dec_attn(q[pb:L], gate[pb:L], cut, pb, T=T)).max() < 3e-4   # k_attn_dec_split_k16v8 restated: same rounding points
+
+
+@pytest.mark.parametrize("dec_chunk", [0, 64])
+def test_int8v_ragged_batch_split_merge_and_wide_verify(capi, orc, dec_chunk):
+    lens = [9, 2000, 37, 513, 1200]
+    ctx = capi.AttnContext(2, [2048, 2048, 64, 1024, 2048], kv_mode="int8v", dec_chunk=dec_chunk)
+    fills = []
+    for s, L in enumerate(lens):
+        planes, q, gate, _ = _oracle_fill(orc, 55 + s, L, int(ctx.max_ctx[s]), int8v=True, fast=True, seq=s)
+        _upload_planes(ctx, planes, layer=1, seq=s); fills.append((planes, q, gate))
+    order = [4, 0, 3, 1, 2]
+    for T in (1, 5):
+        pbs = [lens[s] - T for s in order]
+        q16 = np.stack([orc.cvt_q_half(fills[s][1][lens[s] - T:]) for s in order]); g = np.stack([fills[s][2][lens[s] - T:] for s in order])
+        got = ctx.decode(1, order, pbs, T, _dev(q16).view(torch.float16), _dev(g)).cpu().numpy()
+        ctx.check()
+        for i, s in enumerate(order):
+            _close(got[i], orc.formula_f32(fills[s][1][lens[s] - T:], fills[s][2][lens[s] - T:], fills[s][0], lens[s] - T))
+
+
+@pytest.mark.parametrize("legacy", [False, True], ids=["tcgen05", "mma"])
+def test_int8v_prefill(capi, orc, legacy):
+    planes, q, gate, _ = _oracle_fill(orc, 62, 700, 1024, int8v=True, fast=True)
+    ctx = capi.AttnContext(1, [1024], kv_mode="int8v", legacy_prefill=legacy)
+    _upload_planes(ctx, _cut_v8(orc, planes, 700, 1024))
+    for pb, M in ((300, 70), (0, 1), (0, 17), (0, 130), (353, 17), (190, 510)):
+        n = pb + M
+        sub = _cut_v8(orc, planes, n, 1024)
+        out = ctx.prefill(0, [0], [pb], M, _dev(orc.cvt_q_half(q[pb:n])[None]).view(torch.float16), _dev(gate[pb:n][None]))
+        ctx.check()
+        got = out.cpu().numpy()[0]
+        _close(got, orc.formula_f32(q[pb:n], gate[pb:n], sub, pb))
+        if M <= 130:
+            assert np.abs(got - orc.flash_prefill(orc.cvt_q_half(q[pb:n]), gate[pb:n], sub, pb)).max() < 3e-4   # k_flash_prefill_k16v8 restated
+
+
 # ------------------------------------------------------------------------------------------------ prefill
 @pytest.mark.parametrize("int8,legacy", [(False, False), (False, True), (True, False)], ids=["fp16-tcgen05", "fp16-mma", "int8-mma"])
 def test_prefill_probe_shape(capi, orc, int8, legacy):
@@ -474,15 +563,14 @@ def test_out_fwht_bit_exact(capi, orc):
         capi.out_fwht(torch.zeros(2, 1000, device="cuda"), _dev(sign[:1000]))
 
 
-@pytest.mark.parametrize("int8", [False, True])
-def test_decode_right_after_append_matches_a_synchronised_run(capi, orc, int8):
+@pytest.mark.parametrize("mode", ["fp16", "int8", "int8v"])
+def test_decode_right_after_append_matches_a_synchronised_run(capi, orc, mode):
     # Long enough ranges per CTA (4 sequences x ~24K keys) for the decode kernel to request tiles before it has waited for the append that
     # precedes it on the stream. The step append -> decode must give what append, synchronise, decode gives, also for the newest key, for
     # T = 1 and T = 2, and the same as a context whose work split is fixed (no early requests there: ranges are short).
     lens = [24001, 23057, 24576, 20000]
     gen = torch.Generator(device="cuda"); gen.manual_seed(17)
     kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
-    mode = "int8" if int8 else "fp16"
     ctxs = [capi.AttnContext(1, [l + 16 for l in lens], kv_mode=mode, dec_chunk=c) for c in (0, 1024)]
     for s, l in enumerate(lens):
         for st in range(0, l, 1024):

@@ -114,6 +114,30 @@ def test_int8_paths(orc):
     assert np.abs(pf[-2:] - v8).max() < 2e-5
 
 
+def test_int8v_paths(orc):
+    # keys fp16, values int8 (k_flash_prefill_k16v8 / k_attn_dec_split_k16v8): the key plane is the fp16 cache's, the value plane the int8 cache's
+    L = 130
+    p16, p8, pv = orc.KvPlanes(160), orc.KvPlanes(160, int8=True), orc.KvPlanes(160, int8v=True)
+    qn, kn = synth.norm_weights(16)
+    qf, kp, vp = synth.token_rows(16, L)
+    q, gate = orc.prep(qf, kp, vp, qn, kn, p16, 0)
+    orc.prep(qf, kp, vp, qn, kn, p8, 0)
+    qv, gv = orc.prep(qf, kp, vp, qn, kn, pv, 0)
+    assert np.array_equal(q, qv) and np.array_equal(gate, gv)
+    assert np.array_equal(pv.k, p16.k) and np.array_equal(pv.v, p8.v) and np.array_equal(pv.vsc, p8.vsc) and pv.ksc is None
+    pb = L - 2
+    dv = orc.dec_attn(q[pb:], gate[pb:], pv, pb, T=2)
+    fv = orc.formula_f32(q[pb:], gate[pb:], pv, pb)
+    assert np.abs(dv - fv).max() < TOL_MAX and np.abs(dv - fv).mean() < TOL_MEAN
+    pf = orc.flash_prefill(orc.cvt_q_half(q[100:]), gate[100:], pv, 100)
+    assert np.abs(pf[-2:] - dv).max() < 5e-5   # the two kernels cut the keys into tiles differently: P rounds to fp16 against different running maxima
+    # the mode sits between its neighbours: exact keys move it towards the fp16 result, away from the all-int8 one
+    f16, f8 = orc.formula_f32(q[pb:], gate[pb:], p16, pb), orc.formula_f32(q[pb:], gate[pb:], p8, pb)
+    assert 0 < np.abs(fv - f16).mean() <= np.abs(f8 - f16).mean() * 1.05 and not np.array_equal(fv, f8)
+    f64 = orc.formula_f64(orc.cvt_q_half(q[pb:]), gate[pb:], pv, pb)
+    assert np.abs(dv - f64).max() < 3e-4
+
+
 def test_quantiser_edges_and_ties(orc):
     rows = np.zeros((8, 1024), np.float16)
     # row 0: all zero -> scale 1.0, codes 0
