@@ -26,6 +26,8 @@ EXPORTS = [
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
+    "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
+    "kata_draft_ring_read", "kata_draft_ring_write", "kata_draft_launch_count",
 ]
 
 
@@ -225,3 +227,68 @@ def decode_static(k_rows, v_rows, seq_row0, pos_base, T, q16, gate, first_pos=0,
     rc = L.kata_attn_decode_static(_dp(k_rows), _dp(v_rows), C.c_int64(k_rows.shape[0]), n, rows0, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out),
                                    ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream())
     return rc, out
+
+
+class DraftConfig(C.Structure):
+    _fields_ = [("device", C.c_int32), ("n_layers", C.c_int32), ("ring", C.c_int32), ("window", C.c_int32)]
+
+
+class DraftContext:
+    """The block drafter's K/V rings and attention (include/kata_draft.h; Draft::kbuf/vbuf, src/draft.h:36)."""
+
+    def __init__(self, n_layers: int = 5, ring: int = 4096, window: int = 2048, device: int | None = None):
+        self.L = lib()
+        self.L.kata_draft_last_error.restype = C.c_char_p
+        self.L.kata_draft_ring_ptr.restype = C.c_void_p
+        self.L.kata_draft_launch_count.restype = C.c_uint64
+        self.device = torch.cuda.current_device() if device is None else device
+        self.n_layers, self.ring, self.window = n_layers, ring, window
+        self.h = C.c_void_p()
+        cfg = DraftConfig(self.device, n_layers, ring, window)
+        rc = self.L.kata_draft_create(C.byref(cfg), C.byref(self.h))
+        if rc != OK:
+            raise KataError(rc, "kata_draft_create failed")
+
+    def close(self):
+        if self.h:
+            self.L.kata_draft_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, rc):
+        if rc != OK:
+            raise KataError(rc, self.L.kata_draft_last_error(self.h).decode())
+
+    def reset(self):
+        self._ck(self.L.kata_draft_reset(self.h, _stream()))
+
+    def launches(self) -> int:
+        return int(self.L.kata_draft_launch_count(self.h))
+
+    def qk(self, layer, qin, kin, vin, qnorm, knorm, pos0):
+        """k_draft_qk (returns the fp32 query rows) or, with qin None, k_draft_ctx_kv."""
+        T = kin.shape[0]
+        qout = torch.empty((T, 4096), dtype=torch.float32, device=kin.device) if qin is not None else None
+        self._ck(self.L.kata_draft_qk(self.h, layer, _dp(qin), _dp(kin), _dp(vin), _dp(qnorm), _dp(knorm), _dp(qout), pos0, T, _stream()))
+        return qout
+
+    def attn(self, layer, q, pos0, out=None):
+        T = q.shape[0]
+        out = torch.empty((T, 4096), dtype=torch.float32, device=q.device) if out is None else out
+        self._ck(self.L.kata_draft_attn(self.h, layer, _dp(q), _dp(out), pos0, T, _stream()))
+        return out
+
+    def ring_read(self, layer, value: bool, row0: int = 0, nrows: int | None = None) -> np.ndarray:
+        nrows = self.ring - row0 if nrows is None else nrows
+        buf = np.empty((nrows, 1024), np.uint16)
+        self._ck(self.L.kata_draft_ring_read(self.h, layer, int(value), row0, nrows, buf.ctypes.data_as(C.c_void_p)))
+        return buf
+
+    def ring_write(self, layer, value: bool, row0: int, data: np.ndarray):
+        data = np.ascontiguousarray(data).view(np.uint16).reshape(-1, 1024)
+        self._ck(self.L.kata_draft_ring_write(self.h, layer, int(value), row0, data.shape[0], data.ctypes.data_as(C.c_void_p)))

@@ -346,4 +346,45 @@ void kor_out_fwht(const float* x, const float* sign, float* out, uint32_t rows, 
         }
 }
 
+// ---- the block drafter's attention (shaders/draft.metal:203-281; geometry src/draft.h:8-11): 32 query heads, 8 KV heads, head_dim 128 ----
+void kor_draft_inv_freq(float* out64) { for (int i = 0; i < 64; i++) out64[i] = std::pow(kTheta, -(float)i / 64.0f); }   // shaders/draft.metal:226
+
+// k_draft_qk (shaders/draft.metal:203-233) and, with qin == nullptr, k_draft_ctx_kv (:264-281): per-head RMSNorm(128) * weight, RoPE on the
+// pairs (i, i+64) with theta = pos * inv_freq[i], Q rows to qout (fp32), K rows (fp16) and V rows (fp16 copy) to ring row pos % ring.
+void kor_draft_qk(const float* qin, const float* kin, const float* vin, const float* qnorm, const float* knorm, const float* inv_freq,
+                  float* qout, uint16_t* kring, uint16_t* vring, uint32_t pos0, uint32_t T, uint32_t ring) {
+    const uint32_t H = 32, HKV = 8, D = 128;
+    for (uint32_t t = 0; t < T; t++) for (uint32_t h = qin ? 0 : H; h < H + 2 * HKV; h++) {
+        const uint32_t pos = pos0 + t; const uint64_t row = (uint64_t)(pos % ring) * (HKV * D);
+        if (h >= H + HKV) { const uint32_t vh = h - H - HKV; for (uint32_t d = 0; d < D; d++) vring[row + vh * D + d] = f2h(vin[(uint64_t)t * (HKV * D) + vh * D + d]); continue; }
+        const bool isK = h >= H; const uint32_t hh = isK ? h - H : h;
+        const float* src = isK ? kin + (uint64_t)t * (HKV * D) + hh * D : qin + (uint64_t)t * (H * D) + hh * D; const float* w = isK ? knorm : qnorm;
+        float tot = 0.0f; for (uint32_t sg = 0; sg < 4; sg++) { float sq[32]; for (int i = 0; i < 32; i++) sq[i] = src[32 * sg + i] * src[32 * sg + i]; tot += simd_sum32(sq); }   // part[0] + part[1] + part[2] + part[3]
+        const float r = 1.0f / std::sqrt(tot / 128.0f + 1e-6f);
+        float xs[128], o[128]; for (uint32_t d = 0; d < D; d++) o[d] = xs[d] = src[d] * r * w[d];
+        for (uint32_t i = 0; i < 64; i++) { const float theta = (float)pos * inv_freq[i], c = std::cos(theta), s = std::sin(theta), a = xs[i], b = xs[i + 64]; o[i] = a * c - b * s; o[i + 64] = a * s + b * c; }
+        if (isK) for (uint32_t d = 0; d < D; d++) kring[row + hh * D + d] = f2h(o[d]);
+        else for (uint32_t d = 0; d < D; d++) qout[(uint64_t)t * (H * D) + hh * D + d] = o[d];
+    }
+}
+
+// k_draft_attn (shaders/draft.metal:235-262): row t at position pos0 + t scans the keys [max(0, pos + 1 - win), pos0 + T - 1] in position order
+// with an online softmax in fp32; the score is the sum over the four 32-lane partial dot products, times 1/sqrt(128).
+void kor_draft_attn(const float* q, const uint16_t* kring, const uint16_t* vring, float* out, uint32_t pos0, uint32_t T, uint32_t win, uint32_t ring, uint32_t threads) {
+    const uint32_t H = 32, HKV = 8, D = 128; const float scale = 1.0f / std::sqrt(128.0f);
+    parallel_for(H * T, threads, [&](uint32_t item) {
+        const uint32_t h = item % H, t = item / H, kvh = h / (H / HKV), pos = pos0 + t, lo = pos + 1 > win ? pos + 1 - win : 0, hi = pos0 + T - 1;
+        const float* qv = q + (uint64_t)t * (H * D) + h * D;
+        float m = kNegInf, l = 0.0f, acc[128] = {};
+        for (uint32_t kp = lo; kp <= hi; kp++) {
+            const uint16_t* krow = kring + (uint64_t)(kp % ring) * (HKV * D) + kvh * D; const uint16_t* vrow = vring + (uint64_t)(kp % ring) * (HKV * D) + kvh * D;
+            float tot = 0.0f; for (uint32_t sg = 0; sg < 4; sg++) { float pr[32]; for (int i = 0; i < 32; i++) pr[i] = qv[32 * sg + i] * h2f(krow[32 * sg + i]); tot += simd_sum32(pr); }
+            const float sc = tot * scale, mn = std::max(m, sc), a = std::exp(m - mn), e = std::exp(sc - mn);
+            l = l * a + e; for (uint32_t d = 0; d < D; d++) acc[d] = acc[d] * a + e * h2f(vrow[d]);
+            m = mn;
+        }
+        for (uint32_t d = 0; d < D; d++) out[(uint64_t)t * (H * D) + h * D + d] = acc[d] / l;
+    });
+}
+
 }  // extern "C"

@@ -218,3 +218,38 @@ def kv_quant_rows_np(rows_f16: np.ndarray, half_away: bool = False):
     x64 = x.astype(np.float64)  # x + 0.5 is exact in fp64 for every fp32 x in range, so floor/ceil see the true value
     r = np.where(x64 >= 0, np.floor(x64 + 0.5), np.ceil(x64 - 0.5)) if half_away else np.rint(x)
     return np.clip(r, -127, 127).astype(np.int8), sc[..., 0]
+
+
+# ---- the block drafter's attention (shaders/draft.metal:203-281) ----
+DRAFT_H, DRAFT_KVH, DRAFT_D = 32, 8, 128
+
+
+class DraftRing:
+    """One drafter layer's K and V rings on the host: [ring][8 * 128] fp16 bit patterns, position p at row p % ring (src/draft.h:36)."""
+
+    def __init__(self, ring: int = 4096, window: int = 2048):
+        self.ring, self.window = ring, window
+        self.k = np.zeros((ring, DRAFT_KVH * DRAFT_D), np.uint16)
+        self.v = np.zeros((ring, DRAFT_KVH * DRAFT_D), np.uint16)
+
+
+def draft_inv_freq() -> np.ndarray:
+    out = np.empty(64, np.float32)
+    lib().kor_draft_inv_freq(_p(out))
+    return out
+
+
+def draft_qk(qin, kin, vin, qnorm, knorm, rings: DraftRing, pos0: int):
+    """k_draft_qk (qin given; returns the fp32 query rows) or k_draft_ctx_kv (qin None): K and V rows of positions pos0.. into the rings."""
+    T = kin.shape[0]
+    qout = np.zeros((T, DRAFT_H * DRAFT_D), np.float32) if qin is not None else None
+    lib().kor_draft_qk(_p(qin), _p(kin), _p(vin), _p(qnorm), _p(knorm), _p(draft_inv_freq()), _p(qout), _p(rings.k), _p(rings.v), C.c_uint32(pos0), C.c_uint32(T), C.c_uint32(rings.ring))
+    return qout
+
+
+def draft_attn(q, rings: DraftRing, pos0: int, threads: int = 0):
+    """k_draft_attn: q fp32 [T][4096] -> out fp32 [T][4096]; non-causal inside the block, sliding window behind it."""
+    T = q.shape[0]
+    out = np.zeros((T, DRAFT_H * DRAFT_D), np.float32)
+    lib().kor_draft_attn(_p(q), _p(rings.k), _p(rings.v), _p(out), C.c_uint32(pos0), C.c_uint32(T), C.c_uint32(rings.window), C.c_uint32(rings.ring), C.c_uint32(threads or hw_threads()))
+    return out

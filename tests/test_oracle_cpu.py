@@ -199,3 +199,26 @@ def test_out_fwht_matches_a_dense_hadamard_and_is_an_involution(orc):
     assert np.abs(y - ref).max() < 2e-5
     ones = np.ones(2048, np.float32)
     assert np.abs(orc.out_fwht(orc.out_fwht(x, ones), ones) - x).max() < 2e-5
+
+
+def test_draft_attention_oracle_matches_a_dense_softmax(orc):
+    # k_draft_qk + k_draft_ctx_kv + k_draft_attn restated: window, non-causal block, ring wrap
+    ring, win, T = 256, 100, 8
+    rng = np.random.default_rng(77)
+    rings = orc.DraftRing(ring, win)
+    qn, kn = (1 + 0.05 * rng.standard_normal(128)).astype(np.float32), (1 + 0.05 * rng.standard_normal(128)).astype(np.float32)
+    pos0 = 300                                      # past the ring size: rows wrap
+    ctx_k, ctx_v = rng.standard_normal((win, 1024)).astype(np.float32), rng.standard_normal((win, 1024)).astype(np.float32)
+    orc.draft_qk(None, ctx_k, ctx_v, None, kn, rings, pos0 - win)                 # context rows [200, 300)
+    qin, kin, vin = rng.standard_normal((T, 4096)).astype(np.float32), rng.standard_normal((T, 1024)).astype(np.float32), rng.standard_normal((T, 1024)).astype(np.float32)
+    q = orc.draft_qk(qin, kin, vin, qn, kn, rings, pos0)
+    assert np.allclose(np.sqrt((q.reshape(T, 32, 128) ** 2).mean(-1)), np.sqrt((qn ** 2).mean()), rtol=0.15)     # RMSNorm then a rotation: the row keeps its norm
+    assert np.array_equal(rings.v[(pos0 + 3) % ring].view(np.float16), vin[3].astype(np.float16))
+    out = orc.draft_attn(q, rings, pos0, threads=4)
+    K = rings.k.view(np.float16).astype(np.float64).reshape(ring, 8, 128); V = rings.v.view(np.float16).astype(np.float64).reshape(ring, 8, 128)
+    for t in (0, 5, 7):
+        for h in (0, 13, 31):
+            keys = np.arange(max(0, pos0 + t + 1 - win), pos0 + T)                    # up to the end of the block: not causal
+            s = (K[keys % ring, h // 4] @ q[t, h * 128:(h + 1) * 128].astype(np.float64)) / np.sqrt(128.0)
+            p = np.exp(s - s.max()); p /= p.sum()
+            assert np.abs(out[t, h * 128:(h + 1) * 128] - p @ V[keys % ring, h // 4]).max() < 2e-5
