@@ -49,6 +49,7 @@ WORKLOADS = {
     "chunked_int8_b4": ("chunked", 4, "int8", 7300, 3600),    # the codes are expanded to fp16 per layer for the tcgen05 kernel
     "chunked_int8v_b4": ("chunked", 4, "int8v", 7300, 3600),
     "chunked_small": ("chunked", 4, "fp16", 3072, 1024),      # ~0.4 GB: the size used for ncu captures of the prefill kernel
+    "draft_attn": ("draft", 8, "fp16", 2048, 4096),           # the block drafter's attention: 5 layers, block of 8 rows, window 2048 over a 4096 ring, 4 drafters in rotation (168 MB of rings read per step)
     "out_fwht": ("fwht", 32768, "fp32", 6144, 6144),          # the sign + Walsh-Hadamard transform that follows attention, on 32,768 output rows (805 MB in, 805 MB out)
 }
 
@@ -375,6 +376,8 @@ def run_reference(args, kind_cfg):
     one of the 16 layers for the whole batch at full context; tok/s is extrapolated to 16 layers."""
     from oracle import kata_oracle as orc
     from kata_b200 import synth
+    if kind_cfg[0] in ("draft", "fwht"):   # the reference arm times the headline decode path
+        kind_cfg = WORKLOADS["decode_b8"]
     _, B, kv_mode, lmax, lmin = kind_cfg
     B_global = B * max(1, args.gpus)   # the same global batch as the CUDA arm at this GPU count (weak scaling)
     B = min(B_global, 8)               # bounded sample: at most 8 sequences per step; CPU tok/s does not depend on the batch size
@@ -438,6 +441,88 @@ def run_fwht(args, rank, world, cfg):
                          "us_per_launch": ms / args.steps * 1e3, "algorithmic_bytes_per_launch": nbytes, "traffic": None}}
 
 
+def run_draft(args, rank, world, cfg):
+    """The block drafter's attention (k_draft_qk + k_draft_attn per layer, src/draft.cpp:196-209): one step = one drafter round (5 layers, a block
+    of T rows over a full window) for each of 4 independent drafters, whose rings together exceed L2. HBM-bound: window x 4 KB per layer."""
+    import torch
+    import torch.distributed as dist
+    from kata_b200 import capi
+    T, win, ring, n_layers, n_ctx = cfg[1], cfg[3], cfg[4], 5, 4
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev); gen.manual_seed(99 + rank)
+    ctxs = [capi.DraftContext(n_layers, ring, win) for _ in range(n_ctx)]
+    qn = (1 + 0.05 * torch.randn(128, generator=gen, device=dev)).contiguous(); kn = (1 + 0.05 * torch.randn(128, generator=gen, device=dev)).contiguous()
+    pos0 = 3 * win                                               # a full window behind the block, wrapped around the ring
+    for c in ctxs:                                               # context rows through k_draft_ctx_kv, 64 at a time (Draft::kNMax)
+        for il in range(n_layers):
+            for st in range(pos0 - win, pos0, 64):
+                c.qk(il, None, torch.randn(64, 1024, generator=gen, device=dev), torch.randn(64, 1024, generator=gen, device=dev), None, kn, st)
+    qin = torch.randn(n_ctx, n_layers, T, 4096, generator=gen, device=dev); kin = torch.randn(n_ctx, n_layers, T, 1024, generator=gen, device=dev); vin = torch.randn(n_ctx, n_layers, T, 1024, generator=gen, device=dev)
+    out = torch.empty(n_ctx, n_layers, T, 4096, device=dev)
+    h_in = [torch.randn(n_ctx, n_layers, T, w).pin_memory() for w in (4096, 1024, 1024)]; h_out = torch.empty(n_ctx, n_layers, T, 4096).pin_memory()
+
+    def step(p):
+        for ci, c in enumerate(ctxs):
+            for il in range(n_layers):
+                q = c.qk(il, qin[ci, il], kin[ci, il], vin[ci, il], qn, kn, p)
+                c.attn(il, q, p, out=out[ci, il])
+    sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
+    for i in range(args.warmup):
+        step(pos0 + i * T)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    l0 = sum(c.launches() for c in ctxs)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tw0 = time.perf_counter(); e0.record()
+    for i in range(args.steps):
+        step(pos0 + (args.warmup + i) * T)
+    e1.record(); torch.cuda.synchronize(); tw1 = time.perf_counter()
+    ms = e0.elapsed_time(e1); clocks = sampler.stop(tw0, tw1); launches = sum(c.launches() for c in ctxs) - l0
+    # the attention kernels alone (attention + combine grid per launch), same rotation over drafters and layers
+    pk_pos = pos0 + (args.warmup + args.steps) * T
+    qs = [[c.qk(il, qin[ci, il], kin[ci, il], vin[ci, il], qn, kn, pk_pos) for il in range(n_layers)] for ci, c in enumerate(ctxs)]
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        for ci, c in enumerate(ctxs):
+            for il in range(n_layers):
+                c.attn(il, qs[ci][il], pk_pos, out=out[ci, il])
+    k1.record(); torch.cuda.synchronize()
+    kern_ms = k0.elapsed_time(k1) / (args.steps * n_ctx * n_layers)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        qin.copy_(h_in[0], non_blocking=True); kin.copy_(h_in[1], non_blocking=True); vin.copy_(h_in[2], non_blocking=True)
+        step(pk_pos + (1 + i) * T)
+        h_out.copy_(out, non_blocking=True); torch.cuda.current_stream().synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, e2e_ms = t.tolist()
+    pk = peaks(); nbytes = float(win + T - 1) * 4096.0; ach = nbytes / (kern_ms * 1e-3) / 1e9
+    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * n_ctx * T * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+           "config": {"workload": f"block drafter attention: {n_ctx} drafters/GPU x {n_layers} layers, block of {T} rows, window {win} over a ring of {ring}; norm + RoPE + ring append, then attention, per layer",
+                      "l2": f"{n_ctx} drafters in rotation: {n_ctx * n_layers * (win + T - 1) * 4096 / 1e6:.0f} MB of ring rows read per step (larger than L2)"},
+           "clocks": clocks, "gpu_launches": int(launches),
+           "e2e": {"value": world * n_ctx * T * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": sum(h.numel() * 4 for h in h_in), "d2h_bytes_per_step": h_out.numel() * 4},
+           "roofline": {"bound": "hbm", "kernel": "draft_attn_kernel", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_src": pk["src"],
+                        "us_per_launch": kern_ms * 1e3, "algorithmic_bytes_per_launch": nbytes, "traffic": None}}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import kata_oracle as orc
+        rings = orc.DraftRing(ring, win)
+        rings.k[:] = ctxs[0].ring_read(0, False); rings.v[:] = ctxs[0].ring_read(0, True)
+        qh = qs[0][0].cpu().numpy(); cores = orc.hw_threads(); reps = 20
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.draft_attn(qh, rings, pk_pos, threads=cores)
+        dt = (time.perf_counter() - t0) / reps
+        res["cpu_baseline"] = {"value": T / (dt * n_layers), "unit": "tok/s", "cores": cores, "kind": "port", "sample": f"k_draft_attn restated, 1 of {n_layers} layers of one drafter, mean of {reps} runs ({dt * 1e3:.1f} ms), tok/s extrapolated x{n_layers} layers"}
+    for c in ctxs:
+        c.close()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -468,6 +553,8 @@ def main():
         res = run_splitkv(args, rank, world, cfg)
     elif cfg[0] == "fwht":
         res = run_fwht(args, rank, world, cfg)
+    elif cfg[0] == "draft":
+        res = run_draft(args, rank, world, cfg)
     else:
         from kata_b200 import bench_prefill
         res = bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler)
