@@ -461,40 +461,53 @@ def run_draft(args, rank, world, cfg):
     out = torch.empty(n_ctx, n_layers, T, 4096, device=dev)
     h_in = [torch.randn(n_ctx, n_layers, T, w).pin_memory() for w in (4096, 1024, 1024)]; h_out = torch.empty(n_ctx, n_layers, T, 4096).pin_memory()
 
-    def step(p):
+    qbuf = torch.empty(n_ctx, n_layers, T, 4096, device=dev)
+
+    def step(p, attn_only=False):
         for ci, c in enumerate(ctxs):
             for il in range(n_layers):
-                q = c.qk(il, qin[ci, il], kin[ci, il], vin[ci, il], qn, kn, p)
-                c.attn(il, q, p, out=out[ci, il])
+                if not attn_only:
+                    c.qk(il, qin[ci, il], kin[ci, il], vin[ci, il], qn, kn, p, out=qbuf[ci, il])
+                c.attn(il, qbuf[ci, il], p, out=out[ci, il])
+    # The kernels take a few microseconds each, less than a launch through the Python binding costs: the device-resident figures replay a
+    # CUDA graph of one step (a drafter round at one position), as a native caller's launch loop would run; e2e goes through the plain calls.
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(args.warmup):
+            step(pos0)
+    torch.cuda.current_stream().wait_stream(side); torch.cuda.synchronize()
+    l0 = sum(c.launches() for c in ctxs)
+    g_step, g_attn = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_step):
+        step(pos0)
+    launches = (sum(c.launches() for c in ctxs) - l0) * args.steps
+    with torch.cuda.graph(g_attn):
+        step(pos0, attn_only=True)
     sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
-    for i in range(args.warmup):
-        step(pos0 + i * T)
+    for _ in range(args.warmup):
+        g_step.replay()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    l0 = sum(c.launches() for c in ctxs)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     tw0 = time.perf_counter(); e0.record()
     for i in range(args.steps):
-        step(pos0 + (args.warmup + i) * T)
+        g_step.replay()
     e1.record(); torch.cuda.synchronize(); tw1 = time.perf_counter()
-    ms = e0.elapsed_time(e1); clocks = sampler.stop(tw0, tw1); launches = sum(c.launches() for c in ctxs) - l0
+    ms = e0.elapsed_time(e1); clocks = sampler.stop(tw0, tw1)
     # the attention kernels alone (attention + combine grid per launch), same rotation over drafters and layers
-    pk_pos = pos0 + (args.warmup + args.steps) * T
-    qs = [[c.qk(il, qin[ci, il], kin[ci, il], vin[ci, il], qn, kn, pk_pos) for il in range(n_layers)] for ci, c in enumerate(ctxs)]
-    torch.cuda.synchronize()
+    pk_pos = pos0
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
     for _ in range(args.steps):
-        for ci, c in enumerate(ctxs):
-            for il in range(n_layers):
-                c.attn(il, qs[ci][il], pk_pos, out=out[ci, il])
+        g_attn.replay()
     k1.record(); torch.cuda.synchronize()
     kern_ms = k0.elapsed_time(k1) / (args.steps * n_ctx * n_layers)
     t0 = time.perf_counter()
     for i in range(args.steps):
         qin.copy_(h_in[0], non_blocking=True); kin.copy_(h_in[1], non_blocking=True); vin.copy_(h_in[2], non_blocking=True)
-        step(pk_pos + (1 + i) * T)
+        step(pos0 + (1 + i) * T)
         h_out.copy_(out, non_blocking=True); torch.cuda.current_stream().synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     if world > 1:
@@ -512,7 +525,7 @@ def run_draft(args, rank, world, cfg):
         from oracle import kata_oracle as orc
         rings = orc.DraftRing(ring, win)
         rings.k[:] = ctxs[0].ring_read(0, False); rings.v[:] = ctxs[0].ring_read(0, True)
-        qh = qs[0][0].cpu().numpy(); cores = orc.hw_threads(); reps = 20
+        qh = qbuf[0, 0].cpu().numpy(); cores = orc.hw_threads(); reps = 20
         t0 = time.perf_counter()
         for _ in range(reps):
             orc.draft_attn(qh, rings, pk_pos, threads=cores)

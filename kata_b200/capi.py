@@ -270,10 +270,10 @@ class DraftContext:
     def launches(self) -> int:
         return int(self.L.kata_draft_launch_count(self.h))
 
-    def qk(self, layer, qin, kin, vin, qnorm, knorm, pos0):
+    def qk(self, layer, qin, kin, vin, qnorm, knorm, pos0, out=None):
         """k_draft_qk (returns the fp32 query rows) or, with qin None, k_draft_ctx_kv."""
         T = kin.shape[0]
-        qout = torch.empty((T, 4096), dtype=torch.float32, device=kin.device) if qin is not None else None
+        qout = (torch.empty((T, 4096), dtype=torch.float32, device=kin.device) if out is None else out) if qin is not None else None
         self._ck(self.L.kata_draft_qk(self.h, layer, _dp(qin), _dp(kin), _dp(vin), _dp(qnorm), _dp(knorm), _dp(qout), pos0, T, _stream()))
         return qout
 

@@ -11,8 +11,8 @@
 //
 // HBM-bound and small (window 2048: 8.4 MB of K+V per layer), so the design goes for memory-level parallelism: the window is cut into
 // chunks of at most 128 keys, one CTA per (chunk, KV head) (about one CTA per SM), each CTA requests its whole chunk at once with 16-byte
-// cp.async copies (ring rows are gathered by position mod ring), splits the query block while the copies fly, and its four warps take
-// (row tile, 16-key sub-tile) pairs with private online-softmax state. Warp partials are merged through shared memory, chunk partials
+// cp.async copies in two groups (ring rows are gathered by position mod ring), splits the query block while the copies fly, and its eight
+// warps take (row tile, 16-key sub-tile) pairs with private online-softmax state, starting on the first group while the second lands. Warp partials are merged through shared memory, chunk partials
 // (O, m, l) through a small combine grid launched with programmatic stream serialisation.
 #include <algorithm>
 #include <climits>
@@ -46,7 +46,8 @@ constexpr int kDChunk = 128, kDMaxSplits = 24;   // keys per CTA; chunks per cal
 constexpr int kDRows = 4 * KATA_DRAFT_MAX_BLOCK; // 64 rows of the query block
 constexpr int kOffQhi = 0, kOffQlo = kDRows * kDRowStride, kOffK = 2 * kDRows * kDRowStride, kOffV = kOffK + kDChunk * kDRowStride, kDraftSmem = kOffV + kDChunk * kDRowStride;
 constexpr int kMoStride = 132;                   // floats per row of a warp's partial O in the merge buffer (which reuses the K/V area)
-static_assert(4 * 16 * kMoStride * 4 <= 2 * kDChunk * kDRowStride, "merge buffer must fit the K/V area");
+constexpr int kDWarps = 8, kDThreads = kDWarps * 32;
+static_assert(kDWarps * 16 * kMoStride * 4 <= 2 * kDChunk * kDRowStride, "merge buffer must fit the K/V area");
 
 __constant__ float c_draft_inv_freq[64];   // 1e7^(-i/64), shaders/draft.metal:226
 
@@ -58,55 +59,77 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t&
     hi = *reinterpret_cast<const uint32_t*>(&h); lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-// grid (n_splits, 8 KV heads) x 128 threads
-__global__ void __launch_bounds__(128) draft_attn_kernel(const DraftPlan p, const float* __restrict__ q, const __half* __restrict__ kring, const __half* __restrict__ vring,
+// grid (n_splits, 8 KV heads) x 256 threads
+__global__ void __launch_bounds__(kDThreads) draft_attn_kernel(const DraftPlan p, const float* __restrict__ q, const __half* __restrict__ kring, const __half* __restrict__ vring,
                                                          float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float s_ml[4][16][2];
+    __shared__ float s_ml[kDWarps][16][2];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t4 = lane & 3, split = blockIdx.x, kvh = blockIdx.y;
     const uint32_t sm = smem_u32(smem);
     const int k0 = p.klo + split * p.chunk, k1 = min(k0 + p.chunk, p.khi), nk = k1 - k0, rows_pad = (nk + 15) & ~15;
     pdl_wait(); pdl_launch_dependents();   // the ring rows of this block and q come from the kernel launched just before
 
-    // ---- the chunk's K and V rows, all requested at once (position p lives at ring row p mod ring); rows past the chunk arrive as zeros
-    for (int idx = tid; idx < rows_pad * 16; idx += 128) {
-        const int r = idx >> 4, c = idx & 15; const bool ok = r < nk;
-        const int64_t src = (int64_t)((k0 + (ok ? r : 0)) & p.ring_mask) * kDKVD + kvh * kDD + c * 8;
-        cp_async16(sm + kOffK + r * kDRowStride + c * 16, kring + src, ok ? 16u : 0u);
-        cp_async16(sm + kOffV + r * kDRowStride + c * 16, vring + src, ok ? 16u : 0u);
+    // ---- the chunk's K and V rows, all requested at once in two groups of sub-tiles (position p lives at ring row p mod ring); rows past
+    // the chunk arrive as zeros
+    const int n_sub = rows_pad >> 4, sub_a = (n_sub + 1) >> 1;   // sub-tiles [0, sub_a) form the first group
+    auto request = [&](int row_from, int row_to) {
+        for (int idx = row_from * 16 + tid; idx < row_to * 16; idx += kDThreads) {
+            const int r = idx >> 4, c = idx & 15; const bool ok = r < nk;
+            const int64_t src = (int64_t)((k0 + (ok ? r : 0)) & p.ring_mask) * kDKVD + kvh * kDD + c * 8;
+            cp_async16(sm + kOffK + r * kDRowStride + c * 16, kring + src, ok ? 16u : 0u);
+            cp_async16(sm + kOffV + r * kDRowStride + c * 16, vring + src, ok ? 16u : 0u);
+        }
+        cp_async_commit();
+    };
+    request(0, sub_a * 16); request(sub_a * 16, rows_pad);
+    // ---- the query block (rows t*4 + j, zero up to the next multiple of 16), split into fp16 head and remainder, while the copies fly:
+    // the loads of a thread's (up to 8) chunks are issued together, then converted
+    const int rows = 4 * p.T, n_mt = (rows + 15) >> 4;
+    {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = tid + u * kDThreads, r = idx >> 5, c4 = idx & 31; v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < rows) v[u] = __ldg(reinterpret_cast<const float4*>(q + (int64_t)(r >> 2) * kDQD + (kvh * 4 + (r & 3)) * kDD + c4 * 4));
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = tid + u * kDThreads, r = idx >> 5, c4 = idx & 31;
+            if (r < n_mt * 16) {
+                uint2 hi, lo; split2(v[u].x, v[u].y, hi.x, lo.x); split2(v[u].z, v[u].w, hi.y, lo.y);
+                *reinterpret_cast<uint2*>(smem + kOffQhi + r * kDRowStride + c4 * 8) = hi; *reinterpret_cast<uint2*>(smem + kOffQlo + r * kDRowStride + c4 * 8) = lo;
+            }
+        }
     }
-    cp_async_commit();
-    // ---- the query block (rows t*4 + j, zero past 4T), split into fp16 head and remainder, while the copies fly
-    const int rows = 4 * p.T;
-    for (int idx = tid; idx < kDRows * 32; idx += 128) {
-        const int r = idx >> 5, c4 = idx & 31; float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < rows) v = *reinterpret_cast<const float4*>(q + (int64_t)(r >> 2) * kDQD + (kvh * 4 + (r & 3)) * kDD + c4 * 4);
-        uint2 hi, lo; split2(v.x, v.y, hi.x, lo.x); split2(v.z, v.w, hi.y, lo.y);
-        *reinterpret_cast<uint2*>(smem + kOffQhi + r * kDRowStride + c4 * 8) = hi; *reinterpret_cast<uint2*>(smem + kOffQlo + r * kDRowStride + c4 * 8) = lo;
-    }
-    cp_async_wait<0>();
+    static_assert(8 * kDThreads == kDRows * 32, "a thread stages 8 chunks of the query block");
+    cp_async_wait<1>();
     __syncthreads();
 
     // ---- warp w: row tile w % n_mt, 16-key sub-tiles w / n_mt, + n_kw, ...
-    const int n_mt = (rows + 15) >> 4, n_kw = 4 / n_mt, mt = w % n_mt, kw = w / n_mt; const bool active = kw < n_kw;
+    const int n_kw = kDWarps / n_mt, mt = w % n_mt, kw = w / n_mt; const bool active = kw < n_kw;
     float o[16][4]; float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
     for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
-    if (active) {
+    {
         const int r0 = mt * 16 + g, r1 = r0 + 8;
         const int lo0 = r0 < rows ? p.pos0 + (r0 >> 2) + 1 - p.win : INT_MAX, lo1 = r1 < rows ? p.pos0 + (r1 >> 2) + 1 - p.win : INT_MAX;   // first visible key of rows g and g + 8
         const uint32_t qa_hi = sm + kOffQhi + (mt * 16 + (lane & 15)) * kDRowStride + (lane >> 4) * 16, qa_lo = qa_hi + (kOffQlo - kOffQhi);
         const float sc = 0.08838834764831845f * kLog2e;   // 1/sqrt(128), scores kept in log2 units
-        for (int st = kw; st < (rows_pad >> 4); st += n_kw) {
+        auto run = [&](int st_from, int st_to) {
+        for (int st = st_from; st < st_to; st += n_kw) {
             const uint32_t ka = sm + kOffK + (st * 16 + (lane & 7) + ((lane >> 4) << 3)) * kDRowStride + ((lane >> 3) & 1) * 16;
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // heads and remainders on separate chains
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
                 uint32_t a0, a1, a2, a3, c0, c1, c2, c3, b0, b1, b2, b3;
                 ldsm_x4(qa_hi + kk * 32, a0, a1, a2, a3); ldsm_x4(qa_lo + kk * 32, c0, c1, c2, c3); ldsm_x4(ka + kk * 32, b0, b1, b2, b3);
                 mma16816(s[0], a0, a1, a2, a3, b0, b1); mma16816(s[1], a0, a1, a2, a3, b2, b3);
-                mma16816(s[0], c0, c1, c2, c3, b0, b1); mma16816(s[1], c0, c1, c2, c3, b2, b3);
+                mma16816(s2[0], c0, c1, c2, c3, b0, b1); mma16816(s2[1], c0, c1, c2, c3, b2, b3);
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) s[nt][e] += s2[nt][e];
             const int key0 = k0 + st * 16;
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -141,32 +164,49 @@ __global__ void __launch_bounds__(128) draft_attn_kernel(const DraftPlan p, cons
                 mma16816(o[2 * j2], pl[0], pl[1], pl[2], pl[3], b0, b1); mma16816(o[2 * j2 + 1], pl[0], pl[1], pl[2], pl[3], b2, b3);
             }
         }
+        };
+        // this warp's sub-tiles kw, kw + n_kw, ...: those of the first group now, the rest when the second group has landed
+        const int first_b = kw + ((max(sub_a - kw, 0) + n_kw - 1) / n_kw) * n_kw;   // its first sub-tile >= sub_a
+        if (active) run(kw, sub_a);
+        cp_async_wait<0>();
+        __syncthreads();   // (every warp, whether it has sub-tiles or not)
+        if (active) run(first_b, n_sub);
         l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     }
-    // ---- merge the warps that shared a row tile, write the chunk's partial rows
-    __syncthreads();   // nobody reads K/V any more
+    // ---- merge the warps that shared a row tile, write the chunk's partial rows: the warps exchange their row maxima, each scales its own
+    // partial O by 2^(m - M) in registers, and the scaled partials are summed from shared memory (the merge buffer reuses the K/V area)
+    if (active && t4 == 0) { s_ml[w][g][0] = m0; s_ml[w][g][1] = l0; s_ml[w][g + 8][0] = m1; s_ml[w][g + 8][1] = l1; }
+    __syncthreads();   // the maxima are visible; nobody reads K/V any more
     float* mo_all = reinterpret_cast<float*>(smem + kOffK);
+    const int64_t slot0 = (int64_t)(kvh * p.n_splits + split) * kDRows;
     if (active) {
+        float M0 = -INFINITY, M1 = -INFINITY;
+        for (int k = 0; k < n_kw; k++) { M0 = fmaxf(M0, s_ml[k * n_mt + mt][g][0]); M1 = fmaxf(M1, s_ml[k * n_mt + mt][g + 8][0]); }
+        const float w0 = (m0 == -INFINITY) ? 0.0f : ex2(m0 - M0), w1 = (m1 == -INFINITY) ? 0.0f : ex2(m1 - M1);
         float* mo = mo_all + w * 16 * kMoStride;
 #pragma unroll
-        for (int j = 0; j < 16; j++)
-#pragma unroll
-            for (int c = 0; c < 2; c++) { const int d = 8 * j + 2 * t4 + c; mo[g * kMoStride + d] = o[j][c]; mo[(g + 8) * kMoStride + d] = o[j][2 + c]; }
-        if (t4 == 0) { s_ml[w][g][0] = m0; s_ml[w][g][1] = l0; s_ml[w][g + 8][0] = m1; s_ml[w][g + 8][1] = l1; }
+        for (int j = 0; j < 16; j++) {
+            *reinterpret_cast<float2*>(mo + g * kMoStride + 8 * j + 2 * t4) = make_float2(o[j][0] * w0, o[j][1] * w0);
+            *reinterpret_cast<float2*>(mo + (g + 8) * kMoStride + 8 * j + 2 * t4) = make_float2(o[j][2] * w1, o[j][3] * w1);
+        }
+        if (kw == 0 && t4 == 0) {   // (M, l) of rows g and g + 8 of this row tile
+            float L0 = 0.0f, L1 = 0.0f;
+            for (int k = 0; k < n_kw; k++) {
+                const int ww = k * n_mt + mt; const float a = s_ml[ww][g][0], b = s_ml[ww][g + 8][0];
+                L0 += s_ml[ww][g][1] * ((a == -INFINITY) ? 0.0f : ex2(a - M0)); L1 += s_ml[ww][g + 8][1] * ((b == -INFINITY) ? 0.0f : ex2(b - M1));
+            }
+            const int r0 = mt * 16 + g;
+            if (r0 < rows) { part_ml[(slot0 + r0) * 2] = M0; part_ml[(slot0 + r0) * 2 + 1] = L0; }
+            if (r0 + 8 < rows) { part_ml[(slot0 + r0 + 8) * 2] = M1; part_ml[(slot0 + r0 + 8) * 2 + 1] = L1; }
+        }
     }
     __syncthreads();
-    for (int r = 0; r < rows; r++) {   // thread = head dim
-        const int rmt = r >> 4, rr = r & 15;
-        float M = -INFINITY;
-        for (int k = 0; k < n_kw; k++) M = fmaxf(M, s_ml[k * n_mt + rmt][rr][0]);
-        float L = 0.0f, A = 0.0f;
-        for (int k = 0; k < n_kw; k++) {
-            const int ww = k * n_mt + rmt; const float mm = s_ml[ww][rr][0], wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
-            L += s_ml[ww][rr][1] * wt; A += mo_all[(ww * 16 + rr) * kMoStride + tid] * wt;
-        }
-        const int64_t slot = (int64_t)(kvh * p.n_splits + split) * kDRows + r;
-        part_o[slot * kDD + tid] = A; if (tid == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+    for (int idx = tid; idx < rows * 32; idx += kDThreads) {   // four dims of one row per thread
+        const int r = idx >> 5, c4 = idx & 31, rmt = r >> 4, rr = r & 15;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < n_kw; k++) { const float4 v = *reinterpret_cast<const float4*>(mo_all + ((k * n_mt + rmt) * 16 + rr) * kMoStride + c4 * 4); a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+        *reinterpret_cast<float4*>(part_o + (slot0 + r) * kDD + c4 * 4) = a;
     }
 }
 
@@ -336,7 +376,7 @@ int kata_draft_attn(kata_draft_ctx* c, int32_t layer, const float* d_q, float* d
     p.n_splits = (nkeys + p.chunk - 1) / p.chunk;   // <= kDMaxSplits: create() bounded window + block by kDChunk * kDMaxSplits
     if (p.n_splits > kDMaxSplits) { p.chunk = kDChunk; p.n_splits = (nkeys + kDChunk - 1) / kDChunk; }
     const __half* kr = (const __half*)kata_draft_ring_ptr(c, layer, 0); const __half* vr = (const __half*)kata_draft_ring_ptr(c, layer, 1);
-    cudaError_t e = launch_pdl(draft_attn_kernel, dim3(p.n_splits, kDKV), dim3(128), (size_t)kDraftSmem, (cudaStream_t)stream, p, d_q, kr, vr, c->part_o, c->part_ml);
+    cudaError_t e = launch_pdl(draft_attn_kernel, dim3(p.n_splits, kDKV), dim3(kDThreads), (size_t)kDraftSmem, (cudaStream_t)stream, p, d_q, kr, vr, c->part_o, c->part_ml);
     if (e == cudaSuccess) e = launch_pdl(draft_combine_kernel, dim3(kDH, T), dim3(128), 0, (cudaStream_t)stream, p, (const float*)c->part_o, (const float*)c->part_ml, d_out);
     if (e != cudaSuccess) return dfail(c, KATA_ERR_CUDA, "attn launch: %s", cudaGetErrorString(e));
     c->launches += 2;
