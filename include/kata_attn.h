@@ -115,6 +115,27 @@ int kata_attn_decode_scalar(kata_attn_ctx* ctx, int32_t layer, int32_t n, const 
 int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t M,
                       const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 
+/* No reference counterpart (the reference is single-device). Exchange of the split-KV parts between the GPUs of one box without a library
+ * collective: each rank pushes its part rows {O[256], m, l} (as kata_attn_decode_partial writes them) into every peer's exchange buffer
+ * with plain stores over NVLink, raises a flag per row, waits for the peers' rows in its own buffer and merges + gates, all in one kernel
+ * on the caller's stream. Set-up: every rank creates an exchange (one cudaMalloc, exported as a CUDA IPC handle of
+ * KATA_PEER_HANDLE_BYTES bytes), the ranks swap handles by any host channel, and each opens the others'; inside one process
+ * kata_attn_peer_open_pointers takes the buffers' device addresses instead. All ranks must issue the same sequence of exchange calls.
+ * Waits are bounded (about a second, kata_attn_peer_set_wait_polls): when a peer's rows do not arrive the call's output is left
+ * unwritten and kata_attn_peer_check returns KATA_ERR_DEVICE_WAIT. world <= 8, T in {1, 2}. */
+#define KATA_PEER_HANDLE_BYTES 64
+typedef struct kata_attn_peer kata_attn_peer;
+int kata_attn_peer_create(int32_t device, int32_t rank, int32_t world, kata_attn_peer** out, void* handle_out /* KATA_PEER_HANDLE_BYTES, may be NULL */);
+int kata_attn_peer_open(kata_attn_peer* px, const void* handles /* world x KATA_PEER_HANDLE_BYTES, in rank order; the own slot is ignored */);
+int kata_attn_peer_open_pointers(kata_attn_peer* px, void* const* buffers /* [world] device addresses from kata_attn_peer_buffer */);
+void* kata_attn_peer_buffer(kata_attn_peer* px);
+int kata_attn_peer_set_wait_polls(kata_attn_peer* px, uint32_t polls);
+/* d_part [T*24][258] fp32 (this rank's part), d_gate [T][6144] fp32, d_out [T][6144]: out = merge over ranks, normalised and gated. */
+int kata_attn_peer_exchange_merge(kata_attn_peer* px, const float* d_part, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+int kata_attn_peer_check(kata_attn_peer* px, void* stream);   /* synchronises the stream; KATA_ERR_DEVICE_WAIT after a wait that ran out */
+const char* kata_attn_peer_last_error(const kata_attn_peer* px);
+int kata_attn_peer_destroy(kata_attn_peer* px);              /* call on every rank only after all ranks have finished their exchanges */
+
 /* No reference counterpart. Declares that row 0 of sequence seq's planes holds absolute position first_position (default
  * 0): afterwards every call takes absolute positions and the context maps position p to row p - first_position. Used
  * when a long sequence is split by keys across GPUs and each rank stores only its slice. */

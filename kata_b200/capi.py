@@ -26,6 +26,8 @@ EXPORTS = [
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
+    "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge",
+    "kata_attn_peer_check", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
     "kata_draft_ring_read", "kata_draft_ring_write", "kata_draft_launch_count",
 ]
@@ -292,3 +294,55 @@ class DraftContext:
     def ring_write(self, layer, value: bool, row0: int, data: np.ndarray):
         data = np.ascontiguousarray(data).view(np.uint16).reshape(-1, 1024)
         self._ck(self.L.kata_draft_ring_write(self.h, layer, int(value), row0, data.shape[0], data.ctypes.data_as(C.c_void_p)))
+
+
+class PeerExchange:
+    """Push-and-merge of the split-KV parts between the GPUs of one box (kata_attn_peer_*): one process per GPU, handles swapped
+    through ``torch.distributed`` object collectives (host side, once); the per-layer exchange itself runs no library collective."""
+
+    def __init__(self, rank: int, world: int, device: int | None = None, group=None, buffers=None):
+        self.L = lib()
+        self.L.kata_attn_peer_last_error.restype = C.c_char_p
+        self.L.kata_attn_peer_buffer.restype = C.c_void_p
+        self.rank, self.world = rank, world
+        self.device = torch.cuda.current_device() if device is None else device
+        self.h = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        rc = self.L.kata_attn_peer_create(self.device, rank, world, C.byref(self.h), handle)
+        if rc != OK:
+            raise KataError(rc, "kata_attn_peer_create failed")
+        if buffers is not None:       # same process: device addresses of every rank's buffer (tests)
+            self.open_pointers(buffers)
+        elif world > 1 and group is not False:
+            import torch.distributed as dist
+            got = [None] * world
+            dist.all_gather_object(got, bytes(handle), group=group)
+            blob = (C.c_ubyte * (64 * world)).from_buffer_copy(b"".join(got))
+            self._ck(self.L.kata_attn_peer_open(self.h, blob))
+
+    def buffer(self) -> int:
+        return int(self.L.kata_attn_peer_buffer(self.h) or 0)
+
+    def open_pointers(self, buffers):
+        arr = (C.c_void_p * self.world)(*[C.c_void_p(int(b)) for b in buffers])
+        self._ck(self.L.kata_attn_peer_open_pointers(self.h, arr))
+
+    def set_wait_polls(self, polls: int):
+        self._ck(self.L.kata_attn_peer_set_wait_polls(self.h, C.c_uint32(polls)))
+
+    def _ck(self, rc):
+        if rc != OK:
+            raise KataError(rc, self.L.kata_attn_peer_last_error(self.h).decode())
+
+    def exchange_merge(self, part, T, gate, out=None, out_dtype=torch.float32):
+        out = torch.empty((T, QD), dtype=out_dtype, device=part.device) if out is None else out
+        self._ck(self.L.kata_attn_peer_exchange_merge(self.h, _dp(part), T, _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        return out
+
+    def check(self):
+        self._ck(self.L.kata_attn_peer_check(self.h, _stream()))
+
+    def close(self):
+        if self.h:
+            self.L.kata_attn_peer_destroy(self.h)
+            self.h = C.c_void_p()

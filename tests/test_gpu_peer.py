@@ -1,0 +1,112 @@
+"""The split-KV exchange between GPUs (kata_attn_peer_*): parts pushed into the peers' buffers and merged in one kernel.
+
+One GPU: the single-rank path, and a wait that runs out (a peer that never calls) reported as a status with the context still usable.
+Two GPUs (skipped otherwise): two processes, one per GPU, against the NCCL all-gather + merge and the oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from kata_b200 import multi, synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from kata_b200 import capi as m
+    m.lib()
+    return m
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import kata_oracle as m
+    m.lib()
+    return m
+
+
+def _parts(seed, n_ranks, T):
+    rng = np.random.default_rng(seed)
+    p = rng.standard_normal((n_ranks, T * 24, 258)).astype(np.float32)
+    p[:, :, 256] = rng.uniform(-3, 3, (n_ranks, T * 24)); p[:, :, 257] = rng.uniform(0.5, 40, (n_ranks, T * 24))
+    return p, rng.standard_normal((T, 6144)).astype(np.float32)
+
+
+def test_single_rank_exchange_is_normalise_and_gate(capi):
+    px = capi.PeerExchange(0, 1)
+    for T in (1, 2, 1):
+        p, gate = _parts(T, 1, T)
+        out = px.exchange_merge(torch.from_numpy(p[0]).cuda(), T, torch.from_numpy(gate).cuda())
+        px.check()
+        want = multi.merge_parts_numpy(p, gate.reshape(T * 24, 256)).reshape(T, 6144)
+        assert np.abs(out.cpu().numpy() - want).max() < 1e-5
+    px.close()
+
+
+def test_wait_that_runs_out_is_a_status_not_a_hang(capi):
+    # two ranks' buffers in one process; rank 1 never calls, so rank 0's wait for its rows must give up and say so
+    a = capi.PeerExchange(0, 2, group=False); b = capi.PeerExchange(1, 2, group=False)
+    bufs = [a.buffer(), b.buffer()]
+    a.open_pointers(bufs); b.open_pointers(bufs)
+    a.set_wait_polls(20000)                                    # a few tens of milliseconds
+    p, gate = _parts(3, 1, 2)
+    out = torch.full((2, 6144), 7.0, device="cuda")
+    a.exchange_merge(torch.from_numpy(p[0]).cuda(), 2, torch.from_numpy(gate).cuda(), out=out)
+    with pytest.raises(capi.KataError) as e:
+        a.check()
+    assert e.value.code == 5 and "rank 1" in str(e.value)     # KATA_ERR_DEVICE_WAIT
+    assert (out == 7.0).all()                                  # nothing was written for that call
+    a.check()                                                  # the error word was cleared; the GPU still answers
+    ctx = capi.AttnContext(1, [64])
+    ctx.reset(); ctx.check()
+    a.close(); b.close()
+
+
+def _rank_main(rank, world, port, Lk, k, v, q16, gate, ret):
+    import torch.distributed as dist
+    from kata_b200 import capi
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    lo, hi = multi.split_keys(Lk, world)[rank]
+    ctx = capi.AttnContext(1, [max(hi - lo, 1) + 8])
+    if hi > lo:
+        ctx.plane_write(0, 0, 0, 0, k[lo:hi]); ctx.plane_write(0, 0, 1, 0, v[lo:hi])
+    px = capi.PeerExchange(rank, world)
+    outs = []
+    for T, pb in ((2, Lk - 2), (1, Lk - 1), (1, Lk - 700), (2, Lk - 2)):   # several calls: both buffer parities, changing T
+        qd = torch.from_numpy(q16[pb:pb + T]).cuda().view(torch.float16); gd = torch.from_numpy(gate[pb:pb + T]).cuda()
+        part = ctx.decode_partial(0, 0, pb, T, lo, hi, qd)
+        fused = px.exchange_merge(part, T, gd)
+        parts = torch.empty((world,) + tuple(part.shape), device="cuda")
+        dist.all_gather_into_tensor(parts, part)
+        nccl = ctx.merge_parts(parts, T, gd)
+        ctx.check(); px.check()
+        outs.append((fused.cpu().numpy(), nccl.cpu().numpy()))
+    if rank == 0:
+        ret.put(outs)
+    dist.barrier(); px.close(); dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_push_and_merge_across_two_gpus(orc):
+    import torch.multiprocessing as mp
+    world, Lk = 2, 3000
+    planes = orc.KvPlanes(Lk)
+    qn, kn = synth.norm_weights(83); qf, kp, vp = synth.token_rows_fast(83, Lk)
+    q, gate = orc.prep(qf, kp, vp, qn, kn, planes, 0)
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn"); ret = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, Lk, planes.k, planes.v, orc.cvt_q_half(q), gate, ret)) for r in range(world)]
+    for p in procs: p.start()
+    outs = ret.get(timeout=240)
+    for p in procs: p.join(timeout=60)
+    assert all(p.exitcode == 0 for p in procs)
+    for (fused, nccl), (T, pb) in zip(outs, ((2, Lk - 2), (1, Lk - 1), (1, Lk - 700), (2, Lk - 2))):
+        assert np.array_equal(fused, nccl)                               # the same merge arithmetic, wherever the parts travelled
+        ref = orc.formula_f32(q[pb:pb + T], gate[pb:pb + T], planes, pb)
+        d = np.abs(fused - ref)
+        assert d.max() < 2e-3 and d.mean() < 2e-4
