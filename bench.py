@@ -42,6 +42,7 @@ WORKLOADS = {
     "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
     "decode_int8v_b8": ("decode", 8, "int8v", 32768, 16384),    # keys fp16, values int8 (the reference's KATA_KV=int8v)
     "splitkv_b1": ("splitkv", 1, "fp16", 32768, 32768),       # one 32K sequence, keys split across the ranks, parts pushed to the peers and merged per layer
+    "splitkv_b1_128k": ("splitkv", 1, "fp16", 131072, 131072),  # the same at 131,072 keys, where one GPU's HBM time dominates the exchange
     "pp512": ("prefill", 1, "fp16", 512, 512),
     # chunked: (kind, batch, kv mode, prompt length, restored prefix)
     "chunked_b1": ("chunked", 1, "fp16", 7300, 3600),
@@ -318,10 +319,11 @@ def run_splitkv(args, rank, world, kind_cfg):
     def step(pos, batched):
         for layer in range(N_LAYERS):
             ctx.prep(layer, [0], [pos], 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], h0=0, nh=32 if tail else 24, q16=q16[layer], gate=gate[layer])
-            ctx.decode_partial(layer, 0, pos, 1, lo, big if tail else hi, q16[layer], part=part[layer])
             if batched == "peer":
-                px.exchange_merge(part[layer], 1, gate[layer, 0], out=out[layer])
-            elif not batched:
+                px.decode(ctx, layer, 0, pos, 1, lo, big if tail else hi, q16[layer], gate[layer, 0], out=out[layer])
+                continue
+            ctx.decode_partial(layer, 0, pos, 1, lo, big if tail else hi, q16[layer], part=part[layer])
+            if not batched:
                 if world > 1:
                     dist.all_gather_into_tensor(parts[layer], part[layer])
                 else:

@@ -132,6 +132,10 @@ void* kata_attn_peer_buffer(kata_attn_peer* px);
 int kata_attn_peer_set_wait_polls(kata_attn_peer* px, uint32_t polls);
 /* d_part [T*24][258] fp32 (this rank's part), d_gate [T][6144] fp32, d_out [T][6144]: out = merge over ranks, normalised and gated. */
 int kata_attn_peer_exchange_merge(kata_attn_peer* px, const float* d_part, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+/* kata_attn_decode_partial into the exchange's own part buffer followed by kata_attn_peer_exchange_merge: the whole cross-GPU decode of
+ * one layer (this rank's keys [key_lo, key_hi) of sequence seq) as one call. */
+int kata_attn_peer_decode(kata_attn_peer* px, kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
+                          const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 int kata_attn_peer_check(kata_attn_peer* px, void* stream);   /* synchronises the stream; KATA_ERR_DEVICE_WAIT after a wait that ran out */
 const char* kata_attn_peer_last_error(const kata_attn_peer* px);
 int kata_attn_peer_destroy(kata_attn_peer* px);              /* call on every rank only after all ranks have finished their exchanges */

@@ -26,7 +26,7 @@ EXPORTS = [
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
-    "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge",
+    "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode",
     "kata_attn_peer_check", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
     "kata_draft_ring_read", "kata_draft_ring_write", "kata_draft_launch_count",
@@ -337,6 +337,12 @@ class PeerExchange:
     def exchange_merge(self, part, T, gate, out=None, out_dtype=torch.float32):
         out = torch.empty((T, QD), dtype=out_dtype, device=part.device) if out is None else out
         self._ck(self.L.kata_attn_peer_exchange_merge(self.h, _dp(part), T, _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        return out
+
+    def decode(self, ctx, layer, seq, pos_base, T, key_lo, key_hi, q16, gate, out=None, out_dtype=torch.float32):
+        """This rank's share of a decode whose keys are split across the ranks, exchange and merge included (kata_attn_peer_decode)."""
+        out = torch.empty((T, QD), dtype=out_dtype, device=q16.device) if out is None else out
+        self._ck(self.L.kata_attn_peer_decode(self.h, ctx.h, layer, seq, pos_base, T, key_lo, key_hi, _dp(q16), _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
         return out
 
     def check(self):

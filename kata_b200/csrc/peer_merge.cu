@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(256) peer_push_merge_kernel(const PeerBases pb
 
 struct kata_attn_peer {
     int device = 0, rank = 0, world = 1;
-    float* local = nullptr; int32_t* d_err = nullptr;
+    float* local = nullptr; int32_t* d_err = nullptr; float* d_part = nullptr;   // d_part: this rank's part rows for kata_attn_peer_decode
     kata::PeerBases bases{}; bool opened = false, ipc[kata::kPeerMaxWorld] = {};
     uint32_t seq = 0, max_polls = 1u << 20;   // about a second of polling at 0.5-1 us per poll
     uint64_t launches = 0;
@@ -113,7 +113,7 @@ int kata_attn_peer_create(int32_t device, int32_t rank, int32_t world, kata_attn
     if (!p) return KATA_ERR_NOMEM;
     p->device = device; p->rank = rank; p->world = world;
     PeerGuard guard(device);
-    if (cudaMalloc((void**)&p->local, peer_bytes(world)) != cudaSuccess || cudaMalloc((void**)&p->d_err, 4) != cudaSuccess) { cudaGetLastError(); kata_attn_peer_destroy(p); return KATA_ERR_NOMEM; }
+    if (cudaMalloc((void**)&p->local, peer_bytes(world)) != cudaSuccess || cudaMalloc((void**)&p->d_err, 4) != cudaSuccess || cudaMalloc((void**)&p->d_part, (size_t)kPeerRows * kPartStride * 4) != cudaSuccess) { cudaGetLastError(); kata_attn_peer_destroy(p); return KATA_ERR_NOMEM; }
     cudaMemset(p->local, 0, peer_bytes(world)); cudaMemset(p->d_err, 0, 4);
     p->bases.base[rank] = p->local;
     if (handle_out) {
@@ -168,6 +168,13 @@ int kata_attn_peer_exchange_merge(kata_attn_peer* p, const float* d_part, int32_
     return KATA_OK;
 }
 
+int kata_attn_peer_decode(kata_attn_peer* p, kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
+                          const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
+    if (!p || !ctx) return KATA_ERR_ARG;
+    if (const int rc = kata_attn_decode_partial(ctx, layer, seq, pos_base, T, key_lo, key_hi, d_q16, p->d_part, stream)) return pfail(p, rc, kata_attn_last_error(ctx));
+    return kata_attn_peer_exchange_merge(p, p->d_part, T, d_gate, d_out, out_dtype, stream);
+}
+
 int kata_attn_peer_check(kata_attn_peer* p, void* stream) {
     if (!p) return KATA_ERR_ARG;
     PeerGuard guard(p->device);
@@ -184,6 +191,7 @@ int kata_attn_peer_destroy(kata_attn_peer* p) {
     for (int r = 0; r < p->world; r++) if (p->ipc[r] && p->bases.base[r]) cudaIpcCloseMemHandle(p->bases.base[r]);
     if (p->local) cudaFree(p->local);
     if (p->d_err) cudaFree(p->d_err);
+    if (p->d_part) cudaFree(p->d_part);
     cudaGetLastError();
     delete p;
     return KATA_OK;

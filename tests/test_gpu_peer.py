@@ -80,7 +80,7 @@ def _rank_main(rank, world, port, Lk, k, v, q16, gate, ret):
     for T, pb in ((2, Lk - 2), (1, Lk - 1), (1, Lk - 700), (2, Lk - 2)):   # several calls: both buffer parities, changing T
         qd = torch.from_numpy(q16[pb:pb + T]).cuda().view(torch.float16); gd = torch.from_numpy(gate[pb:pb + T]).cuda()
         part = ctx.decode_partial(0, 0, pb, T, lo, hi, qd)
-        fused = px.exchange_merge(part, T, gd)
+        fused = px.exchange_merge(part, T, gd) if pb != Lk - 1 else px.decode(ctx, 0, 0, pb, T, lo, hi, qd, gd)   # the one-call form once
         parts = torch.empty((world,) + tuple(part.shape), device="cuda")
         dist.all_gather_into_tensor(parts, part)
         nccl = ctx.merge_parts(parts, T, gd)
