@@ -37,6 +37,7 @@ WORKLOADS = {
     "decode_b1": ("decode", 1, "fp16", 32768, 32768),
     "decode_small": ("decode", 4, "fp16", 8192, 8192),        # ~2 GB of cache: the size used for ncu captures
     "decode_int8_small": ("decode", 4, "int8", 16384, 16384),
+    "decode_int8v_small": ("decode", 4, "int8v", 8192, 8192),
     "decode_b64": ("decode", 64, "fp16", 32768, 16384),
     "decode_int8_b8": ("decode", 8, "int8", 32768, 16384),
     "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
