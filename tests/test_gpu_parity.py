@@ -596,3 +596,38 @@ def test_decode_right_after_append_matches_a_synchronised_run(capi, orc, mode):
         miss = ctxs[1].decode(0, seqs, [p - 1 for p in pos], 1, q16[:, :1].contiguous(), g[:, :1].contiguous()).cpu().numpy()
         assert np.abs(miss[:, 0] - a[:, 0]).max() > 3e-4
         pos = [p + T for p in pos]
+
+
+def test_append_and_decode_replay_in_a_cuda_graph(capi, orc):
+    # the calls only enqueue work (no allocation, no synchronisation, metadata by value): a captured step replays with the same result
+    lens = [5000, 3000]
+    ctx = capi.AttnContext(2, [l + 8 for l in lens])
+    gen = torch.Generator(device="cuda"); gen.manual_seed(3)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    for layer in range(2):
+        for s, l in enumerate(lens):
+            for st in range(0, l, 1024):
+                m = min(1024, l - st)
+                ctx.prep(layer, [s], [st], m, None, torch.randn(1, m, 1024, generator=gen, device="cuda"), torch.randn(1, m, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    qf = torch.randn(2, 2, 1, 12288, generator=gen, device="cuda"); kp = torch.randn(2, 2, 1, 1024, generator=gen, device="cuda"); vp = torch.randn(2, 2, 1, 1024, generator=gen, device="cuda")
+    q16 = torch.empty(2, 2, 1, 6144, dtype=torch.float16, device="cuda"); gate = torch.empty(2, 2, 1, 6144, device="cuda"); out = torch.empty(2, 2, 1, 6144, device="cuda")
+
+    def step():
+        for layer in range(2):
+            ctx.prep(layer, [0, 1], lens, 1, qf[layer], kp[layer], vp[layer], qn, kn, q16=q16[layer], gate=gate[layer])
+            ctx.decode(layer, [0, 1], lens, 1, q16[layer], gate[layer], out=out[layer])
+    side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side); torch.cuda.synchronize()
+    ctx.check()
+    eager = out.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    for _ in range(2):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    ctx.check()
