@@ -382,7 +382,7 @@ def test_int8v_prefill(capi, orc, legacy):
 
 
 # ------------------------------------------------------------------------------------------------ prefill
-@pytest.mark.parametrize("int8,legacy", [(False, False), (False, True), (True, False)], ids=["fp16-tcgen05", "fp16-mma", "int8-mma"])
+@pytest.mark.parametrize("int8,legacy", [(False, False), (False, True), (True, False), (True, True)], ids=["fp16-tcgen05", "fp16-mma", "int8-tcgen05", "int8-mma"])
 def test_prefill_probe_shape(capi, orc, int8, legacy):
     # the reference's probe: 70 rows (ragged tail) at position 300, NaN beyond the valid keys; plus M = 1, 15, 16, 17 and pos 0
     planes, q, gate, _ = _oracle_fill(orc, 61, 370, 512, int8=int8, poison=not int8, fast=True)
@@ -524,6 +524,50 @@ def test_full_size_decode_32k_properties(capi, orc):
     planes = orc.KvPlanes(L)
     planes.k[:] = c.plane_read(0, 0, 0, 0, L).view(np.uint16).reshape(L, 1024); planes.v[:] = c.plane_read(0, 0, 1, 0, L).view(np.uint16).reshape(L, 1024)
     _close(a, orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2))
+
+
+@pytest.mark.parametrize("mode", ["int8", "int8v"])
+def test_full_size_quantised_decode_32k_properties(capi, orc, mode):
+    # the int8 caches at the benchmark's context length: against the fp32 formula on the dequantised planes, T=2 verify == two T=1
+    # decodes, result independent of the split, and the value codes / scales equal to the quantiser applied to the fp16 cache's rows
+    L = 32768
+    gen = torch.Generator(device="cuda"); gen.manual_seed(8)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    ctxs = [capi.AttnContext(1, [L + 8], kv_mode=mode, dec_chunk=c) for c in (0, 2048)]
+    c16 = capi.AttnContext(1, [L + 8])
+    for st in range(0, L, 1024):
+        kp = torch.randn(1, 1024, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 1024, 1024, generator=gen, device="cuda")
+        for c in ctxs + [c16]:
+            c.prep(0, [0], [st], 1024, None, kp, vp, None, kn, h0=24, nh=8)
+    qf = torch.randn(1, 2, 12288, generator=gen, device="cuda"); kp = torch.randn(1, 2, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 2, 1024, generator=gen, device="cuda")
+    outs = []
+    for c in ctxs:
+        q16, q32, g = c.prep(0, [0], [L - 2], 2, qf, kp, vp, qn, kn, want_q32=True)
+        outs.append(c.decode(0, [0], [L - 2], 2, q16, g))
+        c.check()
+    c16.prep(0, [0], [L - 2], 2, qf, kp, vp, qn, kn); c16.check()
+    c = ctxs[0]
+    d0 = c.decode(0, [0], [L - 2], 1, q16[:, :1].contiguous(), g[:, :1].contiguous()); d1 = c.decode(0, [0], [L - 1], 1, q16[:, 1:].contiguous(), g[:, 1:].contiguous())
+    c.check()
+    a = outs[0].cpu().numpy()[0]
+    # looser than the fp16 cache's 2e-5: the int8 fragments enter the MMAs as code + 1152 and the bias comes out of the fp32 accumulators
+    # afterwards, so accumulation-order noise is that of sums some hundred times larger than the result
+    assert np.abs(a - outs[1].cpu().numpy()[0]).max() < 1e-4                       # split invariance
+    assert np.abs(a[0] - d0.cpu().numpy()[0, 0]).max() < 1e-4 and np.abs(a[1] - d1.cpu().numpy()[0, 0]).max() < 1e-4
+    planes = orc.KvPlanes(L, int8=(mode == "int8"), int8v=(mode == "int8v"))
+    planes.k[:] = c.plane_read(0, 0, 0, 0, L).view(planes.k.dtype).reshape(L, 1024); planes.v[:] = c.plane_read(0, 0, 1, 0, L).view(np.int8).reshape(L, 1024)
+    if mode == "int8":
+        planes.ksc[:] = c.plane_read(0, 0, 2, 0, L).view(np.uint16).reshape(L, 4)
+    planes.vsc[:] = c.plane_read(0, 0, c.kv_planes() - 1, 0, L).view(np.uint16).reshape(L, 4)
+    _close(a, orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2))
+    # quantise-on-append == the reference quantiser over the rows the fp16 path caches (bit for bit, all 32K rows)
+    ref = orc.KvPlanes(L, int8=True)
+    orc.kv_quant(np.ascontiguousarray(c16.plane_read(0, 0, 0, 0, L).view(np.uint16).reshape(L, 1024)), np.ascontiguousarray(c16.plane_read(0, 0, 1, 0, L).view(np.uint16).reshape(L, 1024)), ref, 0, 0)
+    assert np.array_equal(planes.v, ref.v) and np.array_equal(planes.vsc, ref.vsc)
+    if mode == "int8":
+        assert np.array_equal(planes.k, ref.k) and np.array_equal(planes.ksc, ref.ksc)
+    else:
+        assert np.array_equal(planes.k, c16.plane_read(0, 0, 0, 0, L).view(np.uint16).reshape(L, 1024))
 
 
 def test_full_size_prefill_chunk_over_7k_prefix(capi, orc):
