@@ -42,12 +42,13 @@ using namespace ptx;
 
 constexpr int kDH = KATA_DRAFT_HEADS, kDKV = KATA_DRAFT_KV_HEADS, kDD = KATA_DRAFT_HEAD_DIM, kDQD = KATA_DRAFT_Q_DIM, kDKVD = KATA_DRAFT_KV_DIM;
 constexpr int kDRowStride = 272;                 // bytes per staged row: 128 fp16 + 16 pad (the eight rows of an ldmatrix fall in distinct banks)
-constexpr int kDChunk = 128, kDMaxSplits = 24;   // keys per CTA; chunks per call
+constexpr int kDChunk = 128, kDMaxSplits = 48;   // most keys per CTA; most chunks per call
 constexpr int kDRows = 4 * KATA_DRAFT_MAX_BLOCK; // 64 rows of the query block
 constexpr int kOffQhi = 0, kOffQlo = kDRows * kDRowStride, kOffK = 2 * kDRows * kDRowStride, kOffV = kOffK + kDChunk * kDRowStride, kDraftSmem = kOffV + kDChunk * kDRowStride;
-constexpr int kMoStride = 132;                   // floats per row of a warp's partial O in the merge buffer (which reuses the K/V area)
+constexpr int kMoStride = 132;                   // floats per row of a warp's partial O in the merge buffer (which reuses the shared window from its start)
 constexpr int kDWarps = 8, kDThreads = kDWarps * 32;
-static_assert(kDWarps * 16 * kMoStride * 4 <= 2 * kDChunk * kDRowStride, "merge buffer must fit the K/V area");
+constexpr int kMergeBytes = kDWarps * 16 * kMoStride * 4;
+static_assert(kMergeBytes <= kDraftSmem, "merge buffer must fit the shared window");
 
 __constant__ float c_draft_inv_freq[64];   // 1e7^(-i/64), shaders/draft.metal:226
 
@@ -67,6 +68,7 @@ __global__ void __launch_bounds__(kDThreads) draft_attn_kernel(const DraftPlan p
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, t4 = lane & 3, split = blockIdx.x, kvh = blockIdx.y;
     const uint32_t sm = smem_u32(smem);
     const int k0 = p.klo + split * p.chunk, k1 = min(k0 + p.chunk, p.khi), nk = k1 - k0, rows_pad = (nk + 15) & ~15;
+    const uint32_t off_v = kOffK + p.chunk * kDRowStride;   // the K area holds p.chunk rows
     pdl_wait(); pdl_launch_dependents();   // the ring rows of this block and q come from the kernel launched just before
 
     // ---- the chunk's K and V rows, all requested at once in two groups of sub-tiles (position p lives at ring row p mod ring); rows past
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(kDThreads) draft_attn_kernel(const DraftPlan p
             const int r = idx >> 4, c = idx & 15; const bool ok = r < nk;
             const int64_t src = (int64_t)((k0 + (ok ? r : 0)) & p.ring_mask) * kDKVD + kvh * kDD + c * 8;
             cp_async16(sm + kOffK + r * kDRowStride + c * 16, kring + src, ok ? 16u : 0u);
-            cp_async16(sm + kOffV + r * kDRowStride + c * 16, vring + src, ok ? 16u : 0u);
+            cp_async16(sm + off_v + r * kDRowStride + c * 16, vring + src, ok ? 16u : 0u);
         }
         cp_async_commit();
     };
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(kDThreads) draft_attn_kernel(const DraftPlan p
             }
             uint32_t ph[4], pl[4];   // the probabilities as the A operand of P.V: heads and remainders
             split2(pr[0][0], pr[0][1], ph[0], pl[0]); split2(pr[0][2], pr[0][3], ph[1], pl[1]); split2(pr[1][0], pr[1][1], ph[2], pl[2]); split2(pr[1][2], pr[1][3], ph[3], pl[3]);
-            const uint32_t va = sm + kOffV + (st * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kDRowStride + (lane >> 4) * 16;
+            const uint32_t va = sm + off_v + (st * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kDRowStride + (lane >> 4) * 16;
 #pragma unroll
             for (int j2 = 0; j2 < 8; j2++) {
                 uint32_t b0, b1, b2, b3; ldsm_x4_t(va + j2 * 32, b0, b1, b2, b3);
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(kDThreads) draft_attn_kernel(const DraftPlan p
     // partial O by 2^(m - M) in registers, and the scaled partials are summed from shared memory (the merge buffer reuses the K/V area)
     if (active && t4 == 0) { s_ml[w][g][0] = m0; s_ml[w][g][1] = l0; s_ml[w][g + 8][0] = m1; s_ml[w][g + 8][1] = l1; }
     __syncthreads();   // the maxima are visible; nobody reads K/V any more
-    float* mo_all = reinterpret_cast<float*>(smem + kOffK);
+    float* mo_all = reinterpret_cast<float*>(smem);   // the query block and the K/V rows are no longer needed
     const int64_t slot0 = (int64_t)(kvh * p.n_splits + split) * kDRows;
     if (active) {
         float M0 = -INFINITY, M1 = -INFINITY;
@@ -371,12 +373,12 @@ int kata_draft_attn(kata_draft_ctx* c, int32_t layer, const float* d_q, float* d
     DevGuard guard(c->cfg.device);
     DraftPlan p{}; p.pos0 = pos0; p.T = T; p.win = c->cfg.window; p.ring_mask = c->cfg.ring - 1;
     p.klo = std::max(0, pos0 + 1 - c->cfg.window); p.khi = pos0 + T;   // row 0 has the earliest window start; every row sees up to the end of the block
-    const int nkeys = p.khi - p.klo, want = std::max(1, std::min(kDMaxSplits, c->sm_count / kDKV));
+    const int nkeys = p.khi - p.klo, want = std::max(1, std::min(kDMaxSplits, c->sm_count / kDKV));   // one CTA per SM (two per SM with 64-key chunks measured slower: 10.9 against 10.0 us, and twice the partials for the combine grid)
     p.chunk = std::min(kDChunk, ((nkeys + want - 1) / want + 15) & ~15);
     p.n_splits = (nkeys + p.chunk - 1) / p.chunk;   // <= kDMaxSplits: create() bounded window + block by kDChunk * kDMaxSplits
     if (p.n_splits > kDMaxSplits) { p.chunk = kDChunk; p.n_splits = (nkeys + kDChunk - 1) / kDChunk; }
     const __half* kr = (const __half*)kata_draft_ring_ptr(c, layer, 0); const __half* vr = (const __half*)kata_draft_ring_ptr(c, layer, 1);
-    cudaError_t e = launch_pdl(draft_attn_kernel, dim3(p.n_splits, kDKV), dim3(kDThreads), (size_t)kDraftSmem, (cudaStream_t)stream, p, d_q, kr, vr, c->part_o, c->part_ml);
+    cudaError_t e = launch_pdl(draft_attn_kernel, dim3(p.n_splits, kDKV), dim3(kDThreads), (size_t)std::max(kMergeBytes, kOffK + 2 * p.chunk * kDRowStride), (cudaStream_t)stream, p, d_q, kr, vr, c->part_o, c->part_ml);
     if (e == cudaSuccess) e = launch_pdl(draft_combine_kernel, dim3(kDH, T), dim3(128), 0, (cudaStream_t)stream, p, (const float*)c->part_o, (const float*)c->part_ml, d_out);
     if (e != cudaSuccess) return dfail(c, KATA_ERR_CUDA, "attn launch: %s", cudaGetErrorString(e));
     c->launches += 2;
