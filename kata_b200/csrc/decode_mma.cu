@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
     if (q) return;
     A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
     const float M = s_M, L = s_L;
-    const int T = p.T, t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
+    const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
     if (part_out) { float* po = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po[d] = A; if (d == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
     else {
         const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
