@@ -276,18 +276,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         // Tensor memory hands a thread one row (32 columns at a time); global memory wants a warp on consecutive columns of one row (a thread per
         // row would touch 32 sectors per instruction). Each warp therefore stages 32 rows x 16 columns in shared memory and writes them back
         // row by row, half a warp per row: 64 contiguous bytes of gate in and of output out.
+        float* tile = s_stage[w];                     // [32 rows][17]
+        const int hw = lane >> 4, col = lane & 15, rbase = 32 * (w & 3);
+        const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + col;
+        float gv[16];   // gate logits of the round in flight, fetched one round (16 rows x 16 columns per half warp) ahead
+        // (volatile asm loads: issued where they are written, whatever the compiler would prefer for register live ranges)
+        auto load_gate = [&](int rd, float (&dst)[16]) {
+#pragma unroll
+            for (int rr = 0; rr < 16; rr++) {
+                const int row = 2 * rr + hw; dst[rr] = 0.0f;
+                if (rbase + row < rows_valid) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(dst[rr]) : "l"(gate + obase + (int64_t)row * kQD + rd * 16));
+            }
+        };
+        load_gate(0, gv);   // in flight while the item's last P.V completes
         if (alive && warp_wait(bar(B_ODONE), (gt - 1u) & 1u, err)) {
             tc5::fence_after_sync();
             const float inv = 1.0f / l;
-            float* tile = s_stage[w];                     // [32 rows][17]
-            const int hw = lane >> 4, col = lane & 15, rbase = 32 * (w & 3);
-            const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + col;
-            float gv[16];   // gate logits of the round in flight, fetched one round (16 rows x 16 columns per half warp) ahead
-            auto load_gate = [&](int rd, float (&dst)[16]) {
-#pragma unroll
-                for (int rr = 0; rr < 16; rr++) { const int row = 2 * rr + hw; dst[rr] = (rbase + row < rows_valid) ? __ldg(gate + obase + (int64_t)row * kQD + rd * 16) : 0.0f; }
-            };
-            load_gate(0, gv);
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
                 uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
@@ -301,13 +305,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
 #pragma unroll
                     for (int i = 0; i < 16; i++) tile[lane * 17 + i] = __uint_as_float(o[half * 16 + i]) * inv;
                     __syncwarp();
+                    // all 16 staged values into registers first, then the sigmoids, then the stores: with one loop a shared-memory load could not move
+                    // above the previous iteration's global store (pointers the compiler cannot tell apart) and the 16 iterations ran as one chain
+                    float tv[16];
+#pragma unroll
+                    for (int rr = 0; rr < 16; rr++) tv[rr] = tile[(2 * rr + hw) * 17 + col];
+#pragma unroll
+                    for (int rr = 0; rr < 16; rr++) tv[rr] *= 1.0f / (1.0f + __expf(-gc[rr]));
 #pragma unroll
                     for (int rr = 0; rr < 16; rr++) {
                         const int row = 2 * rr + hw;
                         if (rbase + row < rows_valid) {
                             const int64_t oi = obase + (int64_t)row * kQD + rd * 16;
-                            const float y = tile[row * 17 + col] * (1.0f / (1.0f + __expf(-gc[rr])));
-                            if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
+                            if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(tv[rr]); else reinterpret_cast<float*>(out)[oi] = tv[rr];
                         }
                     }
                     __syncwarp();
