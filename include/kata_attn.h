@@ -43,7 +43,7 @@ extern "C" {
 enum { KATA_OK = 0, KATA_ERR_ARG = 1, KATA_ERR_RANGE = 2, KATA_ERR_MODE = 3, KATA_ERR_CUDA = 4, KATA_ERR_DEVICE_WAIT = 5, KATA_ERR_NOMEM = 6 };
 enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1, KATA_KV_INT8V = 2 };   /* KATA_KV=fp16|int8|int8v (src/engine.cpp:54-59); int8v: keys fp16, values int8 (src/engine.h:71-73) */
 enum { KATA_ROUND_RINT = 0, KATA_ROUND_HALF_AWAY = 1 };  /* rint (ties to even) is what the reference kernel does (shaders/flash.metal:170) */
-enum { KATA_ACT_F32 = 0, KATA_ACT_BF16 = 1 };            /* dtype of qfull / kproj / vproj / out */
+enum { KATA_ACT_F32 = 0, KATA_ACT_BF16 = 1, KATA_ACT_F16 = 2 };   /* dtype of qfull / kproj / vproj / out (the reference's activations are fp32) */
 
 typedef struct kata_attn_ctx kata_attn_ctx;
 
@@ -122,7 +122,7 @@ int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_
  * KATA_PEER_HANDLE_BYTES bytes), the ranks swap handles by any host channel, and each opens the others'; inside one process
  * kata_attn_peer_open_pointers takes the buffers' device addresses instead. All ranks must issue the same sequence of exchange calls.
  * Waits are bounded (about a second, kata_attn_peer_set_wait_polls): when a peer's rows do not arrive the call's output is left
- * unwritten and kata_attn_peer_check returns KATA_ERR_DEVICE_WAIT. world <= 8, T in {1, 2}. */
+ * unwritten and kata_attn_peer_check returns KATA_ERR_DEVICE_WAIT (then see kata_attn_peer_resync). world <= 8, T in {1, 2}. */
 #define KATA_PEER_HANDLE_BYTES 64
 typedef struct kata_attn_peer kata_attn_peer;
 int kata_attn_peer_create(int32_t device, int32_t rank, int32_t world, kata_attn_peer** out, void* handle_out /* KATA_PEER_HANDLE_BYTES, may be NULL */);
@@ -137,6 +137,11 @@ int kata_attn_peer_exchange_merge(kata_attn_peer* px, const float* d_part, int32
 int kata_attn_peer_decode(kata_attn_peer* px, kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
                           const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 int kata_attn_peer_check(kata_attn_peer* px, void* stream);   /* synchronises the stream; KATA_ERR_DEVICE_WAIT after a wait that ran out */
+/* After KATA_ERR_DEVICE_WAIT the ranks' call counters no longer agree (flags are matched against the call number, and the rank whose peer
+ * skipped or failed a call has counted one call more), so every later exchange would time out as well. Once the ranks have agreed over their
+ * host channel that none of them has an exchange in flight (streams synchronised), each calls this with the same call_number: it
+ * synchronises the device, clears the local flags and the error word and sets the counter. Alternatively destroy and recreate on all ranks. */
+int kata_attn_peer_resync(kata_attn_peer* px, uint32_t call_number);
 const char* kata_attn_peer_last_error(const kata_attn_peer* px);
 int kata_attn_peer_destroy(kata_attn_peer* px);              /* call on every rank only after all ranks have finished their exchanges */
 
@@ -171,8 +176,18 @@ int32_t kata_attn_kv_planes(const kata_attn_ctx* ctx);
 size_t kata_attn_kv_plane_row_bytes(const kata_attn_ctx* ctx, int32_t plane);
 int kata_attn_kv_plane_read(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, void* h_dst);
 int kata_attn_kv_plane_write(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, const void* h_src);
-/* Device address of row 0 of a plane (kvPlanePtr). */
+/* Device address of row 0 of a plane (kvPlanePtr, src/engine.h:79-81; the restore at src/ckpt.cpp:98 writes rows through it).
+ * The attention kernels are launched so that they may request cache rows before the kernel enqueued just before them has completed
+ * (rows that kernel does not write). The library knows what its own kernels write; it cannot know what a caller's kernel writes through
+ * this pointer. So: once a plane pointer has been handed out, no row is requested early any more (a few microseconds per long decode),
+ * until the caller starts declaring its writes with kata_attn_mark_rows_written; from then on only declared rows are held back. */
 void* kata_attn_kv_plane_ptr(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t plane);
+/* No reference counterpart (the reference's restore writes shared memory from the host, between forwards). Declares that device work
+ * the caller has enqueued on the stream since the last library call writes rows at positions >= pos_lo of sequence seq (-1: of every
+ * sequence) through plane pointers: the next library call on that stream reads none of these rows before that work has completed.
+ * Several declarations before the next call add up. A caller that uses plane pointers for writing and calls this even once promises to
+ * declare every such write (before the call that follows it on the stream). */
+int kata_attn_mark_rows_written(kata_attn_ctx* ctx, int32_t seq, int32_t pos_lo);
 
 /* No counterpart in the reference. kata_attn_decode for callers that cannot allocate device memory and therefore have no
  * context: engines that give all device memory to their own pools at start-up (a library cudaMalloc then fails), and
@@ -182,7 +197,8 @@ void* kata_attn_kv_plane_ptr(kata_attn_ctx* ctx, int32_t layer, int32_t seq, int
  * library until the process exits. Same semantics and outputs as kata_attn_decode (fp16 cache). Limits: n <=
  * KATA_STATIC_MAX_BATCH (more: KATA_ERR_RANGE), T in {1,2}, at most 148 CTAs. The first call on a device does that
  * device's set-up and must be made outside stream capture. All calls on a device share the scratch: calls that overlap
- * on the GPU race on it and must be serialised by the caller. A bounded device wait that runs out is not reported here. */
+ * on the GPU race on it and must be serialised by the caller, the first call included (two host threads making a device's first call
+ * at the same time also race on the set-up). A bounded device wait that runs out is not reported here. */
 int kata_attn_decode_static(const void* d_k_rows, const void* d_v_rows, int64_t total_rows, int32_t n, const int64_t* seq_row0, const int32_t* pos_base,
                             int32_t T, int32_t first_pos, const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 

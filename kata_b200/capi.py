@@ -18,16 +18,17 @@ OK = 0
 KV_FP16, KV_INT8, KV_INT8V = 0, 1, 2
 _KV_MODES = {"fp16": KV_FP16, "int8": KV_INT8, "int8v": KV_INT8V}   # the reference's KATA_KV values (src/engine.cpp:54)
 ROUND_RINT, ROUND_HALF_AWAY = 0, 1
-ACT_F32, ACT_BF16 = 0, 1
+ACT_F32, ACT_BF16, ACT_F16 = 0, 1, 2
+_ACT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}   # KATA_ACT_*
 QD, KVD, QFULL, MAX_BATCH = 6144, 1024, 12288, 64
 
 EXPORTS = [
     "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
-    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
     "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode",
-    "kata_attn_peer_check", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
+    "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
     "kata_draft_ring_read", "kata_draft_ring_write", "kata_draft_launch_count",
 ]
@@ -147,7 +148,7 @@ class AttnContext:
         pa, pp = _i32(pos0)
         n = len(sa)
         ref = kproj if kproj is not None else qfull
-        act = ACT_BF16 if ref.dtype == torch.bfloat16 else ACT_F32
+        act = _ACT[ref.dtype]
         dev = ref.device
         if h0 < 24:
             q16 = torch.empty((n, T, QD), dtype=torch.float16, device=dev) if q16 is None else q16
@@ -166,7 +167,7 @@ class AttnContext:
         pa, pp = _i32(pos_base)
         n = len(sa)
         out = torch.empty((n, T, QD), dtype=out_dtype, device=q16.device) if out is None else out
-        self._ck(self.L.kata_attn_decode(self.h, layer, n, sp, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        self._ck(self.L.kata_attn_decode(self.h, layer, n, sp, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     def decode_scalar(self, layer, seq_ids, pos_base, T, q32, gate, first_pos=0, out=None):
@@ -182,7 +183,7 @@ class AttnContext:
         pa, pp = _i32(pos_base)
         n = len(sa)
         out = torch.empty((n, M, QD), dtype=out_dtype, device=q16.device) if out is None else out
-        self._ck(self.L.kata_attn_prefill(self.h, layer, n, sp, pp, M, _dp(q16), _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        self._ck(self.L.kata_attn_prefill(self.h, layer, n, sp, pp, M, _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     def decode_partial(self, layer, seq, pos_base, T, key_lo, key_hi, q16, part=None):
@@ -193,7 +194,7 @@ class AttnContext:
     def merge_parts(self, parts, T, gate, out=None, out_dtype=torch.float32):
         n_parts = parts.shape[0]
         out = torch.empty((T, QD), dtype=out_dtype, device=parts.device) if out is None else out
-        self._ck(self.L.kata_attn_merge_parts(self.h, _dp(parts), n_parts, T, _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        self._ck(self.L.kata_attn_merge_parts(self.h, _dp(parts), n_parts, T, _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     # ---- KV planes (prefix-cache contract) ----
@@ -217,6 +218,18 @@ class AttnContext:
     def plane_ptr(self, layer, seq, plane) -> int:
         return int(self.L.kata_attn_kv_plane_ptr(self.h, layer, seq, plane) or 0)
 
+    def mark_rows_written(self, seq: int, pos_lo: int):
+        self._ck(self.L.kata_attn_mark_rows_written(self.h, seq, pos_lo))
+
+    def plane_tensor(self, layer, seq, plane, nrows) -> torch.Tensor:
+        """A uint8 CUDA tensor [nrows][row bytes] aliasing the plane's rows (through kata_attn_kv_plane_ptr): lets a test write rows with a
+        device-side copy, as a device-resident restore would."""
+        rb = self.plane_row_bytes(plane)
+
+        class _Alias:
+            __cuda_array_interface__ = {"shape": (nrows, rb), "typestr": "|u1", "data": (self.plane_ptr(layer, seq, plane), False), "version": 3, "strides": None}
+        return torch.as_tensor(_Alias(), device=torch.device("cuda", self.device))
+
 
 def decode_static(k_rows, v_rows, seq_row0, pos_base, T, q16, gate, first_pos=0, out=None, out_dtype=torch.float32):
     """kata_attn_decode_static: decode over caller-owned fp16 K/V rows ([rows][1024] tensors) with no context and no
@@ -227,7 +240,7 @@ def decode_static(k_rows, v_rows, seq_row0, pos_base, T, q16, gate, first_pos=0,
     pa, pp = _i32(pos_base)
     out = torch.empty((n, T, QD), dtype=out_dtype, device=q16.device) if out is None else out
     rc = L.kata_attn_decode_static(_dp(k_rows), _dp(v_rows), C.c_int64(k_rows.shape[0]), n, rows0, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out),
-                                   ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream())
+                                   _ACT[out.dtype], _stream())
     return rc, out
 
 
@@ -336,17 +349,20 @@ class PeerExchange:
 
     def exchange_merge(self, part, T, gate, out=None, out_dtype=torch.float32):
         out = torch.empty((T, QD), dtype=out_dtype, device=part.device) if out is None else out
-        self._ck(self.L.kata_attn_peer_exchange_merge(self.h, _dp(part), T, _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        self._ck(self.L.kata_attn_peer_exchange_merge(self.h, _dp(part), T, _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     def decode(self, ctx, layer, seq, pos_base, T, key_lo, key_hi, q16, gate, out=None, out_dtype=torch.float32):
         """This rank's share of a decode whose keys are split across the ranks, exchange and merge included (kata_attn_peer_decode)."""
         out = torch.empty((T, QD), dtype=out_dtype, device=q16.device) if out is None else out
-        self._ck(self.L.kata_attn_peer_decode(self.h, ctx.h, layer, seq, pos_base, T, key_lo, key_hi, _dp(q16), _dp(gate), _dp(out), ACT_BF16 if out.dtype == torch.bfloat16 else ACT_F32, _stream()))
+        self._ck(self.L.kata_attn_peer_decode(self.h, ctx.h, layer, seq, pos_base, T, key_lo, key_hi, _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     def check(self):
         self._ck(self.L.kata_attn_peer_check(self.h, _stream()))
+
+    def resync(self, call_number: int):
+        self._ck(self.L.kata_attn_peer_resync(self.h, C.c_uint32(call_number)))
 
     def close(self):
         if self.h:

@@ -166,13 +166,14 @@ int kata_attn_prep(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* se
     Ctx& c = h->c;
     if (T < 1 || T > KATA_MAX_CHUNK) return fail(c, KATA_ERR_RANGE, "prep of %d tokens (1..%d)", T, KATA_MAX_CHUNK);
     if (h0 < 0 || nh < 1 || h0 + nh > 32) return fail(c, KATA_ERR_ARG, "head slots [%d,%d) outside [0,32)", h0, h0 + nh);
-    if (act_dtype != KATA_ACT_F32 && act_dtype != KATA_ACT_BF16) return fail(c, KATA_ERR_ARG, "unknown activation dtype %d", act_dtype);
+    if (act_dtype != KATA_ACT_F32 && act_dtype != KATA_ACT_BF16 && act_dtype != KATA_ACT_F16) return fail(c, KATA_ERR_ARG, "unknown activation dtype %d", act_dtype);
     const bool hasQ = h0 < 24, hasK = h0 < 28 && h0 + nh > 24, hasV = h0 + nh > 28;
     if ((hasQ && (!d_qfull || !d_qnorm)) || (hasK && (!d_kproj || !d_knorm)) || (hasV && !d_vproj)) return fail(c, KATA_ERR_ARG, "a projection or norm weight needed by head slots [%d,%d) is null", h0, h0 + nh);
-    kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos0, T, b, /*touches_cache=*/h0 + nh > 24)) return rc;
+    kata::Batch b{}; if (int rc = make_batch(c, layer, n, seq_ids, pos0, T, b, /*touches_cache=*/h0 + nh > 24)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_prep(c, b, T, d_qfull, d_kproj, d_vproj, act_dtype, d_qnorm, d_knorm, (__half*)d_q16, d_q32, d_gate, h0, nh, (cudaStream_t)stream);
-    if (e == cudaSuccess) { std::fill(c.append_lo.begin(), c.append_lo.end(), INT32_MAX); for (int i = 0; i < n; i++) c.append_lo[b.seq[i]] = std::min(c.append_lo[b.seq[i]], b.pos[i]); c.prev_append = true; }
+    if (e == cudaSuccess && h0 + nh > 24) { c.wrote_no_rows(); for (int i = 0; i < n; i++) c.wrote_rows_from(b.seq[i], b.pos[i]); }
+    else if (e == cudaSuccess) c.wrote_no_rows();
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "prep launch");
 }
 
@@ -181,10 +182,10 @@ int kata_attn_kv_quant(kata_attn_ctx* h, int32_t layer, int32_t seq, const void*
     Ctx& c = h->c;
     if (!c.v8()) return fail(c, KATA_ERR_MODE, "kv_quant needs an int8 or int8v context (this one is %s)", c.tag.c_str());
     if ((c.k8() && !d_ks) || !d_vs || T < 1 || T > KATA_MAX_CHUNK) return fail(c, KATA_ERR_ARG, "kv_quant of %d rows (1..%d) needs the scratch rows of every int8 plane", T, KATA_MAX_CHUNK);
-    kata::Batch b; if (int rc = make_batch(c, layer, 1, &seq, &pos0, T, b)) return rc;
+    kata::Batch b{}; if (int rc = make_batch(c, layer, 1, &seq, &pos0, T, b)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_kv_quant(c, b.row_base[0] + pos0, (const __half*)d_ks, (const __half*)d_vs, T, (cudaStream_t)stream);
-    if (e == cudaSuccess) { std::fill(c.append_lo.begin(), c.append_lo.end(), INT32_MAX); c.append_lo[seq] = pos0; c.prev_append = true; }
+    if (e == cudaSuccess) { c.wrote_no_rows(); c.wrote_rows_from(seq, pos0); }
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "kv_quant launch");
 }
 
@@ -194,8 +195,8 @@ int kata_attn_decode(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t* 
     Ctx& c = h->c;
     if (T < 1 || T > KATA_MAX_VERIFY) return fail(c, KATA_ERR_RANGE, "decode takes 1..%d query tokens, not %d", KATA_MAX_VERIFY, T);
     if (!d_q16 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "decode needs q16, gate and out");
-    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
-    kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, T, b)) return rc;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
+    kata::Batch b{}; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, T, b)) return rc;
     for (int i = 0; i < n; i++) if (first_pos < 0 || first_pos > pos_base[i]) return fail(c, KATA_ERR_RANGE, "first_pos %d outside [0, pos_base=%d]", first_pos, pos_base[i]);
     DeviceGuard guard(c.cfg.device);
     // The kernel takes the 6 heads of a KV head x 2 tokens as its 16-row block. A wide verify (T up to 8, Engine::verifyWide,
@@ -217,11 +218,11 @@ int kata_attn_decode_scalar(kata_attn_ctx* h, int32_t layer, int32_t n, const in
     if (c.cfg.kv_mode != KATA_KV_FP16) return fail(c, KATA_ERR_MODE, "the scalar path reads an fp16 cache only (the reference disables it for int8, src/engine.cpp:169)");
     if (T < 1 || T > KATA_MAX_VERIFY) return fail(c, KATA_ERR_RANGE, "scalar decode takes 1..%d query tokens, not %d", KATA_MAX_VERIFY, T);
     if (!d_q32 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "scalar decode needs q32, gate and out");
-    kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, T, b)) return rc;
+    kata::Batch b{}; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, T, b)) return rc;
     for (int i = 0; i < n; i++) if (first_pos < 0 || first_pos > pos_base[i]) return fail(c, KATA_ERR_RANGE, "first_pos %d outside [0, pos_base=%d]", first_pos, pos_base[i]);
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_decode_scalar(c, b, T, first_pos, d_q32, d_gate, d_out, (cudaStream_t)stream);
-    c.prev_append = false;
+    c.wrote_no_rows();
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "scalar decode launch");
 }
 
@@ -231,11 +232,11 @@ int kata_attn_prefill(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t*
     Ctx& c = h->c;
     if (M < 1 || M > KATA_MAX_CHUNK) return fail(c, KATA_ERR_RANGE, "prefill chunk of %d rows (1..%d)", M, KATA_MAX_CHUNK);
     if (!d_q16 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "prefill needs q16, gate and out");
-    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
-    kata::Batch b; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, M, b)) return rc;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
+    kata::Batch b{}; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, M, b)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_prefill(c, b, M, (const __half*)d_q16, d_gate, d_out, out_dtype, (cudaStream_t)stream);
-    c.prev_append = false;
+    c.wrote_no_rows();
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "prefill launch");
 }
 
@@ -249,7 +250,7 @@ int kata_attn_decode_partial(kata_attn_ctx* h, int32_t layer, int32_t seq, int32
     const int32_t local_rows = std::max(0, std::min(pos_base + T, key_hi) - key_lo);   // rows [0, local_rows) of this context hold keys key_lo..
     if (layer < 0 || layer >= c.cfg.n_layers || seq < 0 || seq >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "layer %d / sequence %d out of range", layer, seq);
     if (local_rows > c.max_ctx[seq]) return fail(c, KATA_ERR_RANGE, "%d local rows exceed max_ctx %d", local_rows, c.max_ctx[seq]);
-    kata::Batch b; b.n = 1; b.pos[0] = pos_base; b.row_base[0] = c.row_of(layer, seq);
+    kata::Batch b{}; b.n = 1; b.seq[0] = seq; b.pos[0] = pos_base; b.row_base[0] = c.row_of(layer, seq);
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_decode_mma_ex(c, b, T, 0, key_lo, &local_rows, (const __half*)d_q16, nullptr, nullptr, KATA_ACT_F32, d_part, (cudaStream_t)stream);
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "decode_partial launch");
@@ -258,10 +259,10 @@ int kata_attn_decode_partial(kata_attn_ctx* h, int32_t layer, int32_t seq, int32
 int kata_attn_merge_parts(kata_attn_ctx* h, const float* d_parts, int32_t n_parts, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c;
-    if (!d_parts || !d_gate || !d_out || n_parts < 1 || T < 1 || T > 2) return fail(c, KATA_ERR_ARG, "merge_parts: %d parts, T=%d", n_parts, T);
+    if (!d_parts || !d_gate || !d_out || n_parts < 1 || T < 1 || T > 2 || out_dtype < KATA_ACT_F32 || out_dtype > KATA_ACT_F16) return fail(c, KATA_ERR_ARG, "merge_parts: %d parts, T=%d", n_parts, T);
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_merge_parts(c, d_parts, n_parts, T, d_gate, d_out, out_dtype, (cudaStream_t)stream);
-    c.prev_append = false;
+    c.wrote_no_rows();
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "merge_parts launch");
 }
 
@@ -282,7 +283,18 @@ void* kata_attn_kv_plane_ptr(kata_attn_ctx* h, int32_t layer, int32_t seq, int32
     if (!h) return nullptr;
     Ctx& c = h->c; PlaneRef r;
     if (!plane_ref(c, plane, r) || layer < 0 || layer >= c.cfg.n_layers || seq < 0 || seq >= c.cfg.n_seqs) return nullptr;
+    c.ext_ptr = true;   // from now on caller kernels may write cache rows: see kata_attn_mark_rows_written
     return r.base + (size_t)c.row_of(layer, seq) * r.row_bytes;
+}
+int kata_attn_mark_rows_written(kata_attn_ctx* h, int32_t seq, int32_t pos_lo) {
+    if (!h) return KATA_ERR_ARG;
+    Ctx& c = h->c;
+    if (seq < -1 || seq >= c.cfg.n_seqs || pos_lo < 0) return fail(c, KATA_ERR_RANGE, "sequence %d (or -1 for all) / first written position %d", seq, pos_lo);
+    c.ext_declared = true;
+    if (!c.prev_mark) c.wrote_no_rows();   // several marks before the next call add up
+    for (int s = 0; s < c.cfg.n_seqs; s++) if (seq < 0 || s == seq) c.wrote_rows_from(s, pos_lo);
+    c.prev_mark = true;
+    return KATA_OK;
 }
 static int plane_copy(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, void* host, bool to_host) {
     if (!h) return KATA_ERR_ARG;

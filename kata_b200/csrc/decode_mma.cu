@@ -76,7 +76,7 @@ __device__ __forceinline__ int cta_of_tile(const DecPlan& p, int tile) {
 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                                                                 const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
+                                                                 const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_kind,
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<MODE>; constexpr bool K8 = G::K8, V8 = G::V8; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             else {
                 const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d0; const float2 gt = *reinterpret_cast<const float2*>(gate + oi);
                 const float y0 = (A0 / L) * sigmoid_fast(gt.x), y1 = (A1 / L) * sigmoid_fast(gt.y);
-                if (out_bf16) reinterpret_cast<__nv_bfloat162*>(out)[oi >> 1] = __floats2bfloat162_rn(y0, y1); else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oi) = make_float2(y0, y1);
+                store_act2(out, oi, y0, y1, out_kind);
             }
         };
         for (int r = merger ? rsel : rows; r < rows; r += kThreads / 128) {
@@ -304,58 +304,58 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 }
 
 // Merge of the per-CTA partials of every split segment, one CTA per (row, segment). Used instead of the in-kernel ticket merge when a segment
-// has many contributors (batch 1 at long context: ~37 per KV head): a single last-arriver CTA then needs ~15 us to pull 220 KB of partials
-// through one SM, while this grid does it in parallel. Warp 0 forms the row maximum, the weights exp(m - M) and the merged l; then the
-// 1024 threads (4 groups of 256 head dims, group q taking contributors q, q+4, ...) accumulate the weighted O rows with independent loads.
-// Launched with programmatic stream serialisation: the grid is set up while the decode kernel drains and waits for it here.
+// has many contributors (batch 1 at long context: ~37 per KV head; 256 per KV head with the reference's 128-key splits at 32K): a single
+// last-arriver CTA would pull all of them through one SM, while this grid does it in parallel. Warp 0 forms the row maximum and the merged l;
+// then the 1024 threads (4 groups of 256 head dims, group q taking contributors q, q+4, ...) accumulate the weighted O rows with independent
+// loads, each thread forming the weight exp(m - M) of its contributor itself (a broadcast load of m), so that nothing is sized by the
+// contributor count. Launched with programmatic stream serialisation: the grid is set up while the decode kernel drains and waits for it here.
 constexpr int kCombineThreads = 1024;
-__global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, float* __restrict__ part_out,
+__global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, float* __restrict__ part_out,
                                                                          const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml) {
-    __shared__ float s_wt[160]; __shared__ float s_acc[3][256]; __shared__ float s_M, s_L;
+    __shared__ float s_acc[3][256]; __shared__ float s_M, s_L;
     const int r = blockIdx.x, seg = blockIdx.y, b = seg >> 2, kvh = seg & 3, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
     const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvh * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
     pdl_wait();              // the decode kernel's partials are complete and visible from here on
     pdl_launch_dependents();
     if (n_c == 1) return;   // a single contributor wrote the final row itself
+    const float* ml = scratch_ml + (int64_t)(c_first + seg) * 32 + r * 2;   // contributor c: ml[c * 32] = m, ml[c * 32 + 1] = l
     if (tid < 32) {
         float M = -INFINITY;
-        for (int c = tid; c < n_c; c += 32) M = fmaxf(M, __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2));
+        for (int c = tid; c < n_c; c += 32) M = fmaxf(M, __ldcg(ml + c * 32));
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
         float L = 0.0f;
-        for (int c = tid; c < n_c; c += 32) {
-            const float mm = __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2); const float wt = (mm == -INFINITY) ? 0.0f : ex2(mm - M);
-            L += __ldcg(scratch_ml + (int64_t)(c_first + c + seg) * 32 + r * 2 + 1) * wt; s_wt[c] = wt;
-        }
+        for (int c = tid; c < n_c; c += 32) { const float mm = __ldcg(ml + c * 32); L += __ldcg(ml + c * 32 + 1) * ((mm == -INFINITY) ? 0.0f : ex2(mm - M)); }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
         if (tid == 0) { s_M = M; s_L = L; }
     }
     __syncthreads();
+    const float M = s_M, L = s_L;
+    const float* po = scratch_o + (int64_t)(c_first + seg) * (12 * kD) + r * kD + d;
     float A = 0.0f;
 #pragma unroll 8
-    for (int c = q; c < n_c; c += 4) A += __ldcg(scratch_o + (int64_t)(c_first + c + seg) * (12 * kD) + r * kD + d) * s_wt[c];
+    for (int c = q; c < n_c; c += 4) { const float mm = __ldcg(ml + c * 32); A += __ldcg(po + (int64_t)c * (12 * kD)) * ((mm == -INFINITY) ? 0.0f : ex2(mm - M)); }
     if (q) s_acc[q - 1][d] = A;
     __syncthreads();
     if (q) return;
     A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
-    const float M = s_M, L = s_L;
     const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-    if (part_out) { float* po = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po[d] = A; if (d == 0) { po[256] = M * 0.6931471805599453f; po[257] = L; } }
+    if (part_out) { float* po2 = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po2[d] = A; if (d == 0) { po2[256] = M * 0.6931471805599453f; po2[257] = L; } }
     else {
         const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
-        if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
+        store_act(out, oi, y, out_kind);
     }
 }
 
 // Merge of per-rank partials {O[256], m, l} (m in natural-log units) and the output gate: k_attn_dec_combine with "split" = rank.
-__global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restrict__ parts, const int n_parts, const int T, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16) {
+__global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restrict__ parts, const int n_parts, const int T, const float* __restrict__ gate, void* __restrict__ out, const int out_kind) {
     const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x; const int64_t row = (int64_t)t * kH + h, stride = (int64_t)T * kH * kPartStride;
     float M = -INFINITY; for (int r = 0; r < n_parts; r++) M = fmaxf(M, parts[r * stride + row * kPartStride + 256]);
     float L = 0.0f, A = 0.0f;
     for (int r = 0; r < n_parts; r++) { const float* pp = parts + r * stride + row * kPartStride; const float mm = pp[256]; const float wt = (mm == -INFINITY) ? 0.0f : expf(mm - M); L += pp[257] * wt; A += pp[tid] * wt; }
     const int64_t oi = (int64_t)t * kQD + h * kD + tid; const float y = (A / L) * (1.0f / (1.0f + expf(-gate[oi])));
-    if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
+    store_act(out, oi, y, out_kind);
 }
 
 }  // namespace
@@ -396,18 +396,19 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
     // Early loads pay when a CTA streams for long (batch 8 at 16-32K: -2 us of 140); with short ranges (batch 1: 55 tiles per CTA) they take
     // bandwidth from the previous kernel's last CTAs, which everybody then waits for (+2 us of 31): switched off there.
-    if (p.q_tiles < 128) for (int i = 0; i < b.n; i++) p.safe_row[i] = 0;
+    // Nor are rows loaded early while caller kernels may be writing any of them through a plane pointer without having said which.
+    if (p.q_tiles < 128 || (c.ext_ptr && !c.ext_declared)) for (int i = 0; i < b.n; i++) p.safe_row[i] = 0;
     p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
-#define KATA_DEC(M) launch_pdl(decode_mma_kernel<M>, dim3(n_ctas), dim3(kThreads), Geo<M>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype == KATA_ACT_BF16, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
+#define KATA_DEC(M) launch_pdl(decode_mma_kernel<M>, dim3(n_ctas), dim3(kThreads), Geo<M>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
     static_assert(Geo<KATA_KV_INT8>::kTile == 32 && Geo<KATA_KV_INT8V>::kTile == 16 && Geo<KATA_KV_FP16>::kTile == 16, "the tile views of the context are built for these tile heights");
     const cudaError_t le = mode == KATA_KV_INT8 ? KATA_DEC(KATA_KV_INT8) : mode == KATA_KV_INT8V ? KATA_DEC(KATA_KV_INT8V) : KATA_DEC(KATA_KV_FP16);
 #undef KATA_DEC
-    c.prev_append = false;   // this kernel writes no cache rows
+    c.wrote_no_rows();   // this kernel writes no cache rows
     if (le != cudaSuccess) return le;
     c.launches++;
     if (!p.merge_in_kernel) {
-        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, 4 * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)(out_dtype == KATA_ACT_BF16), part_out, (const float*)c.part_o, (const float*)c.part_ml);
+        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, 4 * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)out_dtype, part_out, (const float*)c.part_o, (const float*)c.part_ml);
         if (e != cudaSuccess) return e;
         c.launches++;
     }
@@ -419,7 +420,7 @@ cudaError_t launch_decode_mma(Ctx& c, const Batch& b, int T, int first_pos, int,
 }
 
 cudaError_t launch_merge_parts(Ctx& c, const float* parts, int n_parts, int T, const float* gate, void* out, int out_dtype, cudaStream_t s) {
-    merge_parts_kernel<<<dim3(kH, T), 256, 0, s>>>(parts, n_parts, T, gate, out, out_dtype == KATA_ACT_BF16);
+    merge_parts_kernel<<<dim3(kH, T), 256, 0, s>>>(parts, n_parts, T, gate, out, out_dtype);
     c.launches++;
     return cudaGetLastError();
 }
@@ -466,7 +467,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
                                        int32_t T, int32_t first_pos, const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
     using namespace kata;
     if (!d_k_rows || !d_v_rows || !seq_row0 || !pos_base || !d_q16 || !d_gate || !d_out) return KATA_ERR_ARG;
-    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16) return KATA_ERR_ARG;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return KATA_ERR_ARG;
     if (n < 1 || n > kStaticMaxBatch || T < 1 || T > 2 || total_rows < 1 || total_rows > 0x7fffffffLL) return KATA_ERR_RANGE;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KATA_ERR_CUDA;
@@ -493,8 +494,8 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     if (!make_tile_tmap(&tm_k, const_cast<void*>(d_k_rows), 2, total_rows, 16, 4) || !make_tile_tmap(&tm_v, const_cast<void*>(d_v_rows), 2, total_rows, 16, 4)) return KATA_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
     if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
-    decode_mma_kernel<KATA_KV_FP16><<<n_ctas, kThreads, Geo<KATA_KV_FP16>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype == KATA_ACT_BF16, nullptr, nullptr, nullptr,
+    decode_mma_kernel<KATA_KV_FP16><<<n_ctas, kThreads, Geo<KATA_KV_FP16>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype, nullptr, nullptr, nullptr,
                                                                          sd.scratch->part_o, sd.scratch->part_ml, sd.scratch->counters, &sd.scratch->err);
-    if (!p.merge_in_kernel) decode_combine_kernel<<<dim3(6 * T, 4 * n), kCombineThreads, 0, s>>>(p, d_gate, d_out, (int)(out_dtype == KATA_ACT_BF16), nullptr, sd.scratch->part_o, sd.scratch->part_ml);
+    if (!p.merge_in_kernel) decode_combine_kernel<<<dim3(6 * T, 4 * n), kCombineThreads, 0, s>>>(p, d_gate, d_out, (int)out_dtype, nullptr, sd.scratch->part_o, sd.scratch->part_ml);
     return cudaGetLastError() == cudaSuccess ? KATA_OK : KATA_ERR_CUDA;
 }

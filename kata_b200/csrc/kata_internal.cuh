@@ -1,6 +1,8 @@
 // Internal declarations shared by the translation units of libkata_attn: the context object, the per-call batch
 // descriptor handed to kernels by value, and the launcher prototypes.
 #pragma once
+#include <algorithm>
+#include <climits>
 #include <utility>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -46,6 +48,12 @@ struct Ctx {
     // What the kernel launched last through this context wrote into the cache: nothing (prev_append false), or rows from position append_lo[s]
     // on in sequence s. The decode kernel may load rows that kernel cannot be writing before it waits for it (dependent launch).
     bool prev_append = false; std::vector<int32_t> append_lo;
+    // Caller kernels may write cache rows through kata_attn_kv_plane_ptr. Once such a pointer has been handed out (ext_ptr) and until the caller
+    // has started to declare its writes with kata_attn_mark_rows_written (ext_declared), no row is loaded before the wait. A mark stands for
+    // "the kernel enqueued just before the next library call writes rows from this position on" (prev_mark: the record comes from marks).
+    bool ext_ptr = false, ext_declared = false, prev_mark = false;
+    void wrote_no_rows() { if (prev_append) std::fill(append_lo.begin(), append_lo.end(), INT32_MAX); prev_append = false; prev_mark = false; }
+    void wrote_rows_from(int seq, int pos) { append_lo[seq] = std::min(append_lo[seq], pos); prev_append = true; }
     // scalar-path scratch (k_attn_split partials)
     float* sc_pm = nullptr; float* sc_pl = nullptr; float* sc_pacc = nullptr;
     // TMA descriptors over the K and V arenas viewed as [row][kv head][256]: 16-row x 128-byte boxes, 128-byte swizzle
@@ -81,6 +89,17 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+// Output rows in the activation dtype the caller asked for (kind = KATA_ACT_*): fp32, bf16 or fp16, rounded to nearest even.
+__device__ __forceinline__ void store_act(void* out, int64_t i, float y, int kind) {
+    if (kind == KATA_ACT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(y);
+    else if (kind == KATA_ACT_F16) reinterpret_cast<__half*>(out)[i] = __float2half_rn(y);
+    else reinterpret_cast<float*>(out)[i] = y;
+}
+__device__ __forceinline__ void store_act2(void* out, int64_t i, float y0, float y1, int kind) {   // elements i, i+1; i even
+    if (kind == KATA_ACT_BF16) reinterpret_cast<__nv_bfloat162*>(out)[i >> 1] = __floats2bfloat162_rn(y0, y1);
+    else if (kind == KATA_ACT_F16) reinterpret_cast<__half2*>(out)[i >> 1] = __floats2half2_rn(y0, y1);
+    else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + i) = make_float2(y0, y1);
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }                  // every earlier kernel of the stream is complete and visible
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }   // the next kernel may be set up from now on

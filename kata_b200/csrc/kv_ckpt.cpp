@@ -80,8 +80,10 @@ int kata_ckpt_probe(const char* path, const int32_t* tokens, uint32_t n_tokens, 
 }
 
 // Writes a checkpoint file holding the header, the tokens and the KV (and MTP-KV) segments of the first n positions of
-// sequence `seq`; the GDN, conv, hidden-state and logits segments are holes of the right size. Written to path.tmp and
-// renamed, as the reference's writer does (src/ckpt.cpp:132-138).
+// sequence `seq`; the GDN, conv, hidden-state and logits segments are holes of the right size. The file is written as
+// path.tmp and left there: with its valid header, hashes and size the reference's restore (src/ckpt.cpp:91-101) would accept
+// it and load all-zero recurrent state and logits, so it must not appear under its final name before the engine has filled
+// its own segments. kata_ckpt_publish then renames it, as the reference's writer does (src/ckpt.cpp:132-138).
 int kata_ckpt_write_kv(kata_attn_ctx* trunk, kata_attn_ctx* mtp, int32_t seq, const char* path, const int32_t* tokens, uint32_t n, uint64_t model_fp, uint32_t n_attn,
                        uint64_t gdn_bytes, uint64_t conv_bytes, int32_t last_tok) {
     if (!trunk || !path || !tokens || n == 0) return KATA_ERR_ARG;
@@ -97,9 +99,16 @@ int kata_ckpt_write_kv(kata_attn_ctx* trunk, kata_attn_ctx* mtp, int32_t seq, co
         for (int pl = 0; ok && pl < kata_attn_kv_planes(trunk); pl++) { const uint64_t rb = kata_attn_kv_plane_row_bytes(trunk, pl); buf.resize((size_t)n * rb);
             ok = kata_attn_kv_plane_read(trunk, (int32_t)a, seq, pl, 0, (int32_t)n, buf.data()) == KATA_OK && wr(fd, buf.data(), buf.size(), o[3] + (uint64_t)n * ((uint64_t)a * kvRow + pre)); pre += rb; } }
     for (int v = 0; ok && mtp && v < 2; v++) { buf.resize((size_t)n * kMtpRow); ok = kata_attn_kv_plane_read(mtp, 0, seq, v, 0, (int32_t)n, buf.data()) == KATA_OK && wr(fd, buf.data(), buf.size(), o[4] + (uint64_t)v * n * kMtpRow); }
+    ok = ok && fsync(fd) == 0;
     close(fd);
-    if (!ok || rename(tmp.c_str(), path) != 0) { unlink(tmp.c_str()); return KATA_ERR_CUDA; }
+    if (!ok) { unlink(tmp.c_str()); return KATA_ERR_CUDA; }
     return KATA_OK;
+}
+
+int kata_ckpt_publish(const char* path) {
+    if (!path) return KATA_ERR_ARG;
+    const std::string tmp = std::string(path) + ".tmp";
+    return rename(tmp.c_str(), path) == 0 ? KATA_OK : KATA_ERR_ARG;
 }
 
 // Restores the KV (and MTP-KV) segments of a checkpoint into sequence `seq` after the checks of kata_ckpt_probe. On any

@@ -13,7 +13,8 @@
 // start overwriting parity s & 1 in call s + 2) before every peer has raised its flags of call s + 1, which a peer does only after
 // its merge of call s has read parity s & 1.
 // Every wait is bounded (about a second); a wait that runs out sets the exchange's error word, the row's output is left unwritten,
-// and kata_attn_peer_check reports KATA_ERR_DEVICE_WAIT; the context stays usable.
+// and kata_attn_peer_check reports KATA_ERR_DEVICE_WAIT; the GPU and the attention context stay usable. The exchange itself is then out
+// of step (the ranks' call numbers differ): kata_attn_peer_resync on every rank, or a fresh exchange, puts it right.
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -37,7 +38,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t
 
 // grid (24 heads, T) x 256 threads
 __global__ void __launch_bounds__(256) peer_push_merge_kernel(const PeerBases pb, const int rank, const int world, const uint32_t seq, const uint32_t max_polls,
-                                                              const float* __restrict__ part, const int T, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err) {
+                                                              const float* __restrict__ part, const int T, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, int32_t* err) {
     __shared__ int s_ok;
     const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, row = t * kH + h, parity = (int)(seq & 1u);
     pdl_wait(); pdl_launch_dependents();   // the local part comes from the decode kernel launched just before
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(256) peer_push_merge_kernel(const PeerBases pb
         L += __ldcg(pp + 257) * wt; A += __ldcg(pp + tid) * wt;
     }
     const int64_t oi = (int64_t)t * kQD + h * kD + tid; const float y = (A / L) * (1.0f / (1.0f + expf(-gate[oi])));
-    if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[oi] = y;
+    store_act(out, oi, y, out_kind);
 }
 
 }  // namespace
@@ -158,11 +159,11 @@ int kata_attn_peer_set_wait_polls(kata_attn_peer* p, uint32_t polls) { if (!p ||
 int kata_attn_peer_exchange_merge(kata_attn_peer* p, const float* d_part, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
     if (!p) return KATA_ERR_ARG;
     if (!p->opened) return pfail(p, KATA_ERR_MODE, "the peers' buffers have not been opened");
-    if (!d_part || !d_gate || !d_out || T < 1 || T > 2 || (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16)) return pfail(p, KATA_ERR_ARG, "exchange_merge: part, gate, out, T in {1, 2}");
+    if (!d_part || !d_gate || !d_out || T < 1 || T > 2 || (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16)) return pfail(p, KATA_ERR_ARG, "exchange_merge: part, gate, out, T in {1, 2}");
     PeerGuard guard(p->device);
     const uint32_t seq = ++p->seq;
     const cudaError_t e = launch_pdl(peer_push_merge_kernel, dim3(kH, T), dim3(256), 0, (cudaStream_t)stream, p->bases, p->rank, p->world, seq, p->max_polls, d_part, (int)T, d_gate, d_out,
-                                     (int)(out_dtype == KATA_ACT_BF16), p->d_err);
+                                     (int)out_dtype, p->d_err);
     if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "exchange launch", e);
     p->launches++;
     return KATA_OK;
@@ -181,6 +182,19 @@ int kata_attn_peer_check(kata_attn_peer* p, void* stream) {
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream); if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "synchronize", e);
     int32_t flag = 0; e = cudaMemcpy(&flag, p->d_err, 4, cudaMemcpyDeviceToHost); if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "read error word", e);
     if (flag) { cudaMemset(p->d_err, 0, 4); char b[128]; snprintf(b, sizeof b, "the wait for rank %d's rows ran out; that call's output is invalid", flag - 30); return pfail(p, KATA_ERR_DEVICE_WAIT, b); }
+    return KATA_OK;
+}
+
+int kata_attn_peer_resync(kata_attn_peer* p, uint32_t call_number) {
+    if (!p) return KATA_ERR_ARG;
+    PeerGuard guard(p->device);
+    cudaError_t e = cudaDeviceSynchronize(); if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "synchronize", e);
+    const size_t flag_bytes = (size_t)2 * p->world * kPeerRows * 4;
+    e = cudaMemset(reinterpret_cast<uint8_t*>(p->local) + peer_flag_off(p->world, 0, 0, 0) * 4, 0, flag_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->d_err, 0, 4);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "resync", e);
+    p->seq = call_number;
     return KATA_OK;
 }
 

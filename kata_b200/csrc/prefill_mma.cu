@@ -25,7 +25,7 @@ template <bool K8, bool V8> struct PfGeo {   // K8 / V8: the K / V plane holds i
 };
 
 template <bool K8, bool V8>
-__global__ void __launch_bounds__(kPfThreads, 2) prefill_mma_kernel(const Batch b, const int M, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16,
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_mma_kernel(const Batch b, const int M, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_kind,
                                                                     const uint8_t* __restrict__ k_arena, const uint8_t* __restrict__ v_arena, const __half* __restrict__ ksc, const __half* __restrict__ vsc) {
     using G = PfGeo<K8, V8>;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -91,13 +91,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_mma_kernel(const Batch 
             if (!V8) {
                 const int d = dim_of<false>(j, 0, t4); const float2 gt = *reinterpret_cast<const float2*>(gate + base + d);
                 const float y0 = st.o[j][2 * half] * inv * sigmoid_fast(gt.x), y1 = st.o[j][2 * half + 1] * inv * sigmoid_fast(gt.y);
-                if (out_bf16) *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(out) + base + d) = __floats2bfloat162_rn(y0, y1);
-                else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + base + d) = make_float2(y0, y1);
+                store_act2(out, base + d, y0, y1, out_kind);
             } else {
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
                     const int d = dim_of<true>(j, c, t4); const float y = st.o[j][2 * half + c] * inv * sigmoid_fast(gate[base + d]);
-                    if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[base + d] = __float2bfloat16_rn(y); else reinterpret_cast<float*>(out)[base + d] = y;
+                    store_act(out, base + d, y, out_kind);
                 }
             }
         }
@@ -114,7 +113,7 @@ cudaError_t configure_prefill_mma(int kv_mode) {   // per device, once per conte
 
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
     const dim3 grid((M + kBM - 1) / kBM, kH, b.n);
-#define KATA_PFM(K8, V8) prefill_mma_kernel<K8, V8><<<grid, kPfThreads, PfGeo<K8, V8>::kSmem, s>>>(b, M, q16, gate, out, out_dtype == KATA_ACT_BF16, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc)
+#define KATA_PFM(K8, V8) prefill_mma_kernel<K8, V8><<<grid, kPfThreads, PfGeo<K8, V8>::kSmem, s>>>(b, M, q16, gate, out, out_dtype, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.ksc, c.vsc)
     if (c.cfg.kv_mode == KATA_KV_INT8) KATA_PFM(true, true); else if (c.cfg.kv_mode == KATA_KV_INT8V) KATA_PFM(false, true); else KATA_PFM(false, false);
 #undef KATA_PFM
     c.launches++;

@@ -62,7 +62,7 @@ struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh
 // P~ = half(p * vsc[key]), l from p. int8v (k_flash_prefill_k16v8, shaders/flash.metal:198-250): K tiles straight from the fp16 plane, V staged and scaled.
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                                                                   const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_bf16, int32_t* err,
+                                                                   const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, int32_t* err,
                                                                    const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc) {
     constexpr bool KS = MODE == KATA_KV_INT8, SCALED = MODE != KATA_KV_FP16;   // KS: scores take the key scale; SCALED: P takes the value scale
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                         const int row = 2 * rr + hw;
                         if (rbase + row < rows_valid) {
                             const int64_t oi = obase + (int64_t)row * kQD + rd * 16;
-                            if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[oi] = __float2bfloat16_rn(tv[rr]); else reinterpret_cast<float*>(out)[oi] = tv[rr];
+                            store_act(out, oi, tv[rr], out_kind);
                         }
                     }
                     __syncwarp();
@@ -394,11 +394,11 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     cudaLaunchAttribute at[2]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
-#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)(out_dtype == KATA_ACT_BF16), c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc)
+#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)out_dtype, c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc)
     const cudaError_t le = mode == KATA_KV_INT8 ? KATA_PF(KATA_KV_INT8, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8V ? KATA_PF(KATA_KV_INT8V, c.tm_k64h, c.tm_v128h_stage) : KATA_PF(KATA_KV_FP16, c.tm_k64h, c.tm_v128h);
 #undef KATA_PF
     if (le != cudaSuccess) return le;
-    c.prev_append = false;
+    c.wrote_no_rows();
     c.launches++;
     return cudaGetLastError();
 }

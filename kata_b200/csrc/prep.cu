@@ -21,6 +21,7 @@ namespace {
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return __ldg(p); }
 template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <> __device__ __forceinline__ float ldf<__half>(const __half* p) { return __half2float(*p); }
 
 // One warp per (head slot, token) row. Lane j holds dims j, 32+j, ..., 224+j, so the sum of squares is formed exactly as
 // the reference's threadgroup does it (an xor butterfly inside each group of 32 consecutive dims, then the 8 group sums
@@ -199,7 +200,8 @@ cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const 
     cudaError_t le = cudaSuccess;
 #define KATA_PREP(TIN, K8, V8) le = launch_pdl(prep_kernel<TIN, K8, V8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round)
     if (act_dtype == KATA_ACT_F32) { if (mode == KATA_KV_INT8) KATA_PREP(float, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(float, false, true); else KATA_PREP(float, false, false); }
-    else { if (mode == KATA_KV_INT8) KATA_PREP(__nv_bfloat16, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__nv_bfloat16, false, true); else KATA_PREP(__nv_bfloat16, false, false); }
+    else if (act_dtype == KATA_ACT_BF16) { if (mode == KATA_KV_INT8) KATA_PREP(__nv_bfloat16, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__nv_bfloat16, false, true); else KATA_PREP(__nv_bfloat16, false, false); }
+    else { if (mode == KATA_KV_INT8) KATA_PREP(__half, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__half, false, true); else KATA_PREP(__half, false, false); }
 #undef KATA_PREP
     if (le != cudaSuccess) return le;
     c.launches++;

@@ -8,13 +8,19 @@
 // K/V rows rounded to fp16 when cached; Q * 1/16 rounded to fp16 on the matrix paths; P rounded to fp16 before P.V).
 // Each function cites the reference lines it follows (paths relative to the reference project root).
 //
-// Pinning status: the reference stores NO golden vectors for this path and its kernels are Metal shaders that cannot
-// be compiled or run outside macOS, so bitwise parity of this oracle with the reference is UNPINNED ("parity
-// unpinned"). What pins it instead: (1) the reference's only operator-level check, tools/probe_flash.cpp:25-35, is
-// restated here (kor_formula_f64) and the restated kernels agree with it on that probe's own procedure (seed
-// mt19937(5), posBase 300, M 70, NaN poison) within the error the reference reports (6.6e-5); (2) the reference's
-// cross-path equalities (scalar split == matrix split == flash prefill, T=2 verify == two T=1 decodes) hold between
-// the restated kernels; (3) the int8 quantiser is cross-checked bit-for-bit against an independent numpy restatement.
+// Pinning status. The reference stores NO golden vectors for this path and its kernels are Metal shaders that cannot be
+// compiled or run outside macOS. The only CPU arithmetic the reference holds for this path is its own check,
+// tools/probe_flash.cpp:29-34 (fp64 softmax(q.k) v sigmoid(g)) with its input recipe (:16-19, mt19937(5), N(0,1)) and NaN
+// poison (:26). Those lines ARE compiled here, lifted by line range into oracle/_ref/probe_ref.cpp by `make ref`
+// (probe_ref_shim.h supplies host buffers in place of MTL::Buffer), and tests/test_probe_ref_cpu.py requires:
+//   (1) kor_formula_f64 below == the reference's fp64 values bit for bit on the reference's own inputs;
+//   (2) the restated matrix kernel (kor_flash_prefill) and the fp32 formula within 2e-4 / 2e-5 of them as judged by the
+//       reference's own loop (the reference reports 6.6e-5 for its Metal kernel on this procedure).
+// So the FORMULA level of this oracle is pinned to reference code compiled here. What stays UNPINNED ("parity unpinned"
+// for these): the accumulation order inside the MSL kernels (restated from source, never executed here), and the prep /
+// quantiser kernels, for which the reference has no CPU code; the quantiser is cross-checked bit for bit against an
+// independent numpy restatement, and the reference's cross-path equalities (scalar split == matrix split == flash
+// prefill, T=2 verify == two T=1 decodes) hold between the restated kernels.
 //
 // Third-party arithmetic not in the reference tree: Apple MetalPerformancePrimitives matmul2d (Apple SDK
 // "MacOSX27.0", closed source) performs Q.K^T and P.V at shaders/flash.metal:44,58,116,130. Its accumulation order

@@ -2,7 +2,9 @@
 
 TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline / reference arm
 of ``bench.py``. The ``kata_b200`` package never imports it. Parity status of the oracle itself is described in the
-header of ``kata_oracle.cpp`` ("parity unpinned": the reference stores no golden vectors for this path).
+header of ``kata_oracle.cpp``: the fp64 formula is pinned bit for bit to the reference's own check compiled here
+(``oracle/_ref``, ``probe_ref.py``); the restated shader kernels' accumulation order and the prep/quantiser kernels remain
+"parity unpinned" (the reference stores no golden vectors and its kernels are Metal).
 """
 from __future__ import annotations
 

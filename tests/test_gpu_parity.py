@@ -502,28 +502,33 @@ def test_full_size_decode_32k_properties(capi, orc):
     L = 32768
     gen = torch.Generator(device="cuda"); gen.manual_seed(5)
     kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
-    ctxs = [capi.AttnContext(1, [L + 8], dec_chunk=c) for c in (0, 2048)]
+    # split sizes: from the SM count (0), 2048 keys, and the reference's own 128 keys (src/engine.cpp:120: 256 splits per KV head here) and 256
+    ctxs = [capi.AttnContext(1, [L + 8], dec_chunk=c) for c in (0, 2048, 128, 256)]
     for st in range(0, L, 1024):
         kp = torch.randn(1, 1024, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 1024, 1024, generator=gen, device="cuda")
         for c in ctxs:
             c.prep(0, [0], [st], 1024, None, kp, vp, None, kn, h0=24, nh=8)
     qf = torch.randn(1, 2, 12288, generator=gen, device="cuda"); kp = torch.randn(1, 2, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 2, 1024, generator=gen, device="cuda")
-    outs = []
+    outs, outs1 = [], []
     for c in ctxs:
         q16, q32, g = c.prep(0, [0], [L - 2], 2, qf, kp, vp, qn, kn, want_q32=True)
         outs.append(c.decode(0, [0], [L - 2], 2, q16, g))
+        outs1.append(c.decode(0, [0], [L - 1], 1, q16[:, 1:].contiguous(), g[:, 1:].contiguous()))
         c.check()
     c = ctxs[0]
     sc = c.decode_scalar(0, [0], [L - 2], 2, q32, g)
     d0 = c.decode(0, [0], [L - 2], 1, q16[:, :1].contiguous(), g[:, :1].contiguous()); d1 = c.decode(0, [0], [L - 1], 1, q16[:, 1:].contiguous(), g[:, 1:].contiguous())
     c.check()
     a = outs[0].cpu().numpy()[0]
-    assert np.abs(a - outs[1].cpu().numpy()[0]).max() < 2e-5                       # split invariance
+    for o, o1 in zip(outs[1:], outs1[1:]):                                          # split invariance, T = 2 and T = 1
+        assert np.abs(a - o.cpu().numpy()[0]).max() < 2e-5 and np.abs(a[1] - o1.cpu().numpy()[0, 0]).max() < 2e-5
     assert np.abs(a[0] - d0.cpu().numpy()[0, 0]).max() < 2e-5 and np.abs(a[1] - d1.cpu().numpy()[0, 0]).max() < 2e-5
     _close(a, sc.cpu().numpy()[0])                                                  # matrix path vs scalar path
     planes = orc.KvPlanes(L)
     planes.k[:] = c.plane_read(0, 0, 0, 0, L).view(np.uint16).reshape(L, 1024); planes.v[:] = c.plane_read(0, 0, 1, 0, L).view(np.uint16).reshape(L, 1024)
-    _close(a, orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2))
+    ref = orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2)
+    for o in outs:
+        _close(o.cpu().numpy()[0], ref)
 
 
 @pytest.mark.parametrize("mode", ["int8", "int8v"])
@@ -533,17 +538,18 @@ def test_full_size_quantised_decode_32k_properties(capi, orc, mode):
     L = 32768
     gen = torch.Generator(device="cuda"); gen.manual_seed(8)
     kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
-    ctxs = [capi.AttnContext(1, [L + 8], kv_mode=mode, dec_chunk=c) for c in (0, 2048)]
+    ctxs = [capi.AttnContext(1, [L + 8], kv_mode=mode, dec_chunk=c) for c in (0, 2048, 128, 256)]   # 128: the reference's split size (src/engine.cpp:120)
     c16 = capi.AttnContext(1, [L + 8])
     for st in range(0, L, 1024):
         kp = torch.randn(1, 1024, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 1024, 1024, generator=gen, device="cuda")
         for c in ctxs + [c16]:
             c.prep(0, [0], [st], 1024, None, kp, vp, None, kn, h0=24, nh=8)
     qf = torch.randn(1, 2, 12288, generator=gen, device="cuda"); kp = torch.randn(1, 2, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 2, 1024, generator=gen, device="cuda")
-    outs = []
+    outs, outs1 = [], []
     for c in ctxs:
         q16, q32, g = c.prep(0, [0], [L - 2], 2, qf, kp, vp, qn, kn, want_q32=True)
         outs.append(c.decode(0, [0], [L - 2], 2, q16, g))
+        outs1.append(c.decode(0, [0], [L - 1], 1, q16[:, 1:].contiguous(), g[:, 1:].contiguous()))
         c.check()
     c16.prep(0, [0], [L - 2], 2, qf, kp, vp, qn, kn); c16.check()
     c = ctxs[0]
@@ -552,14 +558,17 @@ def test_full_size_quantised_decode_32k_properties(capi, orc, mode):
     a = outs[0].cpu().numpy()[0]
     # looser than the fp16 cache's 2e-5: the int8 fragments enter the MMAs as code + 1152 and the bias comes out of the fp32 accumulators
     # afterwards, so accumulation-order noise is that of sums some hundred times larger than the result
-    assert np.abs(a - outs[1].cpu().numpy()[0]).max() < 1e-4                       # split invariance
+    for o, o1 in zip(outs[1:], outs1[1:]):                                          # split invariance, T = 2 and T = 1
+        assert np.abs(a - o.cpu().numpy()[0]).max() < 1e-4 and np.abs(a[1] - o1.cpu().numpy()[0, 0]).max() < 1e-4
     assert np.abs(a[0] - d0.cpu().numpy()[0, 0]).max() < 1e-4 and np.abs(a[1] - d1.cpu().numpy()[0, 0]).max() < 1e-4
     planes = orc.KvPlanes(L, int8=(mode == "int8"), int8v=(mode == "int8v"))
     planes.k[:] = c.plane_read(0, 0, 0, 0, L).view(planes.k.dtype).reshape(L, 1024); planes.v[:] = c.plane_read(0, 0, 1, 0, L).view(np.int8).reshape(L, 1024)
     if mode == "int8":
         planes.ksc[:] = c.plane_read(0, 0, 2, 0, L).view(np.uint16).reshape(L, 4)
     planes.vsc[:] = c.plane_read(0, 0, c.kv_planes() - 1, 0, L).view(np.uint16).reshape(L, 4)
-    _close(a, orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2))
+    ref_f = orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, L - 2)
+    for o in outs:
+        _close(o.cpu().numpy()[0], ref_f)
     # quantise-on-append == the reference quantiser over the rows the fp16 path caches (bit for bit, all 32K rows)
     ref = orc.KvPlanes(L, int8=True)
     orc.kv_quant(np.ascontiguousarray(c16.plane_read(0, 0, 0, 0, L).view(np.uint16).reshape(L, 1024)), np.ascontiguousarray(c16.plane_read(0, 0, 1, 0, L).view(np.uint16).reshape(L, 1024)), ref, 0, 0)
@@ -675,3 +684,90 @@ def test_append_and_decode_replay_in_a_cuda_graph(capi, orc):
         torch.cuda.synchronize()
         assert torch.equal(out, eager)
     ctx.check()
+
+
+def test_partial_decode_right_after_append_on_another_sequence(capi, orc):
+    # The split-KV step of a rank: append the new row, then at once the partial decode of the same sequence (not sequence 0), with ranges
+    # long enough (one CTA per 4096 keys) for the kernel to request tiles before it has waited for the append. The merged part must
+    # contain the newest key: equal to the plain decode of the same rows, and to the fp32 formula.
+    lens = [40, 9000]
+    ctx = capi.AttnContext(1, [64, 9100], dec_chunk=4096)
+    gen = torch.Generator(device="cuda"); gen.manual_seed(23)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    for s, l in enumerate(lens):
+        for st in range(0, l, 1024):
+            m = min(1024, l - st)
+            ctx.prep(0, [s], [st], m, None, torch.randn(1, m, 1024, generator=gen, device="cuda"), torch.randn(1, m, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    pos = lens[1]
+    for T in (1, 2):
+        qf = torch.randn(1, T, 12288, generator=gen, device="cuda"); kp = 3.0 * torch.randn(1, T, 1024, generator=gen, device="cuda"); vp = 3.0 * torch.randn(1, T, 1024, generator=gen, device="cuda")
+        torch.cuda.synchronize()
+        q16, q32, g = ctx.prep(0, [1], [pos], T, qf, kp, vp, qn, kn, want_q32=True)
+        part = ctx.decode_partial(0, 1, pos, T, 0, 1 << 30, q16)
+        got = ctx.merge_parts(part[None], T, g[0]).cpu().numpy()
+        ctx.check()
+        want = ctx.decode(0, [1], [pos], T, q16, g).cpu().numpy()[0]
+        assert np.abs(got - want).max() < 1e-5
+        planes = orc.KvPlanes(pos + T)
+        planes.k[:] = ctx.plane_read(0, 1, 0, 0, pos + T).view(np.uint16).reshape(-1, 1024); planes.v[:] = ctx.plane_read(0, 1, 1, 0, pos + T).view(np.uint16).reshape(-1, 1024)
+        _close(got, orc.formula_f32(q32.cpu().numpy()[0], g.cpu().numpy()[0], planes, pos))
+        pos += T
+
+
+@pytest.mark.parametrize("declare", [False, True], ids=["undeclared", "declared"])
+def test_decode_right_after_rows_written_through_the_plane_pointer(capi, orc, declare):
+    # A device-side restore (the counterpart of the reference's plane-wise restore, src/ckpt.cpp:98): a caller's copy kernel writes every
+    # row of a sequence through kata_attn_kv_plane_ptr and the decode follows on the same stream without a synchronisation. Without a
+    # declaration the library stops requesting rows early; with kata_attn_mark_rows_written it holds back the declared rows. Either way
+    # the result must equal that of the context the rows came from.
+    lens = [24001, 23057, 24576, 20000]
+    gen = torch.Generator(device="cuda"); gen.manual_seed(29)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    src = capi.AttnContext(1, [l + 16 for l in lens]); dst = capi.AttnContext(1, [l + 16 for l in lens])
+    for s, l in enumerate(lens):
+        for st in range(0, l, 1024):
+            m = min(1024, l - st)
+            src.prep(0, [s], [st], m, None, torch.randn(1, m, 1024, generator=gen, device="cuda"), torch.randn(1, m, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    seqs = [0, 1, 2, 3]; pos = [l - 1 for l in lens]
+    qf = torch.randn(4, 1, 12288, generator=gen, device="cuda")
+    q16, _, g = src.prep(0, seqs, pos, 1, qf, None, None, qn, None, h0=0, nh=24)
+    want = src.decode(0, seqs, pos, 1, q16, g)
+    src.check()
+    views = [(src.plane_tensor(0, s, pl, lens[s]), dst.plane_tensor(0, s, pl, lens[s])) for s in seqs for pl in (0, 1)]
+    for rep in range(3):
+        dst.reset()
+        torch.cuda.synchronize()
+        for a, b in views:
+            b.copy_(a)                      # the caller's kernels: 375 MB of rows, still in flight when the decode is enqueued
+        if declare:
+            dst.mark_rows_written(-1, 0)
+        got = dst.decode(0, seqs, pos, 1, q16, g)
+        dst.check()
+        assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("path", ["prefill-tcgen05", "prefill-mma", "decode-T2"])
+def test_references_own_check_judges_the_cuda_kernels(capi, path):
+    # The reference's CPU check compiled from its own lines (tools/probe_flash.cpp:16-19, 26-34; oracle/_ref): its generator makes K, V, Q
+    # and the gate, the cache beyond the 370 valid keys is NaN, and its fp64 loop judges what the CUDA kernel wrote for the 70 rows at
+    # position 300. The reference reports 6.6e-5 for its own Metal kernel on this procedure.
+    from oracle import probe_ref
+    if probe_ref.build() is None:
+        pytest.skip("no prebuilt oracle/_ref/libprobe_ref.so on this machine")
+
+    def kernel(q16, k, v, g, pb, m):
+        rows = 512                                                   # 370 valid rows, NaN rows behind them
+        ctx = capi.AttnContext(1, [rows], legacy_prefill=(path == "prefill-mma"))
+        ctx.plane_write(0, 0, 0, 0, k[:rows]); ctx.plane_write(0, 0, 1, 0, v[:rows])
+        dq = _dev(q16[:m]).view(torch.float16).reshape(1, m, 6144); dg = _dev(g[:m]).reshape(1, m, 6144)
+        if path.startswith("prefill"):
+            out = ctx.prefill(0, [0], [pb], m, dq, dg)
+        else:
+            out = torch.cat([ctx.decode(0, [0], [pb + t], 2, dq[:, t:t + 2].contiguous(), dg[:, t:t + 2].contiguous()) for t in range(0, m, 2)], dim=1)
+        ctx.check()
+        res = out.cpu().numpy()[0]
+        ctx.close()
+        return res
+
+    res = probe_ref.run(kernel)
+    assert res.non_finite == 0 and res.worst < 2e-4, res.worst

@@ -62,6 +62,19 @@ def test_wait_that_runs_out_is_a_status_not_a_hang(capi):
     a.check()                                                  # the error word was cleared; the GPU still answers
     ctx = capi.AttnContext(1, [64])
     ctx.reset(); ctx.check()
+    # The two exchanges are now out of step (a has counted one call, b none): without a resynchronisation every later exchange would time
+    # out. After kata_attn_peer_resync with the same call number on both, b's rows reach a. (One GPU runs the two kernels one after the
+    # other, so b, which goes first, cannot see a's rows and gives up after its short limit, as expected; a, second, finds b's rows.)
+    a.resync(10); b.resync(10)
+    b.set_wait_polls(2000)
+    p2, gate2 = _parts(4, 2, 1)
+    b.exchange_merge(torch.from_numpy(p2[1]).cuda(), 1, torch.from_numpy(gate2).cuda())
+    out_a = a.exchange_merge(torch.from_numpy(p2[0]).cuda(), 1, torch.from_numpy(gate2).cuda())
+    a.check()
+    with pytest.raises(capi.KataError):
+        b.check()
+    want = multi.merge_parts_numpy(p2, gate2.reshape(24, 256)).reshape(1, 6144)
+    assert np.abs(out_a.cpu().numpy() - want).max() < 1e-5
     a.close(); b.close()
 
 

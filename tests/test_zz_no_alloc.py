@@ -50,6 +50,29 @@ def test_decode_static_matches_context_decode_twice():
         assert torch.isfinite(got).all() and d.max().item() < 2e-3 and d.mean().item() < 2e-4, (d.max().item(), d.mean().item())
         assert d.max().item() < 1e-5   # same kernel, same work split: the two paths should agree far inside the tolerance
 
+    # Eight sequences of 2-3K keys: every (sequence, KV head) segment is cut between a few CTAs, so the merge runs inside the decode kernel
+    # on the tickets kept in the static array; the second call finds the tickets the first one left (re-armed by the kernel, cleared on
+    # the stream before each launch).
+    lens8 = [2100 + 113 * i for i in range(8)]
+    ctx8 = capi.AttnContext(1, [3072] * 8)
+    for s, L in enumerate(lens8):
+        for start in range(0, L, 1024):
+            m = min(1024, L - start)
+            ctx8.prep(0, [s], [start], m, None, torch.randn(1, m, 1024, generator=gen, device="cuda"), torch.randn(1, m, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+    k8 = torch.cat([torch.from_numpy(ctx8.plane_read(0, s, 0, 0, 3072).view(np.float16).reshape(3072, 1024).copy()) for s in range(8)]).cuda().contiguous()
+    v8 = torch.cat([torch.from_numpy(ctx8.plane_read(0, s, 1, 0, 3072).view(np.float16).reshape(3072, 1024).copy()) for s in range(8)]).cuda().contiguous()
+    for rep in range(2):
+        pos8 = [L - 1 - rep for L in lens8]
+        qfull = torch.randn(8, 1, 12288, generator=gen, device="cuda")
+        q16 = (qfull.view(8, 1, 24, 512)[..., :256].reshape(8, 1, 6144) * 0.0625).to(torch.float16).contiguous()
+        gate = qfull.view(8, 1, 24, 512)[..., 256:].reshape(8, 1, 6144).contiguous()
+        want = ctx8.decode(0, list(range(8)), pos8, 1, q16, gate)
+        ctx8.check()
+        rc, got = capi.decode_static(k8, v8, [3072 * s for s in range(8)], pos8, 1, q16, gate)
+        torch.cuda.synchronize()
+        assert rc == capi.OK and torch.isfinite(got).all() and (got - want).abs().max().item() < 1e-5
+    ctx8.close()
+
     # sizes beyond the stated maximum are rejected with a range error before anything is launched
     n = 9
     rc, _ = capi.decode_static(k_rows, v_rows, [0] * n, [0] * n, 1, torch.zeros(n, 1, 6144, dtype=torch.float16, device="cuda"), torch.zeros(n, 1, 6144, device="cuda"))
