@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the gated-GQA attention path.
 
-    python bench.py --gpus N --steps K --warmup W [--workload decode_b8|decode_b1|decode_b64|decode_int8_b8|pp512|chunked_b1]
+    python bench.py --gpus N --steps K --warmup W [--workload decode_b8|decode_b1|decode_b64|decode_int8_b8|pp512|chunked_b1|...] [--extras all|none|a,b,...]
     python bench.py --impl reference ...      # the reference's scalar CPU math (oracle port) on the host cores
 
 Default workload (the one the headline metric is quoted on): decode at 32K context across all 16 attention layers, fp16
@@ -12,6 +12,12 @@ the whole cached context (split-KV decode with the merge and the output gate fus
 
 Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, barrier and synchronize on both
 sides, max over ranks. The KV working set per step (GBs) is far larger than L2, so no explicit flush is needed.
+
+The printed line is that of the default workload. Its "extras" object carries the other configurations of the benchmark
+statement, each measured in the same process right after it with fewer steps (pp512, decode at batch 1 and 64, int8 KV at
+8K and 32K, chunked prefill at batch 1 and 16; with several ranks: one sequence split by keys across the ranks), each with
+value, ms_per_step, clocks, e2e, roofline and a cpu_baseline of its own; "sustained" repeats the default step for two
+seconds and gives the rate with the clock the GPU settles at.
 """
 from __future__ import annotations
 
@@ -41,6 +47,8 @@ WORKLOADS = {
     "decode_b64": ("decode", 64, "fp16", 32768, 16384),
     "decode_int8_b8": ("decode", 8, "int8", 32768, 16384),
     "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
+    "decode_int8_8k_b1": ("decode", 1, "int8", 8192, 8192),      # benchmark config 4 at its short context
+    "decode_int8_8k_b32": ("decode", 32, "int8", 8192, 8192),
     "decode_int8v_b8": ("decode", 8, "int8v", 32768, 16384),    # keys fp16, values int8 (the reference's KATA_KV=int8v)
     "splitkv_b1": ("splitkv", 1, "fp16", 32768, 32768),       # one 32K sequence, keys split across the ranks, parts pushed to the peers and merged per layer
     "splitkv_b1_128k": ("splitkv", 1, "fp16", 131072, 131072),  # the same at 131,072 keys, where one GPU's HBM time dominates the exchange
@@ -54,6 +62,12 @@ WORKLOADS = {
     "draft_attn": ("draft", 8, "fp16", 2048, 4096),           # the block drafter's attention: 5 layers, block of 8 rows, window 2048 over a 4096 ring, 4 drafters in rotation (168 MB of rings read per step)
     "out_fwht": ("fwht", 32768, "fp32", 6144, 6144),          # the sign + Walsh-Hadamard transform that follows attention, on 32,768 output rows (805 MB in, 805 MB out)
 }
+
+
+EXTRAS_ONE_GPU = ["pp512", "decode_b1", "decode_b64", "decode_int8_b8", "decode_int8_b32", "decode_int8_8k_b1", "decode_int8_8k_b32", "chunked_b1", "chunked_b16"]
+EXTRAS_MULTI_GPU = ["splitkv_b1", "splitkv_b1_128k"]      # strong scaling: one sequence, keys split across the ranks
+EXTRAS_BUDGET_S = 400.0                                    # extras not started after this many seconds of the run are skipped (and say so)
+METRIC = "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak"
 
 
 def peaks():
@@ -126,15 +140,22 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------- the CUDA arm
-def run_decode(args, rank, world, kind_cfg):
+def decode_workload_name(kv_mode, lmax, lmin, B):
+    return f"decode, {N_LAYERS} layers, {kv_mode} KV, ctx {lmax}, batch {B}/GPU (lengths uniform [{lmin},{lmax}]), 1 new token/step, append+attend per layer"
+
+
+def run_decode(args, rank, world, kind_cfg, steps=None, warmup=None, sustained_s=0.0, want_cpu=True):
     import torch
     import torch.distributed as dist
     from kata_b200 import capi, synth
 
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
     _, B, kv_mode, lmax, lmin = kind_cfg
     dev = torch.device("cuda", torch.cuda.current_device())
-    steps_total = args.warmup + args.steps + 2
-    lens = synth.seq_lengths(1234 + rank, B, lmin, lmax).astype(np.int64)
+    steps_total = warmup + steps + 2
+    # Weak scaling: every rank holds B sequences with the SAME length draw, so the work per GPU is fixed as N grows (the contents differ per rank).
+    lens = synth.seq_lengths(1234, B, lmin, lmax).astype(np.int64)
     lens = np.minimum(lens, lmax)
     ctx = capi.AttnContext(N_LAYERS, [int(l) + 2 * steps_total + 8 for l in lens], kv_mode=kv_mode)
     gen = torch.Generator(device=dev); gen.manual_seed(4321 + rank)
@@ -176,9 +197,9 @@ def run_decode(args, rank, world, kind_cfg):
         torch.cuda.synchronize()
 
     sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step(pos); pos = pos + 1
-        torch.cuda.current_stream().synchronize()   # as in serving, where every step ends with the host holding its result; also lets the decode range sizing settle
+        torch.cuda.current_stream().synchronize()   # as in serving, where every step ends with the host holding its result
     ctx.check()
     l0 = ctx.launches()
     barrier()
@@ -187,7 +208,7 @@ def run_decode(args, rank, world, kind_cfg):
     torch.cuda.profiler.start()   # lets `ncu --profile-from-start off` capture exactly the timed steps; a no-op otherwise
     e0.record()
     pos_timed0 = pos.copy()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step(pos); pos = pos + 1
     e1.record()
     barrier()
@@ -199,6 +220,24 @@ def run_decode(args, rank, world, kind_cfg):
     ctx.check()
     assert torch.isfinite(out).all()
 
+    # the same step repeated for sustained_s seconds at a fixed position (the appended row is rewritten in place): where the clock settles
+    sustained = None
+    if sustained_s > 0:
+        pos_s = (pos - 1).tolist()
+        s2 = ClockSampler(torch.cuda.current_device()); s2.start()
+        barrier()
+        n_s, ts0 = 0, time.perf_counter()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        while time.perf_counter() - ts0 < sustained_s:
+            for _ in range(16):
+                step(pos_s)
+            n_s += 16
+            torch.cuda.current_stream().synchronize()
+        g1.record(); torch.cuda.synchronize(); ts1 = time.perf_counter()
+        ms_s = g0.elapsed_time(g1)
+        sustained = {"seconds": ms_s * 1e-3, "steps": n_s, "value": B * n_s / (ms_s * 1e-3), "unit": "tok/s (this rank)", "ms_per_step": ms_s / n_s, "clocks": s2.stop(ts0, ts1)}
+
     # the dominant kernel alone: the decode launches of the same steps, timed on the same stream
     pos_k = pos_timed0.tolist()
     for layer in L_:
@@ -206,7 +245,7 @@ def run_decode(args, rank, world, kind_cfg):
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
-    reps = max(2, args.steps)
+    reps = max(2, steps)
     for _ in range(reps):
         for layer in L_:
             ctx.decode(layer, seqs, pos_k, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
@@ -232,60 +271,91 @@ def run_decode(args, rank, world, kind_cfg):
     step_e2e(pos_e)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step_e2e(pos_e); pos_e = pos_e + 1
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     h2d = N_LAYERS * B * (12288 + 2048) * 4
     d2h = N_LAYERS * B * 6144 * 4
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
     row_bytes = {"fp16": 4096, "int8": 2064, "int8v": 3080}[kv_mode]   # K+V bytes per key per layer (int8: codes + both fp16 scales; int8v: fp16 keys, value codes + their scales)
-    mean_len = float(np.mean([pos_timed0 + i + 1 for i in range(args.steps)]))   # keys attended per sequence per step (the new key included)
     bytes_per_launch = float(np.sum(pos_timed0 + 1)) * row_bytes
+    per_rank = None
+    if world > 1:
+        mine = torch.tensor([ms / steps, e2e_ms / steps, kern_ms * 1e3, float(np.sum(pos_timed0 + 1))], device=dev, dtype=torch.float64)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        allr = torch.stack(allr).cpu().numpy()
+        per_rank = {"ms_per_step": [round(float(x), 4) for x in allr[:, 0]], "e2e_ms_per_step": [round(float(x), 4) for x in allr[:, 1]],
+                    "decode_us_per_launch": [round(float(x), 2) for x in allr[:, 2]], "keys_per_launch": [int(x) for x in allr[:, 3]],
+                    "kv_gb_per_s_sum_over_ranks": float(np.sum(allr[:, 3] * row_bytes * N_LAYERS / (allr[:, 0] * 1e-3)) / 1e9)}
+        ms, e2e_ms = float(allr[:, 0].max()) * steps, float(allr[:, 1].max()) * steps
+    mean_len = float(np.mean([pos_timed0 + i + 1 for i in range(steps)]))   # keys attended per sequence per step (the new key included)
     pk = peaks()
     ach = bytes_per_launch / (kern_ms * 1e-3) / 1e9
     res = {
-        "metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * B * args.steps / (ms * 1e-3), "unit": "tok/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "metric": METRIC, "value": world * B * steps / (ms * 1e-3), "unit": "tok/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16" if kv_mode == "fp16" else "int8", "data": "synthetic",
-        "config": {"workload": f"decode, {N_LAYERS} layers, {kv_mode} KV, ctx 32768, batch {B}/GPU (lengths uniform [{lmin},{lmax}]), 1 new token/step, append+attend per layer",
-                   "batch_per_gpu": B, "global_batch": world * B, "mean_context": mean_len, "parallelism": f"batch-sharded x{world}", "l2": "inputs larger than L2 (no flush needed)"},
+        "config": {"workload": decode_workload_name(kv_mode, lmax, lmin, B),
+                   "batch_per_gpu": B, "global_batch": world * B, "mean_context": mean_len, "parallelism": f"batch-sharded x{world}",
+                   "lengths": "the same length draw on every rank (per-GPU work fixed as N grows); cache contents differ per rank",
+                   "l2": "inputs larger than L2 (no flush needed)" if bytes_per_launch * N_LAYERS > 2.5e8 else "all 16 layers' caches together are not much larger than L2: part of the reads may be L2 hits"},
         "clocks": clocks, "gpu_launches": int(launches),
-        "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_src": pk["src"],
+        "e2e": {"value": world * B * steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" + (" (+ decode_combine_kernel: segments cut between more than 8 CTAs)" if B == 1 and lmax > 8192 else ""), "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"], "peak_src": pk["src"],
                      "frac_of_nominal_8TBs": ach / 8000.0, "us_per_launch": kern_ms * 1e3, "algorithmic_bytes_per_launch": bytes_per_launch,
-                     "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO, "traffic_note": "dram read+write bytes per launch, scaled from the ncu capture of the decode_small workload (138.1 MB for 134.3 MB algorithmic)"},
+                     "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO if kv_mode == "fp16" else None,
+                     "traffic_note": "not measured in this run: algorithmic bytes x 1.028, a constant taken from the ncu capture of the decode_small workload (138.1 MB of dram read+write for 134.3 MB algorithmic, profiles/decode_mma_kernel__decode_small.md)"},
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        res["cpu_baseline"] = cpu_baseline_decode(ctx, lens, pos_timed0, B, kv_mode)
+    if per_rank:
+        res["config"]["per_rank"] = per_rank
+    if sustained:
+        res["sustained"] = sustained
+    if rank == 0 and want_cpu and not args.no_cpu_baseline:
+        res["cpu_baseline"] = cpu_baseline_decode(ctx, pos_timed0, B, kv_mode)
     ctx.close()
+    del qfull, kproj, vproj, q16, gate, out, dq, dk, dv
+    torch.cuda.empty_cache()
     return res
 
 
-def cpu_baseline_decode(ctx, lens, pos, B, kv_mode):
-    """The oracle's scalar decode (the reference's k_attn_decode math) on the host cores, on a bounded sample: layer 0 of
-    the same caches (copied back from the GPU), all sequences at full length; tok/s extrapolated to 16 layers."""
+def cpu_baseline_decode(ctx, pos, B, kv_mode):
+    """The oracle on the host cores, on a bounded sample: layer 0 of the same caches (copied back from the GPU) for up to 8 sequences at
+    full length; tok/s extrapolated to 16 layers. fp16 cache: the reference's scalar decode (k_attn_decode restated). int8 caches: the
+    oracle's fp32 evaluation of the formula on the dequantised planes (the reference has no scalar decode over int8 planes)."""
     from oracle import kata_oracle as orc
-    if kv_mode != "fp16":
-        return {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": "not run for int8 (the scalar CPU decode reads an fp16 cache)"}
-    nb = min(B, 8)
-    ks = [ctx.plane_read(0, s, 0, 0, int(pos[s]) + 1).view(np.uint16) for s in range(nb)]
-    vs = [ctx.plane_read(0, s, 1, 0, int(pos[s]) + 1).view(np.uint16) for s in range(nb)]
+    nb = min(B, 8 if kv_mode == "fp16" else 4)
     rng = np.random.default_rng(1)
     q = rng.standard_normal((nb, 6144)).astype(np.float32); g = rng.standard_normal((nb, 6144)).astype(np.float32)
     cores = orc.hw_threads()
-    t0 = time.perf_counter()
-    orc.decode_batch(q, g, ks, vs, [int(p) for p in pos[:nb]], threads=cores)
-    dt = time.perf_counter() - t0
+    if kv_mode == "fp16":
+        ks = [ctx.plane_read(0, s, 0, 0, int(pos[s]) + 1).view(np.uint16) for s in range(nb)]
+        vs = [ctx.plane_read(0, s, 1, 0, int(pos[s]) + 1).view(np.uint16) for s in range(nb)]
+        t0 = time.perf_counter()
+        orc.decode_batch(q, g, ks, vs, [int(p) for p in pos[:nb]], threads=cores)
+        dt = time.perf_counter() - t0
+        what = "k_attn_decode restated"
+    else:
+        planes = []
+        for s in range(nb):
+            n = int(pos[s]) + 1
+            pl = orc.KvPlanes(n, int8=(kv_mode == "int8"), int8v=(kv_mode == "int8v"))
+            pl.k[:] = ctx.plane_read(0, s, 0, 0, n).view(pl.k.dtype).reshape(n, 1024); pl.v[:] = ctx.plane_read(0, s, 1, 0, n).view(np.int8).reshape(n, 1024)
+            if kv_mode == "int8":
+                pl.ksc[:] = ctx.plane_read(0, s, 2, 0, n).view(np.uint16).reshape(n, 4)
+            pl.vsc[:] = ctx.plane_read(0, s, ctx.kv_planes() - 1, 0, n).view(np.uint16).reshape(n, 4)
+            planes.append(pl)
+        t0 = time.perf_counter()
+        for s in range(nb):
+            orc.formula_f32(q[s:s + 1], g[s:s + 1], planes[s], int(pos[s]), threads=cores)
+        dt = time.perf_counter() - t0
+        what = "fp32 formula over the dequantised planes"
     return {"value": nb / (dt * N_LAYERS), "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"1 of {N_LAYERS} layers, {nb} sequences at full length ({dt:.2f} s), tok/s extrapolated x{N_LAYERS} layers"}
+            "sample": f"{what}: 1 of {N_LAYERS} layers, {nb} sequences at full length ({dt:.2f} s), tok/s extrapolated x{N_LAYERS} layers"}
 
 
-def run_splitkv(args, rank, world, kind_cfg):
+def run_splitkv(args, rank, world, kind_cfg, steps=None, warmup=None):
     """Batch 1, context split by keys across the ranks: every rank holds keys [lo, hi) of all 16 layers and computes its (O, m, l) part per
     layer; the ranks push their parts into each other's exchange buffers over NVLink and merge in the same kernel (kata_attn_peer_*). The
     NCCL all-gather + merge per layer, and one batched all-gather for the 16 layers, are timed beside it. Strong scaling: total work fixed."""
@@ -293,9 +363,11 @@ def run_splitkv(args, rank, world, kind_cfg):
     import torch.distributed as dist
     from kata_b200 import capi, multi
 
+    steps = steps if steps is None else steps
+    warmup = warmup if warmup is None else warmup
     _, _, kv_mode, L, _ = kind_cfg
     dev = torch.device("cuda", torch.cuda.current_device())
-    steps_total = 3 * (args.warmup + args.steps) + 2   # three timed runs (peer exchange, NCCL per layer, one batched all-gather) at successive positions
+    steps_total = 3 * (warmup + steps) + 2   # three timed runs (peer exchange, NCCL per layer, one batched all-gather) at successive positions
     lo, hi = multi.split_keys(L, world)[rank]
     tail = rank == world - 1
     ctx = capi.AttnContext(N_LAYERS, [max(hi - lo, 1) + steps_total + 8], kv_mode=kv_mode)
@@ -345,12 +417,12 @@ def run_splitkv(args, rank, world, kind_cfg):
         torch.cuda.synchronize()
 
     def timed(batched, pos):
-        for i in range(args.warmup):
+        for i in range(warmup):
             step(pos, batched); pos += 1
         ctx.check(); barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter(); e0.record()
-        for i in range(args.steps):
+        for i in range(steps):
             step(pos, batched); pos += 1
         e1.record(); barrier(); t1 = time.perf_counter()
         return e0.elapsed_time(e1), t0, t1
@@ -358,23 +430,24 @@ def run_splitkv(args, rank, world, kind_cfg):
     sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
     l0 = ctx.launches()
     ms, tw0, tw1 = timed("peer", L)
-    launches = (ctx.launches() - l0) * args.steps // (args.steps + args.warmup) + N_LAYERS * args.steps
+    launches = (ctx.launches() - l0) * steps // (steps + warmup) + N_LAYERS * steps
     clocks = sampler.stop(tw0, tw1)
     px.check(); ref_out = out.clone()
-    ms_n, _, _ = timed(False, L + args.warmup + args.steps)
-    ms_b, _, _ = timed(True, L + 2 * (args.warmup + args.steps))
+    ms_n, _, _ = timed(False, L + warmup + steps)
+    ms_b, _, _ = timed(True, L + 2 * (warmup + steps))
     ctx.check(); assert torch.isfinite(out).all() and torch.isfinite(ref_out).all()
     if world > 1:
         t = torch.tensor([ms, ms_n, ms_b], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, ms_n, ms_b = t.tolist()
     pk = peaks(); bytes_step = N_LAYERS * (L + 1) * 4096.0
-    ach = bytes_step / (ms / args.steps * 1e-3) / 1e9
-    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-           "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+    ach = bytes_step / (ms / steps * 1e-3) / 1e9
+    res = {"metric": METRIC, "value": steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+           "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
            "config": {"workload": f"decode, {N_LAYERS} layers, fp16 KV, ctx {L}, batch 1, keys split over {world} rank(s), parts pushed into the peers' buffers and merged in one kernel per layer", "global_batch": 1,
-                      "parallelism": f"split-KV x{world}", "tok_s_with_nccl_all_gather_and_merge_per_layer": args.steps / (ms_n * 1e-3),
-                      "tok_s_with_one_batched_all_gather_for_16_layers": args.steps / (ms_b * 1e-3), "l2": "inputs larger than L2"},
+                      "parallelism": f"split-KV x{world}", "tok_s_with_nccl_all_gather_and_merge_per_layer": steps / (ms_n * 1e-3),
+                      "tok_s_with_one_batched_all_gather_for_16_layers": steps / (ms_b * 1e-3), "l2": "inputs larger than L2"},
            "clocks": clocks, "gpu_launches": int(launches), "e2e": {"value": None, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "not measured for this workload"},
-           "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": ach, "peak": pk["hbm_gbs"] * world, "unit": "GB/s", "frac": ach / (pk["hbm_gbs"] * world), "peak_src": pk["src"], "traffic": None}}
+           "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": ach, "peak": pk["hbm_gbs"] * world, "unit": "GB/s", "frac": ach / (pk["hbm_gbs"] * world), "peak_src": pk["src"],
+                        "note": "fraction of N x the single-GPU copy rate: whole-step time (append, partial decode, exchange and merge per layer) against the bytes of the whole sequence", "us_per_launch": ms / steps / N_LAYERS * 1e3, "traffic": None}}
     if world > 1:
         dist.barrier()
     px.close(); ctx.close()
@@ -385,19 +458,20 @@ def run_splitkv(args, rank, world, kind_cfg):
 def run_reference(args, kind_cfg):
     """The reference's own CPU implementation of the path: its scalar attention math (k_attn_decode restated in the
     oracle; the reference's kernels are Metal and cannot run here) on all host threads. Each step is a bounded sample:
-    one of the 16 layers for the whole batch at full context; tok/s is extrapolated to 16 layers."""
+    one of the 16 layers for the whole batch at full context. ms_per_step is the time a step (one layer) really took;
+    value is tok/s for the 16 layers of the workload, i.e. that time x16 (labelled in cpu_baseline.sample)."""
     from oracle import kata_oracle as orc
     from kata_b200 import synth
-    if kind_cfg[0] in ("draft", "fwht"):   # the reference arm times the headline decode path
+    if kind_cfg[0] != "decode" or kind_cfg[2] != "fp16":   # the reference arm times the headline decode path
         kind_cfg = WORKLOADS["decode_b8"]
     _, B, kv_mode, lmax, lmin = kind_cfg
-    B_global = B * max(1, args.gpus)   # the same global batch as the CUDA arm at this GPU count (weak scaling)
-    B = min(B_global, 8)               # bounded sample: at most 8 sequences per step; CPU tok/s does not depend on the batch size
-    lens = synth.seq_lengths(1234, B, lmin, lmax)
+    world = max(1, args.gpus)
+    B_s = min(B, 8)                    # bounded sample: at most 8 sequences per step; CPU tok/s does not depend on the batch size
+    lens = synth.seq_lengths(1234, B, lmin, lmax)[:B_s]
     rng = np.random.default_rng(99)
     ks = [rng.standard_normal((int(l) + 1, 1024), dtype=np.float32).astype(np.float16).view(np.uint16) for l in lens]
     vs = [rng.standard_normal((int(l) + 1, 1024), dtype=np.float32).astype(np.float16).view(np.uint16) for l in lens]
-    q = rng.standard_normal((B, 6144)).astype(np.float32); g = rng.standard_normal((B, 6144)).astype(np.float32)
+    q = rng.standard_normal((B_s, 6144)).astype(np.float32); g = rng.standard_normal((B_s, 6144)).astype(np.float32)
     cores = orc.hw_threads()
     pos = [int(l) for l in lens]
     for _ in range(min(args.warmup, 1)):
@@ -406,11 +480,13 @@ def run_reference(args, kind_cfg):
     for _ in range(args.steps):
         orc.decode_batch(q, g, ks, vs, pos, threads=cores)
     dt = (time.perf_counter() - t0) / args.steps
-    val = B / (dt * N_LAYERS)
-    return {"impl": "reference", "metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt * N_LAYERS * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-            "config": {"workload": f"decode, {N_LAYERS} layers, fp16 KV, ctx 32768, global batch {B_global} (lengths uniform [{lmin},{lmax}]), scalar CPU attention", "global_batch": B_global},
-            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": f"each step = 1 of {N_LAYERS} layers for {B} sequences at full context; x{N_LAYERS} layers extrapolated (CPU tok/s is independent of the batch size)"},
+    val = B_s / (dt * N_LAYERS)
+    return {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": decode_workload_name(kv_mode, lmax, lmin, B), "batch_per_gpu": B, "global_batch": world * B,
+                       "note": "host cores only: a CPU's tok/s does not grow with the GPU count, so the sample below stands for every N"},
+            "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
+                             "sample": f"each timed step = 1 of the {N_LAYERS} layers for {B_s} sequences at full context (ms_per_step is that one layer); value = sequences / (ms_per_step x {N_LAYERS} layers)"},
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
@@ -444,7 +520,7 @@ def run_fwht(args, rank, world, cfg):
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, e2e_ms = t.tolist()
     pk = peaks(); nbytes = rows * width * 8.0; ach = nbytes / (ms / args.steps * 1e-3) / 1e9
-    return {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * rows * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+    return {"metric": METRIC, "value": world * rows * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"attention output transform (sign, 1024-point Walsh-Hadamard per block, 1/32) over {rows} rows of {width} floats per GPU", "l2": "inputs larger than L2 (no flush needed)"},
             "clocks": clocks, "gpu_launches": int(args.steps),
@@ -525,7 +601,7 @@ def run_draft(args, rank, world, cfg):
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms, e2e_ms = t.tolist()
     pk = peaks(); nbytes = float(win + T - 1) * 4096.0; ach = nbytes / (kern_ms * 1e-3) / 1e9
-    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * n_ctx * T * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+    res = {"metric": METRIC, "value": world * n_ctx * T * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
            "config": {"workload": f"block drafter attention: {n_ctx} drafters/GPU x {n_layers} layers, block of {T} rows, window {win} over a ring of {ring}; norm + RoPE + ring append, then attention, per layer",
                       "l2": f"{n_ctx} drafters in rotation: {n_ctx * n_layers * (win + T - 1) * 4096 / 1e6:.0f} MB of ring rows read per step (larger than L2)"},
@@ -548,22 +624,51 @@ def run_draft(args, rank, world, cfg):
     return res
 
 
+def compact(res):
+    """The keys of a workload's result that go into the default line's "extras"."""
+    keep = {k: res[k] for k in ("value", "unit", "ms_per_step", "steps", "warmup", "clocks", "e2e", "gpu_launches", "dtype", "scaling") if k in res}
+    keep["workload"] = res["config"]["workload"]
+    for k in ("l2", "kernel", "tok_s_with_nccl_all_gather_and_merge_per_layer", "tok_s_with_one_batched_all_gather_for_16_layers", "tok_s_one_gpu_same_harness"):
+        if k in res["config"]:
+            keep[k] = res["config"][k]
+    r = res.get("roofline", {})
+    keep["roofline"] = {k: r[k] for k in ("bound", "kernel", "achieved", "peak", "unit", "frac", "us_per_launch", "peak_src", "note") if k in r}
+    if "cpu_baseline" in res:
+        keep["cpu_baseline"] = res["cpu_baseline"]
+    return keep
+
+
+def run_workload(name, args, rank, world, steps=None, warmup=None, sustained_s=0.0):
+    cfg = WORKLOADS[name]
+    if cfg[0] == "decode":
+        return run_decode(args, rank, world, cfg, steps=steps, warmup=warmup, sustained_s=sustained_s)
+    if cfg[0] == "splitkv":
+        return run_splitkv(args, rank, world, cfg, steps=steps, warmup=warmup)
+    if cfg[0] == "fwht":
+        return run_fwht(args, rank, world, cfg)
+    if cfg[0] == "draft":
+        return run_draft(args, rank, world, cfg)
+    import bench_prefill
+    return bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler, steps=steps, warmup=warmup)
+
+
 def main():
+    t_start = time.perf_counter()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="kata_b200", choices=["kata_b200", "reference"])
     ap.add_argument("--workload", default="decode_b8", choices=sorted(WORKLOADS))
+    ap.add_argument("--extras", default=None, help="all | none | comma-separated workload names; default: all for the default workload, none otherwise")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "kata_b200" else args.warmup
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg = WORKLOADS[args.workload]
 
     if args.impl == "reference":
         if rank == 0:
-            print(json.dumps(run_reference(args, cfg)), flush=True)
+            print(json.dumps(run_reference(args, WORKLOADS[args.workload])), flush=True)
         return
 
     import torch
@@ -572,17 +677,35 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    if cfg[0] == "decode":
-        res = run_decode(args, rank, world, cfg)
-    elif cfg[0] == "splitkv":
-        res = run_splitkv(args, rank, world, cfg)
-    elif cfg[0] == "fwht":
-        res = run_fwht(args, rank, world, cfg)
-    elif cfg[0] == "draft":
-        res = run_draft(args, rank, world, cfg)
-    else:
-        from kata_b200 import bench_prefill
-        res = bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler)
+    default = args.workload == "decode_b8"
+    res = run_workload(args.workload, args, rank, world, sustained_s=2.0 if default else 0.0)
+    want = args.extras if args.extras is not None else ("all" if default else "none")
+    names = [] if want == "none" else (EXTRAS_ONE_GPU if world == 1 else EXTRAS_MULTI_GPU) if want == "all" else [n for n in want.split(",") if n]
+    if names:
+        extras = {}
+        e_steps, e_warm = max(3, min(args.steps, 10)), 3
+        for name in names:
+            if name not in WORKLOADS:
+                extras[name] = {"skipped": "unknown workload"}
+                continue
+            over = torch.tensor([1.0 if time.perf_counter() - t_start > EXTRAS_BUDGET_S else 0.0], device="cuda")
+            if world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(over, op=dist.ReduceOp.MAX)   # every rank takes the same decision
+            if over.item() > 0:
+                extras[name] = {"skipped": f"not started: the run had already taken more than {EXTRAS_BUDGET_S:.0f} s"}
+                continue
+            t0 = time.perf_counter()
+            try:
+                r = run_workload(name, args, rank, world, steps=e_steps, warmup=e_warm)
+                extras[name] = compact(r); extras[name]["wall_s"] = round(time.perf_counter() - t0, 1)
+            except Exception as ex:   # an extra that fails must not take the headline line with it; it says what happened
+                if world > 1:
+                    raise
+                extras[name] = {"failed": f"{type(ex).__name__}: {ex}"[:300]}
+                torch.cuda.empty_cache()
+        res["extras"] = extras
+    res["wall_s"] = round(time.perf_counter() - t_start, 1)
     if rank == 0:
         print(json.dumps(res), flush=True)
     if world > 1:

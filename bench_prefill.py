@@ -18,11 +18,13 @@ def _flops(pos0: int, m: int) -> float:
     return float(sum(range(pos0 + 1, pos0 + m + 1))) * 24 * 256 * 4
 
 
-def run(args, rank, world, cfg, pk, ClockSampler):
+def run(args, rank, world, cfg, pk, ClockSampler, steps=None, warmup=None):
     import torch
     import torch.distributed as dist
     from kata_b200 import capi
 
+    steps = steps if steps is None else steps
+    warmup = warmup if warmup is None else warmup
     kind, B, kv_mode, total, prefix = cfg
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev); gen.manual_seed(99 + rank)
@@ -89,13 +91,13 @@ def run(args, rank, world, cfg, pk, ClockSampler):
         torch.cuda.synchronize()
 
     sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     ctx.check()
     l0 = ctx.launches(); barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     tw0 = time.perf_counter(); torch.cuda.profiler.start(); e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     e1.record(); barrier(); torch.cuda.profiler.stop(); tw1 = time.perf_counter()
     ms = e0.elapsed_time(e1); launches = ctx.launches() - l0
@@ -108,7 +110,7 @@ def run(args, rank, world, cfg, pk, ClockSampler):
     for (p0, m) in full:
         ctx.prefill(0, seqs, [p0] * B, m, q16, gate, out=out)
     torch.cuda.synchronize(); k0.record()
-    reps = max(2, args.steps)
+    reps = max(2, steps)
     for _ in range(reps):
         for (p0, m) in full:
             for layer in range(N_LAYERS):
@@ -120,7 +122,7 @@ def run(args, rank, world, cfg, pk, ClockSampler):
     host = [torch.randn(B, mmax, 12288).to(bf).pin_memory(), torch.randn(B, mmax, 1024).to(bf).pin_memory(), torch.randn(B, mmax, 1024).to(bf).pin_memory(), torch.empty(B, mmax, 6144).pin_memory()]
     step(host=host); barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step(host=host)
     barrier(); e2e_ms = (time.perf_counter() - t0) * 1e3
     if world > 1:
@@ -129,13 +131,41 @@ def run(args, rank, world, cfg, pk, ClockSampler):
     ach = flops_launch / (kern_ms * 1e-3) / 1e12
     h2d = N_LAYERS * B * toks * (12288 + 2048) * 2; d2h = N_LAYERS * B * toks * 6144 * 4
     name = "pp512" if kind == "prefill" else f"chunked prefill {restore}->{total} in 512-token chunks after a plane restore at {restore}, then a T=2 verify"
-    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * B * toks * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
-           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+    res = {"metric": "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak", "value": world * B * toks * steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+           "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
            "config": {"workload": f"{name}; {N_LAYERS} layers, {kv_mode} KV, bf16 projections, batch {B}/GPU, prep+prefill per layer", "batch_per_gpu": B, "global_batch": world * B,
-                      "l2": "L2 flushed implicitly: each step streams the 16 layers' caches and activations (larger than L2 for the chunked workload); pp512 at batch 1 fits L2 and says so"},
+                      "l2": ("each step streams the 16 layers' caches and activations, together larger than L2 (no flush needed)" if kind == "chunked" or B > 4 else
+                             "NOT larger than L2: one layer's K/V for 512 tokens is 2 MB and the 16 layers' activations 450 MB are streamed once; the kernel is launch- and latency-bound at this size, not bandwidth-bound"),
+                      "kernel": "prefill_tc5_kernel (tcgen05, cta_group::2)" + ("" if kv_mode == "fp16" else " after expand_codes_kernel")},
            "clocks": clocks, "gpu_launches": int(launches),
-           "e2e": {"value": world * B * toks * args.steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-           "roofline": {"bound": "tensor", "kernel": "prefill kernel (see config.kernel)", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / pk["bf16_tflops"], "peak_src": pk["src"],
+           "e2e": {"value": world * B * toks * steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+           "roofline": {"bound": "tensor", "kernel": "prefill_tc5_kernel", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / pk["bf16_tflops"], "frac_of_sustained": ach / pk["bf16_tflops_sustained"], "peak_src": pk["src"],
                         "us_per_launch": kern_ms * 1e3, "algorithmic_flops_per_launch": flops_launch, "traffic": None}}
+    if rank == 0 and not args.no_cpu_baseline and kv_mode == "fp16":
+        res["cpu_baseline"] = cpu_baseline(ctx, full[-1], q16, gate, chunks)
     ctx.close()
+    del qfull, kproj, vproj, q16, gate, out, host
+    torch.cuda.empty_cache()
     return res
+
+
+def cpu_baseline(ctx, chunk, q16, gate, chunks):
+    """The reference's own CPU check (tools/probe_flash.cpp:29-34: fp64 softmax(q k) v sigmoid(g) per token and head), as restated in
+    the oracle's kor_formula_f64 (bit-equal to the reference's lines compiled in oracle/_ref on the reference's inputs), on all host
+    threads, on a bounded sample: the last full chunk of sequence 0, layer 0, every 4th query row; extrapolated to all rows, chunks and
+    layers by FLOPs."""
+    from oracle import kata_oracle as orc
+    p0, m = chunk
+    n = p0 + m
+    planes = orc.KvPlanes(n)
+    planes.k[:] = ctx.plane_read(0, 0, 0, 0, n).view(np.uint16).reshape(n, 1024); planes.v[:] = ctx.plane_read(0, 0, 1, 0, n).view(np.uint16).reshape(n, 1024)
+    q = q16[0, :m].cpu().numpy().view(np.uint16); g = gate[0, :m].cpu().numpy()
+    cores = orc.hw_threads(); t_step = 4 if p0 == 0 else 16   # a bounded sample: a few seconds of host time
+    t0 = time.perf_counter()
+    orc.formula_f64(np.ascontiguousarray(q), np.ascontiguousarray(g), planes, p0, t_step=t_step, threads=cores)
+    dt = time.perf_counter() - t0
+    flops_sample = sum(p0 + r + 1 for r in range(0, m, t_step)) * 24 * 256 * 4.0
+    rate = flops_sample / dt                                  # useful FLOP/s of the fp64 loop on these cores
+    step_flops = N_LAYERS * sum(_flops(c0, cm) for c0, cm in chunks)   # one sequence, all chunks, all layers
+    return {"value": sum(cm for _, cm in chunks) * rate / step_flops, "unit": "tok/s", "cores": cores, "kind": "port", "useful_gflops": rate / 1e9,
+            "sample": f"fp64 check loop of tools/probe_flash.cpp restated (kor_formula_f64), layer 0, sequence 0, chunk at position {p0}, every {t_step}th of {m} rows ({dt:.2f} s); tok/s extrapolated by useful FLOPs to all rows, chunks and {N_LAYERS} layers"}
