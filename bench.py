@@ -363,8 +363,8 @@ def run_splitkv(args, rank, world, kind_cfg, steps=None, warmup=None):
     import torch.distributed as dist
     from kata_b200 import capi, multi
 
-    steps = steps if steps is None else steps
-    warmup = warmup if warmup is None else warmup
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
     _, _, kv_mode, L, _ = kind_cfg
     dev = torch.device("cuda", torch.cuda.current_device())
     steps_total = 3 * (warmup + steps) + 2   # three timed runs (peer exchange, NCCL per layer, one batched all-gather) at successive positions

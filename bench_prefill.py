@@ -23,8 +23,8 @@ def run(args, rank, world, cfg, pk, ClockSampler, steps=None, warmup=None):
     import torch.distributed as dist
     from kata_b200 import capi
 
-    steps = steps if steps is None else steps
-    warmup = warmup if warmup is None else warmup
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
     kind, B, kv_mode, total, prefix = cfg
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev); gen.manual_seed(99 + rank)

@@ -111,7 +111,8 @@ int kata_attn_decode_scalar(kata_attn_ctx* ctx, int32_t layer, int32_t n, const 
 
 /* k_flash_prefill / k_flash_prefill_q8 / k_flash_prefill_k16v8 (shaders/flash.metal:10-68, 198-250; encoded at src/engine.cpp:279, 614): causal flash
  * attention of M <= KATA_MAX_CHUNK query rows per sequence at positions pos_base[b]+r over keys [0, pos_base[b]+r] of
- * the cache (this chunk's rows must already have been appended by kata_attn_prep). d_q16, d_gate, d_out: [n][M][6144]. */
+ * the cache (this chunk's rows must already have been appended by kata_attn_prep). d_q16, d_gate, d_out: [n][M][6144], each on a 16-byte
+ * boundary (the kernel moves them in 128-bit pieces). */
 int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t M,
                       const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 

@@ -149,7 +149,7 @@ template <bool I8> __device__ __forceinline__ void stage_q_chunk(uint8_t* q_row_
     for (int e = 0; e < 8; e++) dst[q8_col_of_dim((c16 & 1) * 8 + e)] = hv[e];
 }
 
-__device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_fast(float x) { return ptx::sigmoid_approx(x); }
 
 }  // namespace kata
 

@@ -232,6 +232,7 @@ int kata_attn_prefill(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t*
     Ctx& c = h->c;
     if (M < 1 || M > KATA_MAX_CHUNK) return fail(c, KATA_ERR_RANGE, "prefill chunk of %d rows (1..%d)", M, KATA_MAX_CHUNK);
     if (!d_q16 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "prefill needs q16, gate and out");
+    if (((uintptr_t)d_q16 | (uintptr_t)d_gate | (uintptr_t)d_out) & 15) return fail(c, KATA_ERR_ARG, "prefill needs q16, gate and out on 16-byte boundaries");
     if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
     kata::Batch b{}; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, M, b)) return rc;
     DeviceGuard guard(c.cfg.device);

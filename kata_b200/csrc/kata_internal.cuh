@@ -101,6 +101,11 @@ __device__ __forceinline__ void store_act2(void* out, int64_t i, float y0, float
     else if (kind == KATA_ACT_F16) reinterpret_cast<__half2*>(out)[i >> 1] = __floats2half2_rn(y0, y1);
     else *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + i) = make_float2(y0, y1);
 }
+__device__ __forceinline__ void store_act4(void* out, int64_t i, float4 y, int kind) {   // elements i .. i+3; i a multiple of 4
+    if (kind == KATA_ACT_BF16) { const __nv_bfloat162 a = __floats2bfloat162_rn(y.x, y.y), b = __floats2bfloat162_rn(y.z, y.w); *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b)); }
+    else if (kind == KATA_ACT_F16) { const __half2 a = __floats2half2_rn(y.x, y.y), b = __floats2half2_rn(y.z, y.w); *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b)); }
+    else *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + i) = y;
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }                  // every earlier kernel of the stream is complete and visible
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }   // the next kernel may be set up from now on
 #endif

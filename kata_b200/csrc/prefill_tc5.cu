@@ -37,6 +37,14 @@ namespace {
 
 using namespace ptx;
 
+// Development aid, compiled only with -DKATA_PF_TRACE (never in the shipped library): CTA 0 records %globaltimer stamps of its phases.
+#ifdef KATA_PF_TRACE
+__device__ unsigned long long g_pf_trace[128];
+__device__ __forceinline__ void pf_stamp(int slot) { if (blockIdx.x == 0 && slot < 128) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_pf_trace[slot] = t; } }
+#else
+__device__ __forceinline__ void pf_stamp(int) {}
+#endif
+
 constexpr int kTcThreads = 352, kBMq = 128, kBNk = 128;
 constexpr int kBlk = 128 * 128;                  // one column block of 128 rows x 128 bytes (Q, V)
 constexpr int kBlkKh = 64 * 128;                 // one column block of a K half-tile: 64 keys x 128 bytes
@@ -78,9 +86,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     const int my_items = pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
     const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + kTileB + 2 * kHalfB, bars = base + kTileB + 4 * kHalfB;   // K stage s at k_sm + s * kHalfB, V stage s at v_sm + s * kHalfB
-    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128], s_stage[8][32 * 17]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
+    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128]; __shared__ __align__(16) float s_stage[8][16 * 36]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
+    if (tid == 0) pf_stamp(0);
     if (tid == 0) {
         for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1 || i == B_OFREE) ? 16u : 1u);   // 'P ready', 'O free': one arrival per softmax warp of both CTAs
         fence_mbar_init();
@@ -92,7 +101,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem = s_tmem, t_o = tmem, t_s0 = tmem + 256;
-    pdl_wait(); pdl_launch_dependents();   // launched with programmatic stream serialisation: the set-up above overlapped the previous kernel (the chunk's prep); its rows and Q are read from here on
+    if (tid == 0) pf_stamp(1);
+    pdl_wait(); pdl_launch_dependents();
+    if (tid == 0) pf_stamp(2);   // launched with programmatic stream serialisation: the set-up above overlapped the previous kernel (the chunk's prep); its rows and Q are read from here on
     // Running counters shared by construction: gt = key tiles so far over all items of this pair (stage, score buffer and phase of the
     // per-tile barriers), it = items so far (phase of the per-item barriers).
 
@@ -115,16 +126,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             }
         }
     } else if (w == 9) {
-        // ---- this CTA's half (128 dims) of every V tile
-        if (lane == 0) {
-            uint32_t gt = 0; bool ok = true;
-            for (int it = 0; ok && it < my_items; it++) {
-                const PfItem t = item_of(it);
-                for (int j = 0; j < t.n_tiles; j++, gt++) {
+        // ---- this CTA's half (128 dims) of every V tile (lane 0). When the item's last tile has been requested the whole warp asks L2 for the
+        // item's gate tile (this CTA's head: rows_valid rows of 1 KB, 24 KB apart), which the epilogue reads one or two tiles of work later:
+        // its first touch of those rows would otherwise be a DRAM round trip per epilogue step.
+        uint32_t gt = 0; bool ok = true;
+        for (int it = 0; ok && it < my_items; it++) {
+            const PfItem t = item_of(it);
+            for (int j = 0; j < t.n_tiles; j++, gt++) {
+                if (lane == 0) {
                     const uint32_t st = gt & 1u;
-                    if (gt >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 12); ok = false; break; }
-                    if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
-                    tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, t.row0v + j * kBNk, 2 * (int)rank, t.kvh, bar(B_VFULL0 + st));
+                    if (gt >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 12); ok = false; }
+                    if (ok) {
+                        if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
+                        tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, t.row0v + j * kBNk, 2 * (int)rank, t.kvh, bar(B_VFULL0 + st));
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (!ok) break;
+                if (j == t.n_tiles - 1) {
+                    const float* gt0 = gate + ((int64_t)t.bi * M + t.q0) * kQD + t.h * kD;
+                    for (int row = lane; row < t.rows_valid; row += 32) prefetch_l2_bulk(gt0 + (int64_t)row * kQD, kD * 4);
                 }
             }
         }
@@ -145,6 +166,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 const PfItem t = item_of(it);
                 ok = mbar_wait_bounded(bar(B_QFULL), (uint32_t)it & 1u, err) && mbar_wait_bounded(bar(B_KFULL0 + (gt & 1u)), (gt >> 1) & 1u, err);
                 if (!ok) { atomicExch(err, 13); break; }
+                pf_stamp(3);
                 tc5::fence_after_sync(); issue_s(gt);
                 if (t.n_tiles == 1) tc5::commit2(bar(B_QEMPTY));
                 for (int j = 0; j < t.n_tiles; j++, gt++) {
@@ -165,6 +187,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                         tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j | ks) != 0);
                     tc5::commit2(bar(B_ODONE));
                     tc5::commit2(bar(B_VEMPTY0 + (gt & 1u)));
+                    pf_stamp(8 + (int)gt);
                 }
             }
         }
@@ -183,6 +206,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         for (int j = 0; j < n_tiles; j++, gt++) {
             const uint32_t t_s = t_s0 + (gt & 1u) * 128u + lane_sel;
             if (alive && !warp_wait(bar(B_SFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
+            if (tid == 0) pf_stamp(24 + (int)gt);
             tc5::fence_after_sync();
             if (SCALED) {   // the tile's 128 K scales and 128 V scales: one value per softmax thread into shared memory, then everybody reads its 64 + 64
                 const int key = min(j * kBNk + (tid & 127), max(kend - 1, 0));
@@ -267,62 +291,74 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive_leader(bar(B_PREADY0 + (gt & 1u)));
+            if (tid == 0) pf_stamp(40 + (int)gt);
             } while (0);
         }
         // ---- epilogue: O / l * sigmoid(gate); the two threads of a row add their partial l and write 128 columns each
         s_lsum[g][r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         l += s_lsum[g ^ 1][r];
-        // Tensor memory hands a thread one row (32 columns at a time); global memory wants a warp on consecutive columns of one row (a thread per
-        // row would touch 32 sectors per instruction). Each warp therefore stages 32 rows x 16 columns in shared memory and writes them back
-        // row by row, half a warp per row: 64 contiguous bytes of gate in and of output out.
-        float* tile = s_stage[w];                     // [32 rows][17]
-        const int hw = lane >> 4, col = lane & 15, rbase = 32 * (w & 3);
-        const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + col;
-        float gv[16];   // gate logits of the round in flight, fetched one round (16 rows x 16 columns per half warp) ahead
-        // (volatile asm loads: issued where they are written, whatever the compiler would prefer for register live ranges)
-        auto load_gate = [&](int rd, float (&dst)[16]) {
+        // Tensor memory hands a thread one row (32 columns at a time); global memory wants consecutive lanes on consecutive bytes of one row.
+        // Per 32-column block each warp stages its 32 rows in two passes of 16 rows x 32 columns through shared memory (row stride 36 floats:
+        // the 128-bit stores of 8 rows and the 128-bit loads of one row both spread over all 32 banks) and writes them back with 8 lanes
+        // per row: every 128-bit gate load and output store of a quarter warp is one whole 128-byte line. The gate values of a block are
+        // requested (from L2, where the V producer warp has asked for them) one block ahead.
+        float* tile = s_stage[w];                     // [16 rows][36]
+        const int rq = lane >> 3, cq = (lane & 7) * 4, rbase = 32 * (w & 3);
+        const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + cq;
+        float4 gv[8];   // gate logits of the block in flight: [pass][k] -> warp row 16 * pass + 4 * k + rq, columns cq .. cq + 3 of the block
+        auto load_gate = [&](int c, float4 (&dst)[8]) {
 #pragma unroll
-            for (int rr = 0; rr < 16; rr++) {
-                const int row = 2 * rr + hw; dst[rr] = 0.0f;
-                if (rbase + row < rows_valid) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(dst[rr]) : "l"(gate + obase + (int64_t)row * kQD + rd * 16));
+            for (int i = 0; i < 8; i++) {
+                const int row = 16 * (i >> 2) + 4 * (i & 3) + rq; dst[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (rbase + row < rows_valid) asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(dst[i].x), "=f"(dst[i].y), "=f"(dst[i].z), "=f"(dst[i].w) : "l"(gate + obase + (int64_t)row * kQD + c * 32));
             }
         };
         load_gate(0, gv);   // in flight while the item's last P.V completes
+        if (tid == 0) pf_stamp(56);
         if (alive && warp_wait(bar(B_ODONE), (gt - 1u) & 1u, err)) {
+            if (tid == 0) pf_stamp(57);
             tc5::fence_after_sync();
             const float inv = 1.0f / l;
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
                 uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
+                if (tid == 0) pf_stamp(58 + 2 * c);
+                float4 gc[8];
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    const int rd = 2 * c + half;
-                    float gc[16];
+                for (int i = 0; i < 8; i++) gc[i] = gv[i];
+                if (tid == 0) pf_stamp(59 + 2 * c);
+                if (c + 1 < 4) load_gate(c + 1, gv);
 #pragma unroll
-                    for (int rr = 0; rr < 16; rr++) gc[rr] = gv[rr];
-                    if (rd + 1 < 8) load_gate(rd + 1, gv);
+                for (int pass = 0; pass < 2; pass++) {
+                    if ((lane >> 4) == pass) {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) tile[lane * 17 + i] = __uint_as_float(o[half * 16 + i]) * inv;
-                    __syncwarp();
-                    // all 16 staged values into registers first, then the sigmoids, then the stores: with one loop a shared-memory load could not move
-                    // above the previous iteration's global store (pointers the compiler cannot tell apart) and the 16 iterations ran as one chain
-                    float tv[16];
-#pragma unroll
-                    for (int rr = 0; rr < 16; rr++) tv[rr] = tile[(2 * rr + hw) * 17 + col];
-#pragma unroll
-                    for (int rr = 0; rr < 16; rr++) tv[rr] *= 1.0f / (1.0f + __expf(-gc[rr]));
-#pragma unroll
-                    for (int rr = 0; rr < 16; rr++) {
-                        const int row = 2 * rr + hw;
-                        if (rbase + row < rows_valid) {
-                            const int64_t oi = obase + (int64_t)row * kQD + rd * 16;
-                            store_act(out, oi, tv[rr], out_kind);
-                        }
+                        for (int i = 0; i < 8; i++)
+                            *reinterpret_cast<float4*>(tile + (lane & 15) * 36 + 4 * i) = make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv, __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
                     }
                     __syncwarp();
+                    float4 tv[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) tv[k] = *reinterpret_cast<const float4*>(tile + (4 * k + rq) * 36 + cq);
+                    __syncwarp();
+                    if (tid == 0 && c == 1) pf_stamp(70 + 4 * pass);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float4 gg = gc[pass * 4 + k];
+                        tv[k].x *= sigmoid_approx(gg.x); tv[k].y *= sigmoid_approx(gg.y); tv[k].z *= sigmoid_approx(gg.z); tv[k].w *= sigmoid_approx(gg.w);
+                    }
+#ifdef KATA_PF_TRACE
+                    if (tid == 0 && c == 1 && tv[0].x + tv[1].y + tv[2].z + tv[3].w != 1234.5f) pf_stamp(71 + 4 * pass);
+#endif
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int row = 16 * pass + 4 * k + rq;
+                        if (rbase + row < rows_valid) store_act4(out, obase + (int64_t)row * kQD + c * 32, tv[k], out_kind);
+                    }
+                    if (tid == 0 && c == 1) pf_stamp(72 + 4 * pass);
                 }
             }
+            if (tid == 0) pf_stamp(66);
             // this warp is done with the item's O: the first P.V of the next item may overwrite it
             tc5::fence_before_sync();
             __syncwarp();
@@ -330,10 +366,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         } else if (alive) { atomicExch(err, 19); alive = false; }
         }
     }
+    if (tid == 0) pf_stamp(67);
     tc5::fence_before_sync();
     __syncthreads();
     tc5::cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or arrive on its barriers
     if (w == 0) tc5::tmem_dealloc2(tmem, 512);
+    if (tid == 0) pf_stamp(68);
 }
 
 // int8 planes: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
@@ -360,6 +398,10 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const 
 }
 
 }  // namespace
+
+#ifdef KATA_PF_TRACE
+extern "C" int kata_debug_pf_trace(unsigned long long* h128) { return (int)cudaMemcpyFromSymbol(h128, g_pf_trace, sizeof(g_pf_trace)); }
+#endif
 
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
 cudaError_t configure_prefill_mma(int kv_mode);
