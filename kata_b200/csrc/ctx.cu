@@ -18,6 +18,7 @@ int decode_max_slots(int sm_count);
 cudaError_t configure_decode(int kv_mode);
 cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s);
 cudaError_t configure_prefill(int kv_mode);
+size_t prefill_part_o_bytes(); size_t prefill_part_ml_bytes();
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s, int tok_stride = 0, int tok0 = 0);
 }  // namespace kata
@@ -98,6 +99,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     if (ok && cfg->kv_mode == KATA_KV_FP16)
         ok = cudaMalloc((void**)&c.sc_pm, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess && cudaMalloc((void**)&c.sc_pl, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess &&
              cudaMalloc((void**)&c.sc_pacc, kata::scalar_scratch_floats_acc() * 4) == cudaSuccess;
+    ok = ok && cudaMalloc((void**)&c.pf_part_o, kata::prefill_part_o_bytes()) == cudaSuccess && cudaMalloc((void**)&c.pf_part_ml, kata::prefill_part_ml_bytes()) == cudaSuccess;
     int64_t stage_rows = 0;
     if (ok && c.v8()) {   // staging arena of the tcgen05 prefill: one layer of every sequence, the int8 planes' codes expanded to fp16
         for (int sq = 0; sq < cfg->n_seqs; sq++) { c.stage_row0.push_back(stage_rows); stage_rows += cfg->max_ctx[sq]; }
@@ -124,7 +126,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
 int kata_attn_destroy(kata_attn_ctx* h) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c; DeviceGuard guard(c.cfg.device);
-    void* ptrs[] = {c.k_arena, c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, c.sc_pm, c.sc_pl, c.sc_pacc, c.k16_stage, c.v16_stage};
+    void* ptrs[] = {c.k_arena, c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, c.sc_pm, c.sc_pl, c.sc_pacc, c.k16_stage, c.v16_stage, c.pf_part_o, c.pf_part_ml};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete h;
     return KATA_OK;

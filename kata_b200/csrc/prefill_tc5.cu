@@ -4,9 +4,15 @@
 // online softmax, P rounded to fp16 before P.V, l summed from the unrounded p, output O / l * sigmoid(gate).
 //
 // A work item = 128 query rows of two heads of the same KV-head group (row r of the chunk sits at position pos_base + r and sees keys
-// [0, pos_base + r]), done by two CTAs (a cluster, cta_group::2). The kernel is persistent: one CTA pair per two SMs walks the items
-// (longest first, dealt round-robin) with its barriers, tensor memory and pipelines kept across items; the next item's Q, K and V loads and
-// first score MMAs run under the current item's epilogue. The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
+// [0, pos_base + r]), done by two CTAs (a cluster, cta_group::2). The kernel is persistent: one CTA pair per two SMs, with its barriers,
+// tensor memory and pipelines kept across items; the next item's Q, K and V loads and first score MMAs run under the current item's epilogue.
+// Work split: the key tiles of all items form one list (longest items first) which the host cuts into one contiguous range per pair,
+// balanced by tiles plus a per-part allowance for the epilogue, so that a launch with fewer items than pairs (one sequence: 48 items for 74
+// pairs) still uses every SM. A pair whose range ends inside an item computes that item over a sub-range of its key tiles ("part") and
+// writes the unnormalised O rows with their (m, l) to scratch; prefill_combine_kernel (a dependent launch over all SMs) then merges the
+// parts of every cut item with the split-KV rule of the decode path (weights exp(m - M)), normalises, gates and writes the rows. (Merging in
+// the CTA that finishes an item's last part was tried first: one SM pulling 400 KB through its few resident warps took 20 us per item.)
+// The host cuts items only when its estimate says the shorter critical path pays for the combine pass. The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
 // accumulators and half of every K tile (64 of the 128 keys) and V tile (128 of the 256 dims); the tensor cores of the two SMs exchange
 // the halves, so each SM writes and reads half the K/V bytes through its shared memory, which is what bounds an M = 128 tile with
 // 256-wide heads (Q, K, V tiles plus their TMA writes ask for more than the 128 bytes per clock an SM's shared memory delivers).
@@ -25,6 +31,11 @@
 // the softmax warps work on the current ones; K and V tiles are loaded one tile ahead. The running maximum is only raised when a row's
 // new maximum exceeds it by more than 8 (in log2 units); then the warp rescales its O rows in tensor memory after waiting for the
 // previous P.V. P stays below 2^8, well inside fp16.
+// Phases: a parity wait cannot tell phase k of an mbarrier from phase k - 2, and the softmax warps wait for 'O done' and 'V landed' only now and
+// then (a rescale, the epilogue, a tail tile), so each of the two has one barrier per tile parity: tile k waits on barrier k & 1 for phase k >> 1,
+// and the phase before it on that barrier (tile k - 2) is complete whenever a warp holds the scores of tile k, because the commit that
+// announced them covers every MMA issued before. (With a single 'O done' barrier a warp that ran ahead of its peers through a two-tile part
+// read O before the part's P.V had completed.)
 // Every wait is bounded and shares the context's abort word; tensor memory is always released before the CTAs exit.
 #include <algorithm>
 
@@ -54,7 +65,7 @@ constexpr int kSmemTc = kTileB + 4 * kHalfB + 1024 + 256; // Q, 2 x K half, 2 x 
 constexpr uint32_t kIdescS = tc5::idesc_f16(256, 128, false), kIdescPV = tc5::idesc_f16(256, 256, true);
 
 // barrier slots (8 bytes each) after the tiles
-enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_VLANDED, B_SFULL0, B_SFULL1, B_PREADY0, B_PREADY1, B_ODONE, B_QEMPTY, B_OFREE, B_COUNT };
+enum { B_QFULL = 0, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1, B_VLANDED0, B_VLANDED1, B_SFULL0, B_SFULL1, B_PREADY0, B_PREADY1, B_ODONE0, B_ODONE1, B_QEMPTY, B_OFREE, B_COUNT };
 
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const int32_t* abort_flag) {   // same outcome for every lane of the warp
     const bool ok = mbar_wait_bounded(bar, parity, abort_flag);
@@ -63,7 +74,12 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const i
 
 // One work item = (query tile, head pair, sequence); items are ordered longest first and dealt round-robin to the CTA pairs.
 struct PfStage { int64_t kv_row0[KATA_MAX_BATCH]; };   // SCALED: first row of sequence b in the fp16 staging arena (position 0)
-struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh, bi; int64_t sc_row0; };   // row0 / row0v: row of position 0 in the arena the K / V tiles come from
+struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh, bi; int64_t sc_row0; int idx, j0, j1, slot; bool whole; };   // row0 / row0v: row of position 0 in the arena the K / V tiles come from; [j0, j1): this part's key tiles
+constexpr int kMaxPairs = 74;      // CTA pairs of a launch (one per two SMs of a B200)
+constexpr int kPartE = 2;          // host-side allowance, in key tiles, for what a part costs besides its tiles (Q load, epilogue or partial write)
+// Pair p works on the flat tile list from (item item0[p], tile tile0[p]) up to, not including, (item0[p+1], tile0[p+1]).
+struct PfPlan { int32_t n_pairs; int32_t item0[kMaxPairs + 1]; int32_t tile0[kMaxPairs + 1]; };
+constexpr size_t kPartOFloats = (size_t)kBMq * kD, kPartSlots = 2 * 2 * kMaxPairs;   // a slot = one CTA's 128 x 256 partial O; two parts per pair, two CTAs per pair
 
 // MODE = the context's cache mode. An int8 plane's tiles are its codes expanded to fp16 (exact integers) in a staging arena whose rows are
 // kv_row0[b] + position; the per-key scales are applied as k_flash_prefill_q8 does (shaders/flash.metal:10-68 with Q8): S = (Q.Kq) * ksc[key],
@@ -71,19 +87,22 @@ struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                                                                    const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, int32_t* err,
-                                                                   const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc) {
+                                                                   const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
+                                                                   const __grid_constant__ PfPlan plan, float* part_o, float* part_ml) {
     constexpr bool KS = MODE == KATA_KV_INT8, SCALED = MODE != KATA_KV_FP16;   // KS: scores take the key scale; SCALED: P takes the value scale
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t rank = tc5::cluster_rank();
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, n_items = n_q * per_q, n_pairs = gridDim.x / 2, pair = blockIdx.x / 2;
-    auto item_of = [&](int it) {   // it-th item of this CTA pair
-        const int idx = pair + it * n_pairs, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
-        PfItem t; t.bi = rem / (kH / 2); t.h = 2 * (rem % (kH / 2)) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, pair = blockIdx.x / 2;
+    const int item_lo = plan.item0[pair], tile_lo = plan.tile0[pair], item_hi = plan.item0[pair + 1], tile_hi = plan.tile0[pair + 1];
+    const int my_items = (item_lo == item_hi && tile_lo >= tile_hi) ? 0 : item_hi - item_lo + (tile_hi > 0 ? 1 : 0);   // parts of this pair
+    auto item_of = [&](int it) {   // it-th part of this CTA pair
+        const int idx = item_lo + it, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
+        PfItem t; t.idx = idx; t.bi = rem / (kH / 2); t.h = 2 * (rem % (kH / 2)) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
         t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = KS ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.row0v = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
+        t.j0 = it == 0 ? tile_lo : 0; t.j1 = idx == item_hi ? tile_hi : t.n_tiles; t.whole = t.j0 == 0 && t.j1 == t.n_tiles; t.slot = (2 * pair + (it == 0 ? 0 : 1)) * 2 + (int)rank;
         return t;
     };
-    const int my_items = pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
     const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + kTileB + 2 * kHalfB, bars = base + kTileB + 4 * kHalfB;   // K stage s at k_sm + s * kHalfB, V stage s at v_sm + s * kHalfB
     __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128]; __shared__ __align__(16) float s_stage[8][16 * 36]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
@@ -117,7 +136,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 if (it >= 1 && !mbar_wait_bounded(bar(B_QEMPTY), (uint32_t)(it - 1) & 1u, err)) { atomicExch(err, 10); break; }
                 if (rank == 0) mbar_arrive_expect_tx(bar(B_QFULL), 2 * kTileB);
                 for (int kb = 0; kb < 4; kb++) tc5::tma_load_2d_pair(q_sm + kb * kBlk, &tm_q, t.h * kD + kb * 64, t.bi * M + t.q0, bar(B_QFULL));
-                for (int j = 0; j < t.n_tiles; j++, gt++) {
+                for (int j = t.j0; j < t.j1; j++, gt++) {
                     const uint32_t st = gt & 1u;
                     if (gt >= 2 && !mbar_wait_bounded(bar(B_KEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 11); ok = false; break; }
                     if (rank == 0) mbar_arrive_expect_tx(bar(B_KFULL0 + st), 2 * kHalfB);
@@ -132,7 +151,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         uint32_t gt = 0; bool ok = true;
         for (int it = 0; ok && it < my_items; it++) {
             const PfItem t = item_of(it);
-            for (int j = 0; j < t.n_tiles; j++, gt++) {
+            for (int j = t.j0; j < t.j1; j++, gt++) {
                 if (lane == 0) {
                     const uint32_t st = gt & 1u;
                     if (gt >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 12); ok = false; }
@@ -143,7 +162,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 }
                 ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                 if (!ok) break;
-                if (j == t.n_tiles - 1) {
+                if (j == t.j1 - 1 && t.whole) {
                     const float* gt0 = gate + ((int64_t)t.bi * M + t.q0) * kQD + t.h * kD;
                     for (int row = lane; row < t.rows_valid; row += 32) prefetch_l2_bulk(gt0 + (int64_t)row * kQD, kD * 4);
                 }
@@ -168,24 +187,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 if (!ok) { atomicExch(err, 13); break; }
                 pf_stamp(3);
                 tc5::fence_after_sync(); issue_s(gt);
-                if (t.n_tiles == 1) tc5::commit2(bar(B_QEMPTY));
-                for (int j = 0; j < t.n_tiles; j++, gt++) {
-                    if (j + 1 < t.n_tiles) {
+                if (t.j1 - t.j0 == 1) tc5::commit2(bar(B_QEMPTY));
+                for (int j = t.j0; j < t.j1; j++, gt++) {
+                    if (j + 1 < t.j1) {
                         if (!mbar_wait_bounded(bar(B_KFULL0 + ((gt + 1) & 1u)), ((gt + 1) >> 1) & 1u, err)) { atomicExch(err, 14); ok = false; break; }
                         tc5::fence_after_sync(); issue_s(gt + 1);
-                        if (j + 2 == t.n_tiles) tc5::commit2(bar(B_QEMPTY));   // the item's last S MMA: Q may be replaced
+                        if (j + 2 == t.j1) tc5::commit2(bar(B_QEMPTY));   // the part's last S MMA: Q may be replaced
                     }
                     // V of the tile has landed in both CTAs: tell both (their softmax warps zero the rows past the range in the tail tile), then wait for P
                     if (!mbar_wait_bounded(bar(B_VFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
-                    mbar_arrive(bar(B_VLANDED)); tc5::mbar_arrive_peer(bar(B_VLANDED));
+                    mbar_arrive(bar(B_VLANDED0 + (gt & 1u))); tc5::mbar_arrive_peer(bar(B_VLANDED0 + (gt & 1u)));
                     if (!mbar_wait_bounded(bar(B_PREADY0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
-                    if (j == 0 && it >= 1 && !mbar_wait_bounded(bar(B_OFREE), (uint32_t)(it - 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }   // the previous item's O has been read out
+                    if (j == t.j0 && it >= 1 && !mbar_wait_bounded(bar(B_OFREE), (uint32_t)(it - 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }   // the previous item's O has been read out
                     tc5::fence_after_sync();
                     const uint32_t a = t_s0 + (gt & 1u) * 128u, vst = v_sm + (gt & 1u) * kHalfB;   // P: fp16 pairs in the first 64 columns of its S buffer
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++)   // 16 keys per step; V half is MN-major: 64-dim blocks 16 KB apart, 8-key groups 1 KB apart
-                        tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j | ks) != 0);
-                    tc5::commit2(bar(B_ODONE));
+                        tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j != t.j0) || ks != 0);
+                    tc5::commit2(bar(B_ODONE0 + (gt & 1u)));
                     tc5::commit2(bar(B_VEMPTY0 + (gt & 1u)));
                     pf_stamp(8 + (int)gt);
                 }
@@ -200,10 +219,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         // Every thread runs every iteration and meets its partner at the pair barrier whatever happens: a wait that ran out only switches the work off.
         for (int it = 0; it < my_items; it++) {
         const PfItem t = item_of(it);
-        const int q0 = t.q0, rows_valid = t.rows_valid, pos_base = t.pos_base, kend = t.kend, n_tiles = t.n_tiles, h = t.h, bi = t.bi;
+        const int q0 = t.q0, rows_valid = t.rows_valid, pos_base = t.pos_base, kend = t.kend, h = t.h, bi = t.bi, j0 = t.j0, j1 = t.j1;
         const int qpos = pos_base + q0 + r, lim = min(kend, qpos + 1);               // this row sees keys <= qpos (and < kend)
         float m = -INFINITY, l = 0.0f;
-        for (int j = 0; j < n_tiles; j++, gt++) {
+        for (int j = j0; j < j1; j++, gt++) {
             const uint32_t t_s = t_s0 + (gt & 1u) * 128u + lane_sel;
             if (alive && !warp_wait(bar(B_SFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
             if (tid == 0) pf_stamp(24 + (int)gt);
@@ -246,10 +265,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             do {
             if (!alive) break;
             const float mt = fmaxf(mx, s_xmax[gt & 1u][g ^ 1][r]) * kLog2e;
-            const bool need = (j == 0) ? false : (mt > m + 8.0f);
-            if (j == 0) m = mt;
+            const bool need = (j == j0) ? false : (mt > m + 8.0f);
+            if (j == j0) m = mt;
             if (__any_sync(0xffffffffu, need)) {   // raise the reference maximum: rescale this thread's half of the O row after the previous P.V has landed
-                if (!warp_wait(bar(B_ODONE), (gt - 1u) & 1u, err)) { atomicExch(err, 17); alive = false; break; }
+                if (!warp_wait(bar(B_ODONE0 + ((gt - 1u) & 1u)), ((gt - 1u) >> 1) & 1u, err)) { atomicExch(err, 17); alive = false; break; }
                 tc5::fence_after_sync();
                 const float alpha = need ? ex2(m - mt) : 1.0f;
                 if (need) { m = mt; l *= alpha; }
@@ -278,7 +297,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::wait_st();
             if (j * kBNk + kBNk > kend) {   // tail tile: rows of V past the range were loaded as they lie in memory; zero them (0 x garbage must stay 0)
                 // (the MMA thread announces every tile's V once it has landed in both CTAs)
-                if (!warp_wait(bar(B_VLANDED), gt & 1u, err)) { atomicExch(err, 18); alive = false; break; }
+                if (!warp_wait(bar(B_VLANDED0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 18); alive = false; break; }
                 if (g == 0 && j * kBNk + r >= kend) {
                     uint8_t* v_gen = smem_raw + (v_sm + (gt & 1u) * kHalfB - sm0);
 #pragma unroll
@@ -294,7 +313,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             if (tid == 0) pf_stamp(40 + (int)gt);
             } while (0);
         }
-        // ---- epilogue: O / l * sigmoid(gate); the two threads of a row add their partial l and write 128 columns each
+        // ---- epilogue: the two threads of a row add their partial l and handle 128 columns each
         s_lsum[g][r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         l += s_lsum[g ^ 1][r];
@@ -306,6 +325,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         float* tile = s_stage[w];                     // [16 rows][36]
         const int rq = lane >> 3, cq = (lane & 7) * 4, rbase = 32 * (w & 3);
         const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + cq;
+        if (t.whole) {
+        // whole item: O / l * sigmoid(gate) straight to the output rows
         float4 gv[8];   // gate logits of the block in flight: [pass][k] -> warp row 16 * pass + 4 * k + rq, columns cq .. cq + 3 of the block
         auto load_gate = [&](int c, float4 (&dst)[8]) {
 #pragma unroll
@@ -316,7 +337,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         };
         load_gate(0, gv);   // in flight while the item's last P.V completes
         if (tid == 0) pf_stamp(56);
-        if (alive && warp_wait(bar(B_ODONE), (gt - 1u) & 1u, err)) {
+        if (alive && warp_wait(bar(B_ODONE0 + ((gt - 1u) & 1u)), ((gt - 1u) >> 1) & 1u, err)) {
             if (tid == 0) pf_stamp(57);
             tc5::fence_after_sync();
             const float inv = 1.0f / l;
@@ -341,21 +362,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
 #pragma unroll
                     for (int k = 0; k < 4; k++) tv[k] = *reinterpret_cast<const float4*>(tile + (4 * k + rq) * 36 + cq);
                     __syncwarp();
-                    if (tid == 0 && c == 1) pf_stamp(70 + 4 * pass);
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const float4 gg = gc[pass * 4 + k];
                         tv[k].x *= sigmoid_approx(gg.x); tv[k].y *= sigmoid_approx(gg.y); tv[k].z *= sigmoid_approx(gg.z); tv[k].w *= sigmoid_approx(gg.w);
                     }
-#ifdef KATA_PF_TRACE
-                    if (tid == 0 && c == 1 && tv[0].x + tv[1].y + tv[2].z + tv[3].w != 1234.5f) pf_stamp(71 + 4 * pass);
-#endif
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const int row = 16 * pass + 4 * k + rq;
                         if (rbase + row < rows_valid) store_act4(out, obase + (int64_t)row * kQD + c * 32, tv[k], out_kind);
                     }
-                    if (tid == 0 && c == 1) pf_stamp(72 + 4 * pass);
                 }
             }
             if (tid == 0) pf_stamp(66);
@@ -364,6 +380,38 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive_leader(bar(B_OFREE));
         } else if (alive) { atomicExch(err, 19); alive = false; }
+        } else {
+        // part of an item: the unnormalised O rows (fp32) and their (m, l) go to this part's scratch slot for prefill_combine_kernel
+        float* po = part_o + (size_t)t.slot * kPartOFloats + (size_t)rbase * kD + g * 128 + cq;
+        if (alive && warp_wait(bar(B_ODONE0 + ((gt - 1u) & 1u)), ((gt - 1u) >> 1) & 1u, err)) {
+            tc5::fence_after_sync();
+            if (g == 0) *reinterpret_cast<float2*>(part_ml + (size_t)t.slot * (2 * kBMq) + 2 * r) = make_float2(m, l);   // m in log2 units; -inf when the row saw no key of this part
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
+#pragma unroll
+                for (int pass = 0; pass < 2; pass++) {
+                    if ((lane >> 4) == pass) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            *reinterpret_cast<float4*>(tile + (lane & 15) * 36 + 4 * i) = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int row = 16 * pass + 4 * k + rq;
+                        if (rbase + row < rows_valid) __stcg(reinterpret_cast<float4*>(po + (size_t)row * kD + c * 32), *reinterpret_cast<const float4*>(tile + (4 * k + rq) * 36 + cq));
+                    }
+                    __syncwarp();
+                }
+            }
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive_leader(bar(B_OFREE));
+        } else if (alive) { atomicExch(err, 19); alive = false; }
+        if (tid == 0) pf_stamp(80);
+        if (tid == 0) pf_stamp(85);
+        }
         }
     }
     if (tid == 0) pf_stamp(67);
@@ -372,6 +420,52 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     tc5::cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or arrive on its barriers
     if (w == 0) tc5::tmem_dealloc2(tmem, 512);
     if (tid == 0) pf_stamp(68);
+}
+
+// Merge of the parts of every item the plan cuts (k_attn_dec_combine's rule, shaders/flash.metal:143-152, with "split" = part): per row,
+// M = max m_p, weights exp2(m_p - M), O = sum w_p O_p / sum w_p l_p, times sigmoid(gate). grid = (16-row blocks of the 128-row tile, head of
+// the pair, cut item); 256 threads = 16 rows x 16 lanes, a lane taking columns 4*lane .. +3 of each of the four 64-column quarters, so that
+// every 128-bit load and store of 16 lanes is a contiguous 256 bytes. Launched with programmatic stream serialisation behind the prefill kernel.
+struct PfCuts { int32_t n; int32_t idx[kMaxPairs]; int32_t pa[kMaxPairs]; int32_t pb[kMaxPairs]; };   // cut items and the pairs holding their first and last tile
+__global__ void __launch_bounds__(256) prefill_combine_kernel(const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_kind,
+                                                              const __grid_constant__ PfPlan plan, const __grid_constant__ PfCuts cuts,
+                                                              const float* __restrict__ part_o, const float* __restrict__ part_ml) {
+    const int idx = cuts.idx[blockIdx.z], pa = cuts.pa[blockIdx.z], pb = cuts.pb[blockIdx.z], rank = blockIdx.y;
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, qt = n_q - 1 - idx / per_q, rem = idx % per_q, bi = rem / (kH / 2), h = 2 * (rem % (kH / 2)) + rank;
+    const int q0 = qt * kBMq, rows_valid = min(kBMq, M - q0), R = blockIdx.x * 16 + (threadIdx.x >> 4), c4 = (threadIdx.x & 15) * 4;
+    pdl_wait(); pdl_launch_dependents();   // the parts are complete and visible from here on
+    if (R >= rows_valid) return;
+    auto holds = [&](int p) {   // pair p holds a part of the item: its range reaches into the item and is not empty
+        const int i0 = plan.item0[p], t0 = plan.tile0[p], i1 = plan.item0[p + 1], t1 = plan.tile0[p + 1];
+        return i0 <= idx && (i1 > idx || (i1 == idx && t1 > 0)) && (i0 < i1 || t0 < t1);
+    };
+    auto slot_of = [&](int p) { return (2 * p + (plan.item0[p] == idx ? 0 : 1)) * 2 + rank; };   // a pair's first part sits in its slot 0, its last in slot 1
+    const int64_t oi = ((int64_t)bi * M + q0 + R) * kQD + h * kD + c4;
+    float4 gg[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) gg[c] = *reinterpret_cast<const float4*>(gate + oi + c * 64);
+    float Mx = -INFINITY;
+    for (int p = pa; p <= pb; p++) if (holds(p)) Mx = fmaxf(Mx, __ldcg(part_ml + (size_t)slot_of(p) * (2 * kBMq) + 2 * R));
+    float L = 0.0f; float4 A[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) A[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int p = pa; p <= pb; p++) {
+        if (!holds(p)) continue;
+        const int sl = slot_of(p);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (size_t)sl * (2 * kBMq) + 2 * R));
+        const float* src = part_o + (size_t)sl * kPartOFloats + (size_t)R * kD + c4;
+        float4 o4[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) o4[c] = __ldcg(reinterpret_cast<const float4*>(src + c * 64));
+        const float wt = (ml.x == -INFINITY) ? 0.0f : ex2(ml.x - Mx);
+        L += ml.y * wt;
+#pragma unroll
+        for (int c = 0; c < 4; c++) { A[c].x += o4[c].x * wt; A[c].y += o4[c].y * wt; A[c].z += o4[c].z * wt; A[c].w += o4[c].w * wt; }
+    }
+    const float inv = 1.0f / L;
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+        store_act4(out, oi + c * 64, make_float4(A[c].x * inv * sigmoid_approx(gg[c].x), A[c].y * inv * sigmoid_approx(gg[c].y), A[c].z * inv * sigmoid_approx(gg[c].z), A[c].w * inv * sigmoid_approx(gg[c].w)), out_kind);
 }
 
 // int8 planes: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
@@ -403,6 +497,10 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const 
 extern "C" int kata_debug_pf_trace(unsigned long long* h128) { return (int)cudaMemcpyFromSymbol(h128, g_pf_trace, sizeof(g_pf_trace)); }
 #endif
 
+// scratch of the cut items: partial O rows and their (m, l)
+size_t prefill_part_o_bytes() { return kPartSlots * kPartOFloats * sizeof(float); }
+size_t prefill_part_ml_bytes() { return kPartSlots * 2 * kBMq * sizeof(float); }
+
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
 cudaError_t configure_prefill_mma(int kv_mode);
 
@@ -430,18 +528,110 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
         expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1);
         c.launches++;
     }
-    // persistent CTA pairs: at most one pair per two SMs, items dealt round-robin (longest first)
-    const int n_items = ((M + kBMq - 1) / kBMq) * (kH / 2) * b.n, n_pairs = std::max(1, std::min(n_items, c.sm_count / 2));
+    // persistent CTA pairs, at most one per two SMs; the flat list of (item, key tile) is cut into one contiguous range per pair.
+    // The plan depends only on (M, positions): the 16 layers of a chunk reuse the one computed for the first (kept in the context, no allocation).
+    struct Cached { PfPlan plan; PfCuts cuts; };
+    static_assert(sizeof(Cached) <= sizeof(c.pf_plan_cache), "plan cache too small");
+    Cached& cached = *reinterpret_cast<Cached*>(c.pf_plan_cache);
+    bool hit = c.pf_plan_M == M && c.pf_plan_n == b.n;
+    for (int i = 0; hit && i < b.n; i++) hit = c.pf_plan_pos[i] == b.pos[i];
+    if (!hit) {
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, n_items = n_q * per_q, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
+    int32_t* nt_tab = c.pf_plan_tiles;   // key tiles per item (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
+    for (int idx = 0; idx < n_items; idx++) { const int qt = n_q - 1 - idx / per_q, bi = (idx % per_q) / (kH / 2), q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
+    auto tiles_of = [&](int idx) { return (int)nt_tab[idx]; };
+    int64_t W = 0; for (int i = 0; i < n_items; i++) W += tiles_of(i) + kPartE;
+    constexpr int kMinPart = 2;   // a part is at least two key tiles
+    // Plan A: equal ranges of the flat list. With fewer items than pairs the items are cut, but not into ranges shorter than two tiles plus the allowance.
+    auto max_load = [&](const PfPlan& pl) {
+        int worst = 0;
+        for (int p = 0; p < pl.n_pairs; p++) {
+            int w = 0;
+            for (int i = pl.item0[p]; i <= pl.item0[p + 1] && i < n_items; i++) {
+                const int j0 = i == pl.item0[p] ? pl.tile0[p] : 0, j1 = i == pl.item0[p + 1] ? pl.tile0[p + 1] : tiles_of(i);
+                if (j1 > j0) w += j1 - j0 + kPartE;
+            }
+            worst = std::max(worst, w);
+        }
+        return worst;
+    };
+    PfPlan plan{};
+    {
+        const int n_pairs = n_items >= max_pairs ? max_pairs : std::max(std::min(n_items, max_pairs), (int)std::min<int64_t>(max_pairs, W / (kPartE + 2)));
+        plan.n_pairs = n_pairs;
+        int idx = 0; int64_t acc = 0;   // acc: weight of the items before idx
+        for (int p = 1; p < n_pairs; p++) {
+            const double target = (double)W * p / n_pairs;
+            while (idx < n_items && (double)(acc + tiles_of(idx) + kPartE) <= target) { acc += tiles_of(idx) + kPartE; idx++; }
+            int ci = idx, ct = 0;
+            if (idx < n_items) {
+                const int nt = tiles_of(idx), jt = (int)(target - (double)acc + 0.5);
+                if (jt >= kMinPart && nt - jt >= kMinPart) ct = jt; else if (jt >= kMinPart) ci = idx + 1;   // too close to an end: the cut moves to the item boundary
+            }
+            if (ci < plan.item0[p - 1] || (ci == plan.item0[p - 1] && ct < plan.tile0[p - 1])) { ci = plan.item0[p - 1]; ct = plan.tile0[p - 1]; }   // never behind the previous cut
+            plan.item0[p] = ci; plan.tile0[p] = ct;
+        }
+        plan.item0[n_pairs] = n_items; plan.tile0[n_pairs] = 0;
+    }
+    // Plan B (only with fewer items than pairs): one part per pair; the spare pairs go, one at a time, to the item whose parts are longest.
+    // Better than A when the items are short (a 512-token prompt: items of 1 to 4 tiles).
+    if (n_items < max_pairs) {
+        int parts[kMaxPairs]; int total = n_items;
+        for (int i = 0; i < n_items; i++) parts[i] = 1;
+        for (; total < max_pairs; total++) {
+            int best = -1, best_len = 0;
+            for (int i = 0; i < n_items; i++) { const int len = (tiles_of(i) + parts[i] - 1) / parts[i]; if (tiles_of(i) / (parts[i] + 1) >= kMinPart && len > best_len) { best = i; best_len = len; } }
+            if (best < 0) break;
+            parts[best]++;
+        }
+        PfPlan alt{}; alt.n_pairs = total; int p = 0;
+        for (int i = 0; i < n_items; i++) for (int m = 0; m < parts[i]; m++, p++) { alt.item0[p] = i; alt.tile0[p] = (int)((int64_t)tiles_of(i) * m / parts[i]); }
+        alt.item0[total] = n_items; alt.tile0[total] = 0;
+        if (max_load(alt) < max_load(plan)) plan = alt;
+    }
+    // Plan U: no item is cut (every cut of plan A moved to the next item boundary). A cut plan has the shorter critical path but pays for the
+    // combine pass: its launch plus the traffic of the cut items' parts, gate and output rows. Estimate both in microseconds (a key tile
+    // of a CTA pair takes about 2.3 us at the rate the kernel sustains) and keep the cheaper.
+    // The items a plan cuts, with the first and last pair holding a part of each (empty pairs in between hold nothing); returns the number of parts.
+    auto cut_items = [&](const PfPlan& pl, PfCuts& out) {
+        int parts = 0; out.n = 0;
+        for (int p = 1; p < pl.n_pairs; p++) {
+            if (pl.tile0[p] == 0) continue;                                   // a cut at an item boundary cuts nothing
+            const int idx = pl.item0[p];
+            const bool repeat = pl.item0[p - 1] == idx && pl.tile0[p - 1] == pl.tile0[p];   // pair p - 1 is empty: the same cut again
+            if (out.n > 0 && out.idx[out.n - 1] == idx) { out.pb[out.n - 1] = p; if (!repeat) parts++; continue; }
+            out.idx[out.n] = idx; out.pa[out.n] = p - 1; out.pb[out.n] = p; out.n++; parts += 2;   // the cut before this one lies at or before the item's first tile: pair p - 1 holds it
+        }
+        return parts;
+    };
+    {
+        PfPlan whole = plan;
+        for (int p = 1; p < whole.n_pairs; p++) if (whole.tile0[p] > 0) { whole.tile0[p] = 0; whole.item0[p] = std::min(whole.item0[p] + 1, n_items); }
+        PfCuts tmp{}; const int parts = cut_items(plan, tmp);
+        const double t_tile = 2.3, t_cut = max_load(plan) * t_tile + (tmp.n ? 4.0 + 2.0 * (parts + 2.0 * tmp.n) * (kPartOFloats * 4.0) / 5.0e6 : 0.0), t_whole = max_load(whole) * t_tile;
+        if (t_whole <= t_cut) plan = whole;
+    }
+    PfCuts cuts{}; cut_items(plan, cuts);
+    cached.plan = plan; cached.cuts = cuts;
+    c.pf_plan_M = M; c.pf_plan_n = b.n; for (int i = 0; i < b.n; i++) c.pf_plan_pos[i] = b.pos[i];
+    }
+    const PfPlan& plan = cached.plan; const PfCuts& cuts = cached.cuts;
+    const int n_pairs = plan.n_pairs;
     cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(2 * n_pairs, 1, 1); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
     cudaLaunchAttribute at[2]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
-#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)out_dtype, c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc)
+#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)out_dtype, c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc, plan, c.pf_part_o, c.pf_part_ml)
     const cudaError_t le = mode == KATA_KV_INT8 ? KATA_PF(KATA_KV_INT8, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8V ? KATA_PF(KATA_KV_INT8V, c.tm_k64h, c.tm_v128h_stage) : KATA_PF(KATA_KV_FP16, c.tm_k64h, c.tm_v128h);
 #undef KATA_PF
     if (le != cudaSuccess) return le;
     c.wrote_no_rows();
     c.launches++;
+    if (cuts.n) {
+        const cudaError_t ce = launch_pdl(prefill_combine_kernel, dim3(kBMq / 16, 2, cuts.n), dim3(256), 0, s, b, M, gate, out, (int)out_dtype, plan, cuts, (const float*)c.pf_part_o, (const float*)c.pf_part_ml);
+        if (ce != cudaSuccess) return ce;
+        c.launches++;
+    }
     return cudaGetLastError();
 }
 
