@@ -16,6 +16,7 @@ size_t scalar_scratch_floats_pm();
 size_t scalar_scratch_floats_acc();
 int decode_max_slots(int sm_count);
 cudaError_t configure_decode(int kv_mode);
+cudaError_t configure_decode_scalar();
 cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s);
 cudaError_t configure_prefill(int kv_mode);
 size_t prefill_part_o_bytes(); size_t prefill_part_ml_bytes();
@@ -114,7 +115,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
             (!c.k8() && !kata::make_tile_tmap(&c.tm_k64h, c.k_arena, 2, rows, 64, 4)) || (!c.v8() && !kata::make_tile_tmap(&c.tm_v128h, c.v_arena, 2, rows, 128, 2)) ||
             (c.k8() && !kata::make_tile_tmap(&c.tm_k64h_stage, c.k16_stage, 2, stage_rows, 64, 4)) || (c.v8() && !kata::make_tile_tmap(&c.tm_v128h_stage, c.v16_stage, 2, stage_rows, 128, 2))) { kata_attn_destroy(h); return KATA_ERR_CUDA; }
     }
-    if (kata::configure_decode(cfg->kv_mode) != cudaSuccess || kata::configure_prefill(cfg->kv_mode) != cudaSuccess) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_CUDA; }
+    if (kata::configure_decode(cfg->kv_mode) != cudaSuccess || kata::configure_prefill(cfg->kv_mode) != cudaSuccess || (cfg->kv_mode == KATA_KV_FP16 && kata::configure_decode_scalar() != cudaSuccess)) { cudaGetLastError(); kata_attn_destroy(h); return KATA_ERR_CUDA; }
     cudaMemset(c.counters, 0, 4 * KATA_MAX_BATCH * 4); cudaMemset(c.d_err, 0, 4);
     float invf[32]; for (int i = 0; i < 32; i++) invf[i] = powf(10000000.0f, -(float)i / 32.0f);   // shaders/attn.metal:26
     kata::set_inv_freq(invf);

@@ -771,3 +771,22 @@ def test_references_own_check_judges_the_cuda_kernels(capi, path):
 
     res = probe_ref.run(kernel)
     assert res.non_finite == 0 and res.worst < 2e-4, res.worst
+
+
+def test_fp32_decode_path_ragged_batch_first_pos_and_token_groups(capi, orc):
+    # the CUDA-core path on a ragged batch: lengths around the 32-key tile and the 128-key chunk, T across the 4-token groups, first_pos = 1
+    lens = [1, 31, 33, 130, 700, 4500]
+    ctx = capi.AttnContext(1, [l + 16 for l in lens])
+    planes, qs, gs = [], [], []
+    for s, L in enumerate(lens):
+        pl, q, g, _ = _oracle_fill(orc, 300 + s, L + 8, L + 16, fast=True, seq=s)
+        _upload_planes(ctx, pl, seq=s); planes.append(pl); qs.append(q); gs.append(g)
+    seqs = list(range(len(lens)))
+    for T, first_pos in ((1, 0), (3, 0), (5, 1), (8, 0)):
+        pos = [max(L - 1, first_pos) for L in lens]   # rows up to pos + T - 1 exist (8 spare rows were filled)
+        dq = _dev(np.stack([qs[s][pos[s]:pos[s] + T] for s in seqs])); dg = _dev(np.stack([gs[s][pos[s]:pos[s] + T] for s in seqs]))
+        out = ctx.decode_scalar(0, seqs, pos, T, dq, dg, first_pos=first_pos).cpu().numpy()
+        ctx.check()
+        for s in seqs:
+            ref = orc.formula_f32(qs[s][pos[s]:pos[s] + T], gs[s][pos[s]:pos[s] + T], planes[s], pos[s], first_pos=first_pos)
+            assert np.isfinite(out[s]).all() and np.abs(out[s] - ref).max() < 2e-5, (T, first_pos, s)
