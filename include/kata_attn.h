@@ -151,6 +151,15 @@ int kata_attn_peer_destroy(kata_attn_peer* px);              /* call on every ra
  * when a long sequence is split by keys across GPUs and each rank stores only its slice. */
 int kata_attn_set_position_offset(kata_attn_ctx* ctx, int32_t seq, int32_t first_position);
 
+/* No reference counterpart (the reference is single-device). Sharding by KV-head group: this context computes KV heads
+ * [kv_head_lo, kv_head_lo + kv_head_n) only (default: all 4). kata_attn_prep then normalises, rotates and appends only those K/V heads and
+ * writes q16 / q32 / gate only for their query heads (6 per KV head: heads 6*kv .. 6*kv + 5); kata_attn_decode and kata_attn_prefill read
+ * only those heads' cache columns and write only those heads' 256-wide column blocks of d_out, leaving the rest untouched. Attention needs
+ * no exchange between the ranks of such a group; a consumer that wants whole rows gathers the column blocks (T * 6144 / ranks values per
+ * rank). Row layout and planes are unchanged (a rank's other heads stay zero). kata_attn_decode_scalar, kata_attn_decode_partial and the
+ * mma.sync prefill kernel compute all four heads and return KATA_ERR_MODE on a context that owns a subset. */
+int kata_attn_set_kv_heads(kata_attn_ctx* ctx, int32_t kv_head_lo, int32_t kv_head_n);
+
 /* Split-KV across GPUs (no reference counterpart: the reference is single-device). Each rank holds keys
  * [key_lo, key_hi) of sequence seq in ITS context at rows [0, key_hi-key_lo) (row = key - key_lo) and computes, per
  * (token, head), the unnormalised partial of k_attn_dec_split merged over its local splits:

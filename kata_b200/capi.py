@@ -26,7 +26,7 @@ EXPORTS = [
     "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
-    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_out_fwht",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
     "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode",
     "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
@@ -138,6 +138,10 @@ class AttnContext:
 
     def set_position_offset(self, seq: int, first_position: int):
         self._ck(self.L.kata_attn_set_position_offset(self.h, seq, first_position))
+
+    def set_kv_heads(self, kv_head_lo: int, kv_head_n: int):
+        """This context computes KV heads [lo, lo + n) only (a rank of a head-sharded group)."""
+        self._ck(self.L.kata_attn_set_kv_heads(self.h, kv_head_lo, kv_head_n))
 
     def launches(self) -> int:
         return int(self.L.kata_attn_launch_count(self.h))

@@ -218,6 +218,7 @@ int kata_attn_decode_scalar(kata_attn_ctx* h, int32_t layer, int32_t n, const in
                             const float* d_q32, const float* d_gate, float* d_out, void* stream) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c;
+    if (c.kvh_n != KATA_KV_HEADS) return fail(c, KATA_ERR_MODE, "the scalar path computes all four KV heads (this context owns %d)", c.kvh_n);
     if (c.cfg.kv_mode != KATA_KV_FP16) return fail(c, KATA_ERR_MODE, "the scalar path reads an fp16 cache only (the reference disables it for int8, src/engine.cpp:169)");
     if (T < 1 || T > KATA_MAX_VERIFY) return fail(c, KATA_ERR_RANGE, "scalar decode takes 1..%d query tokens, not %d", KATA_MAX_VERIFY, T);
     if (!d_q32 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "scalar decode needs q32, gate and out");
@@ -237,6 +238,7 @@ int kata_attn_prefill(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t*
     if (!d_q16 || !d_gate || !d_out) return fail(c, KATA_ERR_ARG, "prefill needs q16, gate and out");
     if (((uintptr_t)d_q16 | (uintptr_t)d_gate | (uintptr_t)d_out) & 15) return fail(c, KATA_ERR_ARG, "prefill needs q16, gate and out on 16-byte boundaries");
     if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return fail(c, KATA_ERR_ARG, "unknown output dtype %d", out_dtype);
+    if (c.kvh_n != KATA_KV_HEADS && (c.cfg.flags & 1)) return fail(c, KATA_ERR_MODE, "the mma.sync prefill kernel computes all four KV heads (this context owns %d)", c.kvh_n);
     kata::Batch b{}; if (int rc = make_batch(c, layer, n, seq_ids, pos_base, M, b)) return rc;
     DeviceGuard guard(c.cfg.device);
     cudaError_t e = kata::launch_prefill(c, b, M, (const __half*)d_q16, d_gate, d_out, out_dtype, (cudaStream_t)stream);
@@ -250,6 +252,7 @@ int kata_attn_decode_partial(kata_attn_ctx* h, int32_t layer, int32_t seq, int32
     Ctx& c = h->c;
     if (T < 1 || T > 2) return fail(c, KATA_ERR_RANGE, "decode takes 1 or 2 query tokens, not %d", T);
     if (!d_q16 || !d_part) return fail(c, KATA_ERR_ARG, "decode_partial needs q16 and part");
+    if (c.kvh_n != KATA_KV_HEADS) return fail(c, KATA_ERR_MODE, "decode_partial computes all four KV heads (this context owns %d)", c.kvh_n);
     if (key_lo < 0 || key_hi < key_lo || pos_base < 0) return fail(c, KATA_ERR_RANGE, "key range [%d,%d) / pos_base %d", key_lo, key_hi, pos_base);
     const int32_t local_rows = std::max(0, std::min(pos_base + T, key_hi) - key_lo);   // rows [0, local_rows) of this context hold keys key_lo..
     if (layer < 0 || layer >= c.cfg.n_layers || seq < 0 || seq >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "layer %d / sequence %d out of range", layer, seq);
@@ -268,6 +271,14 @@ int kata_attn_merge_parts(kata_attn_ctx* h, const float* d_parts, int32_t n_part
     cudaError_t e = kata::launch_merge_parts(c, d_parts, n_parts, T, d_gate, d_out, out_dtype, (cudaStream_t)stream);
     c.wrote_no_rows();
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "merge_parts launch");
+}
+
+int kata_attn_set_kv_heads(kata_attn_ctx* h, int32_t kv_head_lo, int32_t kv_head_n) {
+    if (!h) return KATA_ERR_ARG;
+    Ctx& c = h->c;
+    if (kv_head_lo < 0 || kv_head_n < 1 || kv_head_lo + kv_head_n > KATA_KV_HEADS) return fail(c, KATA_ERR_RANGE, "KV heads [%d,%d) outside [0,%d)", kv_head_lo, kv_head_lo + kv_head_n, KATA_KV_HEADS);
+    c.kvh_lo = kv_head_lo; c.kvh_n = kv_head_n; c.pf_plan_M = -1;   // the cached prefill plan was made for another head range
+    return KATA_OK;
 }
 
 int kata_attn_set_position_offset(kata_attn_ctx* h, int32_t seq, int32_t first_position) {

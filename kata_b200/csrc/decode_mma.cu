@@ -58,6 +58,7 @@ template <int MODE> struct Geo {
 
 struct DecPlan {
     int32_t n, T, first_row, key_off, n_ctas, q_tiles, r_tiles;   // CTA c owns tiles [c*q + min(c,r), (c+1)*q + min(c+1,r))
+    int32_t kvh_lo, kvh_n;               // KV heads of this launch: a sequence's tiles are those of heads kvh_lo .. kvh_lo + kvh_n - 1, head after head
     int32_t tok_stride, tok0;            // rows of q16 / gate / out per sequence, and the row of this launch's token 0 (a wide verify runs as launches of 2 tokens)
     int32_t merge_in_kernel;             // 1: the last contributor of a segment merges its partials; 0: decode_combine_kernel does
     int32_t pos[KATA_MAX_BATCH];         // absolute position of token 0
@@ -105,8 +106,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 
     while (tile < tile_end) {
         while (p.tile_start[b + 1] <= tile) b++;
-        const int nt = p.ntiles[b], kvh = (tile - p.tile_start[b]) / nt, lt0 = (tile - p.tile_start[b]) - kvh * nt;
-        const int seg_first = p.tile_start[b] + kvh * nt, seg_end = seg_first + nt, my_end = min(tile_end, seg_end), n_here = my_end - tile;
+        const int nt = p.ntiles[b], kvl = (tile - p.tile_start[b]) / nt, kvh = p.kvh_lo + kvl, lt0 = (tile - p.tile_start[b]) - kvl * nt;
+        const int seg_first = p.tile_start[b] + kvl * nt, seg_end = seg_first + nt, my_end = min(tile_end, seg_end), n_here = my_end - tile;
         const int T = p.T, kend = p.kend[b], pos_rel = p.pos[b] - p.key_off;   // token t sees local rows < min(kend, pos_rel + t + 1)
 
         // ---- this ring's tiles of the segment: local tiles lt0 + ring, lt0 + ring + 4, ...
@@ -313,8 +314,8 @@ constexpr int kCombineThreads = 1024;
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, float* __restrict__ part_out,
                                                                          const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml) {
     __shared__ float s_acc[3][256]; __shared__ float s_M, s_L;
-    const int r = blockIdx.x, seg = blockIdx.y, b = seg >> 2, kvh = seg & 3, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
-    const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvh * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
+    const int r = blockIdx.x, b = blockIdx.y / p.kvh_n, kvl = blockIdx.y % p.kvh_n, kvh = p.kvh_lo + kvl, seg = b * 4 + kvh, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
+    const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvl * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
     pdl_wait();              // the decode kernel's partials are complete and visible from here on
     pdl_launch_dependents();
     if (n_c == 1) return;   // a single contributor wrote the final row itself
@@ -372,7 +373,7 @@ cudaError_t configure_decode(int kv_mode) {
 static int max_contributors(const DecPlan& p) {
     auto cta_of = [&](int tile) { const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
     int m = 1;
-    for (int i = 0; i < p.n; i++) for (int kv = 0; kv < 4; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; m = std::max(m, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
+    for (int i = 0; i < p.n; i++) for (int kv = 0; kv < p.kvh_n; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; m = std::max(m, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
     return m;
 }
 
@@ -380,13 +381,13 @@ static int max_contributors(const DecPlan& p) {
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s, int tok_stride, int tok0) {
     const int mode = c.cfg.kv_mode, kTile = c.k8() ? 32 : 16;
-    DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off; p.tok_stride = tok_stride > 0 ? tok_stride : T; p.tok0 = tok0;
+    DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off; p.kvh_lo = c.kvh_lo; p.kvh_n = c.kvh_n; p.tok_stride = tok_stride > 0 ? tok_stride : T; p.tok0 = tok0;
     int total = 0;
     for (int i = 0; i < b.n; i++) {
         p.pos[i] = b.pos[i]; p.row_base[i] = b.row_base[i]; p.kend[i] = kend_override ? kend_override[i] : b.pos[i] + T;
         p.safe_row[i] = c.prev_append ? std::min<int64_t>(p.kend[i], (int64_t)c.append_lo[b.seq[i]] - key_off) : p.kend[i];
         const int nkeys = std::max(0, p.kend[i] - first_row); p.ntiles[i] = std::max(1, (nkeys + kTile - 1) / kTile);
-        p.tile_start[i] = total; total += 4 * p.ntiles[i];
+        p.tile_start[i] = total; total += c.kvh_n * p.ntiles[i];
     }
     for (int i = b.n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
     const int chunk_tiles = c.cfg.dec_chunk > 0 ? std::max(1, c.cfg.dec_chunk / kTile) : 0;
@@ -408,7 +409,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (le != cudaSuccess) return le;
     c.launches++;
     if (!p.merge_in_kernel) {
-        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, 4 * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)out_dtype, part_out, (const float*)c.part_o, (const float*)c.part_ml);
+        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, c.kvh_n * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)out_dtype, part_out, (const float*)c.part_o, (const float*)c.part_ml);
         if (e != cudaSuccess) return e;
         c.launches++;
     }
@@ -479,7 +480,7 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
         if (cudaDeviceGetAttribute(&sd.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return KATA_ERR_CUDA;
         sd.scratch = static_cast<StaticScratch*>(ptr); sd.ready = true;
     }
-    DecPlan p{}; p.n = n; p.T = T; p.first_row = first_pos; p.key_off = 0; p.tok_stride = T; p.tok0 = 0;
+    DecPlan p{}; p.n = n; p.T = T; p.first_row = first_pos; p.key_off = 0; p.tok_stride = T; p.tok0 = 0; p.kvh_lo = 0; p.kvh_n = kKvh;
     int total = 0;
     for (int i = 0; i < n; i++) {
         if (pos_base[i] < 0 || first_pos < 0 || first_pos > pos_base[i] || seq_row0[i] < 0 || seq_row0[i] + pos_base[i] + T > total_rows) return KATA_ERR_RANGE;

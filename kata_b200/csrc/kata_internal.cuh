@@ -65,6 +65,7 @@ struct Ctx {
     // host-side work plan of the last tcgen05 prefill launch, reused while (chunk length, positions) stay the same (the layers of a chunk)
     alignas(8) unsigned char pf_plan_cache[2048] = {}; int pf_plan_M = -1, pf_plan_n = -1; int32_t pf_plan_pos[KATA_MAX_BATCH] = {}; int32_t pf_plan_tiles[(KATA_MAX_CHUNK / 128) * (KATA_HEADS / 2) * KATA_MAX_BATCH] = {};
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out
+    int kvh_lo = 0, kvh_n = KATA_KV_HEADS;   // KV heads this context computes (kata_attn_set_kv_heads): a rank of a head-sharded group owns a subset
     int sm_count = 148;
     uint64_t launches = 0;
     std::string err;

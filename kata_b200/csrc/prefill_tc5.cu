@@ -78,7 +78,7 @@ struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh
 constexpr int kMaxPairs = 74;      // CTA pairs of a launch (one per two SMs of a B200)
 constexpr int kPartE = 2;          // host-side allowance, in key tiles, for what a part costs besides its tiles (Q load, epilogue or partial write)
 // Pair p works on the flat tile list from (item item0[p], tile tile0[p]) up to, not including, (item0[p+1], tile0[p+1]).
-struct PfPlan { int32_t n_pairs; int32_t item0[kMaxPairs + 1]; int32_t tile0[kMaxPairs + 1]; };
+struct PfPlan { int32_t n_pairs; int32_t item0[kMaxPairs + 1]; int32_t tile0[kMaxPairs + 1]; int32_t hp_lo, hp_n; };   // hp_lo, hp_n: the head pairs (3 per KV head) this launch computes
 constexpr size_t kPartOFloats = (size_t)kBMq * kD, kPartSlots = 2 * 2 * kMaxPairs;   // a slot = one CTA's 128 x 256 partial O; two parts per pair, two CTAs per pair
 
 // MODE = the context's cache mode. An int8 plane's tiles are its codes expanded to fp16 (exact integers) in a staging arena whose rows are
@@ -93,12 +93,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t rank = tc5::cluster_rank();
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, pair = blockIdx.x / 2;
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = plan.hp_n * b.n, pair = blockIdx.x / 2;
     const int item_lo = plan.item0[pair], tile_lo = plan.tile0[pair], item_hi = plan.item0[pair + 1], tile_hi = plan.tile0[pair + 1];
     const int my_items = (item_lo == item_hi && tile_lo >= tile_hi) ? 0 : item_hi - item_lo + (tile_hi > 0 ? 1 : 0);   // parts of this pair
     auto item_of = [&](int it) {   // it-th part of this CTA pair
         const int idx = item_lo + it, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
-        PfItem t; t.idx = idx; t.bi = rem / (kH / 2); t.h = 2 * (rem % (kH / 2)) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
+        PfItem t; t.idx = idx; t.bi = rem / plan.hp_n; t.h = 2 * (plan.hp_lo + rem % plan.hp_n) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
         t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = KS ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.row0v = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
         t.j0 = it == 0 ? tile_lo : 0; t.j1 = idx == item_hi ? tile_hi : t.n_tiles; t.whole = t.j0 == 0 && t.j1 == t.n_tiles; t.slot = (2 * pair + (it == 0 ? 0 : 1)) * 2 + (int)rank;
         return t;
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(256) prefill_combine_kernel(const Batch b, con
                                                               const __grid_constant__ PfPlan plan, const __grid_constant__ PfCuts cuts,
                                                               const float* __restrict__ part_o, const float* __restrict__ part_ml) {
     const int idx = cuts.idx[blockIdx.z], pa = cuts.pa[blockIdx.z], pb = cuts.pb[blockIdx.z], rank = blockIdx.y;
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, qt = n_q - 1 - idx / per_q, rem = idx % per_q, bi = rem / (kH / 2), h = 2 * (rem % (kH / 2)) + rank;
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = plan.hp_n * b.n, qt = n_q - 1 - idx / per_q, rem = idx % per_q, bi = rem / plan.hp_n, h = 2 * (plan.hp_lo + rem % plan.hp_n) + rank;
     const int q0 = qt * kBMq, rows_valid = min(kBMq, M - q0), R = blockIdx.x * 16 + (threadIdx.x >> 4), c4 = (threadIdx.x & 15) * 4;
     pdl_wait(); pdl_launch_dependents();   // the parts are complete and visible from here on
     if (R >= rows_valid) return;
@@ -536,9 +536,10 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     bool hit = c.pf_plan_M == M && c.pf_plan_n == b.n;
     for (int i = 0; hit && i < b.n; i++) hit = c.pf_plan_pos[i] == b.pos[i];
     if (!hit) {
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = (kH / 2) * b.n, n_items = n_q * per_q, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
+    const int hp_n = 3 * c.kvh_n, hp_lo = 3 * c.kvh_lo;   // head pairs of the KV heads this context computes
+    const int n_q = (M + kBMq - 1) / kBMq, per_q = hp_n * b.n, n_items = n_q * per_q, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
     int32_t* nt_tab = c.pf_plan_tiles;   // key tiles per item (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
-    for (int idx = 0; idx < n_items; idx++) { const int qt = n_q - 1 - idx / per_q, bi = (idx % per_q) / (kH / 2), q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
+    for (int idx = 0; idx < n_items; idx++) { const int qt = n_q - 1 - idx / per_q, bi = (idx % per_q) / hp_n, q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
     auto tiles_of = [&](int idx) { return (int)nt_tab[idx]; };
     int64_t W = 0; for (int i = 0; i < n_items; i++) W += tiles_of(i) + kPartE;
     constexpr int kMinPart = 2;   // a part is at least two key tiles
@@ -612,6 +613,7 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
         if (t_whole <= t_cut) plan = whole;
     }
     PfCuts cuts{}; cut_items(plan, cuts);
+    plan.hp_lo = hp_lo; plan.hp_n = hp_n;
     cached.plan = plan; cached.cuts = cuts;
     c.pf_plan_M = M; c.pf_plan_n = b.n; for (int i = 0; i < b.n; i++) c.pf_plan_pos[i] = b.pos[i];
     }

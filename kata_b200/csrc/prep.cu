@@ -68,11 +68,12 @@ __device__ __forceinline__ void quant_store_row(const __half (&hv)[8], int8_t* d
 template <typename TIn, bool K8, bool V8>
 __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, const TIn* __restrict__ qfull, const TIn* __restrict__ kproj, const TIn* __restrict__ vproj,
                                                    const float* __restrict__ qnorm, const float* __restrict__ knorm, __half* __restrict__ q16, float* __restrict__ q32, float* __restrict__ gate,
-                                                   void* k_arena, void* v_arena, __half* ksc, __half* vsc, const int h0, const int nh, const int round_mode) {
+                                                   void* k_arena, void* v_arena, __half* ksc, __half* vsc, const int h0, const int nh, const int round_mode, const int kvh_mask) {
     pdl_wait(); pdl_launch_dependents();   // launched with programmatic stream serialisation
     const int lane = threadIdx.x & 31, slot = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (slot >= nh) return;
     const int h = h0 + slot, t = blockIdx.y, bi = blockIdx.z;
+    if (!((kvh_mask >> (h < 24 ? h / 6 : (h - 24) & 3)) & 1)) return;   // a head slot of a KV head this context does not own
     const int pos = b.pos[bi] + t; const int64_t row = b.row_base[bi] + pos; const int64_t tok = (int64_t)bi * T + t;
     if (h >= 28) {   // value head: fp16 copy (or quantise) into the cache row
         const int vh = h - 28; __half hv[8];
@@ -198,7 +199,7 @@ cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const 
     const dim3 grid((nh + 7) / 8, T, b.n), block(256);
     const int mode = c.cfg.kv_mode;
     cudaError_t le = cudaSuccess;
-#define KATA_PREP(TIN, K8, V8) le = launch_pdl(prep_kernel<TIN, K8, V8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round)
+#define KATA_PREP(TIN, K8, V8) le = launch_pdl(prep_kernel<TIN, K8, V8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round, ((1 << c.kvh_n) - 1) << c.kvh_lo)
     if (act_dtype == KATA_ACT_F32) { if (mode == KATA_KV_INT8) KATA_PREP(float, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(float, false, true); else KATA_PREP(float, false, false); }
     else if (act_dtype == KATA_ACT_BF16) { if (mode == KATA_KV_INT8) KATA_PREP(__nv_bfloat16, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__nv_bfloat16, false, true); else KATA_PREP(__nv_bfloat16, false, false); }
     else { if (mode == KATA_KV_INT8) KATA_PREP(__half, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__half, false, true); else KATA_PREP(__half, false, false); }

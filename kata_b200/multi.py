@@ -1,6 +1,8 @@
 """Host-side sharding of the attention path across the GPUs of one box (one process per GPU).
 
-Two plans, neither of which has a reference counterpart (the reference is single-device):
+Three plans, none of which has a reference counterpart (the reference is single-device):
+  * KV-head groups -> ranks (up to 4): a rank owns whole KV heads and their 6 query heads each; attention needs no exchange, the output
+    rows are disjoint 256-wide column blocks which the consumer gathers if it wants whole rows;
   * independent sequences of a batch -> ranks, balanced by context length (no data-path collective);
   * one long sequence -> contiguous key ranges per rank; every rank computes the unnormalised partial {O, m, l} of its
     keys (kata_attn_decode_partial), the parts are all-gathered and merged with the reference's split-merge rule
@@ -19,6 +21,19 @@ def shard_sequences(lengths, world: int):
         r = min(range(world), key=lambda k: (load[k], k))
         out[r].append(i); load[r] += int(lengths[i])
     return [sorted(x) for x in out]
+
+
+def shard_kv_heads(world: int):
+    """(first KV head, number of KV heads) per rank for a head-sharded group of 1, 2 or 4 ranks."""
+    if world not in (1, 2, 4):
+        raise ValueError("the 4 KV heads shard over 1, 2 or 4 ranks")
+    per = 4 // world
+    return [(r * per, per) for r in range(world)]
+
+
+def head_columns(kv_head_lo: int, kv_head_n: int):
+    """Column slice of a [.., 6144] query / gate / output row that belongs to KV heads [lo, lo + n): 6 query heads of 256 dims per KV head."""
+    return slice(kv_head_lo * 6 * 256, (kv_head_lo + kv_head_n) * 6 * 256)
 
 
 def split_keys(n_keys: int, world: int, align: int = 16):

@@ -182,3 +182,50 @@ def test_engine_mirror_wide_verify_mtp_rows_quantiser_and_output_transform(orc):
     for a, w in zip(got, (want.k, want.v, want.ksc, want.vsc)):
         assert np.array_equal(a[10:17], w[10:17]) and not a[:10].any()
     L.kata_engine_destroy(e8)
+
+
+def _head_rank_main(rank, world, port, ret):
+    import torch.distributed as dist
+    from kata_b200 import capi
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    L, T = 3070, 2                                                    # 3072 keys: a whole multiple of the 512-key split
+    gen = torch.Generator(device="cuda"); gen.manual_seed(41)          # the same inputs on every rank
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    lo, n = multi.shard_kv_heads(world)[rank]
+    mine = capi.AttnContext(1, [L + 8], dec_chunk=512); mine.set_kv_heads(lo, n)
+    whole = capi.AttnContext(1, [L + 8], dec_chunk=512) if rank == 0 else None
+    for st in range(0, L, 1024):
+        m = min(1024, L - st)
+        kp = torch.randn(1, m, 1024, generator=gen, device="cuda"); vp = torch.randn(1, m, 1024, generator=gen, device="cuda")
+        for c in (mine, whole):
+            if c is not None:
+                c.prep(0, [0], [st], m, None, kp, vp, None, kn, h0=24, nh=8)
+    qf = torch.randn(1, T, 12288, generator=gen, device="cuda"); kp = torch.randn(1, T, 1024, generator=gen, device="cuda"); vp = torch.randn(1, T, 1024, generator=gen, device="cuda")
+    q16, _, g = mine.prep(0, [0], [L], T, qf, kp, vp, qn, kn)
+    out = torch.zeros(1, T, 6144, device="cuda")
+    mine.decode(0, [0], [L], T, q16, g, out=out); mine.check()
+    block = out[0, :, multi.head_columns(lo, n)].contiguous()          # this rank's column block: T x 6144 / world values
+    blocks = [torch.empty_like(block) for _ in range(world)]
+    dist.all_gather(blocks, block)                                     # the one exchange of the head-sharded group, after attention
+    if rank == 0:
+        q16w, _, gw = whole.prep(0, [0], [L], T, qf, kp, vp, qn, kn)
+        want = whole.decode(0, [0], [L], T, q16w, gw); whole.check()
+        ret.put(bool(torch.equal(torch.cat(blocks, dim=1), want[0])))
+    dist.barrier(); dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_kv_head_groups_across_two_gpus():
+    # two ranks own two KV heads each; their column blocks, gathered over NCCL, are the single-GPU rows bit for bit
+    import torch.multiprocessing as mp
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn"); ret = ctx.Queue()
+    procs = [ctx.Process(target=_head_rank_main, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ok = ret.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+    assert ok and all(p.exitcode == 0 for p in procs)

@@ -790,3 +790,63 @@ def test_fp32_decode_path_ragged_batch_first_pos_and_token_groups(capi, orc):
         for s in seqs:
             ref = orc.formula_f32(qs[s][pos[s]:pos[s] + T], gs[s][pos[s]:pos[s] + T], planes[s], pos[s], first_pos=first_pos)
             assert np.isfinite(out[s]).all() and np.abs(out[s] - ref).max() < 2e-5, (T, first_pos, s)
+
+
+@pytest.mark.parametrize("mode", ["fp16", "int8"])
+def test_kv_head_shards_equal_the_whole_context(capi, orc, mode):
+    # Sharding by KV-head group: two contexts, each owning two KV heads (as two ranks would, here on one GPU), against one context that owns
+    # all four, on the same inputs: append, T = 2 decode of a ragged batch, and a prefill chunk over a prefix. Each shard must write
+    # exactly its own 12 query heads' columns (the rest untouched), equal to the whole context's; with a split that cuts every head's keys
+    # at the same places (dec_chunk dividing the head's tiles) the decode is bit-identical.
+    from kata_b200 import multi
+    lens = [1024, 2560]
+    gen = torch.Generator(device="cuda"); gen.manual_seed(31)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    whole = capi.AttnContext(1, [l + 600 for l in lens], kv_mode=mode, dec_chunk=256)
+    shards = []
+    for lo, n in multi.shard_kv_heads(2):
+        c = capi.AttnContext(1, [l + 600 for l in lens], kv_mode=mode, dec_chunk=256); c.set_kv_heads(lo, n); shards.append((c, lo, n))
+    for s, l in enumerate(lens):
+        for st in range(0, l, 512):
+            kp = torch.randn(1, 512, 1024, generator=gen, device="cuda"); vp = torch.randn(1, 512, 1024, generator=gen, device="cuda")
+            for c in [whole] + [x[0] for x in shards]:
+                c.prep(0, [s], [st], 512, None, kp, vp, None, kn, h0=24, nh=8)
+    # a shard's planes hold its own heads' columns and zeros elsewhere
+    for c, lo, n in shards:
+        for pl in (0, 1):
+            a = whole.plane_read(0, 1, pl, 0, 64).reshape(64, 4, -1); b_ = c.plane_read(0, 1, pl, 0, 64).reshape(64, 4, -1)
+            assert np.array_equal(a[:, lo:lo + n], b_[:, lo:lo + n]) and not np.delete(b_, np.s_[lo:lo + n], axis=1).any()
+    SENT = 777.0
+    # decode, T = 2, over the last two rows (rewritten by the prep of the same call): 1024 and 2560 keys are whole multiples of the 256-key
+    # split, so every head's keys are cut at the same places whether a launch holds two heads or four
+    dpos = [l - 2 for l in lens]
+    qf = torch.randn(2, 2, 12288, generator=gen, device="cuda"); kp = torch.randn(2, 2, 1024, generator=gen, device="cuda"); vp = torch.randn(2, 2, 1024, generator=gen, device="cuda")
+    q16, _, g = whole.prep(0, [0, 1], dpos, 2, qf, kp, vp, qn, kn)
+    want = whole.decode(0, [0, 1], dpos, 2, q16, g); whole.check()
+    for c, lo, n in shards:
+        cols = multi.head_columns(lo, n)
+        q16s = torch.full_like(q16, SENT); gs = torch.full_like(g, SENT)
+        c.prep(0, [0, 1], dpos, 2, qf, kp, vp, qn, kn, q16=q16s, gate=gs)
+        assert torch.equal(q16s[..., cols], q16[..., cols]) and torch.equal(gs[..., cols], g[..., cols])
+        rest = torch.ones(6144, dtype=torch.bool, device="cuda"); rest[cols] = False
+        assert (q16s[..., rest] == SENT).all() and (gs[..., rest] == SENT).all()
+        out = torch.full_like(want, SENT)
+        c.decode(0, [0, 1], dpos, 2, q16s, gs, out=out); c.check()
+        assert torch.equal(out[..., cols], want[..., cols]) and (out[..., rest] == SENT).all()
+    # prefill of a 300-row chunk behind the decoded rows (sequence 1 only), tcgen05 kernel
+    M, p0 = 300, lens[1]
+    qf = torch.randn(1, M, 12288, generator=gen, device="cuda"); kp = torch.randn(1, M, 1024, generator=gen, device="cuda"); vp = torch.randn(1, M, 1024, generator=gen, device="cuda")
+    q16, _, g = whole.prep(0, [1], [p0], M, qf, kp, vp, qn, kn)
+    want = whole.prefill(0, [1], [p0], M, q16, g); whole.check()
+    for c, lo, n in shards:
+        cols = multi.head_columns(lo, n)
+        q16s, _, gs = c.prep(0, [1], [p0], M, qf, kp, vp, qn, kn)
+        out = torch.full_like(want, SENT)
+        c.prefill(0, [1], [p0], M, q16s, gs, out=out); c.check()
+        rest = torch.ones(6144, dtype=torch.bool, device="cuda"); rest[cols] = False
+        # (a shard's items are cut between CTA pairs at other places than the whole context's: P is rounded to fp16 against other running maxima)
+        assert (out[..., cols] - want[..., cols]).abs().max().item() < 3e-4 and (out[..., rest] == SENT).all()
+        # what a shard cannot do says so
+        with pytest.raises(capi.KataError) as e:
+            c.decode_scalar(0, [1], [p0], 1, torch.zeros(1, 1, 6144, device="cuda"), torch.zeros(1, 1, 6144, device="cuda"))
+        assert e.value.code == 3

@@ -73,3 +73,38 @@ def test_split_kv_merge_over_gloo(world):
     for p in procs: p.join(timeout=60)
     assert all(p.exitcode == 0 for p in procs)
     assert np.abs(out - full).max() < 2e-5
+
+
+def _head_worker(rank, world, port, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import kata_oracle as orc
+    from kata_b200 import synth
+    qn, kn = synth.norm_weights(5)
+    qf, kp, vp = synth.token_rows_fast(5, 40)
+    planes = orc.KvPlanes(64)
+    q, gate = orc.prep(qf, kp, vp, qn, kn, planes, 0)
+    full = orc.formula_f32(q[38:], gate[38:], planes, 38)            # every rank can form the whole result on the host ...
+    lo, n = multi.shard_kv_heads(world)[rank]
+    mine = torch.from_numpy(np.ascontiguousarray(full[:, multi.head_columns(lo, n)]))   # ... but contributes only the columns of its KV heads
+    got = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(got, mine)
+    whole = torch.cat(got, dim=1).numpy()
+    if rank == 0:
+        ret.put(bool(np.array_equal(whole, full)))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_kv_head_shards_gather_to_whole_rows_over_gloo(world):
+    # the host-side plan of the head-sharded group: disjoint column blocks in rank order make up the row
+    assert multi.shard_kv_heads(2) == [(0, 2), (2, 2)] and multi.head_columns(1, 2) == slice(1536, 4608)
+    ctx = mp.get_context("spawn"); ret = ctx.Queue(); port = _free_port()
+    procs = [ctx.Process(target=_head_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    ok = ret.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+    assert ok
