@@ -10,6 +10,7 @@
 #include <new>
 
 #include "kata_internal.cuh"
+#include "peer_exchange.cuh"
 
 namespace kata {
 size_t scalar_scratch_floats_pm();
@@ -21,7 +22,9 @@ cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64
 cudaError_t configure_prefill(int kv_mode);
 size_t prefill_part_o_bytes(); size_t prefill_part_ml_bytes();
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
-                                 float* part_out, cudaStream_t s, int tok_stride = 0, int tok0 = 0);
+                                 float* part_out, cudaStream_t s, int tok_stride = 0, int tok0 = 0, const PeerSink* sink = nullptr, bool* sink_used = nullptr);
+int decode_partial_impl(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi, const void* d_q16, float* d_part,
+                        const PeerSink* sink, const float* d_gate, void* d_out, int32_t out_dtype, bool* sink_used, void* stream);
 }  // namespace kata
 
 struct kata_attn_ctx { kata::Ctx c; };
@@ -248,19 +251,7 @@ int kata_attn_prefill(kata_attn_ctx* h, int32_t layer, int32_t n, const int32_t*
 
 int kata_attn_decode_partial(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
                              const void* d_q16, float* d_part, void* stream) {
-    if (!h) return KATA_ERR_ARG;
-    Ctx& c = h->c;
-    if (T < 1 || T > 2) return fail(c, KATA_ERR_RANGE, "decode takes 1 or 2 query tokens, not %d", T);
-    if (!d_q16 || !d_part) return fail(c, KATA_ERR_ARG, "decode_partial needs q16 and part");
-    if (c.kvh_n != KATA_KV_HEADS) return fail(c, KATA_ERR_MODE, "decode_partial computes all four KV heads (this context owns %d)", c.kvh_n);
-    if (key_lo < 0 || key_hi < key_lo || pos_base < 0) return fail(c, KATA_ERR_RANGE, "key range [%d,%d) / pos_base %d", key_lo, key_hi, pos_base);
-    const int32_t local_rows = std::max(0, std::min(pos_base + T, key_hi) - key_lo);   // rows [0, local_rows) of this context hold keys key_lo..
-    if (layer < 0 || layer >= c.cfg.n_layers || seq < 0 || seq >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "layer %d / sequence %d out of range", layer, seq);
-    if (local_rows > c.max_ctx[seq]) return fail(c, KATA_ERR_RANGE, "%d local rows exceed max_ctx %d", local_rows, c.max_ctx[seq]);
-    kata::Batch b{}; b.n = 1; b.seq[0] = seq; b.pos[0] = pos_base; b.row_base[0] = c.row_of(layer, seq);
-    DeviceGuard guard(c.cfg.device);
-    cudaError_t e = kata::launch_decode_mma_ex(c, b, T, 0, key_lo, &local_rows, (const __half*)d_q16, nullptr, nullptr, KATA_ACT_F32, d_part, (cudaStream_t)stream);
-    return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "decode_partial launch");
+    return kata::decode_partial_impl(h, layer, seq, pos_base, T, key_lo, key_hi, d_q16, d_part, nullptr, nullptr, nullptr, KATA_ACT_F32, nullptr, stream);
 }
 
 int kata_attn_merge_parts(kata_attn_ctx* h, const float* d_parts, int32_t n_parts, int32_t T, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
@@ -328,3 +319,24 @@ int kata_attn_kv_plane_read(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_
 int kata_attn_kv_plane_write(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t plane, int32_t row0, int32_t nrows, const void* h_src) { return plane_copy(h, layer, seq, plane, row0, nrows, const_cast<void*>(h_src), false); }
 
 }  // extern "C"
+
+// kata_attn_decode_partial, optionally feeding a cross-GPU exchange: with a sink (and the gate and output rows it needs) the launch may hand this
+// rank's rows to the exchange itself (sink_used = true); otherwise they are in d_part as usual.
+int kata::decode_partial_impl(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi, const void* d_q16, float* d_part,
+                              const kata::PeerSink* sink, const float* d_gate, void* d_out, int32_t out_dtype, bool* sink_used, void* stream) {
+    if (sink_used) *sink_used = false;
+    if (!h) return KATA_ERR_ARG;
+    Ctx& c = h->c;
+    if (T < 1 || T > 2) return fail(c, KATA_ERR_RANGE, "decode takes 1 or 2 query tokens, not %d", T);
+    if (!d_q16 || !d_part) return fail(c, KATA_ERR_ARG, "decode_partial needs q16 and part");
+    if (c.kvh_n != KATA_KV_HEADS) return fail(c, KATA_ERR_MODE, "decode_partial computes all four KV heads (this context owns %d)", c.kvh_n);
+    if (key_lo < 0 || key_hi < key_lo || pos_base < 0) return fail(c, KATA_ERR_RANGE, "key range [%d,%d) / pos_base %d", key_lo, key_hi, pos_base);
+    const int32_t local_rows = std::max(0, std::min(pos_base + T, key_hi) - key_lo);   // rows [0, local_rows) of this context hold keys key_lo..
+    if (layer < 0 || layer >= c.cfg.n_layers || seq < 0 || seq >= c.cfg.n_seqs) return fail(c, KATA_ERR_RANGE, "layer %d / sequence %d out of range", layer, seq);
+    if (local_rows > c.max_ctx[seq]) return fail(c, KATA_ERR_RANGE, "%d local rows exceed max_ctx %d", local_rows, c.max_ctx[seq]);
+    kata::Batch b{}; b.n = 1; b.seq[0] = seq; b.pos[0] = pos_base; b.row_base[0] = c.row_of(layer, seq);
+    DeviceGuard guard(c.cfg.device);
+    cudaError_t e = kata::launch_decode_mma_ex(c, b, T, 0, key_lo, &local_rows, (const __half*)d_q16, sink ? d_gate : nullptr, sink ? d_out : nullptr, sink ? out_dtype : KATA_ACT_F32, d_part, (cudaStream_t)stream, 0, 0, sink, sink_used);
+    return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "decode_partial launch");
+}
+

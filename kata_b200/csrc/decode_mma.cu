@@ -27,6 +27,7 @@
 #include <algorithm>
 
 #include "attn_tile.cuh"
+#include "peer_exchange.cuh"
 
 namespace kata {
 namespace {
@@ -312,37 +313,46 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 // contributor count. Launched with programmatic stream serialisation: the grid is set up while the decode kernel drains and waits for it here.
 constexpr int kCombineThreads = 1024;
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, float* __restrict__ part_out,
-                                                                         const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml) {
-    __shared__ float s_acc[3][256]; __shared__ float s_M, s_L;
+                                                                         const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml, const PeerSink px) {
+    __shared__ float s_acc[3][256]; __shared__ float s_M, s_L; __shared__ int s_ok;
     const int r = blockIdx.x, b = blockIdx.y / p.kvh_n, kvl = blockIdx.y % p.kvh_n, kvh = p.kvh_lo + kvl, seg = b * 4 + kvh, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
     const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvl * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
     pdl_wait();              // the decode kernel's partials are complete and visible from here on
     pdl_launch_dependents();
-    if (n_c == 1) return;   // a single contributor wrote the final row itself
-    const float* ml = scratch_ml + (int64_t)(c_first + seg) * 32 + r * 2;   // contributor c: ml[c * 32] = m, ml[c * 32 + 1] = l
-    if (tid < 32) {
-        float M = -INFINITY;
-        for (int c = tid; c < n_c; c += 32) M = fmaxf(M, __ldcg(ml + c * 32));
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-        float L = 0.0f;
-        for (int c = tid; c < n_c; c += 32) { const float mm = __ldcg(ml + c * 32); L += __ldcg(ml + c * 32 + 1) * ((mm == -INFINITY) ? 0.0f : ex2(mm - M)); }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
-        if (tid == 0) { s_M = M; s_L = L; }
-    }
-    __syncthreads();
-    const float M = s_M, L = s_L;
-    const float* po = scratch_o + (int64_t)(c_first + seg) * (12 * kD) + r * kD + d;
-    float A = 0.0f;
-#pragma unroll 8
-    for (int c = q; c < n_c; c += 4) { const float mm = __ldcg(ml + c * 32); A += __ldcg(po + (int64_t)c * (12 * kD)) * ((mm == -INFINITY) ? 0.0f : ex2(mm - M)); }
-    if (q) s_acc[q - 1][d] = A;
-    __syncthreads();
-    if (q) return;
-    A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
     const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
-    if (part_out) { float* po2 = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po2[d] = A; if (d == 0) { po2[256] = M * 0.6931471805599453f; po2[257] = L; } }
+    float A, M, L;
+    if (n_c == 1) {   // a single contributor wrote the final row itself; only a cross-GPU exchange still has work to do with it
+        if (px.world == 0 || q) return;
+        const float* po = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride;
+        A = po[d]; M = po[256] * 1.4426950408889634f; L = po[257];
+    } else {
+        const float* ml = scratch_ml + (int64_t)(c_first + seg) * 32 + r * 2;   // contributor c: ml[c * 32] = m, ml[c * 32 + 1] = l
+        if (tid < 32) {
+            float Mw = -INFINITY;
+            for (int c = tid; c < n_c; c += 32) Mw = fmaxf(Mw, __ldcg(ml + c * 32));
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) Mw = fmaxf(Mw, __shfl_xor_sync(0xffffffffu, Mw, off));
+            float Lw = 0.0f;
+            for (int c = tid; c < n_c; c += 32) { const float mm = __ldcg(ml + c * 32); Lw += __ldcg(ml + c * 32 + 1) * ((mm == -INFINITY) ? 0.0f : ex2(mm - Mw)); }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) Lw += __shfl_xor_sync(0xffffffffu, Lw, off);
+            if (tid == 0) { s_M = Mw; s_L = Lw; }
+        }
+        __syncthreads();
+        M = s_M; L = s_L;
+        const float* po = scratch_o + (int64_t)(c_first + seg) * (12 * kD) + r * kD + d;
+        A = 0.0f;
+#pragma unroll 8
+        for (int c = q; c < n_c; c += 4) { const float mm = __ldcg(ml + c * 32); A += __ldcg(po + (int64_t)c * (12 * kD)) * ((mm == -INFINITY) ? 0.0f : ex2(mm - M)); }
+        if (q) s_acc[q - 1][d] = A;
+        __syncthreads();
+        if (q) return;
+        A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
+    }
+    // 256 threads from here on (thread d = head dim d)
+    if (px.world > 0) {   // split-KV across GPUs: this rank's row goes straight into the exchange (push to the peers, wait for theirs, merge, gate)
+        peer_row_exchange(px, t, head, d, A, M * 0.6931471805599453f, L, gate, out, out_kind, &s_ok, 1);
+    } else if (part_out) { float* po2 = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride; po2[d] = A; if (d == 0) { po2[256] = M * 0.6931471805599453f; po2[257] = L; } }
     else {
         const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
         store_act(out, oi, y, out_kind);
@@ -379,7 +389,8 @@ static int max_contributors(const DecPlan& p) {
 
 // key_off / kend_override serve the split-KV-across-GPUs call: local row = absolute key - key_off, rows [first_row, kend).
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
-                                 float* part_out, cudaStream_t s, int tok_stride, int tok0) {
+                                 float* part_out, cudaStream_t s, int tok_stride, int tok0, const PeerSink* sink, bool* sink_used) {
+    if (sink_used) *sink_used = false;
     const int mode = c.cfg.kv_mode, kTile = c.k8() ? 32 : 16;
     DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off; p.kvh_lo = c.kvh_lo; p.kvh_n = c.kvh_n; p.tok_stride = tok_stride > 0 ? tok_stride : T; p.tok0 = tok0;
     int total = 0;
@@ -409,7 +420,10 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     if (le != cudaSuccess) return le;
     c.launches++;
     if (!p.merge_in_kernel) {
-        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, c.kvh_n * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)out_dtype, part_out, (const float*)c.part_o, (const float*)c.part_ml);
+        // with a cross-GPU exchange to feed (one sequence, rows in [T][6144] order) the combine grid does the exchange as well
+        const bool fuse = sink && sink->world > 0 && b.n == 1 && tok0 == 0 && p.tok_stride == T;
+        const cudaError_t e = launch_pdl(decode_combine_kernel, dim3(6 * T, c.kvh_n * b.n), dim3(kCombineThreads), 0, s, p, gate, out, (int)out_dtype, part_out, (const float*)c.part_o, (const float*)c.part_ml, fuse ? *sink : PeerSink{});
+        if (fuse && sink_used && e == cudaSuccess) *sink_used = true;
         if (e != cudaSuccess) return e;
         c.launches++;
     }
@@ -417,7 +431,7 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
 }
 
 cudaError_t launch_decode_mma(Ctx& c, const Batch& b, int T, int first_pos, int, const __half* q16, const float* gate, void* out, int out_dtype, float* part_out, cudaStream_t s) {
-    return launch_decode_mma_ex(c, b, T, first_pos, 0, nullptr, q16, gate, out, out_dtype, part_out, s, T, 0);
+    return launch_decode_mma_ex(c, b, T, first_pos, 0, nullptr, q16, gate, out, out_dtype, part_out, s, T, 0, nullptr, nullptr);
 }
 
 cudaError_t launch_merge_parts(Ctx& c, const float* parts, int n_parts, int T, const float* gate, void* out, int out_dtype, cudaStream_t s) {
@@ -497,6 +511,6 @@ extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_row
     if (cudaMemsetAsync(sd.scratch->counters, 0, sizeof(StaticScratch::counters) + sizeof(int32_t), s) != cudaSuccess) return KATA_ERR_CUDA;   // tickets and the error word start at zero
     decode_mma_kernel<KATA_KV_FP16><<<n_ctas, kThreads, Geo<KATA_KV_FP16>::kSmem, s>>>(tm_k, tm_v, p, (const __half*)d_q16, d_gate, d_out, out_dtype, nullptr, nullptr, nullptr,
                                                                          sd.scratch->part_o, sd.scratch->part_ml, sd.scratch->counters, &sd.scratch->err);
-    if (!p.merge_in_kernel) decode_combine_kernel<<<dim3(6 * T, 4 * n), kCombineThreads, 0, s>>>(p, d_gate, d_out, (int)out_dtype, nullptr, sd.scratch->part_o, sd.scratch->part_ml);
+    if (!p.merge_in_kernel) decode_combine_kernel<<<dim3(6 * T, 4 * n), kCombineThreads, 0, s>>>(p, d_gate, d_out, (int)out_dtype, nullptr, sd.scratch->part_o, sd.scratch->part_ml, PeerSink{});
     return cudaGetLastError() == cudaSuccess ? KATA_OK : KATA_ERR_CUDA;
 }

@@ -21,59 +21,20 @@
 #include <string>
 
 #include "kata_internal.cuh"
+#include "peer_exchange.cuh"
 
 namespace kata {
+int decode_partial_impl(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi, const void* d_q16, float* d_part,
+                        const PeerSink* sink, const float* d_gate, void* d_out, int32_t out_dtype, bool* sink_used, void* stream);
 namespace {
 
-constexpr int kPeerMaxWorld = 8, kPeerRows = 2 * kH;   // T <= 2 tokens x 24 heads
-
-struct PeerBases { float* base[kPeerMaxWorld]; };
-
-__host__ __device__ inline size_t peer_part_off(int world, int parity, int src_rank, int row) { return (((size_t)parity * world + src_rank) * kPeerRows + row) * kPartStride; }   // in floats
-__host__ __device__ inline size_t peer_flag_off(int world, int parity, int src_rank, int row) { return (size_t)2 * world * kPeerRows * kPartStride + ((size_t)parity * world + src_rank) * kPeerRows + row; }   // in 4-byte words
-inline size_t peer_bytes(int world) { return ((size_t)2 * world * kPeerRows * kPartStride + (size_t)2 * world * kPeerRows) * 4; }
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
-
-// grid (24 heads, T) x 256 threads
-__global__ void __launch_bounds__(256) peer_push_merge_kernel(const PeerBases pb, const int rank, const int world, const uint32_t seq, const uint32_t max_polls,
-                                                              const float* __restrict__ part, const int T, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, int32_t* err) {
+// grid (24 heads, T) x 256 threads: the exchange of rows a decode launch left in d_part
+__global__ void __launch_bounds__(256) peer_push_merge_kernel(const PeerSink px, const float* __restrict__ part, const float* __restrict__ gate, void* __restrict__ out, const int out_kind) {
     __shared__ int s_ok;
-    const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, row = t * kH + h, parity = (int)(seq & 1u);
+    const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
     pdl_wait(); pdl_launch_dependents();   // the local part comes from the decode kernel launched just before
-    const float* mine = part + (int64_t)row * kPartStride;
-    const float v = mine[tid], ml = tid < 2 ? mine[256 + tid] : 0.0f;
-    for (int r = 0; r < world; r++) {   // my row into everybody's buffer (my own included: the merge then reads one place)
-        float* dst = pb.base[r] + peer_part_off(world, parity, rank, row);
-        dst[tid] = v; if (tid < 2) dst[256 + tid] = ml;
-    }
-    __threadfence_system();
-    if (tid == 0) s_ok = 1;
-    __syncthreads();
-    if (tid < world) st_release_sys(reinterpret_cast<uint32_t*>(pb.base[tid]) + peer_flag_off(world, parity, rank, row), seq);
-    if (tid < world) {   // thread b waits for rank b's row
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(pb.base[rank]) + peer_flag_off(world, parity, tid, row);
-        bool ok = false;
-        for (uint32_t i = 0; i < max_polls; i++) {
-            if (ld_acquire_sys(flag) == seq) { ok = true; break; }
-            if ((i & 63u) == 63u && *reinterpret_cast<const volatile int32_t*>(err) != 0) break;   // another row already gave up
-            __nanosleep(500);
-        }
-        if (!ok) { s_ok = 0; atomicExch(err, 30 + tid); }
-    }
-    __syncthreads();
-    if (!s_ok) return;
-    const float* loc = pb.base[rank];
-    float M = -INFINITY;
-    for (int r = 0; r < world; r++) M = fmaxf(M, __ldcg(loc + peer_part_off(world, parity, r, row) + 256));
-    float L = 0.0f, A = 0.0f;
-    for (int r = 0; r < world; r++) {
-        const float* pp = loc + peer_part_off(world, parity, r, row); const float mm = __ldcg(pp + 256), wt = (mm == -INFINITY) ? 0.0f : expf(mm - M);
-        L += __ldcg(pp + 257) * wt; A += __ldcg(pp + tid) * wt;
-    }
-    const int64_t oi = (int64_t)t * kQD + h * kD + tid; const float y = (A / L) * (1.0f / (1.0f + expf(-gate[oi])));
-    store_act(out, oi, y, out_kind);
+    const float* mine = part + (int64_t)(t * kH + h) * kPartStride;
+    peer_row_exchange(px, t, h, tid, mine[tid], mine[256], mine[257], gate, out, out_kind, &s_ok, 1);
 }
 
 }  // namespace
@@ -82,7 +43,7 @@ __global__ void __launch_bounds__(256) peer_push_merge_kernel(const PeerBases pb
 struct kata_attn_peer {
     int device = 0, rank = 0, world = 1;
     float* local = nullptr; int32_t* d_err = nullptr; float* d_part = nullptr;   // d_part: this rank's part rows for kata_attn_peer_decode
-    kata::PeerBases bases{}; bool opened = false, ipc[kata::kPeerMaxWorld] = {};
+    float* bases[kata::kPeerMaxWorld] = {}; bool opened = false, ipc[kata::kPeerMaxWorld] = {};
     uint32_t seq = 0, max_polls = 1u << 20;   // about a second of polling at 0.5-1 us per poll
     uint64_t launches = 0;
     std::string err;
@@ -116,7 +77,7 @@ int kata_attn_peer_create(int32_t device, int32_t rank, int32_t world, kata_attn
     PeerGuard guard(device);
     if (cudaMalloc((void**)&p->local, peer_bytes(world)) != cudaSuccess || cudaMalloc((void**)&p->d_err, 4) != cudaSuccess || cudaMalloc((void**)&p->d_part, (size_t)kPeerRows * kPartStride * 4) != cudaSuccess) { cudaGetLastError(); kata_attn_peer_destroy(p); return KATA_ERR_NOMEM; }
     cudaMemset(p->local, 0, peer_bytes(world)); cudaMemset(p->d_err, 0, 4);
-    p->bases.base[rank] = p->local;
+    p->bases[rank] = p->local;
     if (handle_out) {
         static_assert(sizeof(cudaIpcMemHandle_t) == KATA_PEER_HANDLE_BYTES, "handle size");
         cudaIpcMemHandle_t hd;
@@ -138,7 +99,7 @@ int kata_attn_peer_open(kata_attn_peer* p, const void* handles) {
         void* ptr = nullptr;
         const cudaError_t e = cudaIpcOpenMemHandle(&ptr, hd, cudaIpcMemLazyEnablePeerAccess);
         if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "cudaIpcOpenMemHandle", e);
-        p->bases.base[r] = (float*)ptr; p->ipc[r] = true;
+        p->bases[r] = (float*)ptr; p->ipc[r] = true;
     }
     p->opened = true;
     return KATA_OK;
@@ -146,7 +107,7 @@ int kata_attn_peer_open(kata_attn_peer* p, const void* handles) {
 
 int kata_attn_peer_open_pointers(kata_attn_peer* p, void* const* bases) {
     if (!p || !bases) return KATA_ERR_ARG;
-    for (int r = 0; r < p->world; r++) if (r != p->rank) { if (!bases[r]) return pfail(p, KATA_ERR_ARG, "null peer buffer"); p->bases.base[r] = (float*)bases[r]; }
+    for (int r = 0; r < p->world; r++) if (r != p->rank) { if (!bases[r]) return pfail(p, KATA_ERR_ARG, "null peer buffer"); p->bases[r] = (float*)bases[r]; }
     p->opened = true;
     return KATA_OK;
 }
@@ -161,9 +122,9 @@ int kata_attn_peer_exchange_merge(kata_attn_peer* p, const float* d_part, int32_
     if (!p->opened) return pfail(p, KATA_ERR_MODE, "the peers' buffers have not been opened");
     if (!d_part || !d_gate || !d_out || T < 1 || T > 2 || (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16)) return pfail(p, KATA_ERR_ARG, "exchange_merge: part, gate, out, T in {1, 2}");
     PeerGuard guard(p->device);
-    const uint32_t seq = ++p->seq;
-    const cudaError_t e = launch_pdl(peer_push_merge_kernel, dim3(kH, T), dim3(256), 0, (cudaStream_t)stream, p->bases, p->rank, p->world, seq, p->max_polls, d_part, (int)T, d_gate, d_out,
-                                     (int)out_dtype, p->d_err);
+    PeerSink px{}; for (int r = 0; r < p->world; r++) px.base[r] = p->bases[r];
+    px.rank = p->rank; px.world = p->world; px.seq = ++p->seq; px.max_polls = p->max_polls; px.err = p->d_err;
+    const cudaError_t e = launch_pdl(peer_push_merge_kernel, dim3(kH, T), dim3(256), 0, (cudaStream_t)stream, px, d_part, d_gate, d_out, (int)out_dtype);
     if (e != cudaSuccess) return pfail(p, KATA_ERR_CUDA, "exchange launch", e);
     p->launches++;
     return KATA_OK;
@@ -172,7 +133,15 @@ int kata_attn_peer_exchange_merge(kata_attn_peer* p, const float* d_part, int32_
 int kata_attn_peer_decode(kata_attn_peer* p, kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
                           const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
     if (!p || !ctx) return KATA_ERR_ARG;
-    if (const int rc = kata_attn_decode_partial(ctx, layer, seq, pos_base, T, key_lo, key_hi, d_q16, p->d_part, stream)) return pfail(p, rc, kata_attn_last_error(ctx));
+    if (!p->opened) return pfail(p, KATA_ERR_MODE, "the peers' buffers have not been opened");
+    if (!d_gate || !d_out || (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16)) return pfail(p, KATA_ERR_ARG, "peer_decode: gate, out and a known output dtype");
+    // The exchange of this call, should the decode launch be able to do it itself (it can when its rows leave through the combine grid:
+    // long local slices); the call number is only consumed if it did.
+    PeerSink px{}; for (int r = 0; r < p->world; r++) px.base[r] = p->bases[r];
+    px.rank = p->rank; px.world = p->world; px.seq = p->seq + 1; px.max_polls = p->max_polls; px.err = p->d_err;
+    bool used = false;
+    if (const int rc = decode_partial_impl(ctx, layer, seq, pos_base, T, key_lo, key_hi, d_q16, p->d_part, &px, d_gate, d_out, out_dtype, &used, stream)) return pfail(p, rc, kata_attn_last_error(ctx));
+    if (used) { p->seq++; p->launches++; return KATA_OK; }
     return kata_attn_peer_exchange_merge(p, p->d_part, T, d_gate, d_out, out_dtype, stream);
 }
 
@@ -202,7 +171,7 @@ int kata_attn_peer_destroy(kata_attn_peer* p) {
     if (!p) return KATA_ERR_ARG;
     PeerGuard guard(p->device);
     cudaDeviceSynchronize();
-    for (int r = 0; r < p->world; r++) if (p->ipc[r] && p->bases.base[r]) cudaIpcCloseMemHandle(p->bases.base[r]);
+    for (int r = 0; r < p->world; r++) if (p->ipc[r] && p->bases[r]) cudaIpcCloseMemHandle(p->bases[r]);
     if (p->local) cudaFree(p->local);
     if (p->d_err) cudaFree(p->d_err);
     if (p->d_part) cudaFree(p->d_part);

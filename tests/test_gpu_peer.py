@@ -123,3 +123,28 @@ def test_push_and_merge_across_two_gpus(orc):
         ref = orc.formula_f32(q[pb:pb + T], gate[pb:pb + T], planes, pb)
         d = np.abs(fused - ref)
         assert d.max() < 2e-3 and d.mean() < 2e-4
+
+
+def test_one_rank_peer_decode_equals_plain_decode_short_and_long(capi):
+    # kata_attn_peer_decode on a group of one rank is a plain decode. When a sequence's keys are cut between more than 8 CTAs its rows leave
+    # through the combine grid, which then does the exchange itself (no launch of its own); otherwise (here: one CTA per 1024 keys of a
+    # 300-key sequence) the stand-alone exchange kernel follows the decode kernel. Both must equal kata_attn_decode.
+    px = capi.PeerExchange(0, 1)
+    gen = torch.Generator(device="cuda"); gen.manual_seed(51)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    for L, chunk in ((300, 1024), (300, 0), (20000, 0)):
+        ctx = capi.AttnContext(1, [L + 8], dec_chunk=chunk)
+        for st in range(0, L, 1024):
+            m = min(1024, L - st)
+            ctx.prep(0, [0], [st], m, None, torch.randn(1, m, 1024, generator=gen, device="cuda"), torch.randn(1, m, 1024, generator=gen, device="cuda"), None, kn, h0=24, nh=8)
+        for T in (1, 2):
+            qf = torch.randn(1, T, 12288, generator=gen, device="cuda"); kp = torch.randn(1, T, 1024, generator=gen, device="cuda"); vp = torch.randn(1, T, 1024, generator=gen, device="cuda")
+            q16, _, g = ctx.prep(0, [0], [L], T, qf, kp, vp, qn, kn)
+            want = ctx.decode(0, [0], [L], T, q16, g)
+            l0 = ctx.launches()
+            got = px.decode(ctx, 0, 0, L, T, 0, 1 << 30, q16, g[0])
+            px.check(); ctx.check()
+            assert ctx.launches() - l0 == (1 if chunk else 2)      # decode kernel (+ combine grid, which then carries the exchange)
+            assert (got - want[0]).abs().max().item() < 1e-5
+        ctx.close()
+    px.close()
