@@ -427,6 +427,29 @@ def run_splitkv(args, rank, world, kind_cfg, steps=None, warmup=None):
         e1.record(); barrier(); t1 = time.perf_counter()
         return e0.elapsed_time(e1), t0, t1
 
+    # the same sequence whole on one GPU, in the same harness (every rank on its own GPU, no communication; rank 0's figure is reported)
+    one = capi.AttnContext(N_LAYERS, [L + warmup + steps + 8], kv_mode=kv_mode)
+    g3 = torch.Generator(device=dev); g3.manual_seed(2000 + rank)
+    for layer in range(N_LAYERS):
+        for st in range(0, L, 1024):
+            m = min(1024, L - st)
+            one.prep(layer, [0], [st], m, None, torch.randn(1, m, 1024, generator=g3, device=dev), torch.randn(1, m, 1024, generator=g3, device=dev), None, kn[layer], h0=24, nh=8)
+    out1 = torch.empty(N_LAYERS, 1, 1, 6144, device=dev)
+
+    def step_one(pos):
+        for layer in range(N_LAYERS):
+            one.prep(layer, [0], [pos], 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], q16=q16[layer], gate=gate[layer])
+            one.decode(layer, [0], [pos], 1, q16[layer], gate[layer], out=out1[layer])
+    for i in range(warmup):
+        step_one(L + i)
+    one.check(); barrier()
+    o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    o0.record()
+    for i in range(steps):
+        step_one(L + warmup + i)
+    o1.record(); torch.cuda.synchronize()
+    ms_one = o0.elapsed_time(o1)
+    one.close(); del out1
     sampler = ClockSampler(torch.cuda.current_device()); sampler.start()
     l0 = ctx.launches()
     ms, tw0, tw1 = timed("peer", L)
@@ -443,7 +466,7 @@ def run_splitkv(args, rank, world, kind_cfg, steps=None, warmup=None):
     res = {"metric": METRIC, "value": steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
            "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
            "config": {"workload": f"decode, {N_LAYERS} layers, fp16 KV, ctx {L}, batch 1, keys split over {world} rank(s), parts pushed into the peers' buffers and merged in one kernel per layer", "global_batch": 1,
-                      "parallelism": f"split-KV x{world}", "tok_s_with_nccl_all_gather_and_merge_per_layer": steps / (ms_n * 1e-3),
+                      "parallelism": f"split-KV x{world}", "tok_s_one_gpu_same_harness": steps / (ms_one * 1e-3), "tok_s_with_nccl_all_gather_and_merge_per_layer": steps / (ms_n * 1e-3),
                       "tok_s_with_one_batched_all_gather_for_16_layers": steps / (ms_b * 1e-3), "l2": "inputs larger than L2"},
            "clocks": clocks, "gpu_launches": int(launches), "e2e": {"value": None, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "not measured for this workload"},
            "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": ach, "peak": pk["hbm_gbs"] * world, "unit": "GB/s", "frac": ach / (pk["hbm_gbs"] * world), "peak_src": pk["src"],

@@ -98,7 +98,7 @@ def out_fwht(x, sign, out=None):
 class AttnContext:
     """One context per GPU: the KV caches of ``len(max_ctx)`` sequences x ``n_layers`` layers plus all scratch."""
 
-    def __init__(self, n_layers: int, max_ctx, kv_mode: str = "fp16", quant_round: str = "rint", device: int | None = None, dec_chunk: int = 0, legacy_prefill: bool = False):
+    def __init__(self, n_layers: int, max_ctx, kv_mode: str = "fp16", quant_round: str = "rint", device: int | None = None, dec_chunk: int = 0, legacy_prefill: bool = False, flags: int = 0):
         self.L = lib()
         self.device = torch.cuda.current_device() if device is None else device
         self.max_ctx, mp = _i32(max_ctx)
@@ -106,7 +106,7 @@ class AttnContext:
         if kv_mode not in _KV_MODES:
             raise ValueError(f"kv_mode {kv_mode!r}: one of {sorted(_KV_MODES)}")
         self.int8, self.kv_mode = kv_mode == "int8", kv_mode
-        cfg = Config(self.device, n_layers, self.n_seqs, mp, _KV_MODES[kv_mode], ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, 1 if legacy_prefill else 0)
+        cfg = Config(self.device, n_layers, self.n_seqs, mp, _KV_MODES[kv_mode], ROUND_HALF_AWAY if quant_round == "half_away" else ROUND_RINT, dec_chunk, (1 if legacy_prefill else 0) | int(flags))
         self.h = C.c_void_p()
         rc = self.L.kata_attn_create(C.byref(cfg), C.byref(self.h))
         if rc != OK:

@@ -34,6 +34,14 @@ namespace {
 
 using namespace ptx;
 
+// Development aid, compiled only with -DKATA_PF_TRACE (never in the shipped library): every CTA records %globaltimer stamps of its phases.
+#ifdef KATA_PF_TRACE
+__device__ unsigned long long g_dec_trace[8 * 1536];
+__device__ __forceinline__ void dec_stamp(int slot) { if (blockIdx.x < 1536) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_dec_trace[blockIdx.x * 8 + slot] = t; } }
+#else
+__device__ __forceinline__ void dec_stamp(int) {}
+#endif
+
 constexpr int kRings = 4, kWarps = 3 * kRings + 1, kThreads = kWarps * 32, kMaxStages = 8;
 constexpr int kOffBars = 16 * kQStride;             // 8448: the barrier block: per ring and stage a 'full' and an 'empty' barrier,
 constexpr int kOffEBars = kRings * kMaxStages * 8, kOffPBars = 2 * kOffEBars;   // inside the barrier block: then per ring two 'P full' and two 'P empty' barriers
@@ -59,6 +67,7 @@ template <int MODE> struct Geo {
 
 struct DecPlan {
     int32_t n, T, first_row, key_off, n_ctas, q_tiles, r_tiles;   // CTA c owns tiles [c*q + min(c,r), (c+1)*q + min(c+1,r))
+    int32_t cps;                         // > 0: every (sequence, KV head) segment has the same number of tiles and is cut between exactly cps CTAs of its own (no CTA works on two segments)
     int32_t kvh_lo, kvh_n;               // KV heads of this launch: a sequence's tiles are those of heads kvh_lo .. kvh_lo + kvh_n - 1, head after head
     int32_t tok_stride, tok0;            // rows of q16 / gate / out per sequence, and the row of this launch's token 0 (a wide verify runs as launches of 2 tokens)
     int32_t merge_in_kernel;             // 1: the last contributor of a segment merges its partials; 0: decode_combine_kernel does
@@ -70,8 +79,12 @@ struct DecPlan {
     int32_t ntiles[KATA_MAX_BATCH];      // tiles per KV head of sequence b (>= 1)
 };
 
-__device__ __forceinline__ int cta_first_tile(const DecPlan& p, int c) { return c * p.q_tiles + min(c, p.r_tiles); }
-__device__ __forceinline__ int cta_of_tile(const DecPlan& p, int tile) {
+__host__ __device__ __forceinline__ int cta_first_tile(const DecPlan& p, int c) {
+    if (p.cps) { const int seg = c / p.cps, j = c - seg * p.cps, nt = p.ntiles[0]; return seg * nt + (int)((int64_t)nt * j / p.cps); }
+    return c * p.q_tiles + (c < p.r_tiles ? c : p.r_tiles);
+}
+__host__ __device__ __forceinline__ int cta_of_tile(const DecPlan& p, int tile) {
+    if (p.cps) { const int nt = p.ntiles[0], seg = tile / nt, lt = tile - seg * nt; return seg * p.cps + (int)(((int64_t)(lt + 1) * p.cps + nt - 1) / nt) - 1; }   // the last share whose first tile is <= lt
     const int big = p.r_tiles * (p.q_tiles + 1);
     return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles;
 }
@@ -82,7 +95,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
     using G = Geo<MODE>; constexpr bool K8 = G::K8, V8 = G::V8; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
-    if (threadIdx.x == 0) { prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); }
+    if (threadIdx.x == 0) { prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); dec_stamp(0); }
     if (!p.merge_in_kernel) pdl_launch_dependents();   // the next kernel is the combine grid, which starts no loads of its own before it has waited for this one: it may be set up at once
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, ring = w & 3, h = w >> 2, g = lane >> 2, t4 = lane & 3;   // warps ring, ring+4 and ring+8 sit on the same scheduler: h = 0 score warp, h = 1, 2 value warps
@@ -142,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             }
             if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
             if (lane < kRings) produce(n_early, kStages);
-        } else if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
+        } else if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; if (tid == 0) dec_stamp(1); }
         auto load_scale = [&](int i, const __half* plane) -> uint32_t {
             const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
             return __ldg(reinterpret_cast<const unsigned short*>(plane) + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 4 + kvh);
@@ -198,6 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                     ks_[q >> 1][q & 1] = K8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, k_cur, src))) : 1.0f;
                     vs_[q >> 1][q & 1] = V8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, v_cur, src))) : 1.0f;
                 }
+                if (i == 0 && tid == 0 && it_seg == 0) dec_stamp(2);
                 float pr[2 * NK][4], al0, al1;
                 score_tile<K8, V8, NK>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
                 __syncwarp();
@@ -239,6 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
 
         // ---- merge the 4 rings of the CTA (every issued tile was waited for, so no copy is in flight)
         __syncthreads();
+        if (tid == 0) dec_stamp(3);
         float* mo = reinterpret_cast<float*>(smem + stage_off + ring * G::kRingBytes);
         if (h == 1 || h == 2) {
 #pragma unroll
@@ -303,22 +318,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
         __syncthreads();   // merge buffers and the Q block are reused by the next segment
         tile = my_end;
     }
+    if (tid == 0) dec_stamp(4);
 }
 
 // Merge of the per-CTA partials of every split segment, one CTA per (row, segment). Used instead of the in-kernel ticket merge when a segment
-// has many contributors (batch 1 at long context: ~37 per KV head; 256 per KV head with the reference's 128-key splits at 32K): a single
-// last-arriver CTA would pull all of them through one SM, while this grid does it in parallel. Warp 0 forms the row maximum and the merged l;
-// then the 1024 threads (4 groups of 256 head dims, group q taking contributors q, q+4, ...) accumulate the weighted O rows with independent
-// loads, each thread forming the weight exp(m - M) of its contributor itself (a broadcast load of m), so that nothing is sized by the
-// contributor count. Launched with programmatic stream serialisation: the grid is set up while the decode kernel drains and waits for it here.
+// has many contributors (batch 1 at long context: 37 per KV head; 256 per KV head with the reference's 128-key splits at 32K): a single
+// last-arriver CTA would pull all of them through one SM, while this grid does it in parallel: 1024 threads = 4 groups of 256 head dims,
+// group q folding contributors q, q+4, ... with a running maximum of its own (nothing is sized by the contributor count). Launched with programmatic stream serialisation: the grid is set up while the decode kernel drains and waits for it here.
 constexpr int kCombineThreads = 1024;
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const DecPlan p, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, float* __restrict__ part_out,
                                                                          const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml, const PeerSink px) {
-    __shared__ float s_acc[3][256]; __shared__ float s_M, s_L; __shared__ int s_ok;
+    __shared__ float s_acc[4][256]; __shared__ float s_Mq[4], s_Lq[4]; __shared__ int s_ok;
     const int r = blockIdx.x, b = blockIdx.y / p.kvh_n, kvl = blockIdx.y % p.kvh_n, kvh = p.kvh_lo + kvl, seg = b * 4 + kvh, tid = threadIdx.x, d = tid & 255, q = tid >> 8;
     const int nt = p.ntiles[b], seg_first = p.tile_start[b] + kvl * nt, c_first = cta_of_tile(p, seg_first), c_last = cta_of_tile(p, seg_first + nt - 1), n_c = c_last - c_first + 1;
     pdl_wait();              // the decode kernel's partials are complete and visible from here on
     pdl_launch_dependents();
+#ifdef KATA_PF_TRACE
+    if (tid == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); g_dec_trace[(1400 + blockIdx.y * 12 + blockIdx.x) * 8 + 5] = tt; }
+#endif
     const int t = r / 6, j = r - 6 * t, head = kvh * 6 + j;
     float A, M, L;
     if (n_c == 1) {   // a single contributor wrote the final row itself; only a cross-GPU exchange still has work to do with it
@@ -326,28 +343,35 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
         const float* po = part_out + ((int64_t)(b * p.tok_stride + p.tok0 + t) * kH + head) * kPartStride;
         A = po[d]; M = po[256] * 1.4426950408889634f; L = po[257];
     } else {
+        // Group q of 256 threads takes contributors q, q + 4, ...: every thread requests (m, l, O[d]) of up to twelve of them at once (one round
+        // trip to L2 for the 37 contributors of a 32K sequence; m and l are the same addresses across a group: broadcasts) and folds them
+        // into its own running (M, L, A); the four groups are then folded through shared memory.
         const float* ml = scratch_ml + (int64_t)(c_first + seg) * 32 + r * 2;   // contributor c: ml[c * 32] = m, ml[c * 32 + 1] = l
-        if (tid < 32) {
-            float Mw = -INFINITY;
-            for (int c = tid; c < n_c; c += 32) Mw = fmaxf(Mw, __ldcg(ml + c * 32));
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) Mw = fmaxf(Mw, __shfl_xor_sync(0xffffffffu, Mw, off));
-            float Lw = 0.0f;
-            for (int c = tid; c < n_c; c += 32) { const float mm = __ldcg(ml + c * 32); Lw += __ldcg(ml + c * 32 + 1) * ((mm == -INFINITY) ? 0.0f : ex2(mm - Mw)); }
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) Lw += __shfl_xor_sync(0xffffffffu, Lw, off);
-            if (tid == 0) { s_M = Mw; s_L = Lw; }
-        }
-        __syncthreads();
-        M = s_M; L = s_L;
         const float* po = scratch_o + (int64_t)(c_first + seg) * (12 * kD) + r * kD + d;
-        A = 0.0f;
-#pragma unroll 8
-        for (int c = q; c < n_c; c += 4) { const float mm = __ldcg(ml + c * 32); A += __ldcg(po + (int64_t)c * (12 * kD)) * ((mm == -INFINITY) ? 0.0f : ex2(mm - M)); }
-        if (q) s_acc[q - 1][d] = A;
+        float Mq = -INFINITY, Lq = 0.0f, Aq = 0.0f;
+        for (int c0 = q; c0 < n_c; c0 += 48) {
+            float mm[12], ll[12], oo[12];
+#pragma unroll
+            for (int u = 0; u < 12; u++) {
+                const int c = c0 + 4 * u; const bool ok = c < n_c;
+                mm[u] = ok ? __ldcg(ml + c * 32) : -INFINITY; ll[u] = ok ? __ldcg(ml + c * 32 + 1) : 0.0f; oo[u] = ok ? __ldcg(po + (int64_t)c * (12 * kD)) : 0.0f;
+            }
+            float Mn = Mq;
+#pragma unroll
+            for (int u = 0; u < 12; u++) Mn = fmaxf(Mn, mm[u]);
+            const float keep = (Mq == -INFINITY) ? 0.0f : ex2(Mq - Mn);
+            Aq *= keep; Lq *= keep; Mq = Mn;
+#pragma unroll
+            for (int u = 0; u < 12; u++) { const float wt = (mm[u] == -INFINITY) ? 0.0f : ex2(mm[u] - Mn); Aq = fmaf(oo[u], wt, Aq); Lq = fmaf(ll[u], wt, Lq); }
+        }
+        s_acc[q][d] = Aq;
+        if (d == 0) { s_Mq[q] = Mq; s_Lq[q] = Lq; }
         __syncthreads();
         if (q) return;
-        A += s_acc[0][d] + s_acc[1][d] + s_acc[2][d];
+        M = fmaxf(fmaxf(s_Mq[0], s_Mq[1]), fmaxf(s_Mq[2], s_Mq[3]));
+        A = 0.0f; L = 0.0f;
+#pragma unroll
+        for (int g4 = 0; g4 < 4; g4++) { const float wt = (s_Mq[g4] == -INFINITY) ? 0.0f : ex2(s_Mq[g4] - M); A = fmaf(s_acc[g4][d], wt, A); L = fmaf(s_Lq[g4], wt, L); }
     }
     // 256 threads from here on (thread d = head dim d)
     if (px.world > 0) {   // split-KV across GPUs: this rank's row goes straight into the exchange (push to the peers, wait for theirs, merge, gate)
@@ -357,6 +381,9 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(const D
         const int64_t oi = ((int64_t)b * p.tok_stride + p.tok0 + t) * kQD + head * kD + d; const float y = (A / L) * sigmoid_fast(gate[oi]);
         store_act(out, oi, y, out_kind);
     }
+#ifdef KATA_PF_TRACE
+    if (tid == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); g_dec_trace[(1400 + blockIdx.y * 12 + blockIdx.x) * 8 + 6] = tt; }
+#endif
 }
 
 // Merge of per-rank partials {O[256], m, l} (m in natural-log units) and the output gate: k_attn_dec_combine with "split" = rank.
@@ -371,6 +398,10 @@ __global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restric
 
 }  // namespace
 
+#ifdef KATA_PF_TRACE
+extern "C" int kata_debug_dec_trace(unsigned long long* h) { return (int)cudaMemcpyFromSymbol(h, g_dec_trace, sizeof(g_dec_trace)); }
+#endif
+
 int decode_max_slots(int sm_count) { return sm_count + 4 * KATA_MAX_BATCH; }
 
 // Shared-memory opt-in of the decode kernel on the current device (function attributes are per device: done once per context).
@@ -381,7 +412,7 @@ cudaError_t configure_decode(int kv_mode) {
 }
 
 static int max_contributors(const DecPlan& p) {
-    auto cta_of = [&](int tile) { const int big = p.r_tiles * (p.q_tiles + 1); return tile < big ? tile / (p.q_tiles + 1) : p.r_tiles + (tile - big) / p.q_tiles; };
+    auto cta_of = [&](int tile) { return cta_of_tile(p, tile); };
     int m = 1;
     for (int i = 0; i < p.n; i++) for (int kv = 0; kv < p.kvh_n; kv++) { const int f = p.tile_start[i] + kv * p.ntiles[i]; m = std::max(m, cta_of(f + p.ntiles[i] - 1) - cta_of(f) + 1); }
     return m;
@@ -406,6 +437,14 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     n_ctas = std::max(1, std::min(std::min(n_ctas, total), c.sm_count * 8));
     if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
     p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
+    // A CTA whose range crosses from one segment into the next pays for it (ring merge, partial write, the Q block of the next segment, the
+    // pipeline filled again: 4 to 5 us measured, which made the few such CTAs the last to finish). When all segments are equally long (one
+    // sequence, or a batch of equal lengths) and their number divides nearly all SMs, every segment gets the same number of CTAs of its own.
+    if (!chunk_tiles) {
+        bool same = true; for (int i = 1; i < b.n; i++) same = same && p.ntiles[i] == p.ntiles[0];
+        const int n_seg = b.n * c.kvh_n, cps = n_seg <= c.sm_count ? c.sm_count / n_seg : 0;
+        if (same && cps >= 1 && cps * n_seg * 100 >= c.sm_count * 97 && p.ntiles[0] >= cps && cps * n_seg + 4 * b.n <= c.max_items) { p.cps = cps; p.n_ctas = n_ctas = cps * n_seg; p.q_tiles = p.ntiles[0] / cps; p.r_tiles = 0; }
+    }
     // Early loads pay when a CTA streams for long (batch 8 at 16-32K: -2 us of 140); with short ranges (batch 1: 55 tiles per CTA) they take
     // bandwidth from the previous kernel's last CTAs, which everybody then waits for (+2 us of 31): switched off there.
     // Nor are rows loaded early while caller kernels may be writing any of them through a plane pointer without having said which.
