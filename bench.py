@@ -49,6 +49,7 @@ WORKLOADS = {
     "decode_int8_b32": ("decode", 32, "int8", 32768, 16384),
     "decode_int8_8k_b1": ("decode", 1, "int8", 8192, 8192),      # benchmark config 4 at its short context
     "decode_int8_8k_b32": ("decode", 32, "int8", 8192, 8192),
+    "decode_int8g_b8": ("decode", 8, "int8g", 32768, 16384),    # int8 keys with one scale per 64 dims (four per head row), int8 values
     "decode_int8v_b8": ("decode", 8, "int8v", 32768, 16384),    # keys fp16, values int8 (the reference's KATA_KV=int8v)
     "splitkv_b1": ("splitkv", 1, "fp16", 32768, 32768),       # one 32K sequence, keys split across the ranks, parts pushed to the peers and merged per layer
     "splitkv_b1_128k": ("splitkv", 1, "fp16", 131072, 131072),  # the same at 131,072 keys, where one GPU's HBM time dominates the exchange
@@ -64,7 +65,7 @@ WORKLOADS = {
 }
 
 
-EXTRAS_ONE_GPU = ["pp512", "decode_b1", "decode_b64", "decode_int8_b8", "decode_int8_b32", "decode_int8_8k_b1", "decode_int8_8k_b32", "chunked_b1", "chunked_b16"]
+EXTRAS_ONE_GPU = ["pp512", "decode_b1", "decode_b64", "decode_int8_b8", "decode_int8_b32", "decode_int8_8k_b1", "decode_int8_8k_b32", "decode_int8v_b8", "decode_int8g_b8", "chunked_b1", "chunked_b16"]
 EXTRAS_MULTI_GPU = ["splitkv_b1", "splitkv_b1_128k"]      # strong scaling: one sequence, keys split across the ranks
 EXTRAS_BUDGET_S = 400.0                                    # extras not started after this many seconds of the run are skipped (and say so)
 METRIC = "gated-GQA attn tok/s (decode@32K, pp512); HBM GB/s & TC util vs peak"
@@ -278,7 +279,7 @@ def run_decode(args, rank, world, kind_cfg, steps=None, warmup=None, sustained_s
     h2d = N_LAYERS * B * (12288 + 2048) * 4
     d2h = N_LAYERS * B * 6144 * 4
 
-    row_bytes = {"fp16": 4096, "int8": 2064, "int8v": 3080}[kv_mode]   # K+V bytes per key per layer (int8: codes + both fp16 scales; int8v: fp16 keys, value codes + their scales)
+    row_bytes = {"fp16": 4096, "int8": 2064, "int8v": 3080, "int8g": 2088}[kv_mode]   # K+V bytes per key per layer (int8: codes + both fp16 scales; int8v: fp16 keys, value codes + their scales)
     bytes_per_launch = float(np.sum(pos_timed0 + 1)) * row_bytes
     per_rank = None
     if world > 1:
@@ -340,10 +341,10 @@ def cpu_baseline_decode(ctx, pos, B, kv_mode):
         planes = []
         for s in range(nb):
             n = int(pos[s]) + 1
-            pl = orc.KvPlanes(n, int8=(kv_mode == "int8"), int8v=(kv_mode == "int8v"))
+            pl = orc.KvPlanes(n, int8=(kv_mode == "int8"), int8v=(kv_mode == "int8v"), int8g=(kv_mode == "int8g"))
             pl.k[:] = ctx.plane_read(0, s, 0, 0, n).view(pl.k.dtype).reshape(n, 1024); pl.v[:] = ctx.plane_read(0, s, 1, 0, n).view(np.int8).reshape(n, 1024)
-            if kv_mode == "int8":
-                pl.ksc[:] = ctx.plane_read(0, s, 2, 0, n).view(np.uint16).reshape(n, 4)
+            if kv_mode in ("int8", "int8g"):
+                pl.ksc[:] = ctx.plane_read(0, s, 2, 0, n).view(np.uint16).reshape(n, -1)
             pl.vsc[:] = ctx.plane_read(0, s, ctx.kv_planes() - 1, 0, n).view(np.uint16).reshape(n, 4)
             planes.append(pl)
         t0 = time.perf_counter()

@@ -41,7 +41,9 @@ extern "C" {
 #define KATA_STATIC_MAX_BATCH 8 /* sequences per kata_attn_decode_static call */
 
 enum { KATA_OK = 0, KATA_ERR_ARG = 1, KATA_ERR_RANGE = 2, KATA_ERR_MODE = 3, KATA_ERR_CUDA = 4, KATA_ERR_DEVICE_WAIT = 5, KATA_ERR_NOMEM = 6 };
-enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1, KATA_KV_INT8V = 2 };   /* KATA_KV=fp16|int8|int8v (src/engine.cpp:54-59); int8v: keys fp16, values int8 (src/engine.h:71-73) */
+enum { KATA_KV_FP16 = 0, KATA_KV_INT8 = 1, KATA_KV_INT8V = 2, KATA_KV_INT8G = 3 };   /* KATA_KV=fp16|int8|int8v (src/engine.cpp:54-59); int8v: keys fp16, values int8 (src/engine.h:71-73);
+   int8g (no reference mode): int8 keys with one fp16 scale per 64 dims (4 per head row) and int8 values with one per row: the granularity the reference measured as
+   closing most of the int8 quality gap (docs/reports/M11-int8-kv.en.md:52-55) but could not fold into its matrix kernels (:94-97). rint rounding only. */
 enum { KATA_ROUND_RINT = 0, KATA_ROUND_HALF_AWAY = 1 };  /* rint (ties to even) is what the reference kernel does (shaders/flash.metal:170) */
 enum { KATA_ACT_F32 = 0, KATA_ACT_BF16 = 1, KATA_ACT_F16 = 2 };   /* dtype of qfull / kproj / vproj / out (the reference's activations are fp32) */
 
@@ -67,7 +69,7 @@ int kata_attn_destroy(kata_attn_ctx* ctx);
 /* Engine::resetState, cache part (src/engine.cpp:88-95): zero the caches and scale planes. */
 int kata_attn_reset(kata_attn_ctx* ctx, void* stream);
 
-/* Engine::numericsTag, KV part (src/engine.cpp:517-521): "fp16" or "fp16+kv8"; checkpoints of different tags never mix. */
+/* Engine::numericsTag, KV part (src/engine.cpp:517-521): "fp16", "fp16+kv8", "fp16+kv8v" or "fp16+kv8g"; checkpoints of different tags never mix. */
 const char* kata_attn_numerics_tag(const kata_attn_ctx* ctx);
 const char* kata_attn_last_error(const kata_attn_ctx* ctx);
 
@@ -180,7 +182,7 @@ int kata_attn_out_fwht(const float* d_x, const float* d_sign, float* d_out, int6
 /* KV planes for the prefix cache: Engine::kvPlanes / kvPlaneRow / kvPlanePtr (src/engine.h:74-81), used by
  * PrefixCache::restore and ::writeFile (src/ckpt.cpp:98, 134). Plane order and row sizes match the reference:
  * fp16 -> {K, V} rows of 2048 B; int8 -> {K, V, K scales, V scales} rows of 1024, 1024, 8, 8 B;
- * int8v -> {K, V, V scales} rows of 2048, 1024, 8 B.
+ * int8v -> {K, V, V scales} rows of 2048, 1024, 8 B; int8g -> {K, V, K scales, V scales} rows of 1024, 1024, 32, 8 B (K scales: [head][64-dim group]).
  * The reference reads and writes shared memory directly; here the copy is explicit and synchronous. */
 int32_t kata_attn_kv_planes(const kata_attn_ctx* ctx);
 size_t kata_attn_kv_plane_row_bytes(const kata_attn_ctx* ctx, int32_t plane);
@@ -208,9 +210,14 @@ int kata_attn_mark_rows_written(kata_attn_ctx* ctx, int32_t seq, int32_t pos_lo)
  * KATA_STATIC_MAX_BATCH (more: KATA_ERR_RANGE), T in {1,2}, at most 148 CTAs. The first call on a device does that
  * device's set-up and must be made outside stream capture. All calls on a device share the scratch: calls that overlap
  * on the GPU race on it and must be serialised by the caller, the first call included (two host threads making a device's first call
- * at the same time also race on the set-up). A bounded device wait that runs out is not reported here. */
+ * at the same time also race on the set-up). A bounded device wait that runs out is not reported by this call (it only enqueues work):
+ * kata_attn_decode_static_check tells. */
 int kata_attn_decode_static(const void* d_k_rows, const void* d_v_rows, int64_t total_rows, int32_t n, const int64_t* seq_row0, const int32_t* pos_base,
                             int32_t T, int32_t first_pos, const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+
+/* No counterpart in the reference. Synchronises the stream and returns KATA_ERR_DEVICE_WAIT if a bounded device-side wait ran out in the
+ * last kata_attn_decode_static call on the current device (its output is then invalid), else KATA_OK. Allocates nothing. */
+int kata_attn_decode_static_check(void* stream);
 
 /* Number of kernels this library has launched on this context since creation (for accounting in benchmarks). */
 uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);

@@ -15,8 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libkata_attn.so")
 
 OK = 0
-KV_FP16, KV_INT8, KV_INT8V = 0, 1, 2
-_KV_MODES = {"fp16": KV_FP16, "int8": KV_INT8, "int8v": KV_INT8V}   # the reference's KATA_KV values (src/engine.cpp:54)
+KV_FP16, KV_INT8, KV_INT8V, KV_INT8G = 0, 1, 2, 3
+_KV_MODES = {"fp16": KV_FP16, "int8": KV_INT8, "int8v": KV_INT8V, "int8g": KV_INT8G}   # the reference's KATA_KV values (src/engine.cpp:54)
 ROUND_RINT, ROUND_HALF_AWAY = 0, 1
 ACT_F32, ACT_BF16, ACT_F16 = 0, 1, 2
 _ACT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}   # KATA_ACT_*
@@ -26,7 +26,7 @@ EXPORTS = [
     "kata_attn_create", "kata_attn_destroy", "kata_attn_reset", "kata_attn_numerics_tag", "kata_attn_last_error", "kata_attn_check",
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
-    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
+    "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_decode_static_check", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
     "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode",
     "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",

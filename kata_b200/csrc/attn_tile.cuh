@@ -199,10 +199,14 @@ template <int NJ> struct ValueStateT {   // NJ n-tiles of 8 dims: 16 = one half 
 // Score warp, one tile. Returns the unrounded-then-scaled P values pr[n-tile][4] (n-tile nt = 8 keys: keys key0 + 8*nt + 2*t4 + e are
 // elements e and 2 + e for rows g and g + 8) and the rescale factors of rows g and g + 8. ks/vs: int8 scales of this thread's score
 // columns ([nt][e]); qs: int8 mode, sums over the 256 dims of Q rows g and g+8.
-template <bool I8, bool V8, int NK>   // I8: int8 keys; V8: int8 values (P takes the value scale before it is rounded to fp16)
+// KG (int8 keys with one scale per 64 dims): ksg[nt][e] holds the four fp16 group scales of the key of score column (nt, e) as two packed
+// words, qsg[row half][group] the sums of the staged Q rows g and g + 8 over each 64-dim group; the contraction is then cut into the four
+// groups and each group's partial score takes its own scale: S = sum_g ks_g * (Q_g . Kq_g), the finer key quantisation the reference measured
+// but could not fold into its matrix path (docs/reports/M11-int8-kv.en.md:52-55, 94-97).
+template <bool I8, bool V8, int NK, bool KG = false>   // I8: int8 keys; V8: int8 values (P takes the value scale before it is rounded to fp16)
 __device__ __forceinline__ void score_tile(const uint32_t q_sm, const uint32_t k_sm, const int key0, const int lim0, const int lim1,
                                            const float (&ks)[2 * NK][2], const float (&vs)[2 * NK][2], const float (&qs)[2], ScoreState& st, const int lane,
-                                           float (&pr)[2 * NK][4], float& al0, float& al1) {
+                                           float (&pr)[2 * NK][4], float& al0, float& al1, const uint2 (*ksg)[2] = nullptr, const float (*qsg)[4] = nullptr) {
     using namespace ptx;
     constexpr uint32_t kBlk = 16 * NK * 128;   // bytes of one 128-byte column block of the tile
     constexpr int NT = 2 * NK;
@@ -233,6 +237,42 @@ __device__ __forceinline__ void score_tile(const uint32_t q_sm, const uint32_t k
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) s[nt][e] += s2[nt][e];
+    } else if (KG) {
+        float tot[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) { tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.0f; }
+#pragma unroll
+        for (int g4 = 0; g4 < 4; g4++) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) { s[nt][e] = 0.0f; s2[nt][e] = 0.0f; }
+#pragma unroll
+            for (int k2 = 2 * g4; k2 < 2 * g4 + 2; k2++) {
+                uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+                ldsm_x4(qa + (2 * k2) * 32, a0, a1, a2, a3); ldsm_x4(qa + (2 * k2 + 1) * 32, c0, c1, c2, c3);
+#pragma unroll
+                for (int sb = 0; sb < NK; sb++) {
+                    uint32_t r0, r1, r2, r3;
+                    ldsm_x4(ka + sb * 2048 + (k2 >> 2) * kBlk + ko[k2 & 3], r0, r1, r2, r3);
+                    r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+                    mma16816(s[2 * sb], a0, a1, a2, a3, deq2_biased(r0, 0x4140u), deq2_biased(r0, 0x4342u)); mma16816(s[2 * sb + 1], a0, a1, a2, a3, deq2_biased(r2, 0x4140u), deq2_biased(r2, 0x4342u));
+                    mma16816(s2[2 * sb], c0, c1, c2, c3, deq2_biased(r1, 0x4140u), deq2_biased(r1, 0x4342u)); mma16816(s2[2 * sb + 1], c0, c1, c2, c3, deq2_biased(r3, 0x4140u), deq2_biased(r3, 0x4342u));
+                }
+            }
+            const float b0 = kI8Bias * qsg[0][g4], b1 = kI8Bias * qsg[1][g4];   // this group's scores were formed against code + 1152
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const uint32_t w0 = (g4 < 2) ? ksg[nt][0].x : ksg[nt][0].y, w1 = (g4 < 2) ? ksg[nt][1].x : ksg[nt][1].y;   // packed fp16 scales of groups (0,1) or (2,3)
+                const float k0 = __half2float(__ushort_as_half((unsigned short)((g4 & 1) ? (w0 >> 16) : (w0 & 0xffffu)))), k1 = __half2float(__ushort_as_half((unsigned short)((g4 & 1) ? (w1 >> 16) : (w1 & 0xffffu))));
+                tot[nt][0] = fmaf(s[nt][0] + s2[nt][0] - b0, k0, tot[nt][0]); tot[nt][1] = fmaf(s[nt][1] + s2[nt][1] - b0, k1, tot[nt][1]);
+                tot[nt][2] = fmaf(s[nt][2] + s2[nt][2] - b1, k0, tot[nt][2]); tot[nt][3] = fmaf(s[nt][3] + s2[nt][3] - b1, k1, tot[nt][3]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[nt][e] = tot[nt][e];
     } else {
 #pragma unroll
         for (int k2 = 0; k2 < 8; k2++) {   // int8: 16-byte chunk = 16-dim block; r0: keys 0-7 block 2*k2, r1: keys 0-7 block 2*k2+1, r2, r3: keys 8-15

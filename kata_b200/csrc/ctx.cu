@@ -65,7 +65,7 @@ bool plane_ref(Ctx& c, int plane, PlaneRef& r) {
     // kvPlanePtr (src/engine.h:79-81): plane 2 is the K scales when the keys are int8, else the V scales
     if (plane == 0) { r = {(uint8_t*)c.k_arena, (size_t)kata::kKVD * c.elt_k}; return true; }
     if (plane == 1) { r = {(uint8_t*)c.v_arena, (size_t)kata::kKVD * c.elt_v}; return true; }
-    if (c.k8() && plane == 2) { r = {(uint8_t*)c.ksc, 8}; return true; }
+    if (c.k8() && plane == 2) { r = {(uint8_t*)c.ksc, (size_t)2 * c.ksc_per_row()}; return true; }
     if (c.v8() && plane == (c.k8() ? 3 : 2)) { r = {(uint8_t*)c.vsc, 8}; return true; }
     return false;
 }
@@ -77,7 +77,8 @@ extern "C" {
 int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     if (!cfg || !out) return KATA_ERR_ARG;
     *out = nullptr;
-    if (cfg->n_layers < 1 || cfg->n_seqs < 1 || !cfg->max_ctx || (cfg->kv_mode != KATA_KV_FP16 && cfg->kv_mode != KATA_KV_INT8 && cfg->kv_mode != KATA_KV_INT8V) ||
+    if (cfg->n_layers < 1 || cfg->n_seqs < 1 || !cfg->max_ctx || (cfg->kv_mode != KATA_KV_FP16 && cfg->kv_mode != KATA_KV_INT8 && cfg->kv_mode != KATA_KV_INT8V && cfg->kv_mode != KATA_KV_INT8G) ||
+        (cfg->kv_mode == KATA_KV_INT8G && (cfg->quant_round != KATA_ROUND_RINT || (cfg->flags & 1))) ||
         (cfg->quant_round != KATA_ROUND_RINT && cfg->quant_round != KATA_ROUND_HALF_AWAY) || cfg->dec_chunk < 0) return KATA_ERR_ARG;
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || cfg->device < 0 || cfg->device >= ndev) return KATA_ERR_CUDA;
@@ -86,8 +87,8 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     Ctx& c = h->c; c.cfg = *cfg; c.cfg.max_ctx = nullptr;
     DeviceGuard guard(cfg->device);
     cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, cfg->device);
-    c.elt_k = cfg->kv_mode == KATA_KV_INT8 ? 1 : 2; c.elt_v = cfg->kv_mode == KATA_KV_FP16 ? 2 : 1;
-    c.tag = cfg->kv_mode == KATA_KV_INT8 ? "fp16+kv8" : cfg->kv_mode == KATA_KV_INT8V ? "fp16+kv8v" : "fp16";   // Engine::numericsTag, src/engine.cpp:517-521
+    c.elt_k = (cfg->kv_mode == KATA_KV_INT8 || cfg->kv_mode == KATA_KV_INT8G) ? 1 : 2; c.elt_v = cfg->kv_mode == KATA_KV_FP16 ? 2 : 1;
+    c.tag = cfg->kv_mode == KATA_KV_INT8 ? "fp16+kv8" : cfg->kv_mode == KATA_KV_INT8V ? "fp16+kv8v" : cfg->kv_mode == KATA_KV_INT8G ? "fp16+kv8g" : "fp16";   // Engine::numericsTag, src/engine.cpp:517-521
     int64_t rows = 0;
     for (int s = 0; s < cfg->n_seqs; s++) {
         if (cfg->max_ctx[s] < 1) { delete h; return KATA_ERR_ARG; }
@@ -96,7 +97,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     c.total_rows = rows;
     c.max_items = kata::decode_max_slots(c.sm_count * 8);
     bool ok = cudaMalloc(&c.k_arena, (size_t)rows * kata::kKVD * c.elt_k) == cudaSuccess && cudaMalloc(&c.v_arena, (size_t)rows * kata::kKVD * c.elt_v) == cudaSuccess;
-    if (ok && c.k8()) ok = cudaMalloc((void**)&c.ksc, (size_t)rows * 8) == cudaSuccess;
+    if (ok && c.k8()) ok = cudaMalloc((void**)&c.ksc, (size_t)rows * 2 * c.ksc_per_row()) == cudaSuccess;
     if (ok && c.v8()) ok = cudaMalloc((void**)&c.vsc, (size_t)rows * 8) == cudaSuccess;
     ok = ok && cudaMalloc((void**)&c.part_o, (size_t)c.max_items * 12 * kata::kD * 4) == cudaSuccess && cudaMalloc((void**)&c.part_ml, (size_t)c.max_items * 32 * 4) == cudaSuccess &&
          cudaMalloc((void**)&c.counters, 4 * KATA_MAX_BATCH * 4) == cudaSuccess && cudaMalloc((void**)&c.d_err, 4) == cudaSuccess;
@@ -140,7 +141,7 @@ int kata_attn_reset(kata_attn_ctx* h, void* stream) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c; DeviceGuard guard(c.cfg.device); cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(c.k_arena, 0, (size_t)c.total_rows * kata::kKVD * c.elt_k, s); if (e == cudaSuccess) e = cudaMemsetAsync(c.v_arena, 0, (size_t)c.total_rows * kata::kKVD * c.elt_v, s);
-    if (e == cudaSuccess && c.ksc) e = cudaMemsetAsync(c.ksc, 0, (size_t)c.total_rows * 8, s);
+    if (e == cudaSuccess && c.ksc) e = cudaMemsetAsync(c.ksc, 0, (size_t)c.total_rows * 2 * c.ksc_per_row(), s);
     if (e == cudaSuccess && c.vsc) e = cudaMemsetAsync(c.vsc, 0, (size_t)c.total_rows * 8, s);
     return e == cudaSuccess ? KATA_OK : cuda_fail(c, e, "reset");
 }

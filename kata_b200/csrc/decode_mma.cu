@@ -45,16 +45,17 @@ __device__ __forceinline__ void dec_stamp(int) {}
 constexpr int kRings = 4, kWarps = 3 * kRings + 1, kThreads = kWarps * 32, kMaxStages = 8;
 constexpr int kOffBars = 16 * kQStride;             // 8448: the barrier block: per ring and stage a 'full' and an 'empty' barrier,
 constexpr int kOffEBars = kRings * kMaxStages * 8, kOffPBars = 2 * kOffEBars;   // inside the barrier block: then per ring two 'P full' and two 'P empty' barriers
-constexpr int kOffQsum = kOffBars + 704;            // int8 mode: sum over the 256 dims of each staged Q row (16 floats)
-constexpr int kOffMl = kOffQsum + 64;               // per-ring (m, l) exchange: [4][16][2] floats = 512 B
+constexpr int kOffQsum = kOffBars + 704;            // int8 modes: sum over the 256 dims of each staged Q row (16 floats), then its sums over each 64-dim group ([16][4])
+constexpr int kOffMl = kOffQsum + 320;              // (row sums: 16 floats, then [16][4] sums per 64-dim group) per-ring (m, l) exchange: [4][16][2] floats = 512 B
 constexpr int kOffPair = kOffMl + 512;              // per-ring hand-over from the score warp to the value warp: two slots of (P block 16 x 48 B, 16 rescale factors)
 constexpr int kPairBytes = 2 * PSlot<2>::kBytes;    // 2688 (sized for the 32-key tiles of the int8 mode)
 constexpr int kOffStages = kOffPair + kRings * kPairBytes;   // the stage area itself starts at the next 1024-byte boundary of the shared window (found at run time)
 constexpr int kMergeStride = 264;                   // floats per row of the cross-ring merge buffer
 
-// MODE = the context's cache mode: 0 fp16, 1 int8 (K and V), 2 int8v (K fp16, V int8: k_attn_dec_split_k16v8, shaders/flash.metal:252-306)
+// MODE = the context's cache mode: 0 fp16, 1 int8 (K and V), 2 int8v (K fp16, V int8: k_attn_dec_split_k16v8, shaders/flash.metal:252-306),
+// 3 int8g (as 1 with four key scales per head row, one per 64 dims)
 template <int MODE> struct Geo {
-    static constexpr bool K8 = MODE == KATA_KV_INT8, V8 = MODE != KATA_KV_FP16;
+    static constexpr bool K8 = MODE == KATA_KV_INT8 || MODE == KATA_KV_INT8G, V8 = MODE != KATA_KV_FP16, KG = MODE == KATA_KV_INT8G;
     static constexpr int kKRowBytes = TileGeo<K8>::kRowBytes, kVRowBytes = TileGeo<V8>::kRowBytes;
     static constexpr int kVBoxes = kVRowBytes / 128;              // 128-byte column boxes per V tile
     static constexpr int kNK = K8 ? 2 : 1, kTile = 16 * kNK;      // keys per tile: 16 (fp16 keys) or 32 (int8 keys): 16 KiB of K+V (12 KiB in int8v mode)
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                                                                  const DecPlan p, const __half* __restrict__ q16, const float* __restrict__ gate, void* __restrict__ out, const int out_kind,
                                                                  float* __restrict__ part_out, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                  float* scratch_o, float* scratch_ml, int32_t* counters, int32_t* err) {
-    using G = Geo<MODE>; constexpr bool K8 = G::K8, V8 = G::V8; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
+    using G = Geo<MODE>; constexpr bool K8 = G::K8, V8 = G::V8, KG = G::KG; constexpr int kStages = G::kStages, kTile = G::kTile, NK = G::kNK; using PS = PSlot<NK>;
     if (threadIdx.x == 0) { prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); dec_stamp(0); }
     if (!p.merge_in_kernel) pdl_launch_dependents();   // the next kernel is the combine grid, which starts no loads of its own before it has waited for this one: it may be set up at once
     extern __shared__ __align__(128) uint8_t smem[];
@@ -160,11 +161,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
             const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
             return __ldg(reinterpret_cast<const unsigned short*>(plane) + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 4 + kvh);
         };
-        uint32_t kA = 0, kB = 0, kC = 0, vA = 0, vB = 0, vC = 0;
+        auto load_kscale = [&](int i, uint32_t& lo, uint32_t& hi) {   // the key scale(s) of this lane's key of the ring's i-th tile: one fp16, or (int8g) four as two words
+            if (!KG) { lo = load_scale(i, ksc); return; }
+            const int k0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
+            const uint2 u = __ldg(reinterpret_cast<const uint2*>(ksc + (p.row_base[b] + min(k0 + (lane & (kTile - 1)), max(kend - 1, 0))) * 16 + kvh * 4));
+            lo = u.x; hi = u.y;
+        };
+        uint32_t kA = 0, kB = 0, kC = 0, vA = 0, vB = 0, vC = 0, kA2 = 0, kB2 = 0, kC2 = 0;
         if (V8 && h == 0) {   // score warp: the loads fly while the Q block is staged
-            if (n_mine > 0) { if (K8) kA = load_scale(0, ksc); vA = load_scale(0, vsc); }
-            if (n_mine > 1) { if (K8) kB = load_scale(1, ksc); vB = load_scale(1, vsc); }
-            if (n_mine > 2) { if (K8) kC = load_scale(2, ksc); vC = load_scale(2, vsc); }
+            if (n_mine > 0) { if (K8) load_kscale(0, kA, kA2); vA = load_scale(0, vsc); }
+            if (n_mine > 1) { if (K8) load_kscale(1, kB, kB2); vB = load_scale(1, vsc); }
+            if (n_mine > 2) { if (K8) load_kscale(2, kC, kC2); vC = load_scale(2, vsc); }
         }
         // ---- stage the 16-row Q block (rows t*6+j; rows >= 6T zero); int8 mode permutes columns inside each 16-dim block
         for (int ch = tid; ch < 16 * 32; ch += kThreads) {
@@ -180,13 +187,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 float a = 0.0f;
 #pragma unroll
                 for (int e = 0; e < 4; e++) { const float2 f = __half22float2(hp[e]); a += f.x + f.y; }
+                // a lane's 16 bytes are 8 dims of one 16-dim block (permuted inside it): lanes 8q .. 8q+7 hold the 64-dim group q
 #pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+                for (int off = 4; off >= 1; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+                if (KG && (lane & 7) == 0) reinterpret_cast<float*>(smem + kOffQsum)[16 + r * 4 + (lane >> 3)] = a;
+                a += __shfl_xor_sync(0xffffffffu, a, 8); a += __shfl_xor_sync(0xffffffffu, a, 16);
                 if (lane == 0) reinterpret_cast<float*>(smem + kOffQsum)[r] = a;
             }
             __syncthreads();
         }
         const float qs_[2] = {K8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g] : 0.0f, K8 ? reinterpret_cast<const float*>(smem + kOffQsum)[g + 8] : 0.0f};
+        float qsg_[2][4];
+#pragma unroll
+        for (int g4 = 0; g4 < 4; g4++) { qsg_[0][g4] = KG ? reinterpret_cast<const float*>(smem + kOffQsum)[16 + g * 4 + g4] : 0.0f; qsg_[1][g4] = KG ? reinterpret_cast<const float*>(smem + kOffQsum)[16 + (g + 8) * 4 + g4] : 0.0f; }
 
         if (h == 3) {
             if (lane < kRings) it += (uint32_t)produce(kStages, 1 << 30);   // 'it' of producer lane r counts ring r's tiles
@@ -200,20 +213,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const __grid_co
                 const uint32_t cur = it_seg + (uint32_t)i, stg = cur % kStages, par = (cur / kStages) & 1u, slot = cur & 1u;
                 const uint32_t kt = ring_stage0 + stg * G::kStageBytes;
                 const int key0 = p.first_row + (lt0 + ring + i * kRings) * kTile;
-                const uint32_t k_cur = kA, v_cur = vA; kA = kB; kB = kC; vA = vB; vB = vC;
-                if (V8 && i + 3 < n_mine) { if (K8) kC = load_scale(i + 3, ksc); vC = load_scale(i + 3, vsc); }
+                const uint32_t k_cur = kA, k_cur2 = kA2, v_cur = vA; kA = kB; kB = kC; kA2 = kB2; kB2 = kC2; vA = vB; vB = vC;
+                if (V8 && i + 3 < n_mine) { if (K8) load_kscale(i + 3, kC, kC2); vC = load_scale(i + 3, vsc); }
                 // A wait that runs out is recorded once; afterwards waits are skipped but the control flow (and every arrival) stays intact.
                 if (!dead && !mbar_wait_bounded(bars + stg * 8, par, err)) { dead = true; atomicExch(err, 1); }
-                float ks_[2 * NK][2], vs_[2 * NK][2];
+                float ks_[2 * NK][2], vs_[2 * NK][2]; uint2 ksg_[2 * NK][2];
 #pragma unroll
                 for (int q = 0; q < 4 * NK; q++) {
                     const int src = 8 * (q >> 1) + 2 * t4 + (q & 1);
-                    ks_[q >> 1][q & 1] = K8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, k_cur, src))) : 1.0f;
+                    if (KG) { ksg_[q >> 1][q & 1] = make_uint2(__shfl_sync(0xffffffffu, k_cur, src), __shfl_sync(0xffffffffu, k_cur2, src)); ks_[q >> 1][q & 1] = 1.0f; }
+                    else ks_[q >> 1][q & 1] = K8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, k_cur, src))) : 1.0f;
                     vs_[q >> 1][q & 1] = V8 ? __half2float(__ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, v_cur, src))) : 1.0f;
                 }
                 if (i == 0 && tid == 0 && it_seg == 0) dec_stamp(2);
                 float pr[2 * NK][4], al0, al1;
-                score_tile<K8, V8, NK>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1);
+                score_tile<K8, V8, NK, KG>(q_base, kt, key0, lim_row0, lim_row1, ks_, vs_, qs_, ss, lane, pr, al0, al1, ksg_, qsg_);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(ebars + stg * 8);   // K of this stage is no longer needed
                 if (cur >= 2 && !dead && !mbar_wait_bounded(pempty + slot * 8, ((cur >> 1) - 1u) & 1u, err)) { dead = true; atomicExch(err, 4); }
@@ -406,7 +420,8 @@ int decode_max_slots(int sm_count) { return sm_count + 4 * KATA_MAX_BATCH; }
 
 // Shared-memory opt-in of the decode kernel on the current device (function attributes are per device: done once per context).
 cudaError_t configure_decode(int kv_mode) {
-    return kv_mode == KATA_KV_INT8  ? cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_INT8>::kSmem)
+    return kv_mode == KATA_KV_INT8G ? cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_INT8G>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_INT8G>::kSmem)
+         : kv_mode == KATA_KV_INT8  ? cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_INT8>::kSmem)
          : kv_mode == KATA_KV_INT8V ? cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_INT8V>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_INT8V>::kSmem)
                                     : cudaFuncSetAttribute(decode_mma_kernel<KATA_KV_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<KATA_KV_FP16>::kSmem);
 }
@@ -452,8 +467,8 @@ cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, i
     p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
 #define KATA_DEC(M) launch_pdl(decode_mma_kernel<M>, dim3(n_ctas), dim3(kThreads), Geo<M>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
-    static_assert(Geo<KATA_KV_INT8>::kTile == 32 && Geo<KATA_KV_INT8V>::kTile == 16 && Geo<KATA_KV_FP16>::kTile == 16, "the tile views of the context are built for these tile heights");
-    const cudaError_t le = mode == KATA_KV_INT8 ? KATA_DEC(KATA_KV_INT8) : mode == KATA_KV_INT8V ? KATA_DEC(KATA_KV_INT8V) : KATA_DEC(KATA_KV_FP16);
+    static_assert(Geo<KATA_KV_INT8>::kTile == 32 && Geo<KATA_KV_INT8G>::kTile == 32 && Geo<KATA_KV_INT8V>::kTile == 16 && Geo<KATA_KV_FP16>::kTile == 16, "the tile views of the context are built for these tile heights");
+    const cudaError_t le = mode == KATA_KV_INT8G ? KATA_DEC(KATA_KV_INT8G) : mode == KATA_KV_INT8 ? KATA_DEC(KATA_KV_INT8) : mode == KATA_KV_INT8V ? KATA_DEC(KATA_KV_INT8V) : KATA_DEC(KATA_KV_FP16);
 #undef KATA_DEC
     c.wrote_no_rows();   // this kernel writes no cache rows
     if (le != cudaSuccess) return le;
@@ -516,6 +531,20 @@ StaticDev g_static_dev[64];
 
 }  // namespace
 }  // namespace kata
+
+// Reports what the static scratch's error word says after the calls enqueued so far on `stream` have completed: KATA_ERR_DEVICE_WAIT when a
+// bounded device wait ran out in one of them (their output is then invalid), else KATA_OK. Synchronises the stream; allocates nothing (a
+// 4-byte copy from the array inside the library image). The word is cleared before every launch, so it speaks for the last call.
+extern "C" int kata_attn_decode_static_check(void* stream) {
+    using namespace kata;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KATA_ERR_CUDA;
+    if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return KATA_ERR_CUDA;
+    if (!g_static_dev[dev].ready) return KATA_OK;   // nothing was ever launched on this device
+    int32_t flag = 0;
+    if (cudaMemcpy(&flag, &g_static_dev[dev].scratch->err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return KATA_ERR_CUDA;
+    return flag ? KATA_ERR_DEVICE_WAIT : KATA_OK;
+}
 
 extern "C" int kata_attn_decode_static(const void* d_k_rows, const void* d_v_rows, int64_t total_rows, int32_t n, const int64_t* seq_row0, const int32_t* pos_base,
                                        int32_t T, int32_t first_pos, const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {

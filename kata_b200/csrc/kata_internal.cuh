@@ -40,7 +40,8 @@ struct Ctx {
     std::vector<int64_t> seq_row0;     // arena row of (sequence, layer 0, position 0)
     int64_t total_rows = 0;
     int elt_k = 2, elt_v = 2;           // bytes per cached K / V element (int8: 1, 1; int8v: 2, 1)
-    bool k8() const { return elt_k == 1; } bool v8() const { return elt_v == 1; }
+    bool k8() const { return elt_k == 1; } bool v8() const { return elt_v == 1; } bool kg() const { return cfg.kv_mode == KATA_KV_INT8G; }   // kg: four K scales per head row (one per 64 dims)
+    int ksc_per_row() const { return kg() ? 16 : 4; }
     void* k_arena = nullptr; void* v_arena = nullptr;      // [total_rows][1024] fp16 or int8
     __half* ksc = nullptr; __half* vsc = nullptr;          // [total_rows][4] fp16 scales of the int8 planes
     // decode scratch: per work item (sequence, kv head, split) the unnormalised partial rows and their (m, l)

@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                                                                    const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, int32_t* err,
                                                                    const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
                                                                    const __grid_constant__ PfPlan plan, float* part_o, float* part_ml) {
-    constexpr bool KS = MODE == KATA_KV_INT8, SCALED = MODE != KATA_KV_FP16;   // KS: scores take the key scale; SCALED: P takes the value scale
+    constexpr bool KS = MODE == KATA_KV_INT8, KST = MODE == KATA_KV_INT8 || MODE == KATA_KV_INT8G, SCALED = MODE != KATA_KV_FP16;   // KS: scores take the key scale; KST: K tiles come from the staging arena (int8g: already scaled there); SCALED: P takes the value scale
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t rank = tc5::cluster_rank();
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     auto item_of = [&](int it) {   // it-th part of this CTA pair
         const int idx = item_lo + it, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
         PfItem t; t.idx = idx; t.bi = rem / plan.hp_n; t.h = 2 * (plan.hp_lo + rem % plan.hp_n) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
-        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = KS ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.row0v = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
+        t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = KST ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.row0v = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
         t.j0 = it == 0 ? tile_lo : 0; t.j1 = idx == item_hi ? tile_hi : t.n_tiles; t.whole = t.j0 == 0 && t.j1 == t.n_tiles; t.slot = (2 * pair + (it == 0 ? 0 : 1)) * 2 + (int)rank;
         return t;
     };
@@ -471,7 +471,10 @@ __global__ void __launch_bounds__(256) prefill_combine_kernel(const Batch b, con
 // int8 planes: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
 // the integers themselves (exact in fp16); the scales stay with the softmax. 64 threads per 1024-code row, 16 codes per thread.
 // grid.z = planes to expand: 2 (K then V), or 1 with first_plane = 1 (V only: the keys are fp16 already).
-__global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const int M, const PfStage stg, const uint8_t* __restrict__ kq, const uint8_t* __restrict__ vq, __half* __restrict__ k16, __half* __restrict__ v16, const int first_plane) {
+// ksc_g (int8g contexts only): the key plane has one scale per 64 dims, which a per-key factor in the softmax cannot carry: the K codes are expanded to
+// code * scale (rounded to fp16) here, and the kernel then treats the K tiles as plain fp16 keys.
+__global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const int M, const PfStage stg, const uint8_t* __restrict__ kq, const uint8_t* __restrict__ vq, __half* __restrict__ k16, __half* __restrict__ v16, const int first_plane,
+                                                           const __half* __restrict__ ksc_g) {
     const int bi = blockIdx.y, rows = b.pos[bi] + M; const bool isV = (blockIdx.z + first_plane) != 0;
     const uint8_t* src = isV ? vq : kq; __half* dst = isV ? v16 : k16;
     for (int r = blockIdx.x * 4 + (threadIdx.x >> 6); r < rows; r += gridDim.x * 4) {
@@ -483,7 +486,11 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const 
         for (int e = 0; e < 4; e++) {   // byte x -> fp16 0x64xx = 1024 + (code + 128); minus 1152 gives the code exactly
             const uint32_t lo = prmt(wd[e], 0x64646464u, 0x4140u), hi = prmt(wd[e], 0x64646464u, 0x4342u);
             const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
-            const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias), c2 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+            __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias), c2 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+            if (ksc_g && !isV) {   // this thread's 16 codes lie in one 64-dim group: head c16 / 16, group (c16 % 16) / 4
+                const __half2 sc = __half2half2(ksc_g[(b.row_base[bi] + r) * 16 + (c16 >> 4) * 4 + ((c16 & 15) >> 2)]);
+                a = __hmul2(a, sc); c2 = __hmul2(c2, sc);
+            }
             o[2 * e] = *reinterpret_cast<const uint32_t*>(&a); o[2 * e + 1] = *reinterpret_cast<const uint32_t*>(&c2);
         }
         uint4* d4 = reinterpret_cast<uint4*>(dst + (stg.kv_row0[bi] + r) * kKVD) + 2 * c16;
@@ -507,7 +514,8 @@ cudaError_t configure_prefill_mma(int kv_mode);
 // Shared-memory opt-in of the prefill kernels on the current device (function attributes are per device: done once per context).
 cudaError_t configure_prefill(int kv_mode) {
     cudaError_t e = configure_prefill_mma(kv_mode);
-    if (e == cudaSuccess) e = kv_mode == KATA_KV_INT8  ? cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
+    if (e == cudaSuccess) e = kv_mode == KATA_KV_INT8G ? cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_INT8G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
+                            : kv_mode == KATA_KV_INT8  ? cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_INT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
                             : kv_mode == KATA_KV_INT8V ? cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_INT8V>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc)
                                                        : cudaFuncSetAttribute(prefill_tc5_kernel<KATA_KV_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
     return e;
@@ -519,13 +527,14 @@ cudaError_t configure_prefill(int kv_mode) {
 cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
     const int mode = c.cfg.kv_mode; const bool i8 = c.v8();
     bool windowed = false; for (int i = 0; i < b.n; i++) windowed |= c.pos_off[b.seq[i]] != 0;
+    if (c.kg() && windowed) return cudaErrorNotSupported;   // the mma.sync kernel, which serves windowed int8 caches, has no grouped key scales
     if ((c.cfg.flags & 1) || (i8 && (!c.v16_stage || windowed))) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
     CUtensorMap tm_q;
     if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
     PfStage stg{};
     if (i8) {
         int max_rows = 0; for (int i = 0; i < b.n; i++) { stg.kv_row0[i] = c.stage_row0[b.seq[i]]; max_rows = std::max(max_rows, b.pos[i] + M); }
-        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1);
+        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1, c.kg() ? (const __half*)c.ksc : nullptr);
         c.launches++;
     }
     // persistent CTA pairs, at most one per two SMs; the flat list of (item, key tile) is cut into one contiguous range per pair.
@@ -624,7 +633,7 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
 #define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)out_dtype, c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc, plan, c.pf_part_o, c.pf_part_ml)
-    const cudaError_t le = mode == KATA_KV_INT8 ? KATA_PF(KATA_KV_INT8, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8V ? KATA_PF(KATA_KV_INT8V, c.tm_k64h, c.tm_v128h_stage) : KATA_PF(KATA_KV_FP16, c.tm_k64h, c.tm_v128h);
+    const cudaError_t le = mode == KATA_KV_INT8G ? KATA_PF(KATA_KV_INT8G, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8 ? KATA_PF(KATA_KV_INT8, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8V ? KATA_PF(KATA_KV_INT8V, c.tm_k64h, c.tm_v128h_stage) : KATA_PF(KATA_KV_FP16, c.tm_k64h, c.tm_v128h);
 #undef KATA_PF
     if (le != cudaSuccess) return le;
     c.wrote_no_rows();

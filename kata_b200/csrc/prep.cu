@@ -64,8 +64,24 @@ __device__ __forceinline__ void quant_store_row(const __half (&hv)[8], int8_t* d
     if (lane == 0) *sc_slot = sc;
 }
 
+// The same per 64-dim group of the row (groups = register pairs (2g, 2g + 1) of every lane): four scales, sc4[g]. rint only.
+__device__ __forceinline__ void quant_store_row_g4(const __half (&hv)[8], int8_t* dst_row, __half* sc4, int lane) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        const float v0 = __half2float(hv[2 * g]), v1 = __half2float(hv[2 * g + 1]);
+        float amax = fmaxf(fabsf(v0), fabsf(v1));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const __half sc = amax > 0.0f ? __float2half_rn(__fdiv_rn(amax, 127.0f)) : __float2half_rn(1.0f);
+        const float inv = __fdiv_rn(1.0f, __half2float(sc));
+        dst_row[32 * (2 * g) + lane] = (int8_t)(int)fminf(fmaxf(rintf(__fmul_rn(v0, inv)), -127.0f), 127.0f);
+        dst_row[32 * (2 * g + 1) + lane] = (int8_t)(int)fminf(fmaxf(rintf(__fmul_rn(v1, inv)), -127.0f), 127.0f);
+        if (lane == 0) sc4[g] = sc;
+    }
+}
+
 // grid (ceil(nh / 8), T, n) x 256 threads: warp w of a CTA handles head slot h0 + 8*blockIdx.x + w of one token
-template <typename TIn, bool K8, bool V8>
+template <typename TIn, bool K8, bool V8, bool KG>
 __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, const TIn* __restrict__ qfull, const TIn* __restrict__ kproj, const TIn* __restrict__ vproj,
                                                    const float* __restrict__ qnorm, const float* __restrict__ knorm, __half* __restrict__ q16, float* __restrict__ q32, float* __restrict__ gate,
                                                    void* k_arena, void* v_arena, __half* ksc, __half* vsc, const int h0, const int nh, const int round_mode, const int kvh_mask) {
@@ -128,18 +144,20 @@ __global__ void __launch_bounds__(256) prep_kernel(const Batch b, const int T, c
         if (!K8) {
 #pragma unroll
             for (int s = 0; s < 8; s++) reinterpret_cast<__half*>(k_arena)[row * kKVD + kh * kD + 32 * s + lane] = hv[s];
-        } else quant_store_row(hv, reinterpret_cast<int8_t*>(k_arena) + row * kKVD + kh * kD, ksc + row * 4 + kh, lane, round_mode);
+        } else if (KG) quant_store_row_g4(hv, reinterpret_cast<int8_t*>(k_arena) + row * kKVD + kh * kD, ksc + row * 16 + kh * 4, lane);
+        else quant_store_row(hv, reinterpret_cast<int8_t*>(k_arena) + row * kKVD + kh * kD, ksc + row * 4 + kh, lane, round_mode);
     }
 }
 
 // grid (T) x 256 threads: warp w < 4 key head w, else value head w-4 (the reference's k_kv_quant_sym covers the same 8 rows per token)
-__global__ void __launch_bounds__(256) kv_quant_kernel(const __half* __restrict__ ks, const __half* __restrict__ vs, int8_t* kq, int8_t* vq, __half* ksc, __half* vsc, const int64_t row0, const int round_mode) {
+__global__ void __launch_bounds__(256) kv_quant_kernel(const __half* __restrict__ ks, const __half* __restrict__ vs, int8_t* kq, int8_t* vq, __half* ksc, __half* vsc, const int64_t row0, const int round_mode, const int kg) {
     const int lane = threadIdx.x & 31, wq = threadIdx.x >> 5, t = blockIdx.x; const bool isV = wq >= 4; const int head = wq & 3; const int64_t row = row0 + t;
     if (!isV && !kq) return;   // int8v: the key plane holds fp16 rows
     __half hv[8];
 #pragma unroll
     for (int s = 0; s < 8; s++) hv[s] = (isV ? vs : ks)[(int64_t)t * kKVD + head * kD + 32 * s + lane];
-    quant_store_row(hv, (isV ? vq : kq) + row * kKVD + head * kD, (isV ? vsc : ksc) + row * 4 + head, lane, round_mode);
+    if (!isV && kg) quant_store_row_g4(hv, kq + row * kKVD + head * kD, ksc + row * 16 + head * 4, lane);   // four scales per key row
+    else quant_store_row(hv, (isV ? vq : kq) + row * kKVD + head * kD, (isV ? vsc : ksc) + row * 4 + head, lane, round_mode);
 }
 
 // grid (width / 1024, rows) x 256 threads: element i = tid*4 + r of the block; bits 0-1 of i live in the thread's float4, bits 2-6 in the lane,
@@ -199,7 +217,7 @@ cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const 
     const dim3 grid((nh + 7) / 8, T, b.n), block(256);
     const int mode = c.cfg.kv_mode;
     cudaError_t le = cudaSuccess;
-#define KATA_PREP(TIN, K8, V8) le = launch_pdl(prep_kernel<TIN, K8, V8>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round, ((1 << c.kvh_n) - 1) << c.kvh_lo)
+#define KATA_PREP(TIN, K8, V8) le = mode == KATA_KV_INT8G ? launch_pdl(prep_kernel<TIN, true, true, true>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round, ((1 << c.kvh_n) - 1) << c.kvh_lo) : launch_pdl(prep_kernel<TIN, K8, V8, false>, grid, block, 0, s, b, T, (const TIN*)qfull, (const TIN*)kproj, (const TIN*)vproj, qnorm, knorm, q16, q32, gate, c.k_arena, c.v_arena, c.ksc, c.vsc, h0, nh, (int)c.cfg.quant_round, ((1 << c.kvh_n) - 1) << c.kvh_lo)
     if (act_dtype == KATA_ACT_F32) { if (mode == KATA_KV_INT8) KATA_PREP(float, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(float, false, true); else KATA_PREP(float, false, false); }
     else if (act_dtype == KATA_ACT_BF16) { if (mode == KATA_KV_INT8) KATA_PREP(__nv_bfloat16, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__nv_bfloat16, false, true); else KATA_PREP(__nv_bfloat16, false, false); }
     else { if (mode == KATA_KV_INT8) KATA_PREP(__half, true, true); else if (mode == KATA_KV_INT8V) KATA_PREP(__half, false, true); else KATA_PREP(__half, false, false); }
@@ -210,7 +228,7 @@ cudaError_t launch_prep(Ctx& c, const Batch& b, int T, const void* qfull, const 
 }
 
 cudaError_t launch_kv_quant(Ctx& c, int64_t row0, const __half* ks, const __half* vs, int T, cudaStream_t s) {
-    kv_quant_kernel<<<dim3(T), 256, 0, s>>>(ks, vs, c.k8() ? (int8_t*)c.k_arena : nullptr, (int8_t*)c.v_arena, c.ksc, c.vsc, row0, c.cfg.quant_round);
+    kv_quant_kernel<<<dim3(T), 256, 0, s>>>(ks, vs, c.k8() ? (int8_t*)c.k_arena : nullptr, (int8_t*)c.v_arena, c.ksc, c.vsc, row0, c.cfg.quant_round, c.kg() ? 1 : 0);
     c.launches++;
     return cudaGetLastError();
 }

@@ -77,9 +77,12 @@ inline float tg_sum256(const float* v) { float tot = 0.0f; for (int s = 0; s < 8
 // k_attn_dec_split_q8); mode 2: K fp16, V int8 with its scales (k_flash_prefill_k16v8 / k_attn_dec_split_k16v8, shaders/flash.metal:194-306:
 // the same tile body with the key scale and mean stripped out).
 struct KvView {
-    const void* k; const void* v; const uint16_t* ksc; const uint16_t* vsc; const uint16_t* kmn; bool q8, v8;
-    KvView(const void* k_, const void* v_, const uint16_t* ksc_, const uint16_t* vsc_, const uint16_t* kmn_, int mode) : k(k_), v(v_), ksc(ksc_), vsc(vsc_), kmn(kmn_), q8(mode == 1), v8(mode == 1 || mode == 2) {}
-    float kraw(uint64_t pos, uint32_t kvh, uint32_t d) const { const uint64_t i = pos * kKVD + kvh * kD + d; return q8 ? (float)((const int8_t*)k)[i] : h2f(((const uint16_t*)k)[i]); }
+    // mode 0 fp16; 1 int8 K and V, one scale per (position, KV head); 2 fp16 K, int8 V; 3 int8 K with one scale per 64 dims (ksc is [pos][4 heads][4 groups]),
+    // int8 V per row: the finer K granularity the reference measured (docs/reports/M11-int8-kv.en.md:52-55) but could not fold into its matrix path (:94-97)
+    const void* k; const void* v; const uint16_t* ksc; const uint16_t* vsc; const uint16_t* kmn; bool q8, v8, kg;
+    KvView(const void* k_, const void* v_, const uint16_t* ksc_, const uint16_t* vsc_, const uint16_t* kmn_, int mode) : k(k_), v(v_), ksc(ksc_), vsc(vsc_), kmn(kmn_), q8(mode == 1), v8(mode == 1 || mode == 2 || mode == 3), kg(mode == 3) {}
+    float kSg(uint64_t pos, uint32_t kvh, uint32_t d) const { return h2f(ksc[pos * 16 + kvh * 4 + (d >> 6)]); }   // mode 3: the scale of dim d's group
+    float kraw(uint64_t pos, uint32_t kvh, uint32_t d) const { const uint64_t i = pos * kKVD + kvh * kD + d; return (q8 || kg) ? (float)((const int8_t*)k)[i] : h2f(((const uint16_t*)k)[i]); }
     float vraw(uint64_t pos, uint32_t kvh, uint32_t d) const { const uint64_t i = pos * kKVD + kvh * kD + d; return v8 ? (float)((const int8_t*)v)[i] : h2f(((const uint16_t*)v)[i]); }
     float kS(uint64_t pos, uint32_t kvh) const { return q8 ? h2f(ksc[pos * 4 + kvh]) : 1.0f; }
     float vS(uint64_t pos, uint32_t kvh) const { return v8 ? h2f(vsc[pos * 4 + kvh]) : 1.0f; }
@@ -165,11 +168,18 @@ void kor_prep(const float* qfull, const float* kproj, const float* vproj, const 
 // default; mode 1: symmetric, round half away from zero (not the reference; offered because the benchmark statement
 // names it); mode 2: the reference's asymmetric-K variant (values stay symmetric), rint.
 void kor_kv_quant(const uint16_t* ks, const uint16_t* vs, int8_t* kq, int8_t* vq, uint16_t* ksc, uint16_t* vsc, uint16_t* kmn, uint32_t pos0, uint32_t T, int mode) {
-    auto rnd = [&](float x) { return mode == 1 ? std::round(x) : std::rint(x); };
+    auto rnd = [&](float x) { return mode == 1 ? std::round(x) : std::rint(x); };   // mode 3 (grouped K scales) rounds to even like mode 0
     for (uint32_t t = 0; t < T; t++) for (uint32_t g = kq ? 0 : 4; g < 8; g++) {   // kq == nullptr: values only (keys stay fp16)
         const bool isV = g >= 4; const uint32_t head = g & 3; const uint16_t* src = (isV ? vs : ks) + (uint64_t)t * kKVD + head * kD; const uint64_t pos = (uint64_t)pos0 + t;
         int8_t* dst = (isV ? vq : kq) + pos * kKVD + head * kD;
-        if (isV || mode != 2) {
+        if (!isV && mode == 3) {   // one scale per 64 dims of the key row: same arithmetic as k_kv_quant_sym on each group; ksc is [pos][4 heads][4 groups]
+            for (uint32_t g4 = 0; g4 < 4; g4++) {
+                float amax = 0.0f; for (uint32_t d = 64 * g4; d < 64 * g4 + 64; d++) amax = std::max(amax, std::fabs(h2f(src[d])));
+                const uint16_t sc = amax > 0.0f ? f2h(amax / 127.0f) : f2h(1.0f); const float inv = 1.0f / h2f(sc);
+                for (uint32_t d = 64 * g4; d < 64 * g4 + 64; d++) dst[d] = (int8_t)std::clamp(std::rint(h2f(src[d]) * inv), -127.0f, 127.0f);
+                ksc[pos * 16 + head * 4 + g4] = sc;
+            }
+        } else if (isV || mode != 2) {
             float amax = 0.0f; for (uint32_t d = 0; d < kD; d++) amax = std::max(amax, std::fabs(h2f(src[d])));
             const uint16_t sc = amax > 0.0f ? f2h(amax / 127.0f) : f2h(1.0f); const float inv = 1.0f / h2f(sc);
             for (uint32_t d = 0; d < kD; d++) dst[d] = (int8_t)std::clamp(rnd(h2f(src[d]) * inv), -127.0f, 127.0f);
@@ -296,7 +306,7 @@ void kor_formula_f64(const uint16_t* q16, const void* kc, const void* vc, const 
     const KvView kv(kc, vc, ksc, vsc, kmn, q8); const uint32_t nT = (M + tStep - 1) / tStep, nHh = (kH + hStep - 1) / hStep;
     parallel_for(nT * nHh, threads, [&](uint32_t item) {
         const uint32_t t = (item / nHh) * tStep, h = (item % nHh) * hStep, kvh = h / 6, pos = posBase + t; std::vector<double> s(pos + 1 - firstPos); double m = -1e30;
-        for (uint32_t j = firstPos; j <= pos; j++) { double a = 0; const double ks = kv.kS(j, kvh), km = kv.kM(j, kvh); for (uint32_t d = 0; d < kD; d++) a += (double)h2f(q16[(uint64_t)t * kQD + h * kD + d]) * ((double)kv.kraw(j, kvh, d) * ks + km); s[j - firstPos] = a; m = std::max(m, a); }
+        for (uint32_t j = firstPos; j <= pos; j++) { double a = 0; const double ks = kv.kS(j, kvh), km = kv.kM(j, kvh); for (uint32_t d = 0; d < kD; d++) a += (double)h2f(q16[(uint64_t)t * kQD + h * kD + d]) * ((double)kv.kraw(j, kvh, d) * (kv.kg ? (double)kv.kSg(j, kvh, d) : ks) + km); s[j - firstPos] = a; m = std::max(m, a); }
         double z = 0; for (auto& v : s) { v = std::exp(v - m); z += v; }
         for (uint32_t d = 0; d < kD; d++) { double a = 0; for (uint32_t j = firstPos; j <= pos; j++) a += s[j - firstPos] * ((double)kv.vraw(j, kvh, d) * (double)kv.vS(j, kvh)); a /= z; a *= 1.0 / (1.0 + std::exp(-(double)gate[(uint64_t)t * kQD + h * kD + d])); out[(uint64_t)t * kQD + h * kD + d] = a; }
     });
@@ -309,7 +319,7 @@ void kor_formula_f32(const float* q, const void* kc, const void* vc, const float
     const KvView kv(kc, vc, ksc, vsc, kmn, q8);
     parallel_for(M * kH, threads, [&](uint32_t item) {
         const uint32_t t = item / kH, h = item % kH, kvh = h / 6, pos = posBase + t; std::vector<float> s(pos + 1 - firstPos); float m = kNegInf;
-        for (uint32_t j = firstPos; j <= pos; j++) { float a = 0; const float ks = kv.kS(j, kvh), km = kv.kM(j, kvh); for (uint32_t d = 0; d < kD; d++) a += (q[(uint64_t)t * kQD + h * kD + d] * 0.0625f) * (kv.kraw(j, kvh, d) * ks + km); s[j - firstPos] = a; m = std::max(m, a); }
+        for (uint32_t j = firstPos; j <= pos; j++) { float a = 0; const float ks = kv.kS(j, kvh), km = kv.kM(j, kvh); for (uint32_t d = 0; d < kD; d++) a += (q[(uint64_t)t * kQD + h * kD + d] * 0.0625f) * (kv.kraw(j, kvh, d) * (kv.kg ? kv.kSg(j, kvh, d) : ks) + km); s[j - firstPos] = a; m = std::max(m, a); }
         float z = 0; for (auto& v : s) { v = std::exp(v - m); z += v; }
         float acc[kD] = {}; for (uint32_t j = firstPos; j <= pos; j++) { const float p = s[j - firstPos], vsj = kv.vS(j, kvh); for (uint32_t d = 0; d < kD; d++) acc[d] += p * (kv.vraw(j, kvh, d) * vsj); }
         for (uint32_t d = 0; d < kD; d++) out[(uint64_t)t * kQD + h * kD + d] = (acc[d] / z) * sigmoidf_(gate[(uint64_t)t * kQD + h * kD + d]);

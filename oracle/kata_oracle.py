@@ -61,17 +61,21 @@ def inv_freq() -> np.ndarray:
 class KvPlanes:
     """One attention layer's cache planes on the host, in the reference layout (src/engine.h:73-83):
     K, V: [max_ctx][1024] fp16 (stored as uint16 bit patterns) or int8; scales/mean: [max_ctx][4] fp16.
-    ``mode`` 0: fp16; 1 (``int8=True``): K and V int8; 2 (``int8v=True``): K fp16, V int8 (KATA_KV=int8v, src/engine.cpp:54-59)."""
+    ``mode`` 0: fp16; 1 (``int8=True``): K and V int8; 2 (``int8v=True``): K fp16, V int8 (KATA_KV=int8v, src/engine.cpp:54-59);
+    3 (``int8g=True``): K int8 with one scale per 64 dims (ksc [max_ctx][16] = [head][group]), V int8 per row."""
 
-    def __init__(self, max_ctx: int, int8: bool = False, poison: bool = False, int8v: bool = False):
+    def __init__(self, max_ctx: int, int8: bool = False, poison: bool = False, int8v: bool = False, int8g: bool = False):
         self.max_ctx, self.int8 = max_ctx, int8
-        self.mode = 1 if int8 else 2 if int8v else 0
+        self.mode = 1 if int8 else 2 if int8v else 3 if int8g else 0
         fill = 0x7E00 if poison else 0  # fp16 quiet NaN
         self.ksc = self.vsc = self.kmn = None
         if self.mode == 1:
             self.k = np.zeros((max_ctx, KVD), np.int8)
             self.ksc = np.zeros((max_ctx, 4), np.uint16)
             self.kmn = np.zeros((max_ctx, 4), np.uint16)
+        elif self.mode == 3:
+            self.k = np.zeros((max_ctx, KVD), np.int8)
+            self.ksc = np.zeros((max_ctx, 16), np.uint16)
         else:
             self.k = np.full((max_ctx, KVD), fill, np.uint16)
         if self.mode:
@@ -81,7 +85,7 @@ class KvPlanes:
             self.v = np.full((max_ctx, KVD), fill, np.uint16)
 
     def k_f32(self):
-        return self.k.astype(np.float32) if self.mode == 1 else self.k.view(np.float16).astype(np.float32)
+        return self.k.astype(np.float32) if self.mode in (1, 3) else self.k.view(np.float16).astype(np.float32)
 
     def v_f32(self):
         return self.v.astype(np.float32) if self.mode else self.v.view(np.float16).astype(np.float32)
@@ -100,12 +104,12 @@ def prep(qfull, kproj, vproj, qnorm, knorm, planes: KvPlanes, pos0: int, h0: int
                        C.c_uint32(pos0), C.c_uint32(M), C.c_uint32(h0), C.c_uint32(nh), C.c_uint32(0), C.c_uint32(pos0))
         if h0 + nh > 28:
             kv_quant(None, vs, planes, pos0, quant_mode)
-    elif planes.int8:
+    elif planes.int8 or planes.mode == 3:
         ks = np.zeros((M, KVD), np.uint16)
         vs = np.zeros((M, KVD), np.uint16)
         lib().kor_prep(_p(qf), _p(kproj), _p(vproj), _p(qnorm), _p(knorm), _p(invf), _p(q), _p(gate), _p(ks), _p(vs),
                        C.c_uint32(pos0), C.c_uint32(M), C.c_uint32(h0), C.c_uint32(nh), C.c_uint32(pos0), C.c_uint32(pos0))
-        kv_quant(ks, vs, planes, pos0, quant_mode)
+        kv_quant(ks, vs, planes, pos0, 3 if planes.mode == 3 else quant_mode)
     else:
         lib().kor_prep(_p(qf), _p(kproj), _p(vproj), _p(qnorm), _p(knorm), _p(invf), _p(q), _p(gate), _p(planes.k), _p(planes.v),
                        C.c_uint32(pos0), C.c_uint32(M), C.c_uint32(h0), C.c_uint32(nh), C.c_uint32(0), C.c_uint32(0))
@@ -113,10 +117,10 @@ def prep(qfull, kproj, vproj, qnorm, knorm, planes: KvPlanes, pos0: int, h0: int
 
 
 def kv_quant(ks, vs, planes: KvPlanes, pos0: int, mode: int = 0):
-    """k_kv_quant_sym (mode 0, rint), half-away variant (mode 1), reference asymmetric-K (mode 2)."""
-    assert planes.mode and vs.dtype == np.uint16 and (ks is None) == (planes.mode == 2)
+    """k_kv_quant_sym (mode 0, rint), half-away variant (mode 1), reference asymmetric-K (mode 2), one K scale per 64 dims (mode 3, planes of mode 3)."""
+    assert planes.mode and vs.dtype == np.uint16 and (ks is None) == (planes.mode == 2) and (mode == 3) == (planes.mode == 3)
     T = vs.shape[0]
-    lib().kor_kv_quant(_p(ks), _p(vs), _p(planes.k) if planes.mode == 1 else None, _p(planes.v), _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_uint32(pos0), C.c_uint32(T), C.c_int(mode))
+    lib().kor_kv_quant(_p(ks), _p(vs), _p(planes.k) if planes.mode in (1, 3) else None, _p(planes.v), _p(planes.ksc), _p(planes.vsc), _p(planes.kmn), C.c_uint32(pos0), C.c_uint32(T), C.c_int(mode))
 
 
 def attn_decode(q, gate, planes: KvPlanes, pos: int, threads: int = 1):

@@ -83,7 +83,7 @@ def test_split_kv_across_gpus_nccl(orc):
     assert d.max() < 2e-3 and d.mean() < 2e-4
 
 
-@pytest.mark.parametrize("mode", ["fp16", "int8", "int8v"])
+@pytest.mark.parametrize("mode", ["fp16", "int8", "int8v", "int8g"])
 def test_checkpoint_kv_segments_round_trip(tmp_path, mode):
     # save the KV segments of a prefilled context, restore them into a fresh one: planes identical (the reference's
     # test_cache.sh identity checks), another numerics mode refuses the file, a truncated file is refused and leaves zeros

@@ -39,15 +39,15 @@ def _upload_planes(ctx, planes, layer=0, seq=0, n=None):
     n = planes.max_ctx if n is None else n
     ctx.plane_write(layer, seq, 0, 0, planes.k[:n])
     ctx.plane_write(layer, seq, 1, 0, planes.v[:n])
-    if planes.int8:
+    if planes.int8 or planes.mode == 3:
         ctx.plane_write(layer, seq, 2, 0, planes.ksc[:n])
         ctx.plane_write(layer, seq, 3, 0, planes.vsc[:n])
     elif planes.mode == 2:   # int8v: {K fp16, V int8, V scales}
         ctx.plane_write(layer, seq, 2, 0, planes.vsc[:n])
 
 
-def _oracle_fill(orc, seed, L, max_ctx, int8=False, poison=False, fast=False, layer=0, seq=0, int8v=False):
-    planes = orc.KvPlanes(max_ctx, int8=int8, poison=poison, int8v=int8v)
+def _oracle_fill(orc, seed, L, max_ctx, int8=False, poison=False, fast=False, layer=0, seq=0, int8v=False, int8g=False):
+    planes = orc.KvPlanes(max_ctx, int8=int8, poison=poison, int8v=int8v, int8g=int8g)
     qn, kn = synth.norm_weights(seed, layer)
     qf, kp, vp = (synth.token_rows_fast if fast else synth.token_rows)(seed, L, layer=layer, seq=seq)
     q, gate = orc.prep(qf, kp, vp, qn, kn, planes, 0)
@@ -850,3 +850,77 @@ def test_kv_head_shards_equal_the_whole_context(capi, orc, mode):
         with pytest.raises(capi.KataError) as e:
             c.decode_scalar(0, [1], [p0], 1, torch.zeros(1, 1, 6144, device="cuda"), torch.zeros(1, 1, 6144, device="cuda"))
         assert e.value.code == 3
+
+
+# ------------------------------------------------------------------------------------------------ int8g: int8 keys with one scale per 64 dims
+def test_int8g_planes_quantiser_and_append(capi, orc):
+    # planes {K int8, V int8, K scales [head][group] (32 B), V scales (8 B)}, tag, and the quantiser: stand-alone on arbitrary fp16 rows bit for
+    # bit (codes and all four group scales per head; edge rows: zero groups, ties, clamp), and fused into the append against the oracle
+    ctx = capi.AttnContext(1, [128], kv_mode="int8g")
+    assert ctx.tag() == "fp16+kv8g" and ctx.kv_planes() == 4 and [ctx.plane_row_bytes(i) for i in range(4)] == [1024, 1024, 32, 8]
+    rng = np.random.default_rng(61)
+    ks = (rng.standard_normal((20, 1024)) * rng.choice([1e-4, 1.0, 30.0], size=(20, 16)).repeat(64, axis=1)).astype(np.float16)
+    ks[3, 64:128] = 0; ks[4, :64] = np.float16(0.5) * np.arange(-32, 32).astype(np.float16); ks[5] = 0
+    vs = rng.standard_normal((20, 1024)).astype(np.float16)
+    ctx.kv_quant(0, 0, _dev(ks), _dev(vs), 7); ctx.check()
+    want = orc.KvPlanes(64, int8g=True)
+    orc.kv_quant(ks.view(np.uint16), vs.view(np.uint16), want, 7, 3)
+    got = [ctx.plane_read(0, 0, i, 7, 20) for i in range(4)]
+    assert np.array_equal(got[0].view(np.int8).reshape(20, 1024), want.k[7:27]) and np.array_equal(got[1].view(np.int8).reshape(20, 1024), want.v[7:27])
+    assert np.array_equal(got[2].view(np.uint16).reshape(20, 16), want.ksc[7:27]) and np.array_equal(got[3].view(np.uint16).reshape(20, 4), want.vsc[7:27])
+    codes, sc = orc.kv_quant_rows_np(ks.reshape(20, 16, 64))   # the independent numpy quantiser, group by group
+    assert np.array_equal(codes.reshape(20, 1024), want.k[7:27]) and np.array_equal(sc.view(np.uint16), want.ksc[7:27])
+    # quantise-on-append: V bit-exact; K groups equal except where sin/cos of the rotation differ by an ulp from the host's
+    L = 90
+    planes, q, gate, (qf, kp, vp, qn, kn) = _oracle_fill(orc, 62, L, 128, int8g=True)
+    c2 = capi.AttnContext(1, [128], kv_mode="int8g")
+    c2.prep(0, [0], [0], L, _dev(qf[None]), _dev(kp[None]), _dev(vp[None]), _dev(qn), _dev(kn)); c2.check()
+    assert np.array_equal(c2.plane_read(0, 0, 1, 0, L).view(np.int8).reshape(L, 1024), planes.v[:L]) and np.array_equal(c2.plane_read(0, 0, 3, 0, L).view(np.uint16).reshape(L, 4), planes.vsc[:L])
+    assert (c2.plane_read(0, 0, 2, 0, L).view(np.uint16).reshape(L, 16) != planes.ksc[:L]).mean() < 0.02
+    assert (c2.plane_read(0, 0, 0, 0, L).view(np.int8).reshape(L, 1024) != planes.k[:L]).mean() < 0.02
+    with pytest.raises(capi.KataError):
+        capi.AttnContext(1, [64], kv_mode="int8g", quant_round="half_away")   # the grouped quantiser rounds to even only
+
+
+@pytest.mark.parametrize("T", [1, 2])
+def test_int8g_decode_lengths_and_batch(capi, orc, T):
+    # decode over the grouped-scale cache (planes from the oracle's quantiser) against the fp32 formula on the dequantised planes: lengths
+    # around the 32-key tile, a long one, first_pos = 1, and a ragged batch with a split that cuts segments
+    for L in (1 + T, 31, 33, 64, 700):
+        planes, q, gate, _ = _oracle_fill(orc, 63 + L, L, 1024, int8g=True, fast=True)
+        ctx = capi.AttnContext(1, [1024], kv_mode="int8g")
+        _upload_planes(ctx, planes)
+        pb = L - T
+        out = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(q[pb:L])[None]).view(torch.float16), _dev(gate[pb:L][None]))
+        ctx.check()
+        _close(out.cpu().numpy()[0], orc.formula_f32(q[pb:L], gate[pb:L], planes, pb))
+        if L > 2:
+            o1 = ctx.decode(0, [0], [pb], T, _dev(orc.cvt_q_half(q[pb:L])[None]).view(torch.float16), _dev(gate[pb:L][None]), first_pos=1)
+            _close(o1.cpu().numpy()[0], orc.formula_f32(q[pb:L], gate[pb:L], planes, pb, first_pos=1))
+        ctx.close()
+    lens = [900, 130, 2048]
+    ctx = capi.AttnContext(1, [l + 8 for l in lens], kv_mode="int8g", dec_chunk=64)
+    ps, qs, gs = [], [], []
+    for s, L in enumerate(lens):
+        pl, q, g, _ = _oracle_fill(orc, 90 + s, L, L + 8, int8g=True, fast=True, seq=s)
+        _upload_planes(ctx, pl, seq=s); ps.append(pl); qs.append(q); gs.append(g)
+    pos = [l - T for l in lens]
+    dq = _dev(np.stack([orc.cvt_q_half(qs[s][pos[s]:lens[s]]) for s in range(3)])).view(torch.float16); dg = _dev(np.stack([gs[s][pos[s]:lens[s]] for s in range(3)]))
+    out = ctx.decode(0, [0, 1, 2], pos, T, dq, dg).cpu().numpy(); ctx.check()
+    for s in range(3):
+        _close(out[s], orc.formula_f32(qs[s][pos[s]:lens[s]], gs[s][pos[s]:lens[s]], ps[s], pos[s]))
+
+
+def test_int8g_prefill_and_full_step(capi, orc):
+    # a ragged chunk over a prefix through the tcgen05 kernel (keys expanded to code x group scale), then append + decode on the same context
+    pb, M = 300, 200
+    planes, q, gate, (qf, kp, vp, qn, kn) = _oracle_fill(orc, 95, pb + M + 2, 640, int8g=True, fast=True)
+    ctx = capi.AttnContext(1, [640], kv_mode="int8g")
+    _upload_planes(ctx, planes, n=pb + M)
+    out = ctx.prefill(0, [0], [pb], M, _dev(orc.cvt_q_half(q[pb:pb + M])[None]).view(torch.float16), _dev(gate[pb:pb + M][None]))
+    ctx.check()
+    _close(out.cpu().numpy()[0], orc.formula_f32(q[pb:pb + M], gate[pb:pb + M], planes, pb))
+    p2 = pb + M
+    q16, q32, g = ctx.prep(0, [0], [p2], 2, _dev(qf[p2:p2 + 2][None]), _dev(kp[p2:p2 + 2][None]), _dev(vp[p2:p2 + 2][None]), _dev(qn), _dev(kn), want_q32=True)
+    dec = ctx.decode(0, [0], [p2], 2, q16, g); ctx.check()
+    _close(dec.cpu().numpy()[0], orc.formula_f32(q[p2:p2 + 2], gate[p2:p2 + 2], planes, p2))

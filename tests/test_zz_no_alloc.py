@@ -73,6 +73,8 @@ def test_decode_static_matches_context_decode_twice():
         assert rc == capi.OK and torch.isfinite(got).all() and (got - want).abs().max().item() < 1e-5
     ctx8.close()
 
+    assert capi.lib().kata_attn_decode_static_check(None) == capi.OK   # no bounded wait ran out in the last call
+
     # sizes beyond the stated maximum are rejected with a range error before anything is launched
     n = 9
     rc, _ = capi.decode_static(k_rows, v_rows, [0] * n, [0] * n, 1, torch.zeros(n, 1, 6144, dtype=torch.float16, device="cuda"), torch.zeros(n, 1, 6144, device="cuda"))
