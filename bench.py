@@ -676,6 +676,25 @@ def run_workload(name, args, rank, world, steps=None, warmup=None, sustained_s=0
     return bench_prefill.run(args, rank, world, cfg, peaks(), ClockSampler, steps=steps, warmup=warmup)
 
 
+def table(path):
+    """Markdown table of a saved bench line (the default line with its extras): what profiles/bench_results.md holds."""
+    d = json.loads([l for l in open(path).read().splitlines() if l.startswith("{")][-1])
+    rows = [("decode_b8 (the headline line)", d)] + [(k, v) for k, v in d.get("extras", {}).items()]
+    out = ["| workload | value (tok/s) | ms/step | e2e (tok/s) | dominant kernel, per launch | achieved | frac of measured peak | SM MHz, reasons | CPU baseline (tok/s, cores) |", "|---|---|---|---|---|---|---|---|---|"]
+    for name, v in rows:
+        if "roofline" not in v:
+            out.append(f"| {name} | {v.get('skipped') or v.get('failed')} | | | | | | | |")
+            continue
+        r, c, e, cb = v["roofline"], v.get("clocks", {}), v.get("e2e", {}), v.get("cpu_baseline", {})
+        ev = e.get("value")
+        out.append(f"| {name} | {v['value']:,.0f} | {v['ms_per_step']:.3f} | {'-' if ev is None else format(ev, ',.0f')} | `{r.get('kernel', '')}` {r.get('us_per_launch', 0):.1f} us | {r['achieved']:,.0f} {r['unit']} | {r['frac']:.3f} | {c.get('sm_mhz')}, {','.join(c.get('reasons', [])) or 'none'} | {'-' if not cb or cb.get('value') is None else format(cb['value'], ',.2f')} ({cb.get('cores', '-')}) |")
+    if "sustained" in d:
+        sgl = d["sustained"]
+        out.append("")
+        out.append(f"Sustained: the headline step repeated for {sgl['seconds']:.1f} s: {sgl['value']:,.0f} tok/s, {sgl['ms_per_step']:.3f} ms/step, median SM clock {sgl['clocks'].get('sm_mhz')} MHz, reasons {sgl['clocks'].get('reasons')}.")
+    return "\n".join(out)
+
+
 def main():
     t_start = time.perf_counter()
     ap = argparse.ArgumentParser()
@@ -686,7 +705,11 @@ def main():
     ap.add_argument("--workload", default="decode_b8", choices=sorted(WORKLOADS))
     ap.add_argument("--extras", default=None, help="all | none | comma-separated workload names; default: all for the default workload, none otherwise")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--table", default=None, help="print the markdown table of a saved bench line (a file holding bench.py's output) and exit")
     args = ap.parse_args()
+    if args.table:
+        print(table(args.table))
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "kata_b200" else args.warmup
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
 
