@@ -31,11 +31,12 @@
 // the softmax warps work on the current ones; K and V tiles are loaded one tile ahead. The running maximum is only raised when a row's
 // new maximum exceeds it by more than 8 (in log2 units); then the warp rescales its O rows in tensor memory after waiting for the
 // previous P.V. P stays below 2^8, well inside fp16.
-// Phases: a parity wait cannot tell phase k of an mbarrier from phase k - 2, and the softmax warps wait for 'O done' and 'V landed' only now and
-// then (a rescale, the epilogue, a tail tile), so each of the two has one barrier per tile parity: tile k waits on barrier k & 1 for phase k >> 1,
-// and the phase before it on that barrier (tile k - 2) is complete whenever a warp holds the scores of tile k, because the commit that
-// announced them covers every MMA issued before. (With a single 'O done' barrier a warp that ran ahead of its peers through a two-tile part
-// read O before the part's P.V had completed.)
+// Phases: a parity wait cannot tell phase k of an mbarrier from phase k - 2, and the softmax warps wait for 'O done' only now and then (a
+// rescale, the epilogue), so it has one barrier per tile parity: tile k waits on barrier k & 1 for phase k >> 1, and the phase before it on
+// that barrier (tile k - 2) is complete whenever a warp holds the scores of tile k, because the commit that announced them covers every MMA
+// issued before. (With a single 'O done' barrier a warp that ran ahead of its peers through a two-tile part read O before the part's P.V
+// had completed.) 'V landed' is announced for tail tiles only (the one remote arrival it costs the MMA thread is then off the other tiles'
+// issue path); both sides count the tail tiles of the pair and use the count as the other barriers use the tile number.
 // Every wait is bounded and shares the context's abort word; tensor memory is always released before the CTAs exit.
 #include <algorithm>
 
@@ -50,10 +51,17 @@ using namespace ptx;
 
 // Development aid, compiled only with -DKATA_PF_TRACE (never in the shipped library): CTA 0 records %globaltimer stamps of its phases.
 #ifdef KATA_PF_TRACE
-__device__ unsigned long long g_pf_trace[128];
-__device__ __forceinline__ void pf_stamp(int slot) { if (blockIdx.x == 0 && slot < 128) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_pf_trace[slot] = t; } }
+__device__ unsigned long long g_pf_trace[1280];   // [0,128): phases of the launch; 128 * kind + tile for the per-tile stamps (kinds 1-9)
+__device__ int g_pf_trace_cta = 0, g_pf_trace_level = 1, g_pf_ablate = 0;   // ablate (timing experiments, wrong results): 1 no exp, 2 no score load   // level 0: only the P.V-issued stamp of every tile
+#define PF_TRACE_INIT const int pf_ab = g_pf_ablate; const int pf_tr = ((int)blockIdx.x == g_pf_trace_cta) ? 1 + g_pf_trace_level : 0;   /* read once: a stamp must not cost a global load */
+#define pf_stamp(slot) do { if (pf_tr && (slot) < 1280) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_pf_trace[(slot)] = t_; } } while (0)
+#define pf_stamp_clock(slot) do { if (pf_tr) g_pf_trace[(slot)] = (unsigned long long)clock64(); } while (0)
+#define pf_stamp_tile(kind, tile) do { if ((tile) < 128u && ((kind) == 3 || pf_tr > 1)) pf_stamp(128 * (kind) + (int)(tile)); } while (0)
 #else
-__device__ __forceinline__ void pf_stamp(int) {}
+#define PF_TRACE_INIT
+#define pf_stamp(slot) do { } while (0)
+#define pf_stamp_tile(kind, tile) do { } while (0)
+#define pf_stamp_clock(slot) do { } while (0)
 #endif
 
 constexpr int kTcThreads = 352, kBMq = 128, kBNk = 128;
@@ -108,7 +116,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128]; __shared__ __align__(16) float s_stage[8][16 * 36]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
-    if (tid == 0) pf_stamp(0);
+    PF_TRACE_INIT
+    if (tid == 0) { pf_stamp(0); pf_stamp_clock(126); }
     if (tid == 0) {
         for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1 || i == B_OFREE) ? 16u : 1u);   // 'P ready', 'O free': one arrival per softmax warp of both CTAs
         fence_mbar_init();
@@ -139,6 +148,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 for (int j = t.j0; j < t.j1; j++, gt++) {
                     const uint32_t st = gt & 1u;
                     if (gt >= 2 && !mbar_wait_bounded(bar(B_KEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 11); ok = false; break; }
+                    if (gt >= 2) pf_stamp_tile(8, gt - 2);   // S(gt - 2) has completed
                     if (rank == 0) mbar_arrive_expect_tx(bar(B_KFULL0 + st), 2 * kHalfB);
                     tc5::tma_load_4d_pair(k_sm + st * kHalfB, &tm_k, 0, t.row0 + j * kBNk + 64 * (int)rank, 0, t.kvh, bar(B_KFULL0 + st));
                 }
@@ -155,6 +165,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 if (lane == 0) {
                     const uint32_t st = gt & 1u;
                     if (gt >= 2 && !mbar_wait_bounded(bar(B_VEMPTY0 + st), ((gt >> 1) - 1u) & 1u, err)) { atomicExch(err, 12); ok = false; }
+                    if (gt >= 2) pf_stamp_tile(9, gt - 2);   // P.V(gt - 2) has completed
                     if (ok) {
                         if (rank == 0) mbar_arrive_expect_tx(bar(B_VFULL0 + st), 2 * kHalfB);
                         tc5::tma_load_4d_pair(v_sm + st * kHalfB, &tm_v, 0, t.row0v + j * kBNk, 2 * (int)rank, t.kvh, bar(B_VFULL0 + st));
@@ -170,35 +181,46 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         }
     } else if (w == 10) {
         if (lane == 0 && rank == 0) {
-            uint32_t gt = 0; bool ok = true;
-            auto issue_s = [&](uint32_t g) {   // S of tile g = Q K^T for both CTAs: 4 column blocks x 4 k-steps of 16 dims
+            uint32_t gt = 0, nt = 0; bool ok = true;   // nt: tail tiles so far (barrier and phase of 'V landed')
+            auto issue_s = [&](uint32_t g, const int i0, const int i1) {   // S of tile g = Q K^T for both CTAs: 4 column blocks x 4 k-steps of 16 dims = 16 MMAs, of which [i0, i1)
                 const uint32_t d = t_s0 + (g & 1u) * 128u, kst = k_sm + (g & 1u) * kHalfB;
 #pragma unroll
-                for (int kb = 0; kb < 4; kb++)
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        tc5::mma_ss2(d, tc5::smem_desc_sw128(q_sm + kb * kBlk + ks * 32, 16, 1024), tc5::smem_desc_sw128(kst + kb * kBlkKh + ks * 32, 16, 1024), kIdescS, (kb | ks) != 0);
-                tc5::commit2(bar(B_SFULL0 + (g & 1u)));
-                tc5::commit2(bar(B_KEMPTY0 + (g & 1u)));
+                for (int i = i0; i < i1; i++) {
+                    const int kb = i >> 2, ks = i & 3;
+                    tc5::mma_ss2(d, tc5::smem_desc_sw128(q_sm + kb * kBlk + ks * 32, 16, 1024), tc5::smem_desc_sw128(kst + kb * kBlkKh + ks * 32, 16, 1024), kIdescS, i != 0);
+                }
+                if (i1 == 16) { tc5::commit2(bar(B_SFULL0 + (g & 1u))); tc5::commit2(bar(B_KEMPTY0 + (g & 1u))); }
             };
             for (int it = 0; ok && it < my_items; it++) {
                 const PfItem t = item_of(it);
                 ok = mbar_wait_bounded(bar(B_QFULL), (uint32_t)it & 1u, err) && mbar_wait_bounded(bar(B_KFULL0 + (gt & 1u)), (gt >> 1) & 1u, err);
                 if (!ok) { atomicExch(err, 13); break; }
                 pf_stamp(3);
-                tc5::fence_after_sync(); issue_s(gt);
+                tc5::fence_after_sync(); issue_s(gt, 0, 16);
                 if (t.j1 - t.j0 == 1) tc5::commit2(bar(B_QEMPTY));
                 for (int j = t.j0; j < t.j1; j++, gt++) {
+                    // The tensor pipe holds only a few queued MMAs, so what this thread does between the last MMA of S(gt+1) and the first of
+                    // P.V(gt) is time the pipe may run dry: the barriers P.V(gt) needs are tried while S(gt+1) is being issued ('V full' before
+                    // its first MMA, 'P ready' before its last four; P(gt) is normally there by then) and waited for afterwards only if the
+                    // try failed. Measured on 29-tile parts: 2 % off the launch.
+                    bool v_ok = false, p_ok = false;
                     if (j + 1 < t.j1) {
                         if (!mbar_wait_bounded(bar(B_KFULL0 + ((gt + 1) & 1u)), ((gt + 1) >> 1) & 1u, err)) { atomicExch(err, 14); ok = false; break; }
-                        tc5::fence_after_sync(); issue_s(gt + 1);
+                        pf_stamp_tile(6, gt + 1);
+                        v_ok = mbar_try_wait(bar(B_VFULL0 + (gt & 1u)), (gt >> 1) & 1u) != 0;
+                        tc5::fence_after_sync(); issue_s(gt + 1, 0, 12);
+                        p_ok = mbar_try_wait(bar(B_PREADY0 + (gt & 1u)), (gt >> 1) & 1u) != 0;
+                        issue_s(gt + 1, 12, 16);
+                        pf_stamp_tile(1, gt + 1);
                         if (j + 2 == t.j1) tc5::commit2(bar(B_QEMPTY));   // the part's last S MMA: Q may be replaced
                     }
-                    // V of the tile has landed in both CTAs: tell both (their softmax warps zero the rows past the range in the tail tile), then wait for P
-                    if (!mbar_wait_bounded(bar(B_VFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
-                    mbar_arrive(bar(B_VLANDED0 + (gt & 1u))); tc5::mbar_arrive_peer(bar(B_VLANDED0 + (gt & 1u)));
-                    if (!mbar_wait_bounded(bar(B_PREADY0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
+                    // V of the tile has landed in both CTAs, then wait for P
+                    if (!v_ok && !mbar_wait_bounded(bar(B_VFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
+                    pf_stamp_tile(7, gt);
+                    if (j * kBNk + kBNk > t.kend) { mbar_arrive(bar(B_VLANDED0 + (nt & 1u))); tc5::mbar_arrive_peer(bar(B_VLANDED0 + (nt & 1u))); nt++; }   // a tail tile: the softmax warps of both CTAs zero the rows of V past the range once it has landed
+                    if (!p_ok && !mbar_wait_bounded(bar(B_PREADY0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }
                     if (j == t.j0 && it >= 1 && !mbar_wait_bounded(bar(B_OFREE), (uint32_t)(it - 1) & 1u, err)) { atomicExch(err, 15); ok = false; break; }   // the previous item's O has been read out
+                    pf_stamp_tile(2, gt);
                     tc5::fence_after_sync();
                     const uint32_t a = t_s0 + (gt & 1u) * 128u, vst = v_sm + (gt & 1u) * kHalfB;   // P: fp16 pairs in the first 64 columns of its S buffer
 #pragma unroll
@@ -206,7 +228,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                         tc5::mma_ts2(t_o, a + ks * 8, tc5::smem_desc_sw128(vst + ks * 2048, kBlk, 1024), kIdescPV, (j != t.j0) || ks != 0);
                     tc5::commit2(bar(B_ODONE0 + (gt & 1u)));
                     tc5::commit2(bar(B_VEMPTY0 + (gt & 1u)));
-                    pf_stamp(8 + (int)gt);
+                    pf_stamp_tile(3, gt);
                 }
             }
         }
@@ -215,17 +237,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         const int g = w >> 2, r = tid & 127;
         const uint32_t lane_sel = (uint32_t)((w & 3) * 32) << 16;
         const int pair_bar = 1 + (w & 3);   // named barrier of warps w and w + 4 (64 threads)
-        uint32_t gt = 0; bool alive = true;
+        uint32_t gt = 0, nt = 0; bool alive = true;   // nt: tail tiles so far, counted as the MMA thread counts them
         // Every thread runs every iteration and meets its partner at the pair barrier whatever happens: a wait that ran out only switches the work off.
         for (int it = 0; it < my_items; it++) {
         const PfItem t = item_of(it);
         const int q0 = t.q0, rows_valid = t.rows_valid, pos_base = t.pos_base, kend = t.kend, h = t.h, bi = t.bi, j0 = t.j0, j1 = t.j1;
         const int qpos = pos_base + q0 + r, lim = min(kend, qpos + 1);               // this row sees keys <= qpos (and < kend)
         float m = -INFINITY, l = 0.0f;
-        for (int j = j0; j < j1; j++, gt++) {
+        for (int j = j0; j < j1; nt += (j * kBNk + kBNk > kend) ? 1u : 0u, j++, gt++) {
             const uint32_t t_s = t_s0 + (gt & 1u) * 128u + lane_sel;
             if (alive && !warp_wait(bar(B_SFULL0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 16); alive = false; }
-            if (tid == 0) pf_stamp(24 + (int)gt);
+            if (tid == 0) pf_stamp_tile(4, gt);
             tc5::fence_after_sync();
             if (SCALED) {   // the tile's 128 K scales and 128 V scales: one value per softmax thread into shared memory, then everybody reads its 64 + 64
                 const int key = min(j * kBNk + (tid & 127), max(kend - 1, 0));
@@ -233,9 +255,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 asm volatile("bar.sync 9, 256;" ::: "memory");   // all eight softmax warps, every tile, whatever happened before
             }
             uint32_t v[2][32];
+#ifdef KATA_PF_TRACE
+            if (pf_ab & 2) {
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[c][i] = __float_as_uint((float)(i + (int)gt) * 0.01f);
+            } else
+#endif
+            {
 #pragma unroll
             for (int c = 0; c < 2; c++) tc5::ld32(t_s + g * 64 + c * 32, v[c]);
             tc5::wait_ld();
+            }
             if (KS) {
                 const uint4* kq = reinterpret_cast<const uint4*>(&s_sc[gt & 1u][0][g * 64]);
 #pragma unroll
@@ -287,7 +319,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             for (int c = 0; c < 2; c++)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
+#ifdef KATA_PF_TRACE
+                    const float p0 = (pf_ab & 1) ? fmaf(__uint_as_float(v[c][i]), kLog2e, -msub) : ex2(fmaf(__uint_as_float(v[c][i]), kLog2e, -msub)), p1 = (pf_ab & 1) ? fmaf(__uint_as_float(v[c][i + 1]), kLog2e, -msub) : ex2(fmaf(__uint_as_float(v[c][i + 1]), kLog2e, -msub));
+#else
                     const float p0 = ex2(fmaf(__uint_as_float(v[c][i]), kLog2e, -msub)), p1 = ex2(fmaf(__uint_as_float(v[c][i + 1]), kLog2e, -msub));
+#endif
                     sum += p0 + p1;
                     if (SCALED) { const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&s_sc[gt & 1u][1][g * 64 + c * 32 + i])); pk[c * 16 + (i >> 1)] = pack_h2(p0 * f.x, p1 * f.y); }
                     else pk[c * 16 + (i >> 1)] = pack_h2(p0, p1);
@@ -296,8 +332,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::st32(t_s + g * 32, pk);   // P: keys 0-63 in columns [0,32), keys 64-127 in [32,64) of the S buffer (the partner's scores there are in its registers since the pair barrier)
             tc5::wait_st();
             if (j * kBNk + kBNk > kend) {   // tail tile: rows of V past the range were loaded as they lie in memory; zero them (0 x garbage must stay 0)
-                // (the MMA thread announces every tile's V once it has landed in both CTAs)
-                if (!warp_wait(bar(B_VLANDED0 + (gt & 1u)), (gt >> 1) & 1u, err)) { atomicExch(err, 18); alive = false; break; }
+                // (the MMA thread announces the V of a tail tile once it has landed in both CTAs)
+                if (!warp_wait(bar(B_VLANDED0 + (nt & 1u)), (nt >> 1) & 1u, err)) { atomicExch(err, 18); alive = false; break; }
                 if (g == 0 && j * kBNk + r >= kend) {
                     uint8_t* v_gen = smem_raw + (v_sm + (gt & 1u) * kHalfB - sm0);
 #pragma unroll
@@ -310,7 +346,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive_leader(bar(B_PREADY0 + (gt & 1u)));
-            if (tid == 0) pf_stamp(40 + (int)gt);
+            if (tid == 0) pf_stamp_tile(5, gt);
             } while (0);
         }
         // ---- epilogue: the two threads of a row add their partial l and handle 128 columns each
@@ -414,7 +450,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         }
         }
     }
-    if (tid == 0) pf_stamp(67);
+    if (tid == 0) { pf_stamp(67); pf_stamp_clock(127); }
     tc5::fence_before_sync();
     __syncthreads();
     tc5::cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or arrive on its barriers
@@ -501,7 +537,8 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const 
 }  // namespace
 
 #ifdef KATA_PF_TRACE
-extern "C" int kata_debug_pf_trace(unsigned long long* h128) { return (int)cudaMemcpyFromSymbol(h128, g_pf_trace, sizeof(g_pf_trace)); }
+extern "C" int kata_debug_pf_trace(unsigned long long* h1024) { return (int)cudaMemcpyFromSymbol(h1024, g_pf_trace, sizeof(g_pf_trace)); }
+extern "C" int kata_debug_pf_trace_cta(int cta, int level, int ablate) { cudaMemcpyToSymbol(g_pf_trace_level, &level, sizeof(int)); cudaMemcpyToSymbol(g_pf_ablate, &ablate, sizeof(int)); return (int)cudaMemcpyToSymbol(g_pf_trace_cta, &cta, sizeof(int)); }
 #endif
 
 // scratch of the cut items: partial O rows and their (m, l)
