@@ -161,7 +161,7 @@ def run(args, rank, world, cfg, pk, ClockSampler, steps=None, warmup=None):
            "config": {"workload": f"{name}; {N_LAYERS} layers, {kv_mode} KV, bf16 projections, batch {B}/GPU, prep+prefill per layer", "batch_per_gpu": B, "global_batch": world * B,
                       "l2": ("each step streams the 16 layers' caches and activations, together larger than L2 (no flush needed)" if kind == "chunked" or B > 4 else
                              "NOT larger than L2: one layer's K/V for 512 tokens is 2 MB and the 16 layers' activations 450 MB are streamed once; the kernel is launch- and latency-bound at this size, not bandwidth-bound"),
-                      "kernel": "prefill_tc5_kernel (tcgen05, cta_group::2)" + ("" if kv_mode == "fp16" else " after expand_codes_kernel") + " (+ prefill_combine_kernel when items are cut between CTA pairs)",
+                      "kernel": "prefill_tc5_kernel (tcgen05, cta_group::2)" + ("" if kv_mode == "fp16" else " after expand_codes_kernel") + " (items cut between CTA pairs are merged in the kernel)",
                       "launch": "CUDA graph replay of one step for value and roofline (a layer is shorter than two calls through the Python binding); plain calls for e2e" if use_graph else "plain calls"},
            "clocks": clocks, "gpu_launches": int(launches),
            "e2e": {"value": world * B * toks * steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

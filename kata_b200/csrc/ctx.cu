@@ -20,7 +20,7 @@ cudaError_t configure_decode(int kv_mode);
 cudaError_t configure_decode_scalar();
 cudaError_t launch_out_fwht(const float* x, const float* sign, float* out, int64_t rows, int width, cudaStream_t s);
 cudaError_t configure_prefill(int kv_mode);
-size_t prefill_part_o_bytes(); size_t prefill_part_ml_bytes();
+size_t prefill_part_o_bytes(); size_t prefill_part_ml_bytes(); size_t prefill_part_flag_bytes();
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s, int tok_stride = 0, int tok0 = 0, const PeerSink* sink = nullptr, bool* sink_used = nullptr);
 int decode_partial_impl(kata_attn_ctx* h, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi, const void* d_q16, float* d_part,
@@ -104,7 +104,8 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
     if (ok && cfg->kv_mode == KATA_KV_FP16)
         ok = cudaMalloc((void**)&c.sc_pm, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess && cudaMalloc((void**)&c.sc_pl, kata::scalar_scratch_floats_pm() * 4) == cudaSuccess &&
              cudaMalloc((void**)&c.sc_pacc, kata::scalar_scratch_floats_acc() * 4) == cudaSuccess;
-    ok = ok && cudaMalloc((void**)&c.pf_part_o, kata::prefill_part_o_bytes()) == cudaSuccess && cudaMalloc((void**)&c.pf_part_ml, kata::prefill_part_ml_bytes()) == cudaSuccess;
+    ok = ok && cudaMalloc((void**)&c.pf_part_o, kata::prefill_part_o_bytes()) == cudaSuccess && cudaMalloc((void**)&c.pf_part_ml, kata::prefill_part_ml_bytes()) == cudaSuccess &&
+         cudaMalloc((void**)&c.pf_part_flag, kata::prefill_part_flag_bytes()) == cudaSuccess && cudaMemset(c.pf_part_flag, 0, kata::prefill_part_flag_bytes()) == cudaSuccess;
     int64_t stage_rows = 0;
     if (ok && c.v8()) {   // staging arena of the tcgen05 prefill: one layer of every sequence, the int8 planes' codes expanded to fp16
         for (int sq = 0; sq < cfg->n_seqs; sq++) { c.stage_row0.push_back(stage_rows); stage_rows += cfg->max_ctx[sq]; }
@@ -131,7 +132,7 @@ int kata_attn_create(const kata_attn_config* cfg, kata_attn_ctx** out) {
 int kata_attn_destroy(kata_attn_ctx* h) {
     if (!h) return KATA_ERR_ARG;
     Ctx& c = h->c; DeviceGuard guard(c.cfg.device);
-    void* ptrs[] = {c.k_arena, c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, c.sc_pm, c.sc_pl, c.sc_pacc, c.k16_stage, c.v16_stage, c.pf_part_o, c.pf_part_ml};
+    void* ptrs[] = {c.k_arena, c.v_arena, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err, c.sc_pm, c.sc_pl, c.sc_pacc, c.k16_stage, c.v16_stage, c.pf_part_o, c.pf_part_ml, c.pf_part_flag};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete h;
     return KATA_OK;
@@ -162,7 +163,7 @@ int kata_attn_check(kata_attn_ctx* h, void* stream) {
     Ctx& c = h->c; DeviceGuard guard(c.cfg.device);
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream); if (e != cudaSuccess) return cuda_fail(c, e, "synchronize");
     int32_t flag = 0; e = cudaMemcpy(&flag, c.d_err, 4, cudaMemcpyDeviceToHost); if (e != cudaSuccess) return cuda_fail(c, e, "read error word");
-    if (flag) { cudaMemset(c.d_err, 0, 4); return fail(c, KATA_ERR_DEVICE_WAIT, "a bounded device-side wait ran out (code %d); results of that call are invalid", flag); }
+    if (flag) { cudaMemset(c.d_err, 0, 4); cudaMemset(c.pf_part_flag, 0, kata::prefill_part_flag_bytes()); return fail(c, KATA_ERR_DEVICE_WAIT, "a bounded device-side wait ran out (code %d); results of that call are invalid", flag); }
     return KATA_OK;
 }
 

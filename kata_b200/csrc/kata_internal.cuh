@@ -62,7 +62,7 @@ struct Ctx {
     __half* k16_stage = nullptr; __half* v16_stage = nullptr; std::vector<int64_t> stage_row0;   // int8 mode: one layer of fp16-expanded codes for the tcgen05 prefill, [sum of max_ctx][1024] each; first row per sequence
     CUtensorMap tm_k64h_stage{}, tm_v128h_stage{};
     CUtensorMap tm_k64h{}, tm_v128h{};   // rank-4 views for the tcgen05 prefill (fp16 mode): 64 keys x 256 dims of K, 128 keys x 128 dims of V (the halves a CTA of a pair loads)
-    float* pf_part_o = nullptr; float* pf_part_ml = nullptr;   // tcgen05 prefill: partial rows and (m, l) of items cut between CTA pairs
+    float* pf_part_o = nullptr; float* pf_part_ml = nullptr; int32_t* pf_part_flag = nullptr;   // tcgen05 prefill: partial rows and (m, l) of items cut between CTA pairs; one flag per part (up while the part waits to be folded into its item's head)
     // host-side work plan of the last tcgen05 prefill launch, reused while (chunk length, positions) stay the same (the layers of a chunk)
     alignas(8) unsigned char pf_plan_cache[2048] = {}; int pf_plan_M = -1, pf_plan_n = -1; int32_t pf_plan_pos[KATA_MAX_BATCH] = {}; int32_t pf_plan_tiles[(KATA_MAX_CHUNK / 128) * (KATA_HEADS / 2) * KATA_MAX_BATCH] = {};
     int32_t* d_err = nullptr;           // device error word: nonzero after a bounded wait ran out

@@ -8,11 +8,14 @@
 // tensor memory and pipelines kept across items; the next item's Q, K and V loads and first score MMAs run under the current item's epilogue.
 // Work split: the key tiles of all items form one list (longest items first) which the host cuts into one contiguous range per pair,
 // balanced by tiles plus a per-part allowance for the epilogue, so that a launch with fewer items than pairs (one sequence: 48 items for 74
-// pairs) still uses every SM. A pair whose range ends inside an item computes that item over a sub-range of its key tiles ("part") and
-// writes the unnormalised O rows with their (m, l) to scratch; prefill_combine_kernel (a dependent launch over all SMs) then merges the
-// parts of every cut item with the split-KV rule of the decode path (weights exp(m - M)), normalises, gates and writes the rows. (Merging in
-// the CTA that finishes an item's last part was tried first: one SM pulling 400 KB through its few resident warps took 20 us per item.)
-// The host cuts items only when its estimate says the shorter critical path pays for the combine pass. The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
+// pairs) still uses every SM. The parts of a cut item lie on consecutive pairs: its head (the tiles from 0) is the last part of its pair's
+// range, every other part the first of its pair's. A pair computes such a part first, writes the unnormalised O rows with their (m, l) to
+// scratch and raises the part's flag; the pair that holds the head finishes the item: once its own tiles are done (its Q, K and V tiles are
+// then free) its producer warps copy the other parts into that shared memory as their flags come up, and the softmax warps fold them
+// into O in tensor memory with the split-KV rule of the decode path (weights exp(m - M)) before the usual epilogue. (A merge kernel behind
+// this one was used before: its CTAs could not start until the pairs had left the SMs, and it re-read 30 MB of parts through L2: 15 us after
+// a 50 us launch at batch 1. Merging by plain loads in the CTA that finished an item's last part was tried before that: 20 us per item.)
+// The host cuts items only when its estimate says the shorter critical path pays for the fold. The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
 // accumulators and half of every K tile (64 of the 128 keys) and V tile (128 of the 256 dims); the tensor cores of the two SMs exchange
 // the halves, so each SM writes and reads half the K/V bytes through its shared memory, which is what bounds an M = 128 tile with
 // 256-wide heads (Q, K, V tiles plus their TMA writes ask for more than the 128 bytes per clock an SM's shared memory delivers).
@@ -52,6 +55,8 @@ using namespace ptx;
 // Development aid, compiled only with -DKATA_PF_TRACE (never in the shipped library): CTA 0 records %globaltimer stamps of its phases.
 #ifdef KATA_PF_TRACE
 __device__ unsigned long long g_pf_trace[1280];   // [0,128): phases of the launch; 128 * kind + tile for the per-tile stamps (kinds 1-9)
+__device__ unsigned long long g_pf_cta[148 * 4];   // per CTA: start, wait returned, last P.V of the last part complete, exit
+#define pf_cta_stamp(k) do { if (blockIdx.x < 148) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_pf_cta[blockIdx.x * 4 + (k)] = t_; } } while (0)
 __device__ int g_pf_trace_cta = 0, g_pf_trace_level = 1, g_pf_ablate = 0;   // ablate (timing experiments, wrong results): 1 no exp, 2 no score load   // level 0: only the P.V-issued stamp of every tile
 #define PF_TRACE_INIT const int pf_ab = g_pf_ablate; const int pf_tr = ((int)blockIdx.x == g_pf_trace_cta) ? 1 + g_pf_trace_level : 0;   /* read once: a stamp must not cost a global load */
 #define pf_stamp(slot) do { if (pf_tr && (slot) < 1280) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_pf_trace[(slot)] = t_; } } while (0)
@@ -62,6 +67,7 @@ __device__ int g_pf_trace_cta = 0, g_pf_trace_level = 1, g_pf_ablate = 0;   // a
 #define pf_stamp(slot) do { } while (0)
 #define pf_stamp_tile(kind, tile) do { } while (0)
 #define pf_stamp_clock(slot) do { } while (0)
+#define pf_cta_stamp(k) do { } while (0)
 #endif
 
 constexpr int kTcThreads = 352, kBMq = 128, kBNk = 128;
@@ -84,9 +90,13 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const i
 struct PfStage { int64_t kv_row0[KATA_MAX_BATCH]; };   // SCALED: first row of sequence b in the fp16 staging arena (position 0)
 struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh, bi; int64_t sc_row0; int idx, j0, j1, slot; bool whole; };   // row0 / row0v: row of position 0 in the arena the K / V tiles come from; [j0, j1): this part's key tiles
 constexpr int kMaxPairs = 74;      // CTA pairs of a launch (one per two SMs of a B200)
+constexpr double kCutCostUs = 5.0, kFoldCostUs = 2.7;   // host-side estimate of what cutting items costs a launch: the wait for a part that ends with the launch and the fold of the first part, then of each further part (measured: 2.7 us per part, L2 -> shared memory bound)
 constexpr int kPartE = 2;          // host-side allowance, in key tiles, for what a part costs besides its tiles (Q load, epilogue or partial write)
 // Pair p works on the flat tile list from (item item0[p], tile tile0[p]) up to, not including, (item0[p+1], tile0[p+1]).
 struct PfPlan { int32_t n_pairs; int32_t item0[kMaxPairs + 1]; int32_t tile0[kMaxPairs + 1]; int32_t hp_lo, hp_n; };   // hp_lo, hp_n: the head pairs (3 per KV head) this launch computes
+constexpr int kZoneMl = 128 * 1024;   // landing zone over the Q, K and V tiles: a part's 128 KB of rows as they lie in scratch, then the rows' (m, l)
+// A part's rows in scratch: 16-byte chunk c (columns 4c .. 4c+3) of row r at chunk index c * 128 + r, so that the 32 rows of a warp (a thread holds one row
+// of tensor memory) write and read 512 contiguous bytes per chunk.
 constexpr size_t kPartOFloats = (size_t)kBMq * kD, kPartSlots = 2 * 2 * kMaxPairs;   // a slot = one CTA's 128 x 256 partial O; two parts per pair, two CTAs per pair
 
 // MODE = the context's cache mode. An int8 plane's tiles are its codes expanded to fp16 (exact integers) in a staging arena whose rows are
@@ -96,7 +106,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                                                                    const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_kind, int32_t* err,
                                                                    const PfStage stg, const __half* __restrict__ ksc, const __half* __restrict__ vsc,
-                                                                   const __grid_constant__ PfPlan plan, float* part_o, float* part_ml) {
+                                                                   const __grid_constant__ PfPlan plan, float* part_o, float* part_ml, int32_t* part_flag) {
     constexpr bool KS = MODE == KATA_KV_INT8, KST = MODE == KATA_KV_INT8 || MODE == KATA_KV_INT8G, SCALED = MODE != KATA_KV_FP16;   // KS: scores take the key scale; KST: K tiles come from the staging arena (int8g: already scaled there); SCALED: P takes the value scale
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -111,13 +121,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         t.j0 = it == 0 ? tile_lo : 0; t.j1 = idx == item_hi ? tile_hi : t.n_tiles; t.whole = t.j0 == 0 && t.j1 == t.n_tiles; t.slot = (2 * pair + (it == 0 ? 0 : 1)) * 2 + (int)rank;
         return t;
     };
+    // The parts of a cut item lie on consecutive pairs, its head (tiles from 0) last in its pair's range, every other part first in its pair's.
+    auto pair_empty = [&](int p) { return plan.item0[p] == plan.item0[p + 1] && plan.tile0[p] >= plan.tile0[p + 1]; };
+    auto next_part_pair = [&](int idx, int p) {   // the next pair after p whose range starts inside item idx, or -1
+        for (int q = p + 1; q < plan.n_pairs && plan.item0[q] == idx; q++) if (!pair_empty(q)) return q;
+        return -1;
+    };
+    auto other_slot = [&](int p2) { return (2 * p2) * 2 + (int)rank; };   // the part at the start of pair p2's range, this CTA's head
+    bool merge_here = false; int merge_idx = -1;   // this pair's last part is the head of a cut item: its epilogue folds the other parts in
+    if (my_items > 0) { const PfItem tl = item_of(my_items - 1); merge_here = tl.j0 == 0 && tl.j1 < tl.n_tiles; merge_idx = tl.idx; }
     const uint32_t sm0 = smem_u32(smem_raw), base = (sm0 + 1023u) & ~1023u;
     const uint32_t q_sm = base, k_sm = base + kTileB, v_sm = base + kTileB + 2 * kHalfB, bars = base + kTileB + 4 * kHalfB;   // K stage s at k_sm + s * kHalfB, V stage s at v_sm + s * kHalfB
-    __shared__ uint32_t s_tmem; __shared__ float s_xmax[2][2][128], s_lsum[2][128]; __shared__ __align__(16) float s_stage[8][16 * 36]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
+    __shared__ uint32_t s_tmem; __shared__ int s_pick; __shared__ float s_xmax[2][2][128], s_lsum[2][128]; __shared__ __align__(16) float s_stage[8][16 * 36]; __shared__ __align__(16) __half s_sc[2][2][128];   // SCALED: [tile parity][K, V][key] scales of the tile   // [tile parity][key half][row]: row maxima exchanged by the two threads of a row; their partial l
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
     PF_TRACE_INIT
-    if (tid == 0) { pf_stamp(0); pf_stamp_clock(126); }
+    if (tid == 0) { pf_stamp(0); pf_stamp_clock(126); pf_cta_stamp(0); }
     if (tid == 0) {
         for (int i = 0; i < B_COUNT; i++) mbar_init(bar(i), (i == B_PREADY0 || i == B_PREADY1 || i == B_OFREE) ? 16u : 1u);   // 'P ready', 'O free': one arrival per softmax warp of both CTAs
         fence_mbar_init();
@@ -131,6 +150,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     const uint32_t tmem = s_tmem, t_o = tmem, t_s0 = tmem + 256;
     if (tid == 0) pf_stamp(1);
     pdl_wait(); pdl_launch_dependents();
+    if (tid == 0) pf_cta_stamp(1);
     if (tid == 0) pf_stamp(2);   // launched with programmatic stream serialisation: the set-up above overlapped the previous kernel (the chunk's prep); its rows and Q are read from here on
     // Running counters shared by construction: gt = key tiles so far over all items of this pair (stage, score buffer and phase of the
     // per-tile barriers), it = items so far (phase of the per-item barriers).
@@ -173,7 +193,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 }
                 ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                 if (!ok) break;
-                if (j == t.j1 - 1 && t.whole) {
+                if (j == t.j1 - 1 && t.j0 == 0) {
                     const float* gt0 = gate + ((int64_t)t.bi * M + t.q0) * kQD + t.h * kD;
                     for (int row = lane; row < t.rows_valid; row += 32) prefetch_l2_bulk(gt0 + (int64_t)row * kQD, kD * 4);
                 }
@@ -361,8 +381,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         float* tile = s_stage[w];                     // [16 rows][36]
         const int rq = lane >> 3, cq = (lane & 7) * 4, rbase = 32 * (w & 3);
         const int64_t obase = ((int64_t)bi * M + q0 + rbase) * kQD + h * kD + g * 128 + cq;
-        if (t.whole) {
-        // whole item: O / l * sigmoid(gate) straight to the output rows
+        if (j0 == 0) {
+        // whole item, or the head of a cut item: O / l * sigmoid(gate) straight to the output rows
         float4 gv[8];   // gate logits of the block in flight: [pass][k] -> warp row 16 * pass + 4 * k + rq, columns cq .. cq + 3 of the block
         auto load_gate = [&](int c, float4 (&dst)[8]) {
 #pragma unroll
@@ -373,9 +393,80 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
         };
         load_gate(0, gv);   // in flight while the item's last P.V completes
         if (tid == 0) pf_stamp(56);
-        if (alive && warp_wait(bar(B_ODONE0 + ((gt - 1u) & 1u)), ((gt - 1u) >> 1) & 1u, err)) {
-            if (tid == 0) pf_stamp(57);
+        if (alive && !warp_wait(bar(B_ODONE0 + ((gt - 1u) & 1u)), ((gt - 1u) >> 1) & 1u, err)) { atomicExch(err, 19); alive = false; }
+        {
+            if (tid == 0) { pf_stamp(57); if (it == my_items - 1) pf_cta_stamp(2); }
             tc5::fence_after_sync();
+            if (j1 < t.n_tiles) {
+                // Head of a cut item (always the pair's last part): every MMA of the pair is complete, so the Q, K and V tiles are free and serve as
+                // the landing zone of the other parts' unnormalised rows, one part at a time: when a part's flag is up (raised by the CTA that
+                // wrote it; the wait is bounded like every other) the eight warps copy its 128 KB and its (m, l) with cp.async, 32 chunks of 16
+                // bytes per thread in flight at once, and each thread folds its row of the part into its row of O in tensor memory with the
+                // split-KV rule (k_attn_dec_combine, shaders/flash.metal:143-152, one "split" at a time: new maximum, both sides rescaled).
+                // m is finite here: key 0 is in the head.
+                const uint8_t* zone = smem_raw + (base - sm0);
+                int n_other = 0;
+                for (int p2 = next_part_pair(t.idx, pair); p2 >= 0; p2 = next_part_pair(t.idx, p2)) n_other++;
+                uint64_t done0 = 0, done1 = 0;   // thread 0: the parts folded so far (a cut item has at most 73 other parts)
+                for (int k = 0; k < n_other; k++) {
+                    // Thread 0 picks the next part: the first one not yet folded whose flag is up (a part computed at the start of its pair's range has
+                    // been there for long; one that fills its pair's whole range arrives when this pair's own tiles end), and tells the others.
+                    if (tid == 0) {
+                        int pick = -1;
+                        for (uint32_t i = 0; i < (1u << 20) && pick < 0; i++) {
+                            int q = 0;
+                            for (int p2 = next_part_pair(t.idx, pair); p2 >= 0 && pick < 0; p2 = next_part_pair(t.idx, p2), q++) {
+                                if (((q < 64 ? done0 >> q : done1 >> (q - 64)) & 1ull) != 0) continue;
+                                int got; asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(got) : "l"(part_flag + other_slot(p2)) : "memory");
+                                if (got) { pick = p2; if (q < 64) done0 |= 1ull << q; else done1 |= 1ull << (q - 64); }
+                            }
+                            if (pick < 0 && (i & 63u) == 63u && *reinterpret_cast<const volatile int32_t*>(err) != 0) break;
+                        }
+                        s_pick = pick;
+                    }
+                    asm volatile("bar.sync 10, 256;" ::: "memory");
+                    const int p2 = s_pick;
+                    if (p2 < 0) { if (alive) { atomicExch(err, 20); alive = false; } break; }   // the same for all eight warps
+                    const int sl = other_slot(p2);
+                    if (alive) {   // four groups of copies, one per 32-column block of the two halves, so that a block is folded while the next ones land
+                        const float* src = part_o + (size_t)sl * kPartOFloats;
+                        if (tid < 64) cp_async16(base + (uint32_t)(kZoneMl + tid * 16), part_ml + (size_t)sl * (2 * kBMq) + tid * 4, 16);
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+#pragma unroll
+                            for (int u = 0; u < 8; u++) { const int n = 16 * (u >> 2) + 4 * c + (u & 3); cp_async16(base + (uint32_t)(tid + 256 * n) * 16u, src + (size_t)(tid + 256 * n) * 4, 16); }
+                            cp_async_commit();
+                        }
+                    }
+                    float2 mlq = make_float2(-INFINITY, 0.0f); float mn = m, a = 1.0f, bq = 0.0f;
+                    const float4* zr = reinterpret_cast<const float4*>(zone) + r;
+                    auto fold_block = [&](int c) {   // every lane, whatever its row: the tensor-memory loads and stores are warp-wide instructions (rows past the chunk fold garbage that is never stored)
+                        uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const float4 z = zr[(g * 32 + c * 8 + i) * 128];
+                            o[4 * i] = __float_as_uint(fmaf(__uint_as_float(o[4 * i]), a, bq * z.x)); o[4 * i + 1] = __float_as_uint(fmaf(__uint_as_float(o[4 * i + 1]), a, bq * z.y));
+                            o[4 * i + 2] = __float_as_uint(fmaf(__uint_as_float(o[4 * i + 2]), a, bq * z.z)); o[4 * i + 3] = __float_as_uint(fmaf(__uint_as_float(o[4 * i + 3]), a, bq * z.w));
+                        }
+                        tc5::st32(t_o + lane_sel + g * 128 + c * 32, o);
+                    };
+                    cp_async_wait<3>(); asm volatile("bar.sync 10, 256;" ::: "memory");   // the (m, l) pairs and block 0 have landed (all eight warps, whatever happened)
+                    if (alive) {
+                        mlq = *reinterpret_cast<const float2*>(zone + kZoneMl + r * 8);
+                        mn = fmaxf(m, mlq.x); a = ex2(m - mn); bq = (mlq.x == -INFINITY) ? 0.0f : ex2(mlq.x - mn);
+                        fold_block(0);
+                    }
+                    cp_async_wait<2>(); asm volatile("bar.sync 10, 256;" ::: "memory");
+                    if (alive) fold_block(1);
+                    cp_async_wait<1>(); asm volatile("bar.sync 10, 256;" ::: "memory");
+                    if (alive) fold_block(2);
+                    cp_async_wait<0>(); asm volatile("bar.sync 10, 256;" ::: "memory");
+                    if (alive) { fold_block(3); tc5::wait_st(); l = fmaf(l, a, bq * mlq.y); m = mn; }
+                    asm volatile("bar.sync 10, 256;" ::: "memory");   // everybody has read the part: the zone may take the next one
+                }
+            }
+        }
+        if (alive) {
             const float inv = 1.0f / l;
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
@@ -415,10 +506,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive_leader(bar(B_OFREE));
-        } else if (alive) { atomicExch(err, 19); alive = false; }
+        }
         } else {
-        // part of an item: the unnormalised O rows (fp32) and their (m, l) go to this part's scratch slot for prefill_combine_kernel
-        float* po = part_o + (size_t)t.slot * kPartOFloats + (size_t)rbase * kD + g * 128 + cq;
+        // another part of a cut item (always the pair's first part): the unnormalised O rows (fp32) and their (m, l) go to this part's scratch slot,
+        // from where the pair that holds the item's head takes them
+        float4* po = reinterpret_cast<float4*>(part_o + (size_t)t.slot * kPartOFloats) + r;   // chunk c of this thread's row at po[c * 128]: a warp's 32 rows are 512 contiguous bytes
         if (alive && warp_wait(bar(B_ODONE0 + ((gt - 1u) & 1u)), ((gt - 1u) >> 1) & 1u, err)) {
             tc5::fence_after_sync();
             if (g == 0) *reinterpret_cast<float2*>(part_ml + (size_t)t.slot * (2 * kBMq) + 2 * r) = make_float2(m, l);   // m in log2 units; -inf when the row saw no key of this part
@@ -426,82 +518,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
             for (int c = 0; c < 4; c++) {
                 uint32_t o[32]; tc5::ld32(t_o + lane_sel + g * 128 + c * 32, o); tc5::wait_ld();
 #pragma unroll
-                for (int pass = 0; pass < 2; pass++) {
-                    if ((lane >> 4) == pass) {
-#pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            *reinterpret_cast<float4*>(tile + (lane & 15) * 36 + 4 * i) = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int row = 16 * pass + 4 * k + rq;
-                        if (rbase + row < rows_valid) __stcg(reinterpret_cast<float4*>(po + (size_t)row * kD + c * 32), *reinterpret_cast<const float4*>(tile + (4 * k + rq) * 36 + cq));
-                    }
-                    __syncwarp();
-                }
+                for (int i = 0; i < 8; i++) __stcg(po + (g * 32 + c * 8 + i) * 128, make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3])));
             }
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive_leader(bar(B_OFREE));
+            __threadfence();   // the rows and their (m, l) before the flag
         } else if (alive) { atomicExch(err, 19); alive = false; }
+        // the part is in scratch: raise its flag for the pair that holds the item's head (all eight warps meet here whatever happened; the flag only goes up when all is well)
+        asm volatile("bar.sync 10, 256;" ::: "memory");
+        if (tid == 0 && alive) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(part_flag + t.slot), "r"(1) : "memory");
         if (tid == 0) pf_stamp(80);
-        if (tid == 0) pf_stamp(85);
         }
         }
     }
     if (tid == 0) { pf_stamp(67); pf_stamp_clock(127); }
     tc5::fence_before_sync();
     __syncthreads();
+    if (tid == 0 && merge_here)   // the flags this CTA consumed go down again for the next launch (its writers start after this kernel has completed)
+        for (int p2 = next_part_pair(merge_idx, pair); p2 >= 0; p2 = next_part_pair(merge_idx, p2)) part_flag[other_slot(p2)] = 0;
     tc5::cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or arrive on its barriers
     if (w == 0) tc5::tmem_dealloc2(tmem, 512);
-    if (tid == 0) pf_stamp(68);
-}
-
-// Merge of the parts of every item the plan cuts (k_attn_dec_combine's rule, shaders/flash.metal:143-152, with "split" = part): per row,
-// M = max m_p, weights exp2(m_p - M), O = sum w_p O_p / sum w_p l_p, times sigmoid(gate). grid = (16-row blocks of the 128-row tile, head of
-// the pair, cut item); 256 threads = 16 rows x 16 lanes, a lane taking columns 4*lane .. +3 of each of the four 64-column quarters, so that
-// every 128-bit load and store of 16 lanes is a contiguous 256 bytes. Launched with programmatic stream serialisation behind the prefill kernel.
-struct PfCuts { int32_t n; int32_t idx[kMaxPairs]; int32_t pa[kMaxPairs]; int32_t pb[kMaxPairs]; };   // cut items and the pairs holding their first and last tile
-__global__ void __launch_bounds__(256) prefill_combine_kernel(const Batch b, const int M, const float* __restrict__ gate, void* __restrict__ out, const int out_kind,
-                                                              const __grid_constant__ PfPlan plan, const __grid_constant__ PfCuts cuts,
-                                                              const float* __restrict__ part_o, const float* __restrict__ part_ml) {
-    const int idx = cuts.idx[blockIdx.z], pa = cuts.pa[blockIdx.z], pb = cuts.pb[blockIdx.z], rank = blockIdx.y;
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = plan.hp_n * b.n, qt = n_q - 1 - idx / per_q, rem = idx % per_q, bi = rem / plan.hp_n, h = 2 * (plan.hp_lo + rem % plan.hp_n) + rank;
-    const int q0 = qt * kBMq, rows_valid = min(kBMq, M - q0), R = blockIdx.x * 16 + (threadIdx.x >> 4), c4 = (threadIdx.x & 15) * 4;
-    pdl_wait(); pdl_launch_dependents();   // the parts are complete and visible from here on
-    if (R >= rows_valid) return;
-    auto holds = [&](int p) {   // pair p holds a part of the item: its range reaches into the item and is not empty
-        const int i0 = plan.item0[p], t0 = plan.tile0[p], i1 = plan.item0[p + 1], t1 = plan.tile0[p + 1];
-        return i0 <= idx && (i1 > idx || (i1 == idx && t1 > 0)) && (i0 < i1 || t0 < t1);
-    };
-    auto slot_of = [&](int p) { return (2 * p + (plan.item0[p] == idx ? 0 : 1)) * 2 + rank; };   // a pair's first part sits in its slot 0, its last in slot 1
-    const int64_t oi = ((int64_t)bi * M + q0 + R) * kQD + h * kD + c4;
-    float4 gg[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) gg[c] = *reinterpret_cast<const float4*>(gate + oi + c * 64);
-    float Mx = -INFINITY;
-    for (int p = pa; p <= pb; p++) if (holds(p)) Mx = fmaxf(Mx, __ldcg(part_ml + (size_t)slot_of(p) * (2 * kBMq) + 2 * R));
-    float L = 0.0f; float4 A[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) A[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int p = pa; p <= pb; p++) {
-        if (!holds(p)) continue;
-        const int sl = slot_of(p);
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (size_t)sl * (2 * kBMq) + 2 * R));
-        const float* src = part_o + (size_t)sl * kPartOFloats + (size_t)R * kD + c4;
-        float4 o4[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) o4[c] = __ldcg(reinterpret_cast<const float4*>(src + c * 64));
-        const float wt = (ml.x == -INFINITY) ? 0.0f : ex2(ml.x - Mx);
-        L += ml.y * wt;
-#pragma unroll
-        for (int c = 0; c < 4; c++) { A[c].x += o4[c].x * wt; A[c].y += o4[c].y * wt; A[c].z += o4[c].z * wt; A[c].w += o4[c].w * wt; }
-    }
-    const float inv = 1.0f / L;
-#pragma unroll
-    for (int c = 0; c < 4; c++)
-        store_act4(out, oi + c * 64, make_float4(A[c].x * inv * sigmoid_approx(gg[c].x), A[c].y * inv * sigmoid_approx(gg[c].y), A[c].z * inv * sigmoid_approx(gg[c].z), A[c].w * inv * sigmoid_approx(gg[c].w)), out_kind);
+    if (tid == 0) { pf_stamp(68); pf_cta_stamp(3); }
 }
 
 // int8 planes: expands the codes of rows [0, kend_b) of every sequence of the batch (one layer) to fp16 in the staging arena. The values are
@@ -538,12 +576,14 @@ __global__ void __launch_bounds__(256) expand_codes_kernel(const Batch b, const 
 
 #ifdef KATA_PF_TRACE
 extern "C" int kata_debug_pf_trace(unsigned long long* h1024) { return (int)cudaMemcpyFromSymbol(h1024, g_pf_trace, sizeof(g_pf_trace)); }
+extern "C" int kata_debug_pf_ctas(unsigned long long* h) { return (int)cudaMemcpyFromSymbol(h, g_pf_cta, sizeof(g_pf_cta)); }
 extern "C" int kata_debug_pf_trace_cta(int cta, int level, int ablate) { cudaMemcpyToSymbol(g_pf_trace_level, &level, sizeof(int)); cudaMemcpyToSymbol(g_pf_ablate, &ablate, sizeof(int)); return (int)cudaMemcpyToSymbol(g_pf_trace_cta, &cta, sizeof(int)); }
 #endif
 
 // scratch of the cut items: partial O rows and their (m, l)
 size_t prefill_part_o_bytes() { return kPartSlots * kPartOFloats * sizeof(float); }
 size_t prefill_part_ml_bytes() { return kPartSlots * 2 * kBMq * sizeof(float); }
+size_t prefill_part_flag_bytes() { return kPartSlots * sizeof(int32_t); }
 
 cudaError_t launch_prefill_mma(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s);
 cudaError_t configure_prefill_mma(int kv_mode);
@@ -576,7 +616,7 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     }
     // persistent CTA pairs, at most one per two SMs; the flat list of (item, key tile) is cut into one contiguous range per pair.
     // The plan depends only on (M, positions): the 16 layers of a chunk reuse the one computed for the first (kept in the context, no allocation).
-    struct Cached { PfPlan plan; PfCuts cuts; };
+    struct Cached { PfPlan plan; };
     static_assert(sizeof(Cached) <= sizeof(c.pf_plan_cache), "plan cache too small");
     Cached& cached = *reinterpret_cast<Cached*>(c.pf_plan_cache);
     bool hit = c.pf_plan_M == M && c.pf_plan_n == b.n;
@@ -636,50 +676,36 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
         alt.item0[total] = n_items; alt.tile0[total] = 0;
         if (max_load(alt) < max_load(plan)) plan = alt;
     }
-    // Plan U: no item is cut (every cut of plan A moved to the next item boundary). A cut plan has the shorter critical path but pays for the
-    // combine pass: its launch plus the traffic of the cut items' parts, gate and output rows. Estimate both in microseconds (a key tile
-    // of a CTA pair takes about 2.3 us at the rate the kernel sustains) and keep the cheaper.
-    // The items a plan cuts, with the first and last pair holding a part of each (empty pairs in between hold nothing); returns the number of parts.
-    auto cut_items = [&](const PfPlan& pl, PfCuts& out) {
-        int parts = 0; out.n = 0;
-        for (int p = 1; p < pl.n_pairs; p++) {
-            if (pl.tile0[p] == 0) continue;                                   // a cut at an item boundary cuts nothing
-            const int idx = pl.item0[p];
-            const bool repeat = pl.item0[p - 1] == idx && pl.tile0[p - 1] == pl.tile0[p];   // pair p - 1 is empty: the same cut again
-            if (out.n > 0 && out.idx[out.n - 1] == idx) { out.pb[out.n - 1] = p; if (!repeat) parts++; continue; }
-            out.idx[out.n] = idx; out.pa[out.n] = p - 1; out.pb[out.n] = p; out.n++; parts += 2;   // the cut before this one lies at or before the item's first tile: pair p - 1 holds it
-        }
-        return parts;
-    };
+    // Plan U: no item is cut (every cut of plan A moved to the next item boundary). A cut plan has the shorter critical path but its heads wait for
+    // the other parts to be written and fold them in (a few microseconds at the end of the launch). Estimate both in microseconds (a key tile of a
+    // CTA pair takes about 2.3 us at the rate the kernel sustains, power-capped) and keep the cheaper.
     {
-        PfPlan whole = plan;
-        for (int p = 1; p < whole.n_pairs; p++) if (whole.tile0[p] > 0) { whole.tile0[p] = 0; whole.item0[p] = std::min(whole.item0[p] + 1, n_items); }
-        PfCuts tmp{}; const int parts = cut_items(plan, tmp);
-        const double t_tile = 2.3, t_cut = max_load(plan) * t_tile + (tmp.n ? 4.0 + 2.0 * (parts + 2.0 * tmp.n) * (kPartOFloats * 4.0) / 5.0e6 : 0.0), t_whole = max_load(whole) * t_tile;
+        PfPlan whole = plan; int max_parts = 1, run = 1;   // run: parts so far of the item the current cut lies in
+        for (int p = 1; p < whole.n_pairs; p++) {
+            if (plan.tile0[p] == 0) { run = 1; continue; }
+            const bool same_item = plan.item0[p - 1] == plan.item0[p] && plan.tile0[p - 1] > 0, repeat = same_item && plan.tile0[p - 1] == plan.tile0[p];   // repeat: pair p - 1 is empty, the same cut again
+            run = same_item ? run + (repeat ? 0 : 1) : 2; max_parts = std::max(max_parts, run);
+            whole.tile0[p] = 0; whole.item0[p] = std::min(whole.item0[p] + 1, n_items);
+        }
+        const double t_tile = 2.3, t_cut = max_load(plan) * t_tile + (max_parts > 1 ? kCutCostUs + kFoldCostUs * (max_parts - 2) : 0.0), t_whole = max_load(whole) * t_tile;
         if (t_whole <= t_cut) plan = whole;
     }
-    PfCuts cuts{}; cut_items(plan, cuts);
     plan.hp_lo = hp_lo; plan.hp_n = hp_n;
-    cached.plan = plan; cached.cuts = cuts;
+    cached.plan = plan;
     c.pf_plan_M = M; c.pf_plan_n = b.n; for (int i = 0; i < b.n; i++) c.pf_plan_pos[i] = b.pos[i];
     }
-    const PfPlan& plan = cached.plan; const PfCuts& cuts = cached.cuts;
+    const PfPlan& plan = cached.plan;
     const int n_pairs = plan.n_pairs;
     cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(2 * n_pairs, 1, 1); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kSmemTc; cfg.stream = s;
     cudaLaunchAttribute at[2]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;   // a CTA pair is two neighbours along x
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 2;
-#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)out_dtype, c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc, plan, c.pf_part_o, c.pf_part_ml)
+#define KATA_PF(MD, TK, TV) cudaLaunchKernelEx(&cfg, prefill_tc5_kernel<MD>, tm_q, TK, TV, b, M, gate, out, (int)out_dtype, c.d_err, stg, (const __half*)c.ksc, (const __half*)c.vsc, plan, c.pf_part_o, c.pf_part_ml, c.pf_part_flag)
     const cudaError_t le = mode == KATA_KV_INT8G ? KATA_PF(KATA_KV_INT8G, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8 ? KATA_PF(KATA_KV_INT8, c.tm_k64h_stage, c.tm_v128h_stage) : mode == KATA_KV_INT8V ? KATA_PF(KATA_KV_INT8V, c.tm_k64h, c.tm_v128h_stage) : KATA_PF(KATA_KV_FP16, c.tm_k64h, c.tm_v128h);
 #undef KATA_PF
     if (le != cudaSuccess) return le;
     c.wrote_no_rows();
     c.launches++;
-    if (cuts.n) {
-        const cudaError_t ce = launch_pdl(prefill_combine_kernel, dim3(kBMq / 16, 2, cuts.n), dim3(256), 0, s, b, M, gate, out, (int)out_dtype, plan, cuts, (const float*)c.pf_part_o, (const float*)c.pf_part_ml);
-        if (ce != cudaSuccess) return ce;
-        c.launches++;
-    }
     return cudaGetLastError();
 }
 
