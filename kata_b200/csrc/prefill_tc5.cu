@@ -92,8 +92,14 @@ struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh
 constexpr int kMaxPairs = 74;      // CTA pairs of a launch (one per two SMs of a B200)
 constexpr double kCutCostUs = 5.0, kFoldCostUs = 2.7;   // host-side estimate of what cutting items costs a launch: the wait for a part that ends with the launch and the fold of the first part, then of each further part (measured: 2.7 us per part, L2 -> shared memory bound)
 constexpr int kPartE = 2;          // host-side allowance, in key tiles, for what a part costs besides its tiles (Q load, epilogue or partial write)
-// Pair p works on the flat tile list from (item item0[p], tile tile0[p]) up to, not including, (item0[p+1], tile0[p+1]).
-struct PfPlan { int32_t n_pairs; int32_t item0[kMaxPairs + 1]; int32_t tile0[kMaxPairs + 1]; int32_t hp_lo, hp_n; };   // hp_lo, hp_n: the head pairs (3 per KV head) this launch computes
+// Items in list order: sequences longest first (order[]), per sequence its KV heads, per KV head the query tiles last to first, per query tile the
+// three head pairs of the KV head: the 3 * n_q items of one (sequence, KV head) are neighbours and read the same K and V tiles.
+// A pair first computes `rounds` whole items, dealt in snake order (round k: item n_pairs * k + pair, pairs reversed in odd rounds), so that in
+// every round a dozen pairs work on the same (sequence, KV head) at the same pace and its tiles come from L2 (with contiguous ranges instead, 74
+// pairs on 64 different (sequence, KV head)s pull every item's K and V from HBM: 4 TB/s at batch 16). The items after the rounds are
+// cut into one contiguous range per pair: pair p works on them from (item0[p], tile0[p]) up to, not including, (item0[p+1], tile0[p+1]),
+// item numbers counted from the first item after the rounds; the ranges are sized so that a pair's rounds and range add up to the same load.
+struct PfPlan { int32_t n_pairs, rounds; int32_t item0[kMaxPairs + 1]; int32_t tile0[kMaxPairs + 1]; int32_t hp_lo, hp_n; uint8_t order[KATA_MAX_BATCH]; };   // hp_lo, hp_n: the head pairs (3 per KV head) this launch computes
 constexpr int kZoneMl = 128 * 1024;   // landing zone over the Q, K and V tiles: a part's 128 KB of rows as they lie in scratch, then the rows' (m, l)
 // A part's rows in scratch: 16-byte chunk c (columns 4c .. 4c+3) of row r at chunk index c * 128 + r, so that the 32 rows of a warp (a thread holds one row
 // of tensor memory) write and read 512 contiguous bytes per chunk.
@@ -111,20 +117,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t rank = tc5::cluster_rank();
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = plan.hp_n * b.n, pair = blockIdx.x / 2;
+    const int n_q = (M + kBMq - 1) / kBMq, grp_items = 3 * n_q, kvh_cnt = plan.hp_n / 3, pair = blockIdx.x / 2;
+    const int rounds = plan.rounds, rem0 = rounds * plan.n_pairs;   // rem0: list index of the first item after the rounds
     const int item_lo = plan.item0[pair], tile_lo = plan.tile0[pair], item_hi = plan.item0[pair + 1], tile_hi = plan.tile0[pair + 1];
-    const int my_items = (item_lo == item_hi && tile_lo >= tile_hi) ? 0 : item_hi - item_lo + (tile_hi > 0 ? 1 : 0);   // parts of this pair
-    auto item_of = [&](int it) {   // it-th part of this CTA pair
-        const int idx = item_lo + it, qt = n_q - 1 - idx / per_q, rem = idx % per_q;
-        PfItem t; t.idx = idx; t.bi = rem / plan.hp_n; t.h = 2 * (plan.hp_lo + rem % plan.hp_n) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
+    const int my_parts = (item_lo == item_hi && tile_lo >= tile_hi) ? 0 : item_hi - item_lo + (tile_hi > 0 ? 1 : 0);   // parts of this pair's range
+    const int my_items = rounds + my_parts;
+    auto item_of = [&](int it) {   // it-th item or part of this CTA pair
+        const int k = it - rounds;   // < 0: a whole item of round `it`
+        const int idx = k < 0 ? plan.n_pairs * it + ((it & 1) ? plan.n_pairs - 1 - pair : pair) : rem0 + item_lo + k;
+        const int grp = idx / grp_items, mem = idx % grp_items, qt = n_q - 1 - mem / 3;
+        PfItem t; t.idx = idx; t.bi = plan.order[grp / kvh_cnt]; t.h = 2 * (plan.hp_lo + (grp % kvh_cnt) * 3 + mem % 3) + (int)rank; t.kvh = t.h / kG;   // heads 2i and 2i+1 form a pair (same KV head)
         t.q0 = qt * kBMq; t.rows_valid = min(kBMq, M - t.q0); t.pos_base = b.pos[t.bi]; t.kend = t.pos_base + t.q0 + t.rows_valid; t.n_tiles = (t.kend + kBNk - 1) / kBNk; t.row0 = KST ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.row0v = SCALED ? (int)stg.kv_row0[t.bi] : (int)b.row_base[t.bi]; t.sc_row0 = b.row_base[t.bi];
-        t.j0 = it == 0 ? tile_lo : 0; t.j1 = idx == item_hi ? tile_hi : t.n_tiles; t.whole = t.j0 == 0 && t.j1 == t.n_tiles; t.slot = (2 * pair + (it == 0 ? 0 : 1)) * 2 + (int)rank;
+        t.j0 = k == 0 ? tile_lo : 0; t.j1 = (k >= 0 && item_lo + k == item_hi) ? tile_hi : t.n_tiles; t.whole = t.j0 == 0 && t.j1 == t.n_tiles; t.slot = (2 * pair + (k == 0 ? 0 : 1)) * 2 + (int)rank;
         return t;
     };
     // The parts of a cut item lie on consecutive pairs, its head (tiles from 0) last in its pair's range, every other part first in its pair's.
     auto pair_empty = [&](int p) { return plan.item0[p] == plan.item0[p + 1] && plan.tile0[p] >= plan.tile0[p + 1]; };
-    auto next_part_pair = [&](int idx, int p) {   // the next pair after p whose range starts inside item idx, or -1
-        for (int q = p + 1; q < plan.n_pairs && plan.item0[q] == idx; q++) if (!pair_empty(q)) return q;
+    auto next_part_pair = [&](int idx, int p) {   // the next pair after p whose range starts inside item idx (a list index), or -1
+        for (int q = p + 1; q < plan.n_pairs && plan.item0[q] == idx - rem0; q++) if (!pair_empty(q)) return q;
         return -1;
     };
     auto other_slot = [&](int p2) { return (2 * p2) * 2 + (int)rank; };   // the part at the start of pair p2's range, this CTA's head
@@ -614,7 +624,7 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
         expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1, c.kg() ? (const __half*)c.ksc : nullptr);
         c.launches++;
     }
-    // persistent CTA pairs, at most one per two SMs; the flat list of (item, key tile) is cut into one contiguous range per pair.
+    // persistent CTA pairs, at most one per two SMs; see PfPlan for the way the items are shared out.
     // The plan depends only on (M, positions): the 16 layers of a chunk reuse the one computed for the first (kept in the context, no allocation).
     struct Cached { PfPlan plan; };
     static_assert(sizeof(Cached) <= sizeof(c.pf_plan_cache), "plan cache too small");
@@ -623,42 +633,69 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     for (int i = 0; hit && i < b.n; i++) hit = c.pf_plan_pos[i] == b.pos[i];
     if (!hit) {
     const int hp_n = 3 * c.kvh_n, hp_lo = 3 * c.kvh_lo;   // head pairs of the KV heads this context computes
-    const int n_q = (M + kBMq - 1) / kBMq, per_q = hp_n * b.n, n_items = n_q * per_q, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
-    int32_t* nt_tab = c.pf_plan_tiles;   // key tiles per item (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
-    for (int idx = 0; idx < n_items; idx++) { const int qt = n_q - 1 - idx / per_q, bi = (idx % per_q) / hp_n, q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
+    const int n_q = (M + kBMq - 1) / kBMq, grp_items = 3 * n_q, n_items = grp_items * c.kvh_n * b.n, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
+    uint8_t order[KATA_MAX_BATCH];   // sequences of the batch, longest first (ties in batch order)
+    for (int i = 0; i < b.n; i++) order[i] = (uint8_t)i;
+    std::stable_sort(order, order + b.n, [&](uint8_t x, uint8_t y) { return b.pos[x] > b.pos[y]; });
+    int32_t* nt_tab = c.pf_plan_tiles;   // key tiles per item in list order (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
+    for (int idx = 0; idx < n_items; idx++) { const int grp = idx / grp_items, qt = n_q - 1 - (idx % grp_items) / 3, bi = order[grp / c.kvh_n], q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
     auto tiles_of = [&](int idx) { return (int)nt_tab[idx]; };
-    int64_t W = 0; for (int i = 0; i < n_items; i++) W += tiles_of(i) + kPartE;
     constexpr int kMinPart = 2;   // a part is at least two key tiles
-    // Plan A: equal ranges of the flat list. With fewer items than pairs the items are cut, but not into ranges shorter than two tiles plus the allowance.
-    auto max_load = [&](const PfPlan& pl) {
-        int worst = 0;
+    auto round_item = [&](const PfPlan& pl, int p, int k) { return pl.n_pairs * k + ((k & 1) ? pl.n_pairs - 1 - p : p); };
+    auto max_load = [&](const PfPlan& pl) {   // the heaviest pair: its rounds' items and its range, each item or part with the allowance
+        const int rem0 = pl.rounds * pl.n_pairs; int worst = 0;
         for (int p = 0; p < pl.n_pairs; p++) {
             int w = 0;
-            for (int i = pl.item0[p]; i <= pl.item0[p + 1] && i < n_items; i++) {
-                const int j0 = i == pl.item0[p] ? pl.tile0[p] : 0, j1 = i == pl.item0[p + 1] ? pl.tile0[p + 1] : tiles_of(i);
+            for (int k = 0; k < pl.rounds; k++) w += tiles_of(round_item(pl, p, k)) + kPartE;
+            for (int i = pl.item0[p]; i <= pl.item0[p + 1] && rem0 + i < n_items; i++) {
+                const int j0 = i == pl.item0[p] ? pl.tile0[p] : 0, j1 = i == pl.item0[p + 1] ? pl.tile0[p + 1] : tiles_of(rem0 + i);
                 if (j1 > j0) w += j1 - j0 + kPartE;
             }
             worst = std::max(worst, w);
         }
         return worst;
     };
+    // The items from list index rem0 on, cut into one contiguous range per pair; cap[p] = the weight (tiles + allowance per item) pair p should get.
+    // Cuts keep parts of at least two tiles (a cut too close to an item's end moves to the item boundary) and never run backwards.
+    auto cut_ranges = [&](PfPlan& pl, const double* cap) {
+        const int rem0 = pl.rounds * pl.n_pairs, n_rem = n_items - rem0;
+        int idx = 0; int64_t acc = 0; double target = 0.0;   // acc: weight of the items before idx
+        pl.item0[0] = 0; pl.tile0[0] = 0;
+        for (int p = 1; p < pl.n_pairs; p++) {
+            target += cap[p - 1];
+            while (idx < n_rem && (double)(acc + tiles_of(rem0 + idx) + kPartE) <= target) { acc += tiles_of(rem0 + idx) + kPartE; idx++; }
+            int ci = idx, ct = 0;
+            if (idx < n_rem) {
+                const int nt = tiles_of(rem0 + idx), jt = (int)(target - (double)acc + 0.5);
+                if (jt >= kMinPart && nt - jt >= kMinPart) ct = jt; else if (jt >= kMinPart) ci = idx + 1;
+            }
+            if (ci < pl.item0[p - 1] || (ci == pl.item0[p - 1] && ct < pl.tile0[p - 1])) { ci = pl.item0[p - 1]; ct = pl.tile0[p - 1]; }
+            pl.item0[p] = ci; pl.tile0[p] = ct;
+        }
+        pl.item0[pl.n_pairs] = n_rem; pl.tile0[pl.n_pairs] = 0;
+    };
+    int64_t W = 0; for (int i = 0; i < n_items; i++) W += tiles_of(i) + kPartE;
+    // Plan A: no rounds, equal ranges of the whole list. With fewer items than pairs the items are cut, but not into ranges shorter than two tiles plus the allowance.
     PfPlan plan{};
     {
-        const int n_pairs = n_items >= max_pairs ? max_pairs : std::max(std::min(n_items, max_pairs), (int)std::min<int64_t>(max_pairs, W / (kPartE + 2)));
-        plan.n_pairs = n_pairs;
-        int idx = 0; int64_t acc = 0;   // acc: weight of the items before idx
-        for (int p = 1; p < n_pairs; p++) {
-            const double target = (double)W * p / n_pairs;
-            while (idx < n_items && (double)(acc + tiles_of(idx) + kPartE) <= target) { acc += tiles_of(idx) + kPartE; idx++; }
-            int ci = idx, ct = 0;
-            if (idx < n_items) {
-                const int nt = tiles_of(idx), jt = (int)(target - (double)acc + 0.5);
-                if (jt >= kMinPart && nt - jt >= kMinPart) ct = jt; else if (jt >= kMinPart) ci = idx + 1;   // too close to an end: the cut moves to the item boundary
-            }
-            if (ci < plan.item0[p - 1] || (ci == plan.item0[p - 1] && ct < plan.tile0[p - 1])) { ci = plan.item0[p - 1]; ct = plan.tile0[p - 1]; }   // never behind the previous cut
-            plan.item0[p] = ci; plan.tile0[p] = ct;
-        }
-        plan.item0[n_pairs] = n_items; plan.tile0[n_pairs] = 0;
+        plan.n_pairs = n_items >= max_pairs ? max_pairs : std::max(std::min(n_items, max_pairs), (int)std::min<int64_t>(max_pairs, W / (kPartE + 2)));
+        double cap[kMaxPairs]; for (int p = 0; p < plan.n_pairs; p++) cap[p] = (double)W / plan.n_pairs;
+        cut_ranges(plan, cap);
+    }
+    // Plan R (at least as many items as pairs): whole items in rounds, then the last half to one and a half rounds' worth of items cut into ranges
+    // that level the pairs (capacities by water-filling over the rounds' loads). Its pairs share K and V tiles through L2, so it is taken
+    // unless a ragged batch leaves it clearly less balanced than plan A (long items that only cutting can spread).
+    if (n_items >= max_pairs) {
+        PfPlan alt{}; alt.n_pairs = max_pairs; alt.rounds = n_items / max_pairs;
+        if (n_items - alt.rounds * max_pairs < max_pairs / 2 && alt.rounds >= 1) alt.rounds--;
+        double load[kMaxPairs], cap[kMaxPairs]; double w_rem = 0.0, hi = 0.0, lo = 0.0;
+        for (int p = 0; p < max_pairs; p++) { load[p] = 0.0; for (int k = 0; k < alt.rounds; k++) load[p] += tiles_of(round_item(alt, p, k)) + kPartE; hi = std::max(hi, load[p]); }
+        for (int i = alt.rounds * max_pairs; i < n_items; i++) w_rem += tiles_of(i) + kPartE;
+        hi += w_rem;
+        for (int it = 0; it < 50; it++) { const double mid = 0.5 * (lo + hi); double sum = 0.0; for (int p = 0; p < max_pairs; p++) sum += std::max(0.0, mid - load[p]); if (sum < w_rem) lo = mid; else hi = mid; }
+        for (int p = 0; p < max_pairs; p++) cap[p] = std::max(0.0, hi - load[p]);
+        cut_ranges(alt, cap);
+        if (alt.rounds >= 1 && (double)max_load(alt) <= 1.03 * (double)max_load(plan)) plan = alt;
     }
     // Plan B (only with fewer items than pairs): one part per pair; the spare pairs go, one at a time, to the item whose parts are longest.
     // Better than A when the items are short (a 512-token prompt: items of 1 to 4 tiles).
@@ -676,20 +713,22 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
         alt.item0[total] = n_items; alt.tile0[total] = 0;
         if (max_load(alt) < max_load(plan)) plan = alt;
     }
-    // Plan U: no item is cut (every cut of plan A moved to the next item boundary). A cut plan has the shorter critical path but its heads wait for
+    // Plan U: no item is cut (every cut moved to the next item boundary). A cut plan has the shorter critical path but its heads wait for
     // the other parts to be written and fold them in (a few microseconds at the end of the launch). Estimate both in microseconds (a key tile of a
     // CTA pair takes about 2.3 us at the rate the kernel sustains, power-capped) and keep the cheaper.
     {
+        const int n_rem = n_items - plan.rounds * plan.n_pairs;
         PfPlan whole = plan; int max_parts = 1, run = 1;   // run: parts so far of the item the current cut lies in
         for (int p = 1; p < whole.n_pairs; p++) {
             if (plan.tile0[p] == 0) { run = 1; continue; }
             const bool same_item = plan.item0[p - 1] == plan.item0[p] && plan.tile0[p - 1] > 0, repeat = same_item && plan.tile0[p - 1] == plan.tile0[p];   // repeat: pair p - 1 is empty, the same cut again
             run = same_item ? run + (repeat ? 0 : 1) : 2; max_parts = std::max(max_parts, run);
-            whole.tile0[p] = 0; whole.item0[p] = std::min(whole.item0[p] + 1, n_items);
+            whole.tile0[p] = 0; whole.item0[p] = std::min(whole.item0[p] + 1, n_rem);
         }
         const double t_tile = 2.3, t_cut = max_load(plan) * t_tile + (max_parts > 1 ? kCutCostUs + kFoldCostUs * (max_parts - 2) : 0.0), t_whole = max_load(whole) * t_tile;
         if (t_whole <= t_cut) plan = whole;
     }
+    for (int i = 0; i < b.n; i++) plan.order[i] = order[i];
     plan.hp_lo = hp_lo; plan.hp_n = hp_n;
     cached.plan = plan;
     c.pf_plan_M = M; c.pf_plan_n = b.n; for (int i = 0; i < b.n; i++) c.pf_plan_pos[i] = b.pos[i];
