@@ -415,24 +415,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) prefill_tc5_kernel(const __grid
                 // split-KV rule (k_attn_dec_combine, shaders/flash.metal:143-152, one "split" at a time: new maximum, both sides rescaled).
                 // m is finite here: key 0 is in the head.
                 const uint8_t* zone = smem_raw + (base - sm0);
-                int n_other = 0;
-                for (int p2 = next_part_pair(t.idx, pair); p2 >= 0; p2 = next_part_pair(t.idx, p2)) n_other++;
-                uint64_t done0 = 0, done1 = 0;   // thread 0: the parts folded so far (a cut item has at most 73 other parts)
-                for (int k = 0; k < n_other; k++) {
-                    // Thread 0 picks the next part: the first one not yet folded whose flag is up (a part computed at the start of its pair's range has
-                    // been there for long; one that fills its pair's whole range arrives when this pair's own tiles end), and tells the others.
-                    if (tid == 0) {
-                        int pick = -1;
-                        for (uint32_t i = 0; i < (1u << 20) && pick < 0; i++) {
-                            int q = 0;
-                            for (int p2 = next_part_pair(t.idx, pair); p2 >= 0 && pick < 0; p2 = next_part_pair(t.idx, p2), q++) {
-                                if (((q < 64 ? done0 >> q : done1 >> (q - 64)) & 1ull) != 0) continue;
-                                int got; asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(got) : "l"(part_flag + other_slot(p2)) : "memory");
-                                if (got) { pick = p2; if (q < 64) done0 |= 1ull << q; else done1 |= 1ull << (q - 64); }
-                            }
-                            if (pick < 0 && (i & 63u) == 63u && *reinterpret_cast<const volatile int32_t*>(err) != 0) break;
+                // The parts are folded in the order of their pairs, whatever the order their flags come up in: the sums then round the same way in every launch.
+                for (int nx = next_part_pair(t.idx, pair); nx >= 0; nx = next_part_pair(t.idx, nx)) {
+                    if (tid == 0) {   // one thread waits for the part's flag and tells the others
+                        int got = 0;
+                        for (uint32_t i = 0; i < (1u << 21) && !got; i++) {
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(got) : "l"(part_flag + other_slot(nx)) : "memory");
+                            if (!got && (i & 255u) == 255u && *reinterpret_cast<const volatile int32_t*>(err) != 0) break;
                         }
-                        s_pick = pick;
+                        s_pick = got ? nx : -1;
                     }
                     asm volatile("bar.sync 10, 256;" ::: "memory");
                     const int p2 = s_pick;

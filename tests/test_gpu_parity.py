@@ -600,6 +600,61 @@ def test_full_size_prefill_chunk_over_7k_prefix(capi, orc):
         _close(out[r:r + 1], ref)
 
 
+def _prefill_both_kernels(capi, positions, M, seed):
+    """Rows of a batch at the given positions through the tcgen05 kernel and through the mma.sync kernel of a second context holding the same caches."""
+    gen = torch.Generator(device="cuda"); gen.manual_seed(seed)
+    kn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(256, generator=gen, device="cuda")).contiguous()
+    n = len(positions); ctxs = [capi.AttnContext(1, [p + M for p in positions]), capi.AttnContext(1, [p + M for p in positions], legacy_prefill=True)]
+    seqs = list(range(n)); outs = []
+    top = max(positions)
+    pre_k = torch.randn(n, max(top, 1), 1024, generator=gen, device="cuda"); pre_v = torch.randn(n, max(top, 1), 1024, generator=gen, device="cuda")
+    qf = torch.randn(n, M, 12288, generator=gen, device="cuda"); kp = torch.randn(n, M, 1024, generator=gen, device="cuda"); vp = torch.randn(n, M, 1024, generator=gen, device="cuda")
+    for ctx in ctxs:
+        for s, pb in enumerate(positions):
+            for st in range(0, pb, 1024):
+                m = min(1024, pb - st)
+                ctx.prep(0, [s], [st], m, None, pre_k[s:s + 1, st:st + m].contiguous(), pre_v[s:s + 1, st:st + m].contiguous(), None, kn, h0=24, nh=8)
+        q16, _, g = ctx.prep(0, seqs, list(positions), M, qf, kp, vp, qn, kn)
+        outs.append((ctx, q16, g, ctx.prefill(0, seqs, list(positions), M, q16, g)))
+        ctx.check()
+    return outs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("positions,M", [((900,) * 8, 256), ((40, 3000, 700, 12, 1500), 200), ((2500,), 128), ((5000, 5000), 512)],
+                         ids=["rounds-then-ranges", "ragged-batch", "one-query-tile-cut-many-ways", "two-long-sequences"])
+def test_prefill_work_split_variants(capi, orc, positions, M):
+    # whole items in rounds plus a cut last round (equal sequences), equal ranges of the whole list (a ragged batch), items cut into many parts
+    # (one sequence, one query tile, 74 pairs): whatever the split, the rows equal the mma.sync kernel's within the tolerance, and a second
+    # launch (the flags of the cut items' parts have gone down again) gives the same bits as the first
+    (ctx, q16, g, out), (_, _, _, ref) = _prefill_both_kernels(capi, positions, M, 71)
+    a, b = out.cpu().numpy(), ref.cpu().numpy()
+    assert np.isfinite(a).all()
+    assert np.abs(a - b).max() < TOL_MAX and np.abs(a - b).mean() < TOL_MEAN
+    again = ctx.prefill(0, list(range(len(positions))), list(positions), M, q16, g); ctx.check()
+    assert torch.equal(again, out)
+
+
+@pytest.mark.gpu
+def test_prefill_cut_items_in_a_replayed_cuda_graph(capi, orc):
+    # one sequence: 48 items for 74 pairs, every item cut; the launch is captured once and replayed: each replay must find the part flags down
+    (ctx, q16, g, out), _ = _prefill_both_kernels(capi, (3000,), 512, 72)
+    st = torch.cuda.Stream()
+    buf = torch.empty_like(out)
+    with torch.cuda.stream(st):
+        ctx.prefill(0, [0], [3000], 512, q16, g, out=buf)   # warm-up on the capture stream
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            ctx.prefill(0, [0], [3000], 512, q16, g, out=buf)
+        for _ in range(3):
+            buf.zero_()
+            graph.replay()
+            st.synchronize()
+            assert torch.equal(buf, out)
+    ctx.check()
+
+
 @pytest.mark.gpu
 def test_out_fwht_bit_exact(capi, orc):
     # the transform between attention and the output projection (k_rms_fwht mode 3): same butterflies in the same order -> same bits
