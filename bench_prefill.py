@@ -63,27 +63,49 @@ def run(args, rank, world, cfg, pk, ClockSampler, steps=None, warmup=None):
     def sl(t, m):
         return t if m == mmax else t[:, :m].contiguous()
 
+    # End to end (host is not None): the projections of a (chunk, layer) go up on one copy stream while the one before computes, its output rows come
+    # down on another while the next one computes; device-side input and output buffers are doubled for that.
+    cs_in, cs_out = torch.cuda.Stream(), torch.cuda.Stream()
+    bufs = {}
+
     def step(with_prep=True, host=None):
-        for (p0, m) in chunks:
-            for layer in range(N_LAYERS):
-                if host is not None:
-                    qfull[:, :m].copy_(host[0][:, :m], non_blocking=True); kproj[:, :m].copy_(host[1][:, :m], non_blocking=True); vproj[:, :m].copy_(host[2][:, :m], non_blocking=True)
-                if m == mmax:
-                    if with_prep:
-                        ctx.prep(layer, seqs, [p0] * B, m, qfull, kproj, vproj, qn[layer], kn[layer], q16=q16, gate=gate)
-                    ctx.prefill(layer, seqs, [p0] * B, m, q16, gate, out=out)
-                else:
-                    q_, g_ = (ctx.prep(layer, seqs, [p0] * B, m, sl(qfull, m), sl(kproj, m), sl(vproj, m), qn[layer], kn[layer])[0::2] if with_prep else (sl(q16, m), sl(gate, m)))
-                    o_ = ctx.prefill(layer, seqs, [p0] * B, m, q_, g_)
-                    out[:, :m].copy_(o_)
-                if host is not None:
-                    host[3][:, :m].copy_(out[:, :m], non_blocking=True)
+        cur = torch.cuda.current_stream()
+        if host is not None and not bufs:
+            bufs["in"] = [(qfull, kproj, vproj), (torch.empty_like(qfull), torch.empty_like(kproj), torch.empty_like(vproj))]; bufs["out"] = [out, torch.empty_like(out)]
+        work = [(p0, m, layer) for (p0, m) in chunks for layer in range(N_LAYERS)]
+        ev_in, ev_done, ev_down = {}, {}, {}
+        if host is not None:
+            cs_in.wait_stream(cur); cs_out.wait_stream(cur)
+        for i, (p0, m, layer) in enumerate(work):
+            qf_, kp_, vp_ = (qfull, kproj, vproj) if host is None else bufs["in"][i & 1]
+            out_ = out if host is None else bufs["out"][i & 1]
+            if host is not None:
+                with torch.cuda.stream(cs_in):
+                    if i >= 2: cs_in.wait_event(ev_done[i - 2])          # the item that used this input buffer has computed
+                    qf_[:, :m].copy_(host[0][:, :m], non_blocking=True); kp_[:, :m].copy_(host[1][:, :m], non_blocking=True); vp_[:, :m].copy_(host[2][:, :m], non_blocking=True)
+                    ev_in[i] = torch.cuda.Event(); ev_in[i].record(cs_in)
+                cur.wait_event(ev_in[i])
+                if i >= 2: cur.wait_event(ev_down[i - 2])                 # the rows that sat in this output buffer are on the host
+            if m == mmax:
+                if with_prep:
+                    ctx.prep(layer, seqs, [p0] * B, m, qf_, kp_, vp_, qn[layer], kn[layer], q16=q16, gate=gate)
+                ctx.prefill(layer, seqs, [p0] * B, m, q16, gate, out=out_)
+            else:
+                q_, g_ = (ctx.prep(layer, seqs, [p0] * B, m, sl(qf_, m), sl(kp_, m), sl(vp_, m), qn[layer], kn[layer])[0::2] if with_prep else (sl(q16, m), sl(gate, m)))
+                o_ = ctx.prefill(layer, seqs, [p0] * B, m, q_, g_)
+                out_[:, :m].copy_(o_)
+            if host is not None:
+                ev_done[i] = torch.cuda.Event(); ev_done[i].record(cur)
+                with torch.cuda.stream(cs_out):
+                    cs_out.wait_event(ev_done[i])
+                    host[3][:, :m].copy_(out_[:, :m], non_blocking=True)
+                    ev_down[i] = torch.cuda.Event(); ev_down[i].record(cs_out)
         if kind == "chunked":   # the T=2 verify that follows (target token plus one draft)
             for layer in range(N_LAYERS):
                 q2, _, g2 = ctx.prep(layer, seqs, [total] * B, 2, sl(qfull, 2), sl(kproj, 2), sl(vproj, 2), qn[layer], kn[layer])
                 ctx.decode(layer, seqs, [total] * B, 2, q2, g2)
         if host is not None:
-            torch.cuda.current_stream().synchronize()
+            cs_out.synchronize(); cur.synchronize()
 
     def barrier():
         if world > 1:
@@ -170,6 +192,7 @@ def run(args, rank, world, cfg, pk, ClockSampler, steps=None, warmup=None):
     if rank == 0 and not args.no_cpu_baseline and kv_mode == "fp16":
         res["cpu_baseline"] = cpu_baseline(ctx, full[-1], q16, gate, chunks)
     ctx.close()
+    bufs.clear()
     del qfull, kproj, vproj, q16, gate, out, host
     torch.cuda.empty_cache()
     return res
