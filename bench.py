@@ -253,20 +253,14 @@ def run_decode(args, rank, world, kind_cfg, steps=None, warmup=None, sustained_s
     k1.record(); torch.cuda.synchronize()
     kern_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
 
-    # end to end through the C ABI with HOST (pinned) buffers: H2D of the step's projections, append + attend per layer, D2H of the outputs
+    # end to end through the C ABI with HOST (pinned) buffers: kata_attn_host_step_run takes the step's projections of all layers from host memory,
+    # appends and attends layer by layer and leaves the output rows in host memory (copies of the neighbouring layers under the layer that computes)
     hq = torch.randn(N_LAYERS, B, 1, 12288).pin_memory(); hk = torch.randn(N_LAYERS, B, 1, 1024).pin_memory(); hv = torch.randn(N_LAYERS, B, 1, 1024).pin_memory()
     hout = torch.empty(N_LAYERS, B, 1, 6144).pin_memory()
-    dq, dk, dv = torch.empty_like(qfull), torch.empty_like(kproj), torch.empty_like(vproj)
-    dq_l, dk_l, dv_l = [dq[l] for l in L_], [dk[l] for l in L_], [dv[l] for l in L_]
+    hstep = capi.HostStep(ctx, max_n=B, max_T=1)
 
-    def step_e2e(p):   # one H2D of the step's projections (all layers), the step, one D2H of the step's outputs (copies per layer on streams of their own were
-        # tried: the sixteen extra rounds of stream and event calls cost the Python host more than the 0.15 ms of copies they would hide)
-        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
-        p = p.tolist() if isinstance(p, np.ndarray) else p
-        for layer in L_:
-            ctx.prep(layer, seqs, p, 1, dq_l[layer], dk_l[layer], dv_l[layer], qn_l[layer], kn_l[layer], q16=q16_l[layer], gate=gate_l[layer])
-            ctx.decode(layer, seqs, p, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
-        hout.copy_(out, non_blocking=True)
+    def step_e2e(p):
+        hstep.run(N_LAYERS, seqs, p.tolist() if isinstance(p, np.ndarray) else p, 1, hq, hk, hv, qn, kn, hout)
         torch.cuda.current_stream().synchronize()   # the caller holds the step's result on the host before the next step
 
     pos_e = pos_timed0.copy()
@@ -316,8 +310,8 @@ def run_decode(args, rank, world, kind_cfg, steps=None, warmup=None, sustained_s
         res["sustained"] = sustained
     if rank == 0 and want_cpu and not args.no_cpu_baseline:
         res["cpu_baseline"] = cpu_baseline_decode(ctx, pos_timed0, B, kv_mode)
-    ctx.close()
-    del qfull, kproj, vproj, q16, gate, out, dq, dk, dv
+    hstep.close(); ctx.close()
+    del qfull, kproj, vproj, q16, gate, out
     torch.cuda.empty_cache()
     return res
 

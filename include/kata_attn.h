@@ -222,6 +222,21 @@ int kata_attn_decode_static_check(void* stream);
 /* Number of kernels this library has launched on this context since creation (for accounting in benchmarks). */
 uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);
 
+/* No reference counterpart: the reference's buffers are shared between CPU and GPU (MTL::ResourceStorageModeShared, src/gpu.cpp:26-30), so
+ * Engine::step / verify2 / verifyWide (src/engine.cpp:161-178, 469-483, 602-622) hand attention the very rows the CPU sees. A caller on a
+ * discrete GPU whose projections and output rows live in (pinned) host memory runs a whole step through this routine instead: for each of
+ * n_layers layers the projections are copied up, kata_attn_prep (all 32 head slots) and kata_attn_decode (T <= KATA_MAX_VERIFY tokens per
+ * sequence, fp32 rows out) run, and the rows are copied down; two copy streams and doubled device rows keep the copies of the neighbouring
+ * layers under the layer that computes. Everything is enqueued behind `stream`, which is complete when the last rows are on the host.
+ *   h_qfull [n_layers][n][T][12288], h_kproj, h_vproj [n_layers][n][T][1024]: act_dtype of the create call, host memory (pinned for the copies to overlap);
+ *   d_qnorm, d_knorm [n_layers][256] fp32, device; h_out [n_layers][n][T][6144] fp32, host.
+ * create allocates the device rows for max_n sequences of max_T tokens (on `device`, the context's) and the streams; run allocates nothing. */
+typedef struct kata_attn_host_step kata_attn_host_step;
+int kata_attn_host_step_create(kata_attn_ctx* ctx, int32_t device, int32_t max_n, int32_t max_T, int32_t act_dtype, kata_attn_host_step** out);
+int kata_attn_host_step_destroy(kata_attn_host_step* hs);
+int kata_attn_host_step_run(kata_attn_host_step* hs, int32_t n_layers, int32_t n, const int32_t* seq_ids, const int32_t* pos0, int32_t T, int32_t first_pos,
+                            const void* h_qfull, const void* h_kproj, const void* h_vproj, const float* d_qnorm, const float* d_knorm, float* h_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkata_attn.so")
-SOURCES = ["ctx.cu", "tmap.cu", "prep.cu", "decode_scalar.cu", "decode_mma.cu", "prefill_mma.cu", "prefill_tc5.cu", "draft_attn.cu", "peer_merge.cu", "attn_engine.cpp", "kv_ckpt.cpp"]
+SOURCES = ["ctx.cu", "tmap.cu", "prep.cu", "decode_scalar.cu", "decode_mma.cu", "prefill_mma.cu", "prefill_tc5.cu", "draft_attn.cu", "peer_merge.cu", "attn_engine.cpp", "kv_ckpt.cpp", "host_step.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

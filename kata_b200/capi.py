@@ -27,6 +27,7 @@ EXPORTS = [
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_decode_static_check", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
+    "kata_attn_host_step_create", "kata_attn_host_step_destroy", "kata_attn_host_step_run",
     "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode",
     "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
@@ -311,6 +312,32 @@ class DraftContext:
     def ring_write(self, layer, value: bool, row0: int, data: np.ndarray):
         data = np.ascontiguousarray(data).view(np.uint16).reshape(-1, 1024)
         self._ck(self.L.kata_draft_ring_write(self.h, layer, int(value), row0, data.shape[0], data.ctypes.data_as(C.c_void_p)))
+
+
+class HostStep:
+    """A decode or verify step of all layers with the projections and the output rows in pinned host memory (kata_attn_host_step_*):
+    the copies of the neighbouring layers run under the layer that computes."""
+
+    def __init__(self, ctx: "AttnContext", max_n: int, max_T: int = 1, act_dtype=torch.float32):
+        self.L = lib(); self.ctx = ctx; self.h = C.c_void_p(); self.act = act_dtype
+        rc = self.L.kata_attn_host_step_create(ctx.h, ctx.device, max_n, max_T, _ACT[act_dtype], C.byref(self.h))
+        if rc != OK:
+            raise KataError(rc, "kata_attn_host_step_create failed")
+
+    def run(self, n_layers, seq_ids, pos0, T, h_qfull, h_kproj, h_vproj, d_qnorm, d_knorm, h_out, first_pos=0):
+        """h_*: pinned host tensors [n_layers][n][T][...]; d_qnorm, d_knorm: device [n_layers][256]. Enqueued on the current stream."""
+        sa, sp = _i32(seq_ids); pa, pp = _i32(pos0)
+        for t in (h_qfull, h_kproj, h_vproj, h_out):
+            assert t.device.type == "cpu" and t.is_contiguous()
+        rc = self.L.kata_attn_host_step_run(self.h, n_layers, len(sa), sp, pp, T, first_pos, C.c_void_p(h_qfull.data_ptr()), C.c_void_p(h_kproj.data_ptr()), C.c_void_p(h_vproj.data_ptr()),
+                                            _dp(d_qnorm), _dp(d_knorm), C.c_void_p(h_out.data_ptr()), _stream())
+        if rc != OK:
+            raise KataError(rc, self.L.kata_attn_last_error(self.ctx.h).decode() or "kata_attn_host_step_run failed")
+        return h_out
+
+    def close(self):
+        if self.h:
+            self.L.kata_attn_host_step_destroy(self.h); self.h = C.c_void_p()
 
 
 class PeerExchange:

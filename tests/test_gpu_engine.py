@@ -229,3 +229,34 @@ def test_kv_head_groups_across_two_gpus():
     for p in procs:
         p.join(timeout=120)
     assert ok and all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kv_mode,T", [("fp16", 1), ("int8", 2), ("fp16", 5)])
+def test_host_step_equals_the_device_calls(kv_mode, T):
+    from kata_b200 import capi
+    # a whole step (three layers, ragged batch) with projections and output rows in pinned host memory: same bits as prep + decode on device rows
+    n_layers, lens = 3, [300, 1, 777]
+    gen = torch.Generator(device="cuda"); gen.manual_seed(5)
+    ctxs = [capi.AttnContext(n_layers, [1024] * 3, kv_mode=kv_mode) for _ in range(2)]
+    qn = (1 + 0.05 * torch.randn(n_layers, 256, generator=gen, device="cuda")).contiguous(); kn = (1 + 0.05 * torch.randn(n_layers, 256, generator=gen, device="cuda")).contiguous()
+    seqs = [0, 1, 2]
+    for layer in range(n_layers):
+        for s, L in enumerate(lens):
+            k = torch.randn(1, L, 1024, generator=gen, device="cuda"); v = torch.randn(1, L, 1024, generator=gen, device="cuda")
+            for ctx in ctxs:
+                ctx.prep(layer, [s], [0], L, None, k, v, None, kn[layer], h0=24, nh=8)
+    hq = torch.randn(n_layers, 3, T, 12288).pin_memory(); hk = torch.randn(n_layers, 3, T, 1024).pin_memory(); hv = torch.randn(n_layers, 3, T, 1024).pin_memory()
+    hout = torch.zeros(n_layers, 3, T, 6144).pin_memory()
+    hs = capi.HostStep(ctxs[0], max_n=4, max_T=8)
+    for rep in range(2):   # the second step appends at the next positions and reuses the doubled device rows
+        pos = [L + rep * T for L in lens]
+        hs.run(n_layers, seqs, pos, T, hq, hk, hv, qn, kn, hout)
+        torch.cuda.current_stream().synchronize()
+        ctxs[0].check()
+        for layer in range(n_layers):
+            q16, _, g = ctxs[1].prep(layer, seqs, pos, T, hq[layer].cuda(), hk[layer].cuda(), hv[layer].cuda(), qn[layer], kn[layer])
+            ref = ctxs[1].decode(layer, seqs, pos, T, q16, g)
+            assert torch.equal(ref.cpu(), hout[layer])
+        ctxs[1].check()
+    hs.close()
