@@ -92,7 +92,7 @@ struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh
 constexpr int kMaxPairs = 74;      // CTA pairs of a launch (one per two SMs of a B200)
 constexpr double kCutCostUs = 5.0, kFoldCostUs = 2.7;   // host-side estimate of what cutting items costs a launch: the wait for a part that ends with the launch and the fold of the first part, then of each further part (measured: 2.7 us per part, L2 -> shared memory bound)
 constexpr int kPartE = 2;          // host-side allowance, in key tiles, for what a part costs besides its tiles (Q load, epilogue or partial write)
-// Items in list order: sequences longest first (order[]), per sequence its KV heads, per KV head the query tiles last to first, per query tile the
+// Items in list order: sequences shortest first (order[]), per sequence its KV heads, per KV head the query tiles last to first, per query tile the
 // three head pairs of the KV head: the 3 * n_q items of one (sequence, KV head) are neighbours and read the same K and V tiles.
 // A pair first computes `rounds` whole items, dealt in snake order (round k: item n_pairs * k + pair, pairs reversed in odd rounds), so that in
 // every round a dozen pairs work on the same (sequence, KV head) at the same pace and its tiles come from L2 (with contiguous ranges instead, 74
@@ -625,9 +625,9 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     if (!hit) {
     const int hp_n = 3 * c.kvh_n, hp_lo = 3 * c.kvh_lo;   // head pairs of the KV heads this context computes
     const int n_q = (M + kBMq - 1) / kBMq, grp_items = 3 * n_q, n_items = grp_items * c.kvh_n * b.n, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
-    uint8_t order[KATA_MAX_BATCH];   // sequences of the batch, longest first (ties in batch order)
-    for (int i = 0; i < b.n; i++) order[i] = (uint8_t)i;
-    std::stable_sort(order, order + b.n, [&](uint8_t x, uint8_t y) { return b.pos[x] > b.pos[y]; });
+    uint8_t order[KATA_MAX_BATCH];   // sequences of the batch, shortest first (ties in batch order): the rounds then deal items of like length, and the long
+    for (int i = 0; i < b.n; i++) order[i] = (uint8_t)i;   // items, which only cutting can spread, come last, where the ranges are cut
+    std::stable_sort(order, order + b.n, [&](uint8_t x, uint8_t y) { return b.pos[x] < b.pos[y]; });
     int32_t* nt_tab = c.pf_plan_tiles;   // key tiles per item in list order (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
     for (int idx = 0; idx < n_items; idx++) { const int grp = idx / grp_items, qt = n_q - 1 - (idx % grp_items) / 3, bi = order[grp / c.kvh_n], q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
     auto tiles_of = [&](int idx) { return (int)nt_tab[idx]; };
@@ -675,18 +675,23 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
     }
     // Plan R (at least as many items as pairs): whole items in rounds, then the last half to one and a half rounds' worth of items cut into ranges
     // that level the pairs (capacities by water-filling over the rounds' loads). Its pairs share K and V tiles through L2, so it is taken
-    // unless a ragged batch leaves it clearly less balanced than plan A (long items that only cutting can spread).
+    // with as many rounds as leave it no more than 3 % less balanced than plan A (in a ragged batch the long items, which only cutting can spread,
+    // have to fall into the ranges).
     if (n_items >= max_pairs) {
-        PfPlan alt{}; alt.n_pairs = max_pairs; alt.rounds = n_items / max_pairs;
-        if (n_items - alt.rounds * max_pairs < max_pairs / 2 && alt.rounds >= 1) alt.rounds--;
-        double load[kMaxPairs], cap[kMaxPairs]; double w_rem = 0.0, hi = 0.0, lo = 0.0;
-        for (int p = 0; p < max_pairs; p++) { load[p] = 0.0; for (int k = 0; k < alt.rounds; k++) load[p] += tiles_of(round_item(alt, p, k)) + kPartE; hi = std::max(hi, load[p]); }
-        for (int i = alt.rounds * max_pairs; i < n_items; i++) w_rem += tiles_of(i) + kPartE;
-        hi += w_rem;
-        for (int it = 0; it < 50; it++) { const double mid = 0.5 * (lo + hi); double sum = 0.0; for (int p = 0; p < max_pairs; p++) sum += std::max(0.0, mid - load[p]); if (sum < w_rem) lo = mid; else hi = mid; }
-        for (int p = 0; p < max_pairs; p++) cap[p] = std::max(0.0, hi - load[p]);
-        cut_ranges(alt, cap);
-        if (alt.rounds >= 1 && (double)max_load(alt) <= 1.03 * (double)max_load(plan)) plan = alt;
+        int rounds = n_items / max_pairs;
+        if (n_items - rounds * max_pairs < max_pairs / 2 && rounds >= 1) rounds--;
+        const double flat_load = (double)max_load(plan);
+        for (int attempt = 0; attempt < 4 && rounds >= 1; attempt++, rounds--) {   // fewer rounds leave more (and longer) items to the ranges
+            PfPlan alt{}; alt.n_pairs = max_pairs; alt.rounds = rounds;
+            double load[kMaxPairs], cap[kMaxPairs]; double w_rem = 0.0, hi = 0.0, lo = 0.0;
+            for (int p = 0; p < max_pairs; p++) { load[p] = 0.0; for (int k = 0; k < alt.rounds; k++) load[p] += tiles_of(round_item(alt, p, k)) + kPartE; hi = std::max(hi, load[p]); }
+            for (int i = alt.rounds * max_pairs; i < n_items; i++) w_rem += tiles_of(i) + kPartE;
+            hi += w_rem;
+            for (int it = 0; it < 50; it++) { const double mid = 0.5 * (lo + hi); double sum = 0.0; for (int p = 0; p < max_pairs; p++) sum += std::max(0.0, mid - load[p]); if (sum < w_rem) lo = mid; else hi = mid; }
+            for (int p = 0; p < max_pairs; p++) cap[p] = std::max(0.0, hi - load[p]);
+            cut_ranges(alt, cap);
+            if ((double)max_load(alt) <= 1.03 * flat_load) { plan = alt; break; }
+        }
     }
     // Plan B (only with fewer items than pairs): one part per pair; the spare pairs go, one at a time, to the item whose parts are longest.
     // Better than A when the items are short (a 512-token prompt: items of 1 to 4 tiles).
