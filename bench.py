@@ -186,11 +186,8 @@ def run_decode(args, rank, world, kind_cfg, steps=None, warmup=None, sustained_s
     qfull_l, kproj_l, vproj_l, qn_l, kn_l = [qfull[l] for l in L_], [kproj[l] for l in L_], [vproj[l] for l in L_], [qn[l] for l in L_], [kn[l] for l in L_]
     q16_l, gate_l, out_l = [q16[l] for l in L_], [gate[l] for l in L_], [out[l] for l in L_]
 
-    def step(p):
-        p = p.tolist() if isinstance(p, np.ndarray) else p
-        for layer in L_:
-            ctx.prep(layer, seqs, p, 1, qfull_l[layer], kproj_l[layer], vproj_l[layer], qn_l[layer], kn_l[layer], q16=q16_l[layer], gate=gate_l[layer])
-            ctx.decode(layer, seqs, p, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
+    def step(p):   # the sixteen layers' prep + decode through one call of the C ABI (kata_attn_layers_step: the Engine's layer loop on the native side of the binding)
+        ctx.layers_step(N_LAYERS, seqs, p.tolist() if isinstance(p, np.ndarray) else p, 1, qfull, kproj, vproj, qn, kn, q16, gate, out)
 
     def barrier():
         if world > 1:

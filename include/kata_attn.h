@@ -231,6 +231,14 @@ uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);
  *   h_qfull [n_layers][n][T][12288], h_kproj, h_vproj [n_layers][n][T][1024]: act_dtype of the create call, host memory (pinned for the copies to overlap);
  *   d_qnorm, d_knorm [n_layers][256] fp32, device; h_out [n_layers][n][T][6144] fp32, host.
  * create allocates the device rows for max_n sequences of max_T tokens (on `device`, the context's) and the streams; run allocates nothing. */
+/* The layer loop of Engine::step / verify2 / verifyWide (src/engine.cpp:161-178, 469-483, 602-622: prep, then decode, layer after layer) in one call
+ * for rows that are on the device already: row l of every [n_layers][...] array belongs to layer l (d_qfull [n_layers][n][T][12288], d_kproj, d_vproj
+ * [..][1024] act_dtype; d_qnorm, d_knorm [n_layers][256]; d_q16, d_gate, d_out [n_layers][n][T][6144]). One crossing of the language boundary per token
+ * instead of two per layer; the launches are the same. */
+int kata_attn_layers_step(kata_attn_ctx* ctx, int32_t n_layers, int32_t n, const int32_t* seq_ids, const int32_t* pos0, int32_t T, int32_t first_pos,
+                          const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype, const float* d_qnorm, const float* d_knorm,
+                          void* d_q16, float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+
 typedef struct kata_attn_host_step kata_attn_host_step;
 int kata_attn_host_step_create(kata_attn_ctx* ctx, int32_t device, int32_t max_n, int32_t max_T, int32_t act_dtype, kata_attn_host_step** out);
 int kata_attn_host_step_destroy(kata_attn_host_step* hs);

@@ -92,3 +92,23 @@ extern "C" int kata_attn_host_step_run(kata_attn_host_step* h, int32_t n_layers,
     for (int b = 0; b < std::min(2, (int)n_layers); b++) if (cudaStreamWaitEvent(s, h->ev_down[b], 0) != cudaSuccess) return KATA_ERR_CUDA;
     return KATA_OK;
 }
+
+// The same step for a caller whose rows are on the device already: the layer loop of Engine::step / verify2 / verifyWide (prep, then decode, layer after
+// layer) in one call, so that a host in another language pays one crossing per token instead of two per layer. Row l of every [n_layers][...] array
+// belongs to layer l; nothing is copied.
+extern "C" int kata_attn_layers_step(kata_attn_ctx* ctx, int32_t n_layers, int32_t n, const int32_t* seq_ids, const int32_t* pos0, int32_t T, int32_t first_pos,
+                                     const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype, const float* d_qnorm, const float* d_knorm,
+                                     void* d_q16, float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
+    if (!ctx || n_layers < 1 || n < 1 || T < 1) return KATA_ERR_ARG;
+    if (act_dtype != KATA_ACT_F32 && act_dtype != KATA_ACT_BF16 && act_dtype != KATA_ACT_F16) return KATA_ERR_ARG;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return KATA_ERR_ARG;
+    const size_t rows = (size_t)n * T, esz = act_dtype == KATA_ACT_F32 ? 4 : 2, osz = out_dtype == KATA_ACT_F32 ? 4 : 2;
+    for (int l = 0; l < n_layers; l++) {
+        void* q16 = (char*)d_q16 + (size_t)l * rows * 6144 * 2; float* gate = d_gate + (size_t)l * rows * 6144;
+        int rc = kata_attn_prep(ctx, l, n, seq_ids, pos0, T, (const char*)d_qfull + (size_t)l * rows * 12288 * esz, (const char*)d_kproj + (size_t)l * rows * 1024 * esz,
+                                (const char*)d_vproj + (size_t)l * rows * 1024 * esz, act_dtype, d_qnorm + (size_t)l * 256, d_knorm + (size_t)l * 256, q16, nullptr, gate, 0, 32, stream);
+        if (rc == KATA_OK) rc = kata_attn_decode(ctx, l, n, seq_ids, pos0, T, first_pos, q16, gate, (char*)d_out + (size_t)l * rows * 6144 * osz, out_dtype, stream);
+        if (rc != KATA_OK) return rc;
+    }
+    return KATA_OK;
+}

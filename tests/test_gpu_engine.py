@@ -252,11 +252,22 @@ def test_host_step_equals_the_device_calls(kv_mode, T):
     for rep in range(2):   # the second step appends at the next positions and reuses the doubled device rows
         pos = [L + rep * T for L in lens]
         hs.run(n_layers, seqs, pos, T, hq, hk, hv, qn, kn, hout)
+        if rep == 0:   # the same layers through the one-call loop over device rows
+            dq16 = torch.empty(n_layers, 3, T, 6144, dtype=torch.float16, device="cuda"); dg = torch.empty(n_layers, 3, T, 6144, device="cuda"); dout = torch.empty(n_layers, 3, T, 6144, device="cuda")
+            third = capi.AttnContext(n_layers, [1024] * 3, kv_mode=kv_mode)
+            for layer in range(n_layers):
+                for pl in range(third.kv_planes()):
+                    for s_, L_ in enumerate(lens):
+                        third.plane_write(layer, s_, pl, 0, ctxs[1].plane_read(layer, s_, pl, 0, L_))
+            third.layers_step(n_layers, seqs, pos, T, hq.cuda(), hk.cuda(), hv.cuda(), qn, kn, dq16, dg, dout)
+            third.check(); third.close()
         torch.cuda.current_stream().synchronize()
         ctxs[0].check()
         for layer in range(n_layers):
             q16, _, g = ctxs[1].prep(layer, seqs, pos, T, hq[layer].cuda(), hk[layer].cuda(), hv[layer].cuda(), qn[layer], kn[layer])
             ref = ctxs[1].decode(layer, seqs, pos, T, q16, g)
             assert torch.equal(ref.cpu(), hout[layer])
+            if rep == 0:
+                assert torch.equal(ref, dout[layer])
         ctxs[1].check()
     hs.close()
