@@ -383,6 +383,9 @@ def run_splitkv(args, rank, world, kind_cfg, steps=None, warmup=None):
     px = capi.PeerExchange(rank, world)
 
     def step(pos, batched):
+        if batched == "peer":   # the sixteen layers through one call of the C ABI (kata_attn_peer_layers_step)
+            px.layers_step(ctx, N_LAYERS, 0, pos, 1, lo, big if tail else hi, tail, qfull, kproj, vproj, qn, kn, q16, gate, out)
+            return
         for layer in range(N_LAYERS):
             ctx.prep(layer, [0], [pos], 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], h0=0, nh=32 if tail else 24, q16=q16[layer], gate=gate[layer])
             if batched == "peer":
@@ -430,9 +433,7 @@ def run_splitkv(args, rank, world, kind_cfg, steps=None, warmup=None):
     out1 = torch.empty(N_LAYERS, 1, 1, 6144, device=dev)
 
     def step_one(pos):
-        for layer in range(N_LAYERS):
-            one.prep(layer, [0], [pos], 1, qfull[layer], kproj[layer], vproj[layer], qn[layer], kn[layer], q16=q16[layer], gate=gate[layer])
-            one.decode(layer, [0], [pos], 1, q16[layer], gate[layer], out=out1[layer])
+        one.layers_step(N_LAYERS, [0], [pos], 1, qfull, kproj, vproj, qn, kn, q16, gate, out1)
     for i in range(warmup):
         step_one(L + i)
     one.check(); barrier()

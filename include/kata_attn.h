@@ -139,6 +139,11 @@ int kata_attn_peer_exchange_merge(kata_attn_peer* px, const float* d_part, int32
  * one layer (this rank's keys [key_lo, key_hi) of sequence seq) as one call. */
 int kata_attn_peer_decode(kata_attn_peer* px, kata_attn_ctx* ctx, int32_t layer, int32_t seq, int32_t pos_base, int32_t T, int32_t key_lo, int32_t key_hi,
                           const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+/* The layer loop of a split-KV decode step in one call: per layer kata_attn_prep (head slots [0, 32) when `appends`, i.e. on the rank that owns the
+ * sequence's tail, else the query heads only) and kata_attn_peer_decode, over [n_layers][T][...] device arrays as in kata_attn_layers_step. */
+int kata_attn_peer_layers_step(kata_attn_peer* px, kata_attn_ctx* ctx, int32_t n_layers, int32_t seq, int32_t pos, int32_t T, int32_t key_lo, int32_t key_hi, int32_t appends,
+                               const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype, const float* d_qnorm, const float* d_knorm,
+                               void* d_q16, float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 int kata_attn_peer_check(kata_attn_peer* px, void* stream);   /* synchronises the stream; KATA_ERR_DEVICE_WAIT after a wait that ran out */
 /* After KATA_ERR_DEVICE_WAIT the ranks' call counters no longer agree (flags are matched against the call number, and the rank whose peer
  * skipped or failed a call has counted one call more), so every later exchange would time out as well. Once the ranks have agreed over their

@@ -28,7 +28,7 @@ EXPORTS = [
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_decode_static_check", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
     "kata_attn_layers_step", "kata_attn_host_step_create", "kata_attn_host_step_destroy", "kata_attn_host_step_run",
-    "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode",
+    "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode", "kata_attn_peer_layers_step",
     "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
     "kata_draft_ring_read", "kata_draft_ring_write", "kata_draft_launch_count",
@@ -394,6 +394,12 @@ class PeerExchange:
         """This rank's share of a decode whose keys are split across the ranks, exchange and merge included (kata_attn_peer_decode)."""
         out = torch.empty((T, QD), dtype=out_dtype, device=q16.device) if out is None else out
         self._ck(self.L.kata_attn_peer_decode(self.h, ctx.h, layer, seq, pos_base, T, key_lo, key_hi, _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
+        return out
+
+    def layers_step(self, ctx, n_layers, seq, pos, T, key_lo, key_hi, appends, qfull, kproj, vproj, qnorm, knorm, q16, gate, out):
+        """prep + split-KV decode of layers 0..n_layers-1 in one call (kata_attn_peer_layers_step); every tensor is [n_layers][T][...] on the device."""
+        self._ck(self.L.kata_attn_peer_layers_step(self.h, ctx.h, n_layers, seq, pos, T, key_lo, key_hi, 1 if appends else 0, _dp(qfull), _dp(kproj), _dp(vproj), _ACT[qfull.dtype],
+                                                   _dp(qnorm), _dp(knorm), _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     def check(self):

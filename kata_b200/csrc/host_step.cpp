@@ -112,3 +112,23 @@ extern "C" int kata_attn_layers_step(kata_attn_ctx* ctx, int32_t n_layers, int32
     }
     return KATA_OK;
 }
+
+// The layer loop of a decode step whose one sequence is split by keys over the GPUs of a box: per layer this rank's prep (every rank forms the
+// query; the rank that owns the tail of the sequence also appends the new K/V rows: head slots [0, 32), the others [0, 24)) and kata_attn_peer_decode
+// (this rank's keys [key_lo, key_hi), its part pushed to the peers and the ranks' parts merged). All ranks must make the same call.
+extern "C" int kata_attn_peer_layers_step(kata_attn_peer* px, kata_attn_ctx* ctx, int32_t n_layers, int32_t seq, int32_t pos, int32_t T, int32_t key_lo, int32_t key_hi, int32_t appends,
+                                          const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype, const float* d_qnorm, const float* d_knorm,
+                                          void* d_q16, float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
+    if (!px || !ctx || n_layers < 1 || T < 1) return KATA_ERR_ARG;
+    if (act_dtype != KATA_ACT_F32 && act_dtype != KATA_ACT_BF16 && act_dtype != KATA_ACT_F16) return KATA_ERR_ARG;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return KATA_ERR_ARG;
+    const size_t rows = (size_t)T, esz = act_dtype == KATA_ACT_F32 ? 4 : 2, osz = out_dtype == KATA_ACT_F32 ? 4 : 2;
+    for (int l = 0; l < n_layers; l++) {
+        void* q16 = (char*)d_q16 + (size_t)l * rows * 6144 * 2; float* gate = d_gate + (size_t)l * rows * 6144;
+        int rc = kata_attn_prep(ctx, l, 1, &seq, &pos, T, (const char*)d_qfull + (size_t)l * rows * 12288 * esz, (const char*)d_kproj + (size_t)l * rows * 1024 * esz,
+                                (const char*)d_vproj + (size_t)l * rows * 1024 * esz, act_dtype, d_qnorm + (size_t)l * 256, d_knorm + (size_t)l * 256, q16, nullptr, gate, 0, appends ? 32 : 24, stream);
+        if (rc == KATA_OK) rc = kata_attn_peer_decode(px, ctx, l, seq, pos, T, key_lo, key_hi, q16, gate, (char*)d_out + (size_t)l * rows * 6144 * osz, out_dtype, stream);
+        if (rc != KATA_OK) return rc;
+    }
+    return KATA_OK;
+}
