@@ -1,6 +1,6 @@
 """The oracle against the reference's own CPU check compiled here (oracle/_ref/libprobe_ref.so: tools/probe_flash.cpp lines
 16-19 and 26-34, lifted by line range): the reference's generator and draw order make the inputs, the reference's fp64
-loop is the judge. Pins (i) the oracle's fp64 formula bit for bit, (ii) the restated matrix kernel (k_flash_prefill) and
+loop decides. Pins (i) the oracle's fp64 formula bit for bit, (ii) the restated matrix kernel (k_flash_prefill) and
 the fp32 formula within the error scale the reference reports for its own kernel on this procedure (6.6e-5)."""
 import numpy as np
 import pytest
