@@ -227,6 +227,16 @@ int kata_attn_decode_static_check(void* stream);
 /* Number of kernels this library has launched on this context since creation (for accounting in benchmarks). */
 uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);
 
+/* No reference counterpart (the reference computes one sequence on one queue). How a tcgen05 prefill launch of n sequences at positions pos[]
+ * and M rows each would be shared out over pairs_avail CTA pairs (one per two SMs; at most 74 are used) by a context that computes KV heads
+ * [kvh_lo, kvh_lo + kvh_n): host code only, no GPU needed. Work items are (sequence, KV head, query tile of 128 rows, head pair of the KV head) in the
+ * order: order[] (the batch's sequences, shortest first), KV head, query tile last to first, head pair. Pair p computes `*rounds` whole items
+ * (round k: item n_pairs * k + p, pairs counted backwards in odd rounds) and then the key tiles from (item0[p], tile0[p]) up to, not including,
+ * (item0[p + 1], tile0[p + 1]) of the items that follow the rounds (numbered from 0; a key tile is 128 keys). Returns the number of pairs, or -1
+ * for arguments out of range. item0, tile0: 75 entries; order: n entries; tiles_scratch: 96 * n * kvh_n / 4 entries at least (one per item). */
+int kata_attn_prefill_plan(int32_t M, int32_t n, const int32_t* pos, int32_t kvh_lo, int32_t kvh_n, int32_t pairs_avail, int32_t* tiles_scratch,
+                           int32_t* rounds, int32_t* item0, int32_t* tile0, uint8_t* order);
+
 /* No reference counterpart: the reference's buffers are shared between CPU and GPU (MTL::ResourceStorageModeShared, src/gpu.cpp:26-30), so
  * Engine::step / verify2 / verifyWide (src/engine.cpp:161-178, 469-483, 602-622) hand attention the very rows the CPU sees. A caller on a
  * discrete GPU whose projections and output rows live in (pinned) host memory runs a whole step through this routine instead: for each of

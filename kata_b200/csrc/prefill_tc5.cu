@@ -599,37 +599,16 @@ cudaError_t configure_prefill(int kv_mode) {
     return e;
 }
 
-// tcgen05 kernel (unless the context was created with the legacy-path flag). An int8 cache goes through it as well: the layer's codes are first
-// expanded to fp16 in the context's staging arena (one pass over the prefix, a few per cent of the attention time), the scales are applied in
-// the softmax. The mma.sync kernel remains the cross-check and serves windowed caches (a position offset), which the staging arena does not cover.
-cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
-    const int mode = c.cfg.kv_mode; const bool i8 = c.v8();
-    bool windowed = false; for (int i = 0; i < b.n; i++) windowed |= c.pos_off[b.seq[i]] != 0;
-    if (c.kg() && windowed) return cudaErrorNotSupported;   // the mma.sync kernel, which serves windowed int8 caches, has no grouped key scales
-    if ((c.cfg.flags & 1) || (i8 && (!c.v16_stage || windowed))) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
-    CUtensorMap tm_q;
-    if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
-    PfStage stg{};
-    if (i8) {
-        int max_rows = 0; for (int i = 0; i < b.n; i++) { stg.kv_row0[i] = c.stage_row0[b.seq[i]]; max_rows = std::max(max_rows, b.pos[i] + M); }
-        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1, c.kg() ? (const __half*)c.ksc : nullptr);
-        c.launches++;
-    }
-    // persistent CTA pairs, at most one per two SMs; see PfPlan for the way the items are shared out.
-    // The plan depends only on (M, positions): the 16 layers of a chunk reuse the one computed for the first (kept in the context, no allocation).
-    struct Cached { PfPlan plan; };
-    static_assert(sizeof(Cached) <= sizeof(c.pf_plan_cache), "plan cache too small");
-    Cached& cached = *reinterpret_cast<Cached*>(c.pf_plan_cache);
-    bool hit = c.pf_plan_M == M && c.pf_plan_n == b.n;
-    for (int i = 0; hit && i < b.n; i++) hit = c.pf_plan_pos[i] == b.pos[i];
-    if (!hit) {
-    const int hp_n = 3 * c.kvh_n, hp_lo = 3 * c.kvh_lo;   // head pairs of the KV heads this context computes
-    const int n_q = (M + kBMq - 1) / kBMq, grp_items = 3 * n_q, n_items = grp_items * c.kvh_n * b.n, max_pairs = std::max(1, std::min(kMaxPairs, c.sm_count / 2));
+// The work split of one launch (see PfPlan): depends only on the chunk length, the sequences' positions, the KV heads of the context and the number of
+// CTA pairs. tiles_scratch: room for the key-tile count of every item (n_q * 3 * kvh_n * n entries). Pure host code.
+static void make_prefill_plan(const int M, const int n, const int32_t* pos, const int kvh_lo, const int kvh_n, const int pairs_avail, int32_t* tiles_scratch, PfPlan& plan_out) {
+    const int hp_n = 3 * kvh_n, hp_lo = 3 * kvh_lo;   // head pairs of the KV heads this context computes
+    const int n_q = (M + kBMq - 1) / kBMq, grp_items = 3 * n_q, n_items = grp_items * kvh_n * n, max_pairs = std::max(1, std::min(kMaxPairs, pairs_avail));
     uint8_t order[KATA_MAX_BATCH];   // sequences of the batch, shortest first (ties in batch order): the rounds then deal items of like length, and the long
-    for (int i = 0; i < b.n; i++) order[i] = (uint8_t)i;   // items, which only cutting can spread, come last, where the ranges are cut
-    std::stable_sort(order, order + b.n, [&](uint8_t x, uint8_t y) { return b.pos[x] < b.pos[y]; });
-    int32_t* nt_tab = c.pf_plan_tiles;   // key tiles per item in list order (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
-    for (int idx = 0; idx < n_items; idx++) { const int grp = idx / grp_items, qt = n_q - 1 - (idx % grp_items) / 3, bi = order[grp / c.kvh_n], q0 = qt * kBMq; nt_tab[idx] = (b.pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
+    for (int i = 0; i < n; i++) order[i] = (uint8_t)i;   // items, which only cutting can spread, come last, where the ranges are cut
+    std::stable_sort(order, order + n, [&](uint8_t x, uint8_t y) { return pos[x] < pos[y]; });
+    int32_t* nt_tab = tiles_scratch;   // key tiles per item in list order (room for the largest launch: 8 query tiles x 12 head pairs x 64 sequences)
+    for (int idx = 0; idx < n_items; idx++) { const int grp = idx / grp_items, qt = n_q - 1 - (idx % grp_items) / 3, bi = order[grp / kvh_n], q0 = qt * kBMq; nt_tab[idx] = (pos[bi] + q0 + std::min(kBMq, M - q0) + kBNk - 1) / kBNk; }
     auto tiles_of = [&](int idx) { return (int)nt_tab[idx]; };
     constexpr int kMinPart = 2;   // a part is at least two key tiles
     auto round_item = [&](const PfPlan& pl, int p, int k) { return pl.n_pairs * k + ((k & 1) ? pl.n_pairs - 1 - p : p); };
@@ -724,9 +703,48 @@ cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, con
         const double t_tile = 2.3, t_cut = max_load(plan) * t_tile + (max_parts > 1 ? kCutCostUs + kFoldCostUs * (max_parts - 2) : 0.0), t_whole = max_load(whole) * t_tile;
         if (t_whole <= t_cut) plan = whole;
     }
-    for (int i = 0; i < b.n; i++) plan.order[i] = order[i];
+    for (int i = 0; i < n; i++) plan.order[i] = order[i];
     plan.hp_lo = hp_lo; plan.hp_n = hp_n;
-    cached.plan = plan;
+    plan_out = plan;
+}
+
+// The plan as plain arrays, for tests of the host logic that have no GPU (and for a caller that wants to see how a launch would be shared out):
+// returns the number of pairs; item0/tile0 take n_pairs + 1 entries each, order takes n. tiles_scratch as in make_prefill_plan.
+extern "C" int kata_attn_prefill_plan(int32_t M, int32_t n, const int32_t* pos, int32_t kvh_lo, int32_t kvh_n, int32_t pairs_avail, int32_t* tiles_scratch,
+                                      int32_t* rounds, int32_t* item0, int32_t* tile0, uint8_t* order) {
+    if (M < 1 || M > KATA_MAX_CHUNK || n < 1 || n > KATA_MAX_BATCH || !pos || kvh_lo < 0 || kvh_n < 1 || kvh_lo + kvh_n > KATA_KV_HEADS || !tiles_scratch || !rounds || !item0 || !tile0 || !order) return -1;
+    PfPlan plan{}; make_prefill_plan(M, n, pos, kvh_lo, kvh_n, pairs_avail, tiles_scratch, plan);
+    *rounds = plan.rounds;
+    for (int p = 0; p <= plan.n_pairs; p++) { item0[p] = plan.item0[p]; tile0[p] = plan.tile0[p]; }
+    for (int i = 0; i < n; i++) order[i] = plan.order[i];
+    return plan.n_pairs;
+}
+
+// tcgen05 kernel (unless the context was created with the legacy-path flag). An int8 cache goes through it as well: the layer's codes are first
+// expanded to fp16 in the context's staging arena (one pass over the prefix, a few per cent of the attention time), the scales are applied in
+// the softmax. The mma.sync kernel remains the cross-check and serves windowed caches (a position offset), which the staging arena does not cover.
+cudaError_t launch_prefill(Ctx& c, const Batch& b, int M, const __half* q16, const float* gate, void* out, int out_dtype, cudaStream_t s) {
+    const int mode = c.cfg.kv_mode; const bool i8 = c.v8();
+    bool windowed = false; for (int i = 0; i < b.n; i++) windowed |= c.pos_off[b.seq[i]] != 0;
+    if (c.kg() && windowed) return cudaErrorNotSupported;   // the mma.sync kernel, which serves windowed int8 caches, has no grouped key scales
+    if ((c.cfg.flags & 1) || (i8 && (!c.v16_stage || windowed))) return launch_prefill_mma(c, b, M, q16, gate, out, out_dtype, s);
+    CUtensorMap tm_q;
+    if (!make_matrix_tmap(&tm_q, q16, (int64_t)b.n * M, kQD, 64, 128)) return cudaErrorInvalidValue;
+    PfStage stg{};
+    if (i8) {
+        int max_rows = 0; for (int i = 0; i < b.n; i++) { stg.kv_row0[i] = c.stage_row0[b.seq[i]]; max_rows = std::max(max_rows, b.pos[i] + M); }
+        expand_codes_kernel<<<dim3(std::min((max_rows + 3) / 4, 1024), b.n, c.k8() ? 2 : 1), 256, 0, s>>>(b, M, stg, (const uint8_t*)c.k_arena, (const uint8_t*)c.v_arena, c.k16_stage, c.v16_stage, c.k8() ? 0 : 1, c.kg() ? (const __half*)c.ksc : nullptr);
+        c.launches++;
+    }
+    // persistent CTA pairs, at most one per two SMs; see PfPlan for the way the items are shared out.
+    // The plan depends only on (M, positions): the 16 layers of a chunk reuse the one computed for the first (kept in the context, no allocation).
+    struct Cached { PfPlan plan; };
+    static_assert(sizeof(Cached) <= sizeof(c.pf_plan_cache), "plan cache too small");
+    Cached& cached = *reinterpret_cast<Cached*>(c.pf_plan_cache);
+    bool hit = c.pf_plan_M == M && c.pf_plan_n == b.n;
+    for (int i = 0; hit && i < b.n; i++) hit = c.pf_plan_pos[i] == b.pos[i];
+    if (!hit) {
+    make_prefill_plan(M, b.n, b.pos, c.kvh_lo, c.kvh_n, c.sm_count / 2, c.pf_plan_tiles, cached.plan);
     c.pf_plan_M = M; c.pf_plan_n = b.n; for (int i = 0; i < b.n; i++) c.pf_plan_pos[i] = b.pos[i];
     }
     const PfPlan& plan = cached.plan;
