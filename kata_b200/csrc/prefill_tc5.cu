@@ -6,15 +6,16 @@
 // A work item = 128 query rows of two heads of the same KV-head group (row r of the chunk sits at position pos_base + r and sees keys
 // [0, pos_base + r]), done by two CTAs (a cluster, cta_group::2). The kernel is persistent: one CTA pair per two SMs, with its barriers,
 // tensor memory and pipelines kept across items; the next item's Q, K and V loads and first score MMAs run under the current item's epilogue.
-// Work split: the key tiles of all items form one list (longest items first) which the host cuts into one contiguous range per pair,
-// balanced by tiles plus a per-part allowance for the epilogue, so that a launch with fewer items than pairs (one sequence: 48 items for 74
-// pairs) still uses every SM. The parts of a cut item lie on consecutive pairs: its head (the tiles from 0) is the last part of its pair's
-// range, every other part the first of its pair's. A pair computes such a part first, writes the unnormalised O rows with their (m, l) to
-// scratch and raises the part's flag; the pair that holds the head finishes the item: once its own tiles are done (its Q, K and V tiles are
-// then free) its producer warps copy the other parts into that shared memory as their flags come up, and the softmax warps fold them
-// into O in tensor memory with the split-KV rule of the decode path (weights exp(m - M)) before the usual epilogue. (A merge kernel behind
-// this one was used before: its CTAs could not start until the pairs had left the SMs, and it re-read 30 MB of parts through L2: 15 us after
-// a 50 us launch at batch 1. Merging by plain loads in the CTA that finished an item's last part was tried before that: 20 us per item.)
+// Work split (PfPlan, made on the host): the items of one (sequence, KV head) are neighbours in the list; a pair first computes whole items dealt in
+// rounds, so that a dozen pairs read the same K and V tiles at the same time, then one contiguous range of the key tiles of the remaining items,
+// sized so that all pairs carry the same load; with fewer items than pairs (one sequence: 48 items for 74 pairs) the ranges are all there is and
+// every SM is still used. The parts of a cut item lie on consecutive pairs: its head (the tiles from 0) is the last part of its pair's range,
+// every other part the first of its pair's. A pair computes such a part, writes the unnormalised O rows with their (m, l) to scratch and
+// raises the part's flag; the pair that holds the head finishes the item: once its own tiles are done (its Q, K and V tiles are then free)
+// its softmax warps copy the other parts into that shared memory as their flags come up and fold them into O in tensor memory with the
+// split-KV rule of the decode path (weights exp(m - M)) before the usual epilogue. (A merge kernel behind this one was used before: its CTAs
+// could not start until the pairs had left the SMs, and it re-read 30 MB of parts through L2: 15 us after a 50 us launch at batch 1.
+// Merging by plain loads in the CTA that finished an item's last part was tried before that: 20 us per item.)
 // The host cuts items only when its estimate says the shorter critical path pays for the fold. The pair works on M = 256 tiles: each CTA holds its own head's Q block and O/S
 // accumulators and half of every K tile (64 of the 128 keys) and V tile (128 of the 256 dims); the tensor cores of the two SMs exchange
 // the halves, so each SM writes and reads half the K/V bytes through its shared memory, which is what bounds an M = 128 tile with
@@ -86,7 +87,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const i
     return __all_sync(0xffffffffu, ok);
 }
 
-// One work item = (query tile, head pair, sequence); items are ordered longest first and dealt round-robin to the CTA pairs.
+// One work item = (query tile, head pair, sequence); PfPlan says which pair computes which.
 struct PfStage { int64_t kv_row0[KATA_MAX_BATCH]; };   // SCALED: first row of sequence b in the fp16 staging arena (position 0)
 struct PfItem { int q0, rows_valid, pos_base, kend, n_tiles, row0, row0v, h, kvh, bi; int64_t sc_row0; int idx, j0, j1, slot; bool whole; };   // row0 / row0v: row of position 0 in the arena the K / V tiles come from; [j0, j1): this part's key tiles
 constexpr int kMaxPairs = 74;      // CTA pairs of a launch (one per two SMs of a B200)
@@ -103,7 +104,7 @@ struct PfPlan { int32_t n_pairs, rounds; int32_t item0[kMaxPairs + 1]; int32_t t
 constexpr int kZoneMl = 128 * 1024;   // landing zone over the Q, K and V tiles: a part's 128 KB of rows as they lie in scratch, then the rows' (m, l)
 // A part's rows in scratch: 16-byte chunk c (columns 4c .. 4c+3) of row r at chunk index c * 128 + r, so that the 32 rows of a warp (a thread holds one row
 // of tensor memory) write and read 512 contiguous bytes per chunk.
-constexpr size_t kPartOFloats = (size_t)kBMq * kD, kPartSlots = 2 * 2 * kMaxPairs;   // a slot = one CTA's 128 x 256 partial O; two parts per pair, two CTAs per pair
+constexpr size_t kPartOFloats = (size_t)kBMq * kD, kPartSlots = 2 * 2 * kMaxPairs;   // a slot = one CTA's 128 x 256 partial O, numbered (2 * pair + part) * 2 + CTA; only a pair's first part is ever written (the head of a cut item is merged where it is computed)
 
 // MODE = the context's cache mode. An int8 plane's tiles are its codes expanded to fp16 (exact integers) in a staging arena whose rows are
 // kv_row0[b] + position; the per-key scales are applied as k_flash_prefill_q8 does (shaders/flash.metal:10-68 with Q8): S = (Q.Kq) * ksc[key],
