@@ -120,7 +120,7 @@ int kata_attn_prefill(kata_attn_ctx* ctx, int32_t layer, int32_t n, const int32_
 
 /* No reference counterpart (the reference is single-device). Exchange of the split-KV parts between the GPUs of one box without a library
  * collective: each rank pushes its part rows {O[256], m, l} (as kata_attn_decode_partial writes them) into every peer's exchange buffer
- * with plain stores over NVLink, raises a flag per row, waits for the peers' rows in its own buffer and merges + gates, all in one kernel
+ * with plain 8-byte stores over NVLink (each value together with the call's number, which is its flag), waits for the peers' rows in its own buffer and merges + gates, all in one kernel
  * on the caller's stream. Set-up: every rank creates an exchange (one cudaMalloc, exported as a CUDA IPC handle of
  * KATA_PEER_HANDLE_BYTES bytes), the ranks swap handles by any host channel, and each opens the others'; inside one process
  * kata_attn_peer_open_pointers takes the buffers' device addresses instead. All ranks must issue the same sequence of exchange calls.
@@ -145,10 +145,10 @@ int kata_attn_peer_layers_step(kata_attn_peer* px, kata_attn_ctx* ctx, int32_t n
                                const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype, const float* d_qnorm, const float* d_knorm,
                                void* d_q16, float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 int kata_attn_peer_check(kata_attn_peer* px, void* stream);   /* synchronises the stream; KATA_ERR_DEVICE_WAIT after a wait that ran out */
-/* After KATA_ERR_DEVICE_WAIT the ranks' call counters no longer agree (flags are matched against the call number, and the rank whose peer
+/* After KATA_ERR_DEVICE_WAIT the ranks' call counters no longer agree (the stored values are matched against the call number, and the rank whose peer
  * skipped or failed a call has counted one call more), so every later exchange would time out as well. Once the ranks have agreed over their
  * host channel that none of them has an exchange in flight (streams synchronised), each calls this with the same call_number: it
- * synchronises the device, clears the local flags and the error word and sets the counter. Alternatively destroy and recreate on all ranks. */
+ * synchronises the device, clears the local buffer and the error word and sets the counter. Alternatively destroy and recreate on all ranks. */
 int kata_attn_peer_resync(kata_attn_peer* px, uint32_t call_number);
 const char* kata_attn_peer_last_error(const kata_attn_peer* px);
 int kata_attn_peer_destroy(kata_attn_peer* px);              /* call on every rank only after all ranks have finished their exchanges */

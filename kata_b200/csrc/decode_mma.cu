@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(256) merge_parts_kernel(const float* __restric
     const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x; const int64_t row = (int64_t)t * kH + h, stride = (int64_t)T * kH * kPartStride;
     float M = -INFINITY; for (int r = 0; r < n_parts; r++) M = fmaxf(M, parts[r * stride + row * kPartStride + 256]);
     float L = 0.0f, A = 0.0f;
-    for (int r = 0; r < n_parts; r++) { const float* pp = parts + r * stride + row * kPartStride; const float mm = pp[256]; const float wt = (mm == -INFINITY) ? 0.0f : expf(mm - M); L += pp[257] * wt; A += pp[tid] * wt; }
+    for (int r = 0; r < n_parts; r++) { const float* pp = parts + r * stride + row * kPartStride; const float mm = pp[256]; const float wt = (mm == -INFINITY) ? 0.0f : expf(mm - M); L = fmaf(pp[257], wt, L); A = fmaf(pp[tid], wt, A); }   // one fused multiply-add per part, as the peer exchange forms the same sums
     const int64_t oi = (int64_t)t * kQD + h * kD + tid; const float y = (A / L) * (1.0f / (1.0f + expf(-gate[oi])));
     store_act(out, oi, y, out_kind);
 }
