@@ -148,3 +148,28 @@ def test_one_rank_peer_decode_equals_plain_decode_short_and_long(capi):
             assert (got - want[0]).abs().max().item() < 1e-5
         ctx.close()
     px.close()
+
+
+def test_one_rank_peer_layers_step_equals_the_plain_layer_loop(capi):
+    # kata_attn_peer_layers_step (prep + split-KV decode, layer after layer, in one call) on a group of one rank against kata_attn_layers_step
+    px = capi.PeerExchange(0, 1)
+    gen = torch.Generator(device="cuda"); gen.manual_seed(52)
+    NL, L = 3, 9000
+    kn = (1 + 0.05 * torch.randn(NL, 256, generator=gen, device="cuda")).contiguous(); qn = (1 + 0.05 * torch.randn(NL, 256, generator=gen, device="cuda")).contiguous()
+    ctxs = [capi.AttnContext(NL, [L + 8]) for _ in range(2)]
+    for layer in range(NL):
+        for st in range(0, L, 1024):
+            m = min(1024, L - st)
+            k = torch.randn(1, m, 1024, generator=gen, device="cuda"); v = torch.randn(1, m, 1024, generator=gen, device="cuda")
+            for ctx in ctxs:
+                ctx.prep(layer, [0], [st], m, None, k, v, None, kn[layer], h0=24, nh=8)
+    for T in (1, 2):
+        qf = torch.randn(NL, 1, T, 12288, generator=gen, device="cuda"); kp = torch.randn(NL, 1, T, 1024, generator=gen, device="cuda"); vp = torch.randn(NL, 1, T, 1024, generator=gen, device="cuda")
+        q16 = torch.empty(NL, 1, T, 6144, dtype=torch.float16, device="cuda"); g = torch.empty(NL, 1, T, 6144, device="cuda")
+        want = torch.empty(NL, 1, T, 6144, device="cuda"); got = torch.empty(NL, T, 6144, device="cuda")
+        pos = L + (0 if T == 1 else 1)
+        ctxs[0].layers_step(NL, [0], [pos], T, qf, kp, vp, qn, kn, q16, g, want)
+        px.layers_step(ctxs[1], NL, 0, pos, T, 0, 1 << 30, True, qf, kp, vp, qn, kn, q16.clone(), g.clone(), got)
+        px.check(); ctxs[0].check(); ctxs[1].check()
+        assert (got - want[:, 0]).abs().max().item() < 1e-5
+    px.close()
