@@ -227,6 +227,16 @@ int kata_attn_decode_static_check(void* stream);
 /* Number of kernels this library has launched on this context since creation (for accounting in benchmarks). */
 uint64_t kata_attn_launch_count(const kata_attn_ctx* ctx);
 
+/* No reference counterpart (the reference cuts a sequence into fixed chunks of 128 keys, src/engine.cpp:120-121). How a decode launch over n sequences
+ * with kend[b] - first_row keys each would be shared out: the key tiles (tile_keys = 16 for fp16 keys, 32 for int8 keys) of all (sequence, KV head)
+ * segments form one list, sequence after sequence and KV head after KV head, ntiles[b] tiles per segment; CTA c works on tiles [first_tile[c],
+ * first_tile[c + 1]). cps > 0: segments of equal length got cps CTAs of their own each. merge_in_kernel: 1 when no segment is cut between more than 8
+ * CTAs (the last contributor merges), else the combine grid runs; max_contrib: the CTAs of the most-cut segment. dec_chunk > 0 asks for ranges of that
+ * many keys (the reference's split size) instead of one range per SM. Host code only, no GPU needed. Returns the number of CTAs (first_tile takes one
+ * entry more), -1 for arguments out of range (first_tile_cap too small included). */
+int kata_attn_decode_plan(int32_t n, const int32_t* kend, int32_t first_row, int32_t kvh_n, int32_t tile_keys, int32_t sm_count, int32_t dec_chunk, int32_t max_items,
+                          int32_t* ntiles, int32_t* first_tile, int32_t first_tile_cap, int32_t* cps, int32_t* merge_in_kernel, int32_t* max_contrib);
+
 /* No reference counterpart (the reference computes one sequence on one queue). How a tcgen05 prefill launch of n sequences at positions pos[]
  * and M rows each would be shared out over pairs_avail CTA pairs (one per two SMs; at most 74 are used) by a context that computes KV heads
  * [kvh_lo, kvh_lo + kvh_n): host code only, no GPU needed. Work items are (sequence, KV head, query tile of 128 rows, head pair of the KV head) in the

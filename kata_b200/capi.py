@@ -27,7 +27,7 @@ EXPORTS = [
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_decode_static_check", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
-    "kata_attn_layers_step", "kata_attn_prefill_plan", "kata_attn_host_step_create", "kata_attn_host_step_destroy", "kata_attn_host_step_run",
+    "kata_attn_layers_step", "kata_attn_prefill_plan", "kata_attn_decode_plan", "kata_attn_host_step_create", "kata_attn_host_step_destroy", "kata_attn_host_step_run",
     "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode", "kata_attn_peer_layers_step",
     "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",

@@ -433,38 +433,64 @@ static int max_contributors(const DecPlan& p) {
     return m;
 }
 
+// The work split of a decode launch (host code only): p.n, p.kend[], p.first_row and p.kvh_n are set; fills the tile counts, the CTA ranges and
+// the choice of where the segments' partials are merged. tile_keys: 16 (fp16 keys) or 32 (int8 keys).
+static void split_decode_tiles(DecPlan& p, const int tile_keys, const int sm_count, const int dec_chunk, const int max_items) {
+    int total = 0;
+    for (int i = 0; i < p.n; i++) {
+        const int nkeys = std::max(0, p.kend[i] - p.first_row); p.ntiles[i] = std::max(1, (nkeys + tile_keys - 1) / tile_keys);
+        p.tile_start[i] = total; total += p.kvh_n * p.ntiles[i];
+    }
+    for (int i = p.n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
+    const int chunk_tiles = dec_chunk > 0 ? std::max(1, dec_chunk / tile_keys) : 0;
+    int n_ctas = chunk_tiles ? (total + chunk_tiles - 1) / chunk_tiles : sm_count;
+    n_ctas = std::max(1, std::min(std::min(n_ctas, total), sm_count * 8));
+    if (n_ctas + 4 * p.n > max_items) n_ctas = max_items - 4 * p.n;
+    p.cps = 0; p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
+    // A CTA whose range crosses from one segment into the next pays for it (ring merge, partial write, the Q block of the next segment, the
+    // pipeline filled again: 4 to 5 us measured, which made the few such CTAs the last to finish). When all segments are equally long (one
+    // sequence, or a batch of equal lengths) and their number divides nearly all SMs, every segment gets the same number of CTAs of its own.
+    if (!chunk_tiles) {
+        bool same = true; for (int i = 1; i < p.n; i++) same = same && p.ntiles[i] == p.ntiles[0];
+        const int n_seg = p.n * p.kvh_n, cps = n_seg <= sm_count ? sm_count / n_seg : 0;
+        if (same && cps >= 1 && cps * n_seg * 100 >= sm_count * 97 && p.ntiles[0] >= cps && cps * n_seg + 4 * p.n <= max_items) { p.cps = cps; p.n_ctas = cps * n_seg; p.q_tiles = p.ntiles[0] / cps; p.r_tiles = p.ntiles[0] % cps; }
+    }
+    p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
+}
+
+// The same as plain arrays, for tests of the host logic that have no GPU: kend[b] keys (from first_row on) per sequence. first_tile takes n_ctas + 1
+// entries (CTA c works on tiles [first_tile[c], first_tile[c + 1]) of the list: sequence after sequence, KV head after KV head, ntiles[b] tiles each).
+// Returns the number of CTAs, or -1 for arguments out of range.
+extern "C" int kata_attn_decode_plan(int32_t n, const int32_t* kend, int32_t first_row, int32_t kvh_n, int32_t tile_keys, int32_t sm_count, int32_t dec_chunk, int32_t max_items,
+                                     int32_t* ntiles, int32_t* first_tile, int32_t first_tile_cap, int32_t* cps, int32_t* merge_in_kernel, int32_t* max_contrib) {
+    if (n < 1 || n > KATA_MAX_BATCH || !kend || kvh_n < 1 || kvh_n > KATA_KV_HEADS || (tile_keys != 16 && tile_keys != 32) || sm_count < 1 || max_items <= 4 * n || !ntiles || !first_tile || !cps || !merge_in_kernel || !max_contrib) return -1;
+    DecPlan p{}; p.n = n; p.T = 1; p.first_row = first_row; p.kvh_lo = 0; p.kvh_n = kvh_n;
+    for (int i = 0; i < n; i++) p.kend[i] = kend[i];
+    split_decode_tiles(p, tile_keys, sm_count, dec_chunk, max_items);
+    if (p.n_ctas + 1 > first_tile_cap) return -1;
+    for (int i = 0; i < n; i++) ntiles[i] = p.ntiles[i];
+    for (int cta = 0; cta <= p.n_ctas; cta++) first_tile[cta] = cta < p.n_ctas ? cta_first_tile(p, cta) : p.tile_start[KATA_MAX_BATCH];
+    for (int cta = 0; cta < p.n_ctas; cta++) for (int tile = first_tile[cta]; tile < (cta + 1 < p.n_ctas ? cta_first_tile(p, cta + 1) : p.tile_start[KATA_MAX_BATCH]); tile++) if (cta_of_tile(p, tile) != cta) return -2;   // the two maps disagree
+    *cps = p.cps; *merge_in_kernel = p.merge_in_kernel; *max_contrib = max_contributors(p);
+    return p.n_ctas;
+}
+
 // key_off / kend_override serve the split-KV-across-GPUs call: local row = absolute key - key_off, rows [first_row, kend).
 cudaError_t launch_decode_mma_ex(Ctx& c, const Batch& b, int T, int first_row, int key_off, const int32_t* kend_override, const __half* q16, const float* gate, void* out, int out_dtype,
                                  float* part_out, cudaStream_t s, int tok_stride, int tok0, const PeerSink* sink, bool* sink_used) {
     if (sink_used) *sink_used = false;
     const int mode = c.cfg.kv_mode, kTile = c.k8() ? 32 : 16;
     DecPlan p{}; p.n = b.n; p.T = T; p.first_row = first_row; p.key_off = key_off; p.kvh_lo = c.kvh_lo; p.kvh_n = c.kvh_n; p.tok_stride = tok_stride > 0 ? tok_stride : T; p.tok0 = tok0;
-    int total = 0;
     for (int i = 0; i < b.n; i++) {
         p.pos[i] = b.pos[i]; p.row_base[i] = b.row_base[i]; p.kend[i] = kend_override ? kend_override[i] : b.pos[i] + T;
         p.safe_row[i] = c.prev_append ? std::min<int64_t>(p.kend[i], (int64_t)c.append_lo[b.seq[i]] - key_off) : p.kend[i];
-        const int nkeys = std::max(0, p.kend[i] - first_row); p.ntiles[i] = std::max(1, (nkeys + kTile - 1) / kTile);
-        p.tile_start[i] = total; total += c.kvh_n * p.ntiles[i];
     }
-    for (int i = b.n; i <= KATA_MAX_BATCH; i++) p.tile_start[i] = total;
-    const int chunk_tiles = c.cfg.dec_chunk > 0 ? std::max(1, c.cfg.dec_chunk / kTile) : 0;
-    int n_ctas = chunk_tiles ? (total + chunk_tiles - 1) / chunk_tiles : c.sm_count;
-    n_ctas = std::max(1, std::min(std::min(n_ctas, total), c.sm_count * 8));
-    if (n_ctas + 4 * b.n > c.max_items) n_ctas = c.max_items - 4 * b.n;
-    p.n_ctas = n_ctas; p.q_tiles = total / n_ctas; p.r_tiles = total % n_ctas;
-    // A CTA whose range crosses from one segment into the next pays for it (ring merge, partial write, the Q block of the next segment, the
-    // pipeline filled again: 4 to 5 us measured, which made the few such CTAs the last to finish). When all segments are equally long (one
-    // sequence, or a batch of equal lengths) and their number divides nearly all SMs, every segment gets the same number of CTAs of its own.
-    if (!chunk_tiles) {
-        bool same = true; for (int i = 1; i < b.n; i++) same = same && p.ntiles[i] == p.ntiles[0];
-        const int n_seg = b.n * c.kvh_n, cps = n_seg <= c.sm_count ? c.sm_count / n_seg : 0;
-        if (same && cps >= 1 && cps * n_seg * 100 >= c.sm_count * 97 && p.ntiles[0] >= cps && cps * n_seg + 4 * b.n <= c.max_items) { p.cps = cps; p.n_ctas = n_ctas = cps * n_seg; p.q_tiles = p.ntiles[0] / cps; p.r_tiles = 0; }
-    }
+    split_decode_tiles(p, kTile, c.sm_count, c.cfg.dec_chunk, c.max_items);
+    const int n_ctas = p.n_ctas;
     // Early loads pay when a CTA streams for long (batch 8 at 16-32K: -2 us of 140); with short ranges (batch 1: 55 tiles per CTA) they take
     // bandwidth from the previous kernel's last CTAs, which everybody then waits for (+2 us of 31): switched off there.
     // Nor are rows loaded early while caller kernels may be writing any of them through a plane pointer without having said which.
     if (p.q_tiles < 128 || (c.ext_ptr && !c.ext_declared)) for (int i = 0; i < b.n; i++) p.safe_row[i] = 0;
-    p.merge_in_kernel = max_contributors(p) <= 8;   // contributors of the most-split segment decide where the merge runs
     const CUtensorMap& mk = c.tm_k_tile; const CUtensorMap& mv = c.tm_v_tile;
 #define KATA_DEC(M) launch_pdl(decode_mma_kernel<M>, dim3(n_ctas), dim3(kThreads), Geo<M>::kSmem, s, mk, mv, p, q16, gate, out, out_dtype, part_out, c.ksc, c.vsc, c.part_o, c.part_ml, c.counters, c.d_err)
     static_assert(Geo<KATA_KV_INT8>::kTile == 32 && Geo<KATA_KV_INT8G>::kTile == 32 && Geo<KATA_KV_INT8V>::kTile == 16 && Geo<KATA_KV_FP16>::kTile == 16, "the tile views of the context are built for these tile heights");
