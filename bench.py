@@ -238,15 +238,13 @@ def run_decode(args, rank, world, kind_cfg, steps=None, warmup=None, sustained_s
 
     # the dominant kernel alone: the decode launches of the same steps, timed on the same stream
     pos_k = pos_timed0.tolist()
-    for layer in L_:
-        ctx.decode(layer, seqs, pos_k, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
+    ctx.layers_decode(N_LAYERS, seqs, pos_k, 1, q16, gate, out)
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
     reps = max(2, steps)
-    for _ in range(reps):
-        for layer in L_:
-            ctx.decode(layer, seqs, pos_k, 1, q16_l[layer], gate_l[layer], out=out_l[layer])
+    for _ in range(reps):   # one call of the C ABI per sixteen launches: a layer of the smallest workloads is shorter than a call through the Python binding
+        ctx.layers_decode(N_LAYERS, seqs, pos_k, 1, q16, gate, out)
     k1.record(); torch.cuda.synchronize()
     kern_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
 

@@ -264,6 +264,10 @@ int kata_attn_layers_step(kata_attn_ctx* ctx, int32_t n_layers, int32_t n, const
                           const void* d_qfull, const void* d_kproj, const void* d_vproj, int32_t act_dtype, const float* d_qnorm, const float* d_knorm,
                           void* d_q16, float* d_gate, void* d_out, int32_t out_dtype, void* stream);
 
+/* kata_attn_decode for layers 0..n_layers-1 over the same [n_layers][...] arrays, nothing appended: the attention kernels by themselves. */
+int kata_attn_layers_decode(kata_attn_ctx* ctx, int32_t n_layers, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,
+                            const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream);
+
 typedef struct kata_attn_host_step kata_attn_host_step;
 int kata_attn_host_step_create(kata_attn_ctx* ctx, int32_t device, int32_t max_n, int32_t max_T, int32_t act_dtype, kata_attn_host_step** out);
 int kata_attn_host_step_destroy(kata_attn_host_step* hs);

@@ -27,7 +27,7 @@ EXPORTS = [
     "kata_attn_prep", "kata_attn_kv_quant", "kata_attn_decode", "kata_attn_decode_scalar", "kata_attn_prefill",
     "kata_attn_decode_partial", "kata_attn_merge_parts", "kata_attn_kv_planes", "kata_attn_kv_plane_row_bytes",
     "kata_attn_kv_plane_read", "kata_attn_kv_plane_write", "kata_attn_kv_plane_ptr", "kata_attn_mark_rows_written", "kata_attn_launch_count", "kata_attn_decode_static", "kata_attn_decode_static_check", "kata_attn_set_position_offset", "kata_attn_set_kv_heads", "kata_attn_out_fwht",
-    "kata_attn_layers_step", "kata_attn_prefill_plan", "kata_attn_decode_plan", "kata_attn_host_step_create", "kata_attn_host_step_destroy", "kata_attn_host_step_run",
+    "kata_attn_layers_step", "kata_attn_layers_decode", "kata_attn_prefill_plan", "kata_attn_decode_plan", "kata_attn_host_step_create", "kata_attn_host_step_destroy", "kata_attn_host_step_run",
     "kata_attn_peer_create", "kata_attn_peer_open", "kata_attn_peer_open_pointers", "kata_attn_peer_buffer", "kata_attn_peer_set_wait_polls", "kata_attn_peer_exchange_merge", "kata_attn_peer_decode", "kata_attn_peer_layers_step",
     "kata_attn_peer_check", "kata_attn_peer_resync", "kata_attn_peer_last_error", "kata_attn_peer_destroy",
     "kata_draft_create", "kata_draft_destroy", "kata_draft_reset", "kata_draft_last_error", "kata_draft_qk", "kata_draft_attn", "kata_draft_ring_ptr",
@@ -169,6 +169,12 @@ class AttnContext:
         sa, sp = _i32(seq_ids); pa, pp = _i32(pos0)
         self._ck(self.L.kata_attn_layers_step(self.h, n_layers, len(sa), sp, pp, T, first_pos, _dp(qfull), _dp(kproj), _dp(vproj), _ACT[qfull.dtype], _dp(qnorm), _dp(knorm),
                                               _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
+        return out
+
+    def layers_decode(self, n_layers, seq_ids, pos_base, T, q16, gate, out, first_pos=0):
+        """kata_attn_decode of layers 0..n_layers-1 in one call (the attention kernels by themselves); tensors are [n_layers][...]."""
+        sa, sp = _i32(seq_ids); pa, pp = _i32(pos_base)
+        self._ck(self.L.kata_attn_layers_decode(self.h, n_layers, len(sa), sp, pp, T, first_pos, _dp(q16), _dp(gate), _dp(out), _ACT[out.dtype], _stream()))
         return out
 
     def kv_quant(self, layer, seq, ks, vs, pos0):

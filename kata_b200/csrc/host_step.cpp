@@ -113,6 +113,21 @@ extern "C" int kata_attn_layers_step(kata_attn_ctx* ctx, int32_t n_layers, int32
     return KATA_OK;
 }
 
+// The decode calls alone, layer after layer (the rows prep left in d_q16 and d_gate; nothing is appended): for a caller that times or replays the
+// attention kernels by themselves.
+extern "C" int kata_attn_layers_decode(kata_attn_ctx* ctx, int32_t n_layers, int32_t n, const int32_t* seq_ids, const int32_t* pos_base, int32_t T, int32_t first_pos,
+                                       const void* d_q16, const float* d_gate, void* d_out, int32_t out_dtype, void* stream) {
+    if (!ctx || n_layers < 1 || n < 1 || T < 1 || !d_q16 || !d_gate || !d_out) return KATA_ERR_ARG;
+    if (out_dtype != KATA_ACT_F32 && out_dtype != KATA_ACT_BF16 && out_dtype != KATA_ACT_F16) return KATA_ERR_ARG;
+    const size_t rows = (size_t)n * T, osz = out_dtype == KATA_ACT_F32 ? 4 : 2;
+    for (int l = 0; l < n_layers; l++) {
+        const int rc = kata_attn_decode(ctx, l, n, seq_ids, pos_base, T, first_pos, (const char*)d_q16 + (size_t)l * rows * 6144 * 2, d_gate + (size_t)l * rows * 6144,
+                                        (char*)d_out + (size_t)l * rows * 6144 * osz, out_dtype, stream);
+        if (rc != KATA_OK) return rc;
+    }
+    return KATA_OK;
+}
+
 // The layer loop of a decode step whose one sequence is split by keys over the GPUs of a box: per layer this rank's prep (every rank forms the
 // query; the rank that owns the tail of the sequence also appends the new K/V rows: head slots [0, 32), the others [0, 24)) and kata_attn_peer_decode
 // (this rank's keys [key_lo, key_hi), its part pushed to the peers and the ranks' parts merged). All ranks must make the same call.
